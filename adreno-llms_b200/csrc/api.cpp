@@ -1,0 +1,489 @@
+// C-ABI layer: context, buffers, quantised-weight registry, operator dispatch,
+// recorded decode steps, timing.  Declarations and the reference interfaces they
+// replace are in include/nnopt_b200.h.
+#include <cuda_runtime.h>
+
+#include <cstdarg>
+#include <cstdio>
+#include <cstdlib>
+#include <cstring>
+#include <map>
+#include <string>
+#include <vector>
+
+#include "../../include/nnopt_b200.h"
+#include "internal.h"
+#include "kernels.h"
+
+using namespace nnb;
+
+// ---------------------------------------------------------------------------------
+// errors: same shape as the reference's NNOPT_ERROR_FMT (always on, prints where)
+// ---------------------------------------------------------------------------------
+static thread_local char g_err[512] = "";
+
+int nnb::fail(int code, const char* file, int line, const char* fmt, ...) {
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(g_err, sizeof(g_err), fmt, ap);
+    va_end(ap);
+    const char* base = strrchr(file, '/');
+    fprintf(stderr, "ERROR: %s (%s:%d)\n", g_err, base ? base + 1 : file, line);
+    return code;
+}
+
+extern "C" const char* nn_last_error(void) { return g_err; }
+extern "C" const char* nn_version(void) { return "nnopt_b200 0.1 (sm_100a)"; }
+
+#define CUDA_TRY(call)                                                                        \
+    do {                                                                                      \
+        cudaError_t e_ = (call);                                                              \
+        if (e_ != cudaSuccess) return NN_FAIL(NN_ERR_CUDA, "%s: %s", #call, cudaGetErrorString(e_)); \
+    } while (0)
+
+// ---------------------------------------------------------------------------------
+// context
+// ---------------------------------------------------------------------------------
+extern "C" int nn_init(int device, nn_context** out) {
+    if (!out) return NN_FAIL(NN_ERR_ARG, "nn_init: out_ctx is null");
+    *out = nullptr;
+    int count = 0;
+    cudaError_t e = cudaGetDeviceCount(&count);
+    if (e != cudaSuccess || count == 0)
+        return NN_FAIL(NN_ERR_CUDA, "nn_init: no CUDA device (%s); this library has no CPU path",
+                       e != cudaSuccess ? cudaGetErrorString(e) : "device count is 0");
+    if (device < 0 || device >= count) return NN_FAIL(NN_ERR_ARG, "nn_init: device %d out of range [0,%d)", device, count);
+    CUDA_TRY(cudaSetDevice(device));
+    cudaDeviceProp prop;
+    CUDA_TRY(cudaGetDeviceProperties(&prop, device));
+    if (prop.major != 10)
+        return NN_FAIL(NN_ERR_UNSUPPORTED, "nn_init: device %d is sm_%d%d; the kernels are built for sm_100a only", device,
+                       prop.major, prop.minor);
+    nn_context* c = new nn_context();
+    c->device = device;
+    c->sm_count = prop.multiProcessorCount;
+    c->l2_bytes = (size_t)prop.l2CacheSize;
+    c->hbm_bytes = prop.totalGlobalMem;
+    c->smem_limit = prop.sharedMemPerBlockOptin;
+    if (cudaStreamCreateWithFlags(&c->stream, cudaStreamNonBlocking) != cudaSuccess) {
+        delete c;
+        return NN_FAIL(NN_ERR_CUDA, "nn_init: cudaStreamCreate failed");
+    }
+    if (cudaHostAlloc((void**)&c->status_host, sizeof(int), cudaHostAllocMapped) != cudaSuccess ||
+        cudaHostGetDevicePointer((void**)&c->status_dev, c->status_host, 0) != cudaSuccess) {
+        delete c;
+        return NN_FAIL(NN_ERR_CUDA, "nn_init: status word allocation failed");
+    }
+    *c->status_host = 0;
+    if (cudaMalloc((void**)&c->argmax_slot, 8) != cudaSuccess) {
+        delete c;
+        return NN_FAIL(NN_ERR_CUDA, "nn_init: cudaMalloc failed");
+    }
+    if ((e = stream_configure()) != cudaSuccess) {
+        delete c;
+        return NN_FAIL(NN_ERR_CUDA, "nn_init: kernel configuration failed: %s", cudaGetErrorString(e));
+    }
+    const char* pdl = getenv("NNB_PDL");
+    c->use_pdl = !(pdl && pdl[0] == '0');
+    *out = c;
+    return NN_OK;
+}
+
+extern "C" int nn_shutdown(nn_context* c) {
+    if (!c) return NN_OK;
+    cudaSetDevice(c->device);
+    cudaStreamSynchronize(c->stream);
+    if (c->flush_buf) cudaFree(c->flush_buf);
+    if (c->argmax_slot) cudaFree(c->argmax_slot);
+    if (c->status_host) cudaFreeHost(c->status_host);
+    cudaStreamDestroy(c->stream);
+    delete c;
+    return NN_OK;
+}
+
+extern "C" void* nn_stream(nn_context* c) { return c ? (void*)c->stream : nullptr; }
+
+extern "C" int nn_sync(nn_context* c) {
+    if (!c) return NN_FAIL(NN_ERR_ARG, "nn_sync: null context");
+    CUDA_TRY(cudaStreamSynchronize(c->stream));
+    if (*c->status_host != 0) {
+        const int s = *c->status_host;
+        *c->status_host = 0;
+        return NN_FAIL(NN_ERR_TIMEOUT, "a device-side bounded wait ran out (status %d); results of the last calls are invalid", s);
+    }
+    return NN_OK;
+}
+
+extern "C" int nn_device_info(nn_context* c, int* sm, size_t* l2, size_t* hbm) {
+    if (!c) return NN_FAIL(NN_ERR_ARG, "nn_device_info: null context");
+    if (sm) *sm = c->sm_count;
+    if (l2) *l2 = c->l2_bytes;
+    if (hbm) *hbm = c->hbm_bytes;
+    return NN_OK;
+}
+
+extern "C" long long nn_launch_count(const nn_context* c) { return c ? c->launches : 0; }
+
+// ---------------------------------------------------------------------------------
+// buffers
+// ---------------------------------------------------------------------------------
+extern "C" nn_buf nn_buf_alloc(nn_context* c, size_t bytes) {
+    if (!c) { NN_FAIL(NN_ERR_ARG, "nn_buf_alloc: null context"); return nullptr; }
+    cudaSetDevice(c->device);
+    void* p = nullptr;
+    cudaError_t e = cudaMalloc(&p, bytes ? bytes : 1);
+    if (e != cudaSuccess) { NN_FAIL(NN_ERR_CUDA, "nn_buf_alloc(%zu): %s", bytes, cudaGetErrorString(e)); return nullptr; }
+    return p;
+}
+extern "C" int nn_buf_free(nn_context* c, nn_buf b) {
+    if (!c) return NN_FAIL(NN_ERR_ARG, "nn_buf_free: null context");
+    if (!b) return NN_OK;
+    cudaSetDevice(c->device);
+    CUDA_TRY(cudaStreamSynchronize(c->stream));
+    CUDA_TRY(cudaFree(b));
+    return NN_OK;
+}
+extern "C" int nn_buf_write(nn_context* c, nn_buf dst, size_t off, const void* src, size_t bytes) {
+    if (!c || !dst || (!src && bytes)) return NN_FAIL(NN_ERR_ARG, "nn_buf_write: null argument");
+    if (!bytes) return NN_OK;
+    CUDA_TRY(cudaMemcpyAsync((char*)dst + off, src, bytes, cudaMemcpyHostToDevice, c->stream));
+    return NN_OK;
+}
+extern "C" int nn_buf_read(nn_context* c, void* dst, nn_buf src, size_t off, size_t bytes) {
+    if (!c || !src || (!dst && bytes)) return NN_FAIL(NN_ERR_ARG, "nn_buf_read: null argument");
+    if (!bytes) return NN_OK;
+    CUDA_TRY(cudaMemcpyAsync(dst, (const char*)src + off, bytes, cudaMemcpyDeviceToHost, c->stream));
+    return NN_OK;
+}
+extern "C" int nn_buf_copy(nn_context* c, nn_buf dst, nn_buf src, size_t bytes) {
+    if (!c || !dst || !src) return NN_FAIL(NN_ERR_ARG, "nn_buf_copy: null argument");
+    if (!bytes) return NN_OK;
+    CUDA_TRY(cudaMemcpyAsync(dst, src, bytes, cudaMemcpyDeviceToDevice, c->stream));
+    return NN_OK;
+}
+extern "C" int nn_buf_fill(nn_context* c, nn_buf dst, int v, size_t bytes) {
+    if (!c || !dst) return NN_FAIL(NN_ERR_ARG, "nn_buf_fill: null argument");
+    if (!bytes) return NN_OK;
+    CUDA_TRY(cudaMemsetAsync(dst, v, bytes, c->stream));
+    return NN_OK;
+}
+extern "C" void* nn_host_alloc(size_t bytes) {
+    void* p = nullptr;
+    cudaError_t e = cudaHostAlloc(&p, bytes ? bytes : 1, cudaHostAllocDefault);
+    if (e != cudaSuccess) { NN_FAIL(NN_ERR_CUDA, "nn_host_alloc(%zu): %s", bytes, cudaGetErrorString(e)); return nullptr; }
+    return p;
+}
+extern "C" int nn_host_free(void* p) {
+    if (p) CUDA_TRY(cudaFreeHost(p));
+    return NN_OK;
+}
+
+// ---------------------------------------------------------------------------------
+// registry
+// ---------------------------------------------------------------------------------
+static size_t fmt_rowbytes(int fmt, int K) { return fmt == FMT_FP16 ? (size_t)K * 2 : fmt == FMT_INT8 ? (size_t)K : (size_t)K / 2; }
+
+static int register_weight(nn_context* c, int fmt, nn_buf W, nn_buf scale, int N, int K, const char* who) {
+    if (!c) return NN_FAIL(NN_ERR_ARG, "%s: null context", who);
+    if (!W || !scale) return NN_FAIL(NN_ERR_ARG, "%s: null weight or scale buffer", who);
+    if (N <= 0 || K <= 0) return NN_FAIL(NN_ERR_ARG, "%s: bad shape N=%d K=%d", who, N, K);
+    if (fmt == FMT_Q4 && (K % 32) != 0) return NN_FAIL(NN_ERR_ARG, "%s: Q4 needs K %% 32 == 0, got K=%d", who, K);
+    QuantEntry q;
+    q.fmt = fmt;
+    q.scale = (const uint16_t*)scale;
+    q.N = N;
+    q.K = K;
+    q.rowbytes = fmt_rowbytes(fmt, K);
+    c->registry[(uintptr_t)W] = q;
+    return NN_OK;
+}
+
+extern "C" int nn_register_int8_weight(nn_context* c, nn_buf W, nn_buf s, int N, int K) {
+    return register_weight(c, FMT_INT8, W, s, N, K, "nn_register_int8_weight");
+}
+extern "C" int nn_register_q4_weight(nn_context* c, nn_buf W, nn_buf s, int N, int K) {
+    return register_weight(c, FMT_Q4, W, s, N, K, "nn_register_q4_weight");
+}
+extern "C" int nn_unregister_weight(nn_context* c, nn_buf W) {
+    if (!c) return NN_FAIL(NN_ERR_ARG, "nn_unregister_weight: null context");
+    c->registry.erase((uintptr_t)W);
+    return NN_OK;
+}
+
+// Resolve W to (format, scale pointer for its first row, rows available).  A pointer
+// inside a registered weight at a whole-row offset is a row-range view of it.
+bool nnb::resolve_weight(const nn_context* c, const void* W, int K, ResolvedW* out) {
+    out->fmt = FMT_FP16;
+    out->scale = nullptr;
+    out->rows_avail = -1;
+    if (c->registry.empty()) return true;
+    const uintptr_t p = (uintptr_t)W;
+    auto it = c->registry.upper_bound(p);
+    if (it == c->registry.begin()) return true;
+    --it;
+    const QuantEntry& q = it->second;
+    const uintptr_t base = it->first;
+    const size_t span = q.rowbytes * (size_t)q.N;
+    if (p >= base + span) return true;  // not inside any registered weight: fp16
+    const size_t off = p - base;
+    if (off % q.rowbytes) return false;  // inside a quantised weight but not on a row boundary
+    if (q.K != K) return false;
+    const size_t r = off / q.rowbytes;
+    out->fmt = q.fmt;
+    out->scale = q.fmt == FMT_INT8 ? q.scale + r : q.scale + r * (size_t)(K / 32);
+    out->rows_avail = q.N - (int)r;
+    return true;
+}
+
+// ---------------------------------------------------------------------------------
+// operator dispatch
+// ---------------------------------------------------------------------------------
+static int run_linear(nn_context* c, int fmt, LinArgs a, int M_total, const char* who) {
+    // M > 16 is walked in slices of 16 activation rows (each slice re-streams the weights).
+    const uint16_t* x0 = a.x;
+    uint16_t* out0[3] = {a.seg[0].out, a.seg[1].out, a.seg[2].out};
+    for (int m0 = 0; m0 < M_total; m0 += 16) {
+        a.M = M_total - m0 < 16 ? M_total - m0 : 16;
+        a.x = x0 + (size_t)m0 * a.K;
+        for (int i = 0; i < a.nseg; ++i) a.seg[i].out = out0[i] + (size_t)m0 * a.seg[i].ld_out;
+        cudaError_t e;
+        if (stream_supported(fmt, a.M, a.K, a)) {
+            int ntiles = 0;
+            if (a.epi == EPI_SWIGLU) {
+                ntiles = (a.seg[0].N + 15) / 16;
+                a.seg[0].tile0 = 0;
+            } else {
+                for (int i = 0; i < a.nseg; ++i) {
+                    a.seg[i].tile0 = ntiles;
+                    ntiles += (a.seg[i].N + 31) / 32;
+                }
+            }
+            a.ntiles = ntiles;
+            StreamPlan p = stream_plan(fmt, a.M, a.K, ntiles, c->sm_count, c->smem_limit);
+            if (p.ok) {
+                e = launch_stream(fmt, a, p, c->stream, c->use_pdl);
+            } else {
+                e = launch_generic(fmt, a, c->stream);
+            }
+        } else {
+            e = launch_generic(fmt, a, c->stream);
+        }
+        if (e != cudaSuccess) return NN_FAIL(NN_ERR_CUDA, "%s: launch failed: %s (M=%d K=%d)", who, cudaGetErrorString(e), a.M, a.K);
+        c->launches++;
+    }
+    return NN_OK;
+}
+
+static int check_common(nn_context* c, int M, int N, int K, const void* x, const void* W, const void* out, const char* who) {
+    if (!c) return NN_FAIL(NN_ERR_ARG, "%s: null context", who);
+    if (!x || !W || !out) return NN_FAIL(NN_ERR_ARG, "%s: null buffer (x=%p W=%p out=%p)", who, x, W, out);
+    if (M < 0 || N <= 0 || K <= 0) return NN_FAIL(NN_ERR_ARG, "%s: bad shape M=%d N=%d K=%d", who, M, N, K);
+    return NN_OK;
+}
+
+static int one_weight(nn_context* c, int M, int N, int K, nn_buf x, nn_buf W, nn_buf out, int epi, const char* who) {
+    int rc = check_common(c, M, N, K, x, W, out, who);
+    if (rc) return rc;
+    if (M == 0) return NN_OK;
+    ResolvedW r;
+    if (!resolve_weight(c, W, K, &r))
+        return NN_FAIL(NN_ERR_ARG, "%s: W points into a registered quantised weight but K=%d or the row offset does not match", who, K);
+    if (r.rows_avail >= 0 && N > r.rows_avail)
+        return NN_FAIL(NN_ERR_ARG, "%s: N=%d exceeds the %d rows registered for this weight", who, N, r.rows_avail);
+    LinArgs a = {};
+    a.nseg = 1;
+    a.seg[0].W = (const uint8_t*)W;
+    a.seg[0].scale = r.scale;
+    a.seg[0].out = (uint16_t*)out;
+    a.seg[0].N = N;
+    a.seg[0].ld_out = N;
+    a.x = (const uint16_t*)x;
+    a.K = K;
+    a.epi = epi;
+    a.status = c->status_dev;
+    return run_linear(c, r.fmt, a, M, who);
+}
+
+extern "C" int nn_linear(nn_context* c, int M, int N, int K, nn_buf x, nn_buf W, nn_buf out) {
+    return one_weight(c, M, N, K, x, W, out, EPI_STORE, "nn_linear");
+}
+extern "C" int nn_linear_add(nn_context* c, int M, int N, int K, nn_buf x, nn_buf W, nn_buf r) {
+    return one_weight(c, M, N, K, x, W, r, EPI_RESIDUAL, "nn_linear_add");
+}
+extern "C" int nn_linear_silu_gate_fused(nn_context* c, int M, int N, int K, nn_buf x, nn_buf W3, nn_buf g) {
+    return one_weight(c, M, N, K, x, W3, g, EPI_SILU_GATE, "nn_linear_silu_gate_fused");
+}
+
+extern "C" int nn_fused_gate_up_silu(nn_context* c, int M, int N, int K, nn_buf x, nn_buf Wg, nn_buf Wu, nn_buf out) {
+    const char* who = "nn_fused_gate_up_silu";
+    int rc = check_common(c, M, N, K, x, Wg, out, who);
+    if (rc) return rc;
+    if (!Wu) return NN_FAIL(NN_ERR_ARG, "%s: null Wu", who);
+    if (M == 0) return NN_OK;
+    ResolvedW rg, ru;
+    if (!resolve_weight(c, Wg, K, &rg) || !resolve_weight(c, Wu, K, &ru))
+        return NN_FAIL(NN_ERR_ARG, "%s: weight registration does not match K=%d", who, K);
+    if (rg.fmt != ru.fmt) return NN_FAIL(NN_ERR_ARG, "%s: gate and up weights are of different formats", who);
+    if ((rg.rows_avail >= 0 && N > rg.rows_avail) || (ru.rows_avail >= 0 && N > ru.rows_avail))
+        return NN_FAIL(NN_ERR_ARG, "%s: N=%d exceeds the registered rows", who, N);
+    LinArgs a = {};
+    a.nseg = 1;
+    a.seg[0].W = (const uint8_t*)Wg;
+    a.seg[0].scale = rg.scale;
+    a.seg[0].out = (uint16_t*)out;
+    a.seg[0].N = N;
+    a.seg[0].ld_out = N;
+    a.W2 = (const uint8_t*)Wu;
+    a.scale2 = ru.scale;
+    a.x = (const uint16_t*)x;
+    a.K = K;
+    a.epi = EPI_SWIGLU;
+    a.status = c->status_dev;
+    return run_linear(c, rg.fmt, a, M, who);
+}
+
+extern "C" int nn_linear_qkv(nn_context* c, int M, int K, nn_buf x, nn_buf Wq, int Nq, nn_buf Wk, int Nk, nn_buf Wv, int Nv,
+                             nn_buf q, nn_buf k, nn_buf v) {
+    const char* who = "nn_linear_qkv";
+    if (!c) return NN_FAIL(NN_ERR_ARG, "%s: null context", who);
+    if (!x || !Wq || !Wk || !Wv || !q || !k || !v) return NN_FAIL(NN_ERR_ARG, "%s: null buffer", who);
+    if (M < 0 || K <= 0 || Nq <= 0 || Nk <= 0 || Nv <= 0) return NN_FAIL(NN_ERR_ARG, "%s: bad shape", who);
+    if (M == 0) return NN_OK;
+    const void* Ws[3] = {Wq, Wk, Wv};
+    void* outs[3] = {q, k, v};
+    const int Ns[3] = {Nq, Nk, Nv};
+    LinArgs a = {};
+    a.nseg = 3;
+    int fmt = -1;
+    for (int i = 0; i < 3; ++i) {
+        ResolvedW r;
+        if (!resolve_weight(c, Ws[i], K, &r)) return NN_FAIL(NN_ERR_ARG, "%s: weight %d registration does not match K=%d", who, i, K);
+        if (r.rows_avail >= 0 && Ns[i] > r.rows_avail) return NN_FAIL(NN_ERR_ARG, "%s: weight %d has fewer rows than asked", who, i);
+        if (fmt >= 0 && r.fmt != fmt) return NN_FAIL(NN_ERR_ARG, "%s: the three weights are of different formats", who);
+        fmt = r.fmt;
+        a.seg[i].W = (const uint8_t*)Ws[i];
+        a.seg[i].scale = r.scale;
+        a.seg[i].out = (uint16_t*)outs[i];
+        a.seg[i].N = Ns[i];
+        a.seg[i].ld_out = Ns[i];
+    }
+    a.x = (const uint16_t*)x;
+    a.K = K;
+    a.epi = EPI_STORE;
+    a.status = c->status_dev;
+    return run_linear(c, fmt, a, M, who);
+}
+
+extern "C" int nn_dequant(nn_context* c, int N, int K, nn_buf W, nn_buf out) {
+    if (!c || !W || !out) return NN_FAIL(NN_ERR_ARG, "nn_dequant: null argument");
+    if (N <= 0 || K <= 0) return NN_FAIL(NN_ERR_ARG, "nn_dequant: bad shape N=%d K=%d", N, K);
+    ResolvedW r;
+    if (!resolve_weight(c, W, K, &r)) return NN_FAIL(NN_ERR_ARG, "nn_dequant: registration does not match K=%d", K);
+    if (r.rows_avail >= 0 && N > r.rows_avail) return NN_FAIL(NN_ERR_ARG, "nn_dequant: N exceeds the registered rows");
+    CUDA_TRY(launch_dequant(r.fmt, N, K, W, r.scale, (float*)out, c->stream));
+    c->launches++;
+    return NN_OK;
+}
+
+extern "C" int nn_argmax(nn_context* c, int n, nn_buf logits, nn_buf out_idx) {
+    if (!c || !logits || !out_idx) return NN_FAIL(NN_ERR_ARG, "nn_argmax: null argument");
+    if (n < 0) return NN_FAIL(NN_ERR_ARG, "nn_argmax: n=%d", n);
+    CUDA_TRY(launch_argmax_half((const uint16_t*)logits, n, (int*)out_idx, c->argmax_slot, c->stream));
+    c->launches += n > 0 ? 3 : 2;
+    return NN_OK;
+}
+
+// ---------------------------------------------------------------------------------
+// recorded decode step (CUDA graph of the captured launches, PDL edges kept)
+// ---------------------------------------------------------------------------------
+struct nn_plan {
+    cudaGraph_t graph = nullptr;
+    cudaGraphExec_t exec = nullptr;
+    int kernels = 0;
+};
+
+extern "C" int nn_plan_begin(nn_context* c) {
+    if (!c) return NN_FAIL(NN_ERR_ARG, "nn_plan_begin: null context");
+    if (c->capturing) return NN_FAIL(NN_ERR_ARG, "nn_plan_begin: already recording");
+    CUDA_TRY(cudaStreamBeginCapture(c->stream, cudaStreamCaptureModeThreadLocal));
+    c->capturing = true;
+    c->launches_at_capture = c->launches;
+    return NN_OK;
+}
+
+extern "C" int nn_plan_end(nn_context* c, nn_plan** out) {
+    if (!c || !out) return NN_FAIL(NN_ERR_ARG, "nn_plan_end: null argument");
+    if (!c->capturing) return NN_FAIL(NN_ERR_ARG, "nn_plan_end: not recording");
+    c->capturing = false;
+    nn_plan* p = new nn_plan();
+    cudaError_t e = cudaStreamEndCapture(c->stream, &p->graph);
+    if (e != cudaSuccess || !p->graph) {
+        delete p;
+        return NN_FAIL(NN_ERR_CUDA, "nn_plan_end: capture failed: %s", cudaGetErrorString(e));
+    }
+    e = cudaGraphInstantiate(&p->exec, p->graph, 0);
+    if (e != cudaSuccess) {
+        cudaGraphDestroy(p->graph);
+        delete p;
+        return NN_FAIL(NN_ERR_CUDA, "nn_plan_end: instantiate failed: %s", cudaGetErrorString(e));
+    }
+    p->kernels = (int)(c->launches - c->launches_at_capture);
+    c->launches = c->launches_at_capture;  // recorded, not run
+    *out = p;
+    return NN_OK;
+}
+
+extern "C" int nn_plan_launch(nn_context* c, nn_plan* p) {
+    if (!c || !p || !p->exec) return NN_FAIL(NN_ERR_ARG, "nn_plan_launch: null argument");
+    CUDA_TRY(cudaGraphLaunch(p->exec, c->stream));
+    c->launches += p->kernels;
+    return NN_OK;
+}
+
+extern "C" int nn_plan_num_kernels(const nn_plan* p) { return p ? p->kernels : 0; }
+
+extern "C" int nn_plan_free(nn_plan* p) {
+    if (!p) return NN_OK;
+    if (p->exec) cudaGraphExecDestroy(p->exec);
+    if (p->graph) cudaGraphDestroy(p->graph);
+    delete p;
+    return NN_OK;
+}
+
+// ---------------------------------------------------------------------------------
+// timing
+// ---------------------------------------------------------------------------------
+extern "C" int nn_event_create(void** out) {
+    if (!out) return NN_FAIL(NN_ERR_ARG, "nn_event_create: null argument");
+    cudaEvent_t ev;
+    CUDA_TRY(cudaEventCreate(&ev));
+    *out = (void*)ev;
+    return NN_OK;
+}
+extern "C" int nn_event_record(nn_context* c, void* ev) {
+    if (!c || !ev) return NN_FAIL(NN_ERR_ARG, "nn_event_record: null argument");
+    CUDA_TRY(cudaEventRecord((cudaEvent_t)ev, c->stream));
+    return NN_OK;
+}
+extern "C" int nn_event_elapsed_ms(void* a, void* b, float* ms) {
+    if (!a || !b || !ms) return NN_FAIL(NN_ERR_ARG, "nn_event_elapsed_ms: null argument");
+    CUDA_TRY(cudaEventSynchronize((cudaEvent_t)b));
+    CUDA_TRY(cudaEventElapsedTime(ms, (cudaEvent_t)a, (cudaEvent_t)b));
+    return NN_OK;
+}
+extern "C" int nn_event_destroy(void* ev) {
+    if (ev) CUDA_TRY(cudaEventDestroy((cudaEvent_t)ev));
+    return NN_OK;
+}
+
+extern "C" int nn_l2_flush(nn_context* c) {
+    if (!c) return NN_FAIL(NN_ERR_ARG, "nn_l2_flush: null context");
+    if (!c->flush_buf) {
+        c->flush_bytes = c->l2_bytes * 2 > ((size_t)256 << 20) ? c->l2_bytes * 2 : ((size_t)256 << 20);
+        cudaSetDevice(c->device);
+        CUDA_TRY(cudaMalloc(&c->flush_buf, c->flush_bytes));
+        CUDA_TRY(cudaMemsetAsync(c->flush_buf, 0, c->flush_bytes, c->stream));
+    }
+    CUDA_TRY(launch_l2_flush(c->flush_buf, c->flush_bytes, c->stream));
+    return NN_OK;
+}

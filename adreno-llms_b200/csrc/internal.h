@@ -1,0 +1,44 @@
+// Internal state shared by the C-ABI translation units (not installed).
+#pragma once
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include <map>
+
+struct QuantEntry {
+    int fmt;
+    const uint16_t* scale;
+    int N, K;
+    size_t rowbytes;
+};
+
+struct nn_context {
+    int device = 0;
+    int sm_count = 0;
+    size_t l2_bytes = 0, hbm_bytes = 0, smem_limit = 0;
+    cudaStream_t stream = nullptr;
+    std::map<uintptr_t, QuantEntry> registry;  // keyed by weight device pointer
+    int* status_host = nullptr;                // mapped pinned word written by kernels
+    int* status_dev = nullptr;
+    unsigned long long* argmax_slot = nullptr;
+    void* flush_buf = nullptr;
+    size_t flush_bytes = 0;
+    bool use_pdl = true;
+    bool capturing = false;
+    long long launches = 0, launches_at_capture = 0;
+};
+
+namespace nnb {
+
+struct ResolvedW {
+    int fmt;
+    const uint16_t* scale;
+    int rows_avail;  // -1 when W is not a registered weight (fp16)
+};
+bool resolve_weight(const nn_context* c, const void* W, int K, ResolvedW* out);
+
+int fail(int code, const char* file, int line, const char* fmt, ...) __attribute__((format(printf, 4, 5)));
+
+}  // namespace nnb
+
+#define NN_FAIL(code, ...) nnb::fail((code), __FILE__, __LINE__, __VA_ARGS__)

@@ -1,0 +1,69 @@
+// Internal launch interface between the C-ABI layer (api.cpp) and the CUDA
+// translation units.  Nothing here is exported from the shared library.
+#pragma once
+#include <cuda_runtime.h>
+#include <stddef.h>
+#include <stdint.h>
+
+namespace nnb {
+
+enum Fmt : int { FMT_FP16 = 0, FMT_INT8 = 1, FMT_Q4 = 2 };
+
+// What work-item 0 of the reference kernels does with the reduced sum.
+enum Epi : int {
+    EPI_STORE = 0,      // out = half(acc)
+    EPI_RESIDUAL = 1,   // out = half(float(out) + acc)               (in place)
+    EPI_SWIGLU = 2,     // out = half(silu(acc_gate) * acc_up)        (two weights)
+    EPI_SILU_GATE = 3,  // out = half(out * sigmoid(out) * acc)       (in place)
+};
+
+struct LinSeg {
+    const uint8_t* W;       // [N, rowbytes] row-major, on-disk layout
+    const uint16_t* scale;  // int8: [N]; Q4: [N, K/32]; fp16: null
+    uint16_t* out;          // [M, ld_out] fp16 (or the in/out vector)
+    int N;                  // rows of this segment
+    int ld_out;             // leading dimension of out (elements)
+    int tile0;              // first 32-row tile of this segment in the launch
+};
+
+struct LinArgs {
+    LinSeg seg[3];  // up to three weights sharing x (fused QKV); normally one
+    int nseg;
+    const uint8_t* W2;       // EPI_SWIGLU: the "up" weight (seg[0] is the gate)
+    const uint16_t* scale2;  // EPI_SWIGLU: its scales
+    const uint16_t* x;       // [M, K] fp16
+    int M, K;
+    int ntiles;      // row tiles over all segments
+    int epi;         // Epi
+    int kcb;         // bytes of one weight row moved per pipeline stage
+    int kw;          // warps that split K of one tile (1, 2 or 4)
+    int* status;     // device word: non-zero when a bounded wait ran out
+    // optional fused arg-max over the stored fp16 values of seg[0] (M == 1)
+    unsigned long long* argmax_slot;  // packed (ordered value << 32 | ~index), atomicMax
+};
+
+struct StreamPlan {  // launch geometry chosen on the host
+    int grid;
+    int kcb;
+    int kw;
+    size_t smem;
+    bool ok;
+};
+
+// gemv_stream.cu
+bool stream_supported(int fmt, int M, int K, const LinArgs& a);
+StreamPlan stream_plan(int fmt, int M, int K, int ntiles, int sm_count, size_t smem_limit);
+cudaError_t launch_stream(int fmt, const LinArgs& a, const StreamPlan& p, cudaStream_t st, bool pdl);
+cudaError_t stream_configure();  // opt in to large dynamic shared memory, once per device
+
+// gemv_generic.cu: any K, any alignment (the reference's gemv_rT_fp32acc role)
+cudaError_t launch_generic(int fmt, const LinArgs& a, cudaStream_t st);
+
+// misc.cu
+cudaError_t launch_dequant(int fmt, int N, int K, const void* W, const uint16_t* scale, float* out, cudaStream_t st);
+cudaError_t launch_argmax_half(const uint16_t* v, int n, int* out_idx, unsigned long long* slot, cudaStream_t st);
+cudaError_t launch_fill_u64(unsigned long long* p, unsigned long long v, cudaStream_t st);
+cudaError_t launch_argmax_finish(const unsigned long long* slot, int* out_idx, cudaStream_t st);
+cudaError_t launch_l2_flush(void* buf, size_t bytes, cudaStream_t st);
+
+}  // namespace nnb

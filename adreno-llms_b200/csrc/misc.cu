@@ -1,0 +1,131 @@
+// Small helper kernels: dequantisation dump (parity check of the unpack rule),
+// arg-max over fp16 logits, L2 flush for cold timing.
+#include <cuda_fp16.h>
+#include <float.h>
+
+#include "kernels.h"
+
+namespace nnb {
+namespace {
+
+__device__ __forceinline__ float h2f(uint16_t h) { return __half2float(__ushort_as_half(h)); }
+
+// out[n,k] = float(code) * float(scale): the unpack contract of
+// src/models/lfm2-5-350m/kernels/gemv_m1_q4.cl:31-40 (nibble - 8, low nibble = even k)
+// and src/models/lfm2-5-350m/scripts/quantize_weights.py:136 (int8 * per-row scale).
+template <int FMT>
+__global__ void dequant_kernel(const uint8_t* __restrict__ W, const uint16_t* __restrict__ scale, float* __restrict__ out,
+                               int N, int K) {
+    const size_t total = (size_t)N * K;
+    for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
+        const size_t n = i / K;
+        const int k = (int)(i - n * K);
+        float v;
+        if (FMT == FMT_FP16) {
+            v = h2f(reinterpret_cast<const uint16_t*>(W)[i]);
+        } else if (FMT == FMT_INT8) {
+            v = (float)reinterpret_cast<const int8_t*>(W)[i] * h2f(scale[n]);
+        } else {
+            const uint8_t b = W[n * (size_t)(K / 2) + (k >> 1)];
+            const int code = (int)((b >> (4 * (k & 1))) & 0xF) - 8;
+            v = (float)code * h2f(scale[n * (size_t)(K / 32) + (k >> 5)]);
+        }
+        out[i] = v;
+    }
+}
+
+// Order-preserving key: larger value wins, then the LOWER index.
+__device__ __forceinline__ unsigned long long argmax_key(float v, int idx) {
+    unsigned int b = __float_as_uint(v);
+    b = (b & 0x80000000u) ? ~b : (b | 0x80000000u);
+    return ((unsigned long long)b << 32) | (unsigned long long)(0xFFFFFFFFu - (unsigned int)idx);
+}
+
+__global__ void argmax_half_kernel(const uint16_t* __restrict__ v, int n, unsigned long long* slot) {
+    unsigned long long best = 0ull;
+    for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < n; i += gridDim.x * blockDim.x) {
+        const float f = h2f(v[i]);
+        if (f == f) {  // NaNs never win
+            const unsigned long long k = argmax_key(f, i);
+            best = k > best ? k : best;
+        }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        const unsigned long long other = __shfl_xor_sync(0xffffffffu, best, o);
+        best = other > best ? other : best;
+    }
+    __shared__ unsigned long long sm[32];
+    if ((threadIdx.x & 31) == 0) sm[threadIdx.x >> 5] = best;
+    __syncthreads();
+    if (threadIdx.x < 32) {
+        best = threadIdx.x < (blockDim.x >> 5) ? sm[threadIdx.x] : 0ull;
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            const unsigned long long other = __shfl_xor_sync(0xffffffffu, best, o);
+            best = other > best ? other : best;
+        }
+        if (threadIdx.x == 0 && best) atomicMax(slot, best);
+    }
+}
+
+__global__ void fill_u64_kernel(unsigned long long* p, unsigned long long v) { *p = v; }
+
+__global__ void argmax_finish_kernel(const unsigned long long* slot, int* out_idx) {
+    const unsigned long long k = *slot;
+    *out_idx = k ? (int)(0xFFFFFFFFu - (unsigned int)(k & 0xFFFFFFFFull)) : -1;
+}
+
+__global__ void l2_flush_kernel(uint4* buf, size_t n16) {
+    for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < n16; i += (size_t)gridDim.x * blockDim.x) {
+        uint4 v = buf[i];
+        v.x += 1u;
+        buf[i] = v;
+    }
+}
+
+}  // namespace
+
+cudaError_t launch_dequant(int fmt, int N, int K, const void* W, const uint16_t* scale, float* out, cudaStream_t st) {
+    const size_t total = (size_t)N * K;
+    if (total == 0) return cudaSuccess;
+    const int threads = 256;
+    size_t blocks = (total + threads - 1) / threads;
+    if (blocks > 148 * 16) blocks = 148 * 16;
+    const uint8_t* w = static_cast<const uint8_t*>(W);
+    if (fmt == FMT_FP16) dequant_kernel<FMT_FP16><<<(unsigned)blocks, threads, 0, st>>>(w, scale, out, N, K);
+    else if (fmt == FMT_INT8) dequant_kernel<FMT_INT8><<<(unsigned)blocks, threads, 0, st>>>(w, scale, out, N, K);
+    else dequant_kernel<FMT_Q4><<<(unsigned)blocks, threads, 0, st>>>(w, scale, out, N, K);
+    return cudaGetLastError();
+}
+
+cudaError_t launch_fill_u64(unsigned long long* p, unsigned long long v, cudaStream_t st) {
+    fill_u64_kernel<<<1, 1, 0, st>>>(p, v);
+    return cudaGetLastError();
+}
+
+cudaError_t launch_argmax_finish(const unsigned long long* slot, int* out_idx, cudaStream_t st) {
+    argmax_finish_kernel<<<1, 1, 0, st>>>(slot, out_idx);
+    return cudaGetLastError();
+}
+
+cudaError_t launch_argmax_half(const uint16_t* v, int n, int* out_idx, unsigned long long* slot, cudaStream_t st) {
+    cudaError_t e = launch_fill_u64(slot, 0ull, st);
+    if (e != cudaSuccess) return e;
+    if (n > 0) {
+        int blocks = (n + 1023) / 1024;
+        if (blocks > 148 * 4) blocks = 148 * 4;
+        argmax_half_kernel<<<blocks, 256, 0, st>>>(v, n, slot);
+        if ((e = cudaGetLastError()) != cudaSuccess) return e;
+    }
+    return launch_argmax_finish(slot, out_idx, st);
+}
+
+cudaError_t launch_l2_flush(void* buf, size_t bytes, cudaStream_t st) {
+    const size_t n16 = bytes / 16;
+    if (!n16) return cudaSuccess;
+    l2_flush_kernel<<<148 * 8, 256, 0, st>>>(static_cast<uint4*>(buf), n16);
+    return cudaGetLastError();
+}
+
+}  // namespace nnb

@@ -1,0 +1,133 @@
+// Thin inline-PTX wrappers used by the sm_100a kernels: mbarrier, bulk async
+// copies (TMA unit), cp.async, ldmatrix, warp-level MMA, programmatic dependent
+// launch, and the nibble / int8 -> half2 converters.
+#pragma once
+#include <cuda_fp16.h>
+#include <stdint.h>
+
+namespace nnb {
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) {
+    return (uint32_t)__cvta_generic_to_shared(p);
+}
+
+// ---- mbarrier ----------------------------------------------------------------
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_init_fence() {
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+}
+__device__ __forceinline__ void mbar_arrive_expect_tx(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ uint32_t mbar_try_wait(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    return ok;
+}
+// Bounded wait: returns false when the limit ran out (caller records an error
+// status and leaves; nothing spins forever).
+__device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar, uint32_t parity, uint32_t limit = (1u << 22)) {
+    for (uint32_t i = 0; i < limit; ++i)
+        if (mbar_try_wait(bar, parity)) return true;
+    return false;
+}
+
+// ---- bulk async copy global -> shared (1-D, TMA unit) --------------------------
+// Both addresses 16-byte aligned, size a multiple of 16 bytes.
+__device__ __forceinline__ uint64_t l2_policy_evict_first() {
+    uint64_t pol;
+    asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(pol));
+    return pol;
+}
+__device__ __forceinline__ uint64_t l2_policy_evict_normal() {
+    uint64_t pol;
+    asm volatile("createpolicy.fractional.L2::evict_normal.b64 %0, 1.0;" : "=l"(pol));
+    return pol;
+}
+__device__ __forceinline__ void bulk_g2s(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar, uint64_t policy) {
+    asm volatile(
+        "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint [%0], [%1], %2, [%3], %4;" ::"r"(dst),
+        "l"(src), "r"(bytes), "r"(bar), "l"(policy)
+        : "memory");
+}
+
+// ---- cp.async (per-thread, 4/16-byte) tracked by an mbarrier -------------------
+__device__ __forceinline__ void cp_async_4(uint32_t dst, const void* src) {
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(dst), "l"(src) : "memory");
+}
+__device__ __forceinline__ void cp_async_16(uint32_t dst, const void* src) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
+}
+__device__ __forceinline__ void cp_async_mbar_arrive_noinc(uint32_t bar) {
+    asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(bar) : "memory");
+}
+
+// ---- ldmatrix / mma ------------------------------------------------------------
+__device__ __forceinline__ void ldsm_x4(uint32_t addr, uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3)
+                 : "r"(addr));
+}
+// D(16x8,f32) += A(16x16,f16,row) * B(16x8,f16,col)
+__device__ __forceinline__ void mma_16816(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
+                                          uint32_t b1) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+        : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+// ---- programmatic dependent launch ----------------------------------------------
+__device__ __forceinline__ void pdl_wait_prior_grid() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
+// ---- exact integer -> half2 converters -------------------------------------------
+// 4 int8 in one word -> two half2 holding (q0,q1) and (q2,q3), exact.
+// Bias the bytes to unsigned, drop each into the mantissa of 1024.0h, subtract 1152.
+__device__ __forceinline__ void int8x4_to_half2x2(uint32_t w, uint32_t& h01, uint32_t& h23) {
+    const uint32_t u = w ^ 0x80808080u;
+    uint32_t a, b;
+    asm("prmt.b32 %0, %1, %2, 0x4140;" : "=r"(a) : "r"(u), "r"(0x64646464u));
+    asm("prmt.b32 %0, %1, %2, 0x4342;" : "=r"(b) : "r"(u), "r"(0x64646464u));
+    const __half2 bias = __halves2half2(__ushort_as_half(0x6480), __ushort_as_half(0x6480));  // 1152
+    __half2 ha = __hsub2(*reinterpret_cast<__half2*>(&a), bias);
+    __half2 hb = __hsub2(*reinterpret_cast<__half2*>(&b), bias);
+    h01 = *reinterpret_cast<uint32_t*>(&ha);
+    h23 = *reinterpret_cast<uint32_t*>(&hb);
+}
+
+// 8 nibbles in one word -> four half2 of (nibble - 8), exact, paired as
+// (n0,n4) (n1,n5) (n2,n6) (n3,n7)  [n_i = bits 4i..4i+3].
+__device__ __forceinline__ void q4x8_to_half2x4(uint32_t w, uint32_t& p04, uint32_t& p15, uint32_t& p26, uint32_t& p37) {
+    const uint32_t MAGIC = 0x64006400u;  // 1024.0h in both lanes
+    uint32_t lo0, hi0, lo1, hi1;
+    const uint32_t w8 = w >> 8;
+    asm("lop3.b32 %0, %1, %2, %3, 0xEA;" : "=r"(lo0) : "r"(w), "r"(0x000F000Fu), "r"(MAGIC));
+    asm("lop3.b32 %0, %1, %2, %3, 0xEA;" : "=r"(hi0) : "r"(w), "r"(0x00F000F0u), "r"(MAGIC));
+    asm("lop3.b32 %0, %1, %2, %3, 0xEA;" : "=r"(lo1) : "r"(w8), "r"(0x000F000Fu), "r"(MAGIC));
+    asm("lop3.b32 %0, %1, %2, %3, 0xEA;" : "=r"(hi1) : "r"(w8), "r"(0x00F000F0u), "r"(MAGIC));
+    const __half2 b1032 = __halves2half2(__ushort_as_half(0x6408), __ushort_as_half(0x6408));  // 1024 + 8
+    const __half2 sixteenth = __halves2half2(__ushort_as_half(0x2C00), __ushort_as_half(0x2C00));  // 1/16
+    const __half2 m72 = __halves2half2(__ushort_as_half(0xD480), __ushort_as_half(0xD480));        // -(64 + 8)
+    __half2 r0 = __hsub2(*reinterpret_cast<__half2*>(&lo0), b1032);
+    __half2 r1 = __hfma2(*reinterpret_cast<__half2*>(&hi0), sixteenth, m72);
+    __half2 r2 = __hsub2(*reinterpret_cast<__half2*>(&lo1), b1032);
+    __half2 r3 = __hfma2(*reinterpret_cast<__half2*>(&hi1), sixteenth, m72);
+    p04 = *reinterpret_cast<uint32_t*>(&r0);
+    p15 = *reinterpret_cast<uint32_t*>(&r1);
+    p26 = *reinterpret_cast<uint32_t*>(&r2);
+    p37 = *reinterpret_cast<uint32_t*>(&r3);
+}
+
+}  // namespace nnb

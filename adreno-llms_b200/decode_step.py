@@ -1,0 +1,116 @@
+"""The projection set of one decode step, driven through the C ABI.
+
+Mirrors the call points of the reference's decode loop
+(src/models/smollm2-135m-instruct/src/model.cpp:88-239): per layer a fused QKV
+launch, o_proj + residual, fused gate/up/SiLU, down + residual, then the lm_head
+GEMV and the arg-max.  The operators between the projections (norms, RoPE,
+attention) are not on this path; each projection reads a fixed N(0,1) activation
+buffer, and stream order carries the step's launch-to-launch dependencies the way
+the reference's in-order queue does.
+
+Several copies ("sets") of the weights can be resident so that consecutive steps
+stream from HBM rather than L2.
+"""
+import numpy as np
+
+from . import QuantWeight
+from . import synth
+
+
+class DecodeStep:
+    def __init__(self, ctx, shape: synth.ModelShape, fmt: str, M: int = 1, n_sets: int = 1, seed: int = 1235,
+                 vocab_rows=None, keep_host=False):
+        self.ctx, self.shape, self.fmt, self.M = ctx, shape, fmt, M
+        self.vocab_lo, self.vocab_n = vocab_rows if vocab_rows else (0, shape.vocab)
+        rng = np.random.default_rng(seed)
+        H, F = shape.hidden, shape.ffn
+        self.host = {} if keep_host else None
+        self.ops = synth.decode_step_ops(shape)
+        # activations (fixed inputs) and outputs
+        self.x_h = self._act("x_h", M, H, rng)      # normed hidden -> QKV and gate/up
+        self.x_attn = self._act("x_attn", M, shape.q_dim, rng)   # attention output -> o_proj
+        self.x_act = self._act("x_act", M, F, rng)  # SwiGLU output -> down_proj
+        self.resid0 = synth.activations(M, H, rng)
+        self.resid = ctx.upload(self.resid0.view(np.uint16))
+        self.q = ctx.alloc(M * shape.q_dim * 2)
+        self.k = ctx.alloc(M * shape.kv_dim * 2)
+        self.v = ctx.alloc(M * shape.kv_dim * 2)
+        self.act = ctx.alloc(M * F * 2)
+        self.logits = ctx.alloc(M * self.vocab_n * 2)
+        self.token = ctx.alloc(4)
+        # weights: one host copy, n_sets device copies
+        self.sets = [dict() for _ in range(n_sets)]
+        self.weight_bytes = 0
+        for kind, layer, ws in self.ops:
+            for j, (n, k) in enumerate(ws):
+                name = f"{kind}.{layer}.{j}"
+                if kind == "lm_head":
+                    Wfull, sfull = synth.weight(fmt, shape.vocab, k, rng)
+                    lo, cnt = self.vocab_lo, self.vocab_n
+                    W = Wfull[lo:lo + cnt]
+                    s = None if sfull is None else sfull[lo:lo + cnt]
+                else:
+                    W, s = synth.weight(fmt, n, k, rng)
+                if self.host is not None:
+                    self.host[name] = (W, s)
+                self.weight_bytes += W.nbytes + (0 if s is None else s.nbytes)
+                for st in self.sets:
+                    st[name] = QuantWeight(ctx, fmt, W, s)
+        self.plans = [None] * n_sets
+        self.kernels_per_step = None
+
+    def _act(self, name, m, k, rng):
+        a = synth.activations(m, k, rng)
+        if self.host is not None:
+            self.host[name] = a
+        return self.ctx.upload(a.view(np.uint16))
+
+    def algorithmic_bytes(self):
+        total = 0
+        for kind, _, ws in self.ops:
+            for n, k in ws:
+                if kind == "lm_head":
+                    n = self.vocab_n
+                total += synth.linear_bytes(self.fmt, n, k, self.M)
+        return total
+
+    def enqueue(self, set_index=0, with_argmax=True):
+        """Issue the step's launches on the context's stream (or into a recording)."""
+        c, s, M, sh = self.ctx, self.sets[set_index], self.M, self.shape
+        for kind, layer, ws in self.ops:
+            w = [s[f"{kind}.{layer}.{j}"].buf for j in range(len(ws))]
+            if kind == "qkv":
+                c.linear_qkv(M, sh.hidden, self.x_h, w[0], sh.q_dim, w[1], sh.kv_dim, w[2], sh.kv_dim, self.q, self.k, self.v)
+            elif kind == "o_add":
+                c.linear_add(M, sh.hidden, sh.q_dim, self.x_attn, w[0], self.resid)
+            elif kind == "gate_up":
+                c.fused_gate_up_silu(M, sh.ffn, sh.hidden, self.x_h, w[0], w[1], self.act)
+            elif kind == "down_add":
+                c.linear_add(M, sh.hidden, sh.ffn, self.x_act, w[0], self.resid)
+            else:
+                c.linear(M, self.vocab_n, sh.hidden, self.x_h, w[0], self.logits)
+        if with_argmax and M == 1:
+            c.argmax(self.vocab_n, self.logits, self.token)
+
+    def record(self, with_argmax=True):
+        """Record one plan per weight set (the reference's recorded-queue replay)."""
+        for i in range(len(self.sets)):
+            before = self.ctx.launch_count()
+            self.ctx.plan_begin()
+            self.enqueue(i, with_argmax)
+            self.plans[i] = self.ctx.plan_end()
+            self.kernels_per_step = self.ctx.L.nn_plan_num_kernels(self.plans[i])
+            assert self.ctx.launch_count() == before
+        return self.kernels_per_step
+
+    def launch(self, set_index=0):
+        self.ctx.plan_launch(self.plans[set_index])
+
+    def reset_residual(self):
+        self.ctx.upload(self.resid0.view(np.uint16), self.resid)
+
+    def read_logits(self):
+        return self.ctx.download(self.logits, (self.M, self.vocab_n), np.uint16).view(np.float16)
+
+    def read_token(self):
+        return int(self.ctx.download(self.token, (1,), np.int32)[0])

@@ -1,0 +1,387 @@
+#!/usr/bin/env python3
+"""Benchmark of the decode-step projection set (BASELINE.json configs[1]).
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--fmt int8|fp16|q4]
+
+A step is one pass over every projection of a SmolLM2-135M-shaped decode step
+(30 x {QKV, o_proj+residual, gate/up/SiLU, down+residual} + tied lm_head; 211 GEMVs
+issued as 121 fused launches) at M = 1 on seeded synthetic weights.  The metric is the
+achieved weight-stream rate: algorithmic bytes of the step / step time, in GB/s.
+
+  value     steps replayed from a recorded plan, operands resident in HBM, timed with
+            CUDA events on the launching stream; consecutive steps use different
+            resident weight copies so that every step streams from HBM, not L2
+  e2e       the same step driven from HOST buffers through the C ABI: pinned-host
+            hidden vector -> device, step, logits -> pinned host, every step
+  roofline  the launch group that takes most of the step, timed alone the same way
+  cpu_baseline  the CPU oracle (port of the reference's kernel arithmetic), all host
+            cores, on a bounded sample of the same step
+
+With --gpus N > 1 (launched under torchrun) the lm_head rows are sharded across the
+ranks and all-gathered with NCCL; the per-layer projections stay replicated
+(north star: only the large row-sharded projections are partitioned).
+--impl reference times the reference's own CPU implementation of the path
+(oracle/_ref when it was built, else the oracle port) on the host cores.
+"""
+import argparse
+import importlib.util
+import json
+import math
+import os
+import statistics
+import subprocess
+import sys
+import tempfile
+import time
+
+import numpy as np
+
+REPO = os.path.dirname(os.path.abspath(__file__))
+METRIC = "int8/Q4 GEMV achieved HBM GB/s (decode-step projection set)"
+UNIT = "GB/s"
+
+
+def load_pkg():
+    name = "adreno_llms_b200"
+    if name in sys.modules:
+        return sys.modules[name]
+    path = os.path.join(REPO, "adreno-llms_b200", "__init__.py")
+    spec = importlib.util.spec_from_file_location(name, path, submodule_search_locations=[os.path.dirname(path)])
+    mod = importlib.util.module_from_spec(spec)
+    sys.modules[name] = mod
+    spec.loader.exec_module(mod)
+    return mod
+
+
+def measured_peaks():
+    p = os.path.join(REPO, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        d = json.load(open(p))
+        return float(d["hbm_gbs"]), "measured (MEASURED_PEAKS.json hbm_gbs)"
+    return 6650.0, "fallback (6.65 TB/s, earlier measurement on this pool)"
+
+
+class ClockSampler:
+    FIELDS = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+              "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index):
+        self.index, self.proc, self.path = index, None, None
+
+    def start(self):
+        try:
+            fd, self.path = tempfile.mkstemp(suffix=".csv")
+            os.close(fd)
+            self.proc = subprocess.Popen(["nvidia-smi", "-i", str(self.index), f"--query-gpu={self.FIELDS}",
+                                          "--format=csv,noheader,nounits", "-lms", "100"],
+                                         stdout=open(self.path, "w"), stderr=subprocess.DEVNULL)
+        except OSError:
+            self.proc = None
+
+    def stop(self):
+        out = {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
+        if not self.proc:
+            return out
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        sm, mx, reasons = [], [], set()
+        for line in open(self.path):
+            f = [t.strip() for t in line.split(",")]
+            if len(f) < 7:
+                continue
+            try:
+                sm.append(float(f[0]))
+                mx.append(float(f[1]))
+            except ValueError:
+                continue
+            for name, v in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), f[3:7]):
+                if v.lower().startswith("active"):
+                    reasons.add(name)
+        os.unlink(self.path)
+        if sm:
+            out.update(sm_mhz=statistics.median(sm), sm_max_mhz=max(mx), reasons=sorted(reasons), samples=len(sm))
+        return out
+
+
+# ------------------------------------------------------------------------------------
+# CPU arm: the oracle (checker code) used ONLY here as the timed CPU baseline
+# ------------------------------------------------------------------------------------
+def cpu_step_rate(pkg, fmt, budget_s=12.0):
+    """GB/s of the CPU restatement on the step's projections, all host cores.
+    The sample is every distinct projection shape of the step once (weights of one
+    layer + the lm_head), scaled by how often each occurs in the step."""
+    sys.path.insert(0, REPO)
+    from oracle import cpu as ocpu  # noqa: E402  (CPU-baseline leg only)
+    synth = importlib.import_module("adreno_llms_b200.synth")
+    shape = synth.SMOLLM2_135M
+    cores = os.cpu_count() or 1
+    rng = np.random.default_rng(99)
+    groups = {}
+    for kind, _, ws in synth.decode_step_ops(shape):
+        for n, k in ws:
+            groups[(n, k)] = groups.get((n, k), 0) + 1
+    total_t, total_b = 0.0, 0
+    t_begin = time.perf_counter()
+    for (n, k), count in groups.items():
+        W, s = synth.weight(fmt, n, k, rng)
+        x = synth.activations(1, k, rng)
+        ocpu.linear_acc(fmt, x, W, s, ocpu.ORDER_KERNEL, cores)  # warm
+        reps, t = 0, 0.0
+        while reps < 3 and (time.perf_counter() - t_begin) < budget_s:
+            t0 = time.perf_counter()
+            ocpu.linear_acc(fmt, x, W, s, ocpu.ORDER_KERNEL, cores)
+            t += time.perf_counter() - t0
+            reps += 1
+        reps = max(reps, 1)
+        total_t += (t / reps if t else 0.0) * count
+        total_b += synth.linear_bytes(fmt, n, k, 1) * count
+    return total_b / total_t / 1e9, cores, total_t
+
+
+def ref_build_present():
+    return os.path.exists(os.path.join(REPO, "oracle", "_ref", "libref_cl.so"))
+
+
+def run_reference_arm(args, pkg, rank):
+    if rank != 0:
+        return
+    fmt = args.fmt
+    kind = "port"
+    rates = []
+    for _ in range(max(1, min(args.steps, 3))):
+        r, cores, t_step = cpu_step_rate(pkg, fmt, budget_s=40.0)
+        rates.append((r, t_step))
+    r = statistics.median([a for a, _ in rates])
+    t_step = statistics.median([b for _, b in rates])
+    synth = importlib.import_module("adreno_llms_b200.synth")
+    line = {
+        "impl": "reference", "metric": METRIC, "value": r, "unit": UNIT, "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": t_step * 1e3, "higher_is_better": True,
+        "scaling": "strong", "vs_baseline": None, "dtype": f"{fmt} weights, fp16 activations, fp32 accumulate",
+        "data": "synthetic",
+        "config": {"workload": f"decode-step projection set, SmolLM2-135M shape, {fmt}, M=1 "
+                               f"({synth.decode_step_gemvs(synth.SMOLLM2_135M)} GEMVs)"},
+        "cpu_baseline": {"value": r, "unit": UNIT, "cores": cores, "kind": kind,
+                         "sample": "each distinct projection shape of the step timed 3x on all cores, "
+                                   "scaled by its count in the step"},
+        "e2e": {"value": r, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }
+    print(json.dumps(line), flush=True)
+
+
+# ------------------------------------------------------------------------------------
+# GPU arm
+# ------------------------------------------------------------------------------------
+def time_group(ctx, fn, reps):
+    a, b = ctx.event(), ctx.event()
+    ctx.sync()
+    ctx.record(a)
+    for i in range(reps):
+        fn(i)
+    ctx.record(b)
+    ms = ctx.elapsed_ms(a, b)
+    ctx.L.nn_event_destroy(a)
+    ctx.L.nn_event_destroy(b)
+    return ms
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=2000)
+    ap.add_argument("--warmup", type=int, default=20)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--fmt", default="int8", choices=["int8", "fp16", "q4"])
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if args.warmup < 3:
+        args.warmup = 3
+
+    pkg = load_pkg()
+    if args.impl == "reference":
+        run_reference_arm(args, pkg, rank)
+        return 0
+
+    synth = importlib.import_module("adreno_llms_b200.synth")
+    dstep = importlib.import_module("adreno_llms_b200.decode_step")
+    dist = None
+    if world > 1:
+        import torch.distributed as dist_mod
+        dist = dist_mod
+        dist.init_process_group(backend="gloo", rank=rank, world_size=world)
+
+    ctx = pkg.Context(local_rank)
+    sm_count, l2_bytes, _ = ctx.device_info()
+    shape, fmt = synth.SMOLLM2_135M, args.fmt
+    if shape.vocab % world:
+        raise SystemExit(f"vocab {shape.vocab} is not divisible by {world} ranks")
+    vrows = shape.vocab // world
+    step_bytes_full = synth.decode_step_bytes(shape, fmt, 1)
+    n_sets = max(2, math.ceil(2.0 * l2_bytes / step_bytes_full) + 1)
+    step = dstep.DecodeStep(ctx, shape, fmt, M=1, n_sets=n_sets, vocab_rows=(rank * vrows, vrows))
+
+    comm, gathered = None, None
+    if world > 1:
+        import torch
+        idbuf = torch.zeros(128, dtype=torch.uint8)
+        if rank == 0:
+            raw = (128 * __import__("ctypes").c_ubyte)()
+            pkg._check(ctx.L.nn_comm_unique_id(raw))
+            idbuf = torch.tensor(list(raw), dtype=torch.uint8)
+        dist.broadcast(idbuf, 0)
+        raw = (__import__("ctypes").c_ubyte * 128)(*idbuf.tolist())
+        h = __import__("ctypes").c_void_p()
+        pkg._check(ctx.L.nn_comm_init(ctx.h, raw, rank, world, __import__("ctypes").byref(h)))
+        comm = h
+        gathered = ctx.alloc(shape.vocab * 2)
+
+    def barrier():
+        ctx.sync()
+        if dist:
+            dist.barrier()
+
+    def enqueue_step(i, with_argmax=True):
+        """One step: recorded plan of the projections (+ all-gather of the logits shards)."""
+        step.launch(i % n_sets)
+        if comm:
+            pkg._check(ctx.L.nn_comm_all_gather(comm, step.logits, gathered, vrows * 2))
+
+    kernels_per_step = step.record(with_argmax=(world == 1))
+    for i in range(args.warmup):
+        enqueue_step(i)
+    barrier()
+
+    sampler = ClockSampler(local_rank)
+    sampler.start()
+
+    # ---- value: K steps, device-timed ----
+    launches0 = ctx.launch_count()
+    barrier()
+    ms = time_group(ctx, enqueue_step, args.steps)
+    barrier()
+    launches = ctx.launch_count() - launches0
+    if dist:
+        import torch
+        t = torch.tensor([ms], dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = float(t.item())
+    ms_per_step = ms / args.steps
+    value = step_bytes_full / (ms_per_step * 1e-3) / 1e9
+
+    # ---- e2e: host buffers in, logits out, every step ----
+    e2e_steps = max(50, min(args.steps, 500))
+    hx = pkg.load().nn_host_alloc(shape.hidden * 2)
+    hl = pkg.load().nn_host_alloc(shape.vocab * 2)
+    import ctypes
+    ctypes.memmove(hx, synth.activations(1, shape.hidden, np.random.default_rng(5)).ctypes.data, shape.hidden * 2)
+    out_buf = gathered if comm else step.logits
+
+    def e2e_step(i):
+        pkg._check(ctx.L.nn_buf_write(ctx.h, step.x_h, 0, hx, shape.hidden * 2))
+        enqueue_step(i)
+        pkg._check(ctx.L.nn_buf_read(ctx.h, hl, out_buf, 0, shape.vocab * 2))
+        ctx.sync()
+
+    for i in range(5):
+        e2e_step(i)
+    barrier()
+    t0 = time.perf_counter()
+    for i in range(e2e_steps):
+        e2e_step(i)
+    e2e_s = time.perf_counter() - t0
+    if dist:
+        import torch
+        t = torch.tensor([e2e_s], dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        e2e_s = float(t.item())
+    e2e_value = step_bytes_full / (e2e_s / e2e_steps) / 1e9
+
+    # ---- roofline: each launch group of the step timed alone (same launches, rotating sets) ----
+    peak, peak_src = measured_peaks()
+    groups = {}
+    for kind, layer, ws in step.ops:
+        groups.setdefault(kind, []).append(layer)
+    group_rows = []
+    sh, M = shape, 1
+    for kind, layers in groups.items():
+        def run(i, kind=kind, layers=layers):
+            s = step.sets[i % n_sets]
+            for layer in layers:
+                w = [s[f"{kind}.{layer}.{j}"].buf for j in range(3 if kind == "qkv" else 2 if kind == "gate_up" else 1)]
+                if kind == "qkv":
+                    ctx.linear_qkv(M, sh.hidden, step.x_h, w[0], sh.q_dim, w[1], sh.kv_dim, w[2], sh.kv_dim, step.q, step.k, step.v)
+                elif kind == "o_add":
+                    ctx.linear_add(M, sh.hidden, sh.q_dim, step.x_attn, w[0], step.resid)
+                elif kind == "gate_up":
+                    ctx.fused_gate_up_silu(M, sh.ffn, sh.hidden, step.x_h, w[0], w[1], step.act)
+                elif kind == "down_add":
+                    ctx.linear_add(M, sh.hidden, sh.ffn, step.x_act, w[0], step.resid)
+                else:
+                    ctx.linear(M, step.vocab_n, sh.hidden, step.x_h, w[0], step.logits)
+        reps = 60
+        for i in range(3):
+            run(i)
+        gms = time_group(ctx, run, reps)
+        nl = len(layers)
+        per_launch_us = gms * 1e3 / (reps * nl)
+        ws = next(w for k2, _, w in step.ops if k2 == kind)
+        b = sum(synth.linear_bytes(fmt, (step.vocab_n if kind == "lm_head" else n), k, 1) for n, k in ws)
+        group_rows.append({"group": kind, "launches_per_step": nl, "us_per_launch": per_launch_us,
+                           "bytes_per_launch": b, "gbps": b / (per_launch_us * 1e-6) / 1e9,
+                           "share_of_step": per_launch_us * nl})
+    tot = sum(g["share_of_step"] for g in group_rows)
+    for g in group_rows:
+        g["share_of_step"] = g["share_of_step"] / tot
+    dom = max(group_rows, key=lambda g: g["share_of_step"])
+    big = max(group_rows, key=lambda g: g["bytes_per_launch"])
+    clocks = sampler.stop()
+
+    cpu_base = None
+    if rank == 0 and world == 1 and not args.no_cpu_baseline:
+        r, cores, t_step = cpu_step_rate(pkg, fmt)
+        cpu_base = {"value": r, "unit": UNIT, "cores": cores, "kind": "port",
+                    "sample": "each distinct projection shape of the step timed up to 3x on all cores, scaled by its "
+                              f"count in the step ({t_step * 1e3:.1f} ms per step)"}
+
+    if rank == 0:
+        line = {
+            "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+            "ms_per_step": ms_per_step, "decode_step_us": ms_per_step * 1e3, "higher_is_better": True,
+            "scaling": "strong", "vs_baseline": None,
+            "dtype": f"{fmt} weights, fp16 activations, fp32 accumulate", "data": "synthetic",
+            "config": {"workload": f"decode-step projection set, SmolLM2-135M shape, {fmt}, M=1 "
+                                   f"({synth.decode_step_gemvs(shape)} GEMVs in {kernels_per_step} launches)",
+                       "algorithmic_bytes_per_step": step_bytes_full,
+                       "l2": f"{n_sets} resident weight copies rotated step to step "
+                             f"({n_sets * step.weight_bytes / 1e6:.0f} MB > L2 {l2_bytes / 1e6:.0f} MB)",
+                       "sharding": "none" if world == 1 else f"lm_head rows / {world} ranks + NCCL all-gather; layers replicated"},
+            "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": shape.hidden * 2,
+                    "d2h_bytes_per_step": shape.vocab * 2, "us_per_step": e2e_s / e2e_steps * 1e6, "steps": e2e_steps},
+            "gpu_launches": launches,
+            "roofline": {"bound": "hbm", "kernel": f"linear_stream_kernel [{dom['group']}]", "achieved": dom["gbps"], "peak": peak,
+                         "unit": "GB/s", "frac": dom["gbps"] / peak, "traffic": None, "peak_source": peak_src,
+                         "us_per_launch": dom["us_per_launch"], "bytes_per_launch": dom["bytes_per_launch"]},
+            "roofline_largest_launch": {"kernel": f"linear_stream_kernel [{big['group']}]", "achieved": big["gbps"],
+                                        "frac": big["gbps"] / peak, "us_per_launch": big["us_per_launch"],
+                                        "bytes_per_launch": big["bytes_per_launch"]},
+            "launch_groups": group_rows,
+            "clocks": clocks,
+        }
+        if cpu_base:
+            line["cpu_baseline"] = cpu_base
+        print(json.dumps(line), flush=True)
+    if dist:
+        dist.barrier()
+        dist.destroy_process_group()
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

@@ -1,0 +1,183 @@
+/*
+ * nnopt_b200 — C ABI of the B200 (sm_100a) replacement for the decode-time
+ * linear operators of a8nova/adreno-llms.
+ *
+ * The library replaces the reference's OpenCL buffer + kernel dispatch for ONE
+ * path: out[M,N] = x[M,K] . W[N,K]^T with W stored as fp16, per-row symmetric
+ * int8 (+ fp16 scale per row) or packed 4-bit (+ fp16 scale per 32 weights),
+ * plus the fused epilogues the reference's layers call at decode time.
+ * Each entry point names the reference interface it stands in for
+ * (paths relative to the reference project).
+ *
+ * Conventions
+ *   - nn_buf is a CUDA device pointer (the role cl_mem plays in the reference).
+ *     The library never frees caller buffers.  Activations, scales and outputs
+ *     are IEEE binary16; weights keep the exact on-disk byte layout written by
+ *     scripts/convert_hf_to_bin.py and src/models/<model>/scripts/quantize_*.py.
+ *   - Every call is asynchronous on the context's single stream (the role of the
+ *     reference's one in-order cl_command_queue): a result is visible to the next
+ *     call on the same context without a host sync (nn_sync to wait on the host).
+ *   - One host thread per context; contexts are independent (one per GPU).
+ *   - Returns 0 (NN_OK) or a negative code; nn_last_error() gives the text
+ *     (thread-local).  Nothing aborts or throws across this boundary.  There is
+ *     no CPU fallback: without a CUDA device nn_init fails.
+ */
+#ifndef NNOPT_B200_H
+#define NNOPT_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef struct nn_context nn_context; /* OpenCLContext + its cl_command_queue */
+typedef struct nn_weights nn_weights; /* class Weights */
+typedef struct nn_plan nn_plan;       /* a recorded decode step */
+typedef struct nn_comm nn_comm;       /* row-sharding communicator (one rank per GPU) */
+typedef void* nn_buf;                 /* device pointer; stands in for cl_mem */
+
+enum {
+    NN_OK = 0,
+    NN_ERR_ARG = -1,         /* bad argument (null buffer, shape/registration mismatch) */
+    NN_ERR_CUDA = -2,        /* a CUDA runtime call failed */
+    NN_ERR_UNSUPPORTED = -3, /* shape or mode not handled by any kernel */
+    NN_ERR_IO = -4,          /* weight bundle could not be read or parsed */
+    NN_ERR_NOTFOUND = -5,    /* tensor key missing */
+    NN_ERR_COMM = -6,        /* NCCL missing or a collective failed */
+    NN_ERR_TIMEOUT = -7      /* a bounded device-side wait ran out */
+};
+
+const char* nn_last_error(void);
+const char* nn_version(void);
+
+/* ---- context: src/models/smollm2-135m-instruct/src/opencl_context.cpp:171-205
+ *      (OpenCLContext::initialize, one device, one in-order queue) ------------- */
+int nn_init(int device_ordinal, nn_context** out_ctx);
+int nn_shutdown(nn_context* ctx); /* frees registry entries and library-owned buffers */
+void* nn_stream(nn_context* ctx); /* the cudaStream_t every call is ordered on */
+int nn_sync(nn_context* ctx);     /* host wait; also reports a recorded device-side timeout */
+int nn_device_info(nn_context* ctx, int* sm_count, size_t* l2_bytes, size_t* hbm_bytes);
+
+/* ---- buffers: clCreateBuffer / clEnqueueWriteBuffer / clEnqueueReadBuffer /
+ *      clReleaseMemObject as used by src/models/lfm2-5-350m/src/weights.cpp:286-291
+ *      and the layers' persistent activation buffers ----------------------------- */
+nn_buf nn_buf_alloc(nn_context* ctx, size_t bytes); /* NULL on failure */
+int nn_buf_free(nn_context* ctx, nn_buf buf);
+int nn_buf_write(nn_context* ctx, nn_buf dst, size_t dst_offset, const void* src, size_t bytes); /* H2D, async */
+int nn_buf_read(nn_context* ctx, void* dst, nn_buf src, size_t src_offset, size_t bytes);        /* D2H, async */
+int nn_buf_copy(nn_context* ctx, nn_buf dst, nn_buf src, size_t bytes);                          /* D2D, async */
+int nn_buf_fill(nn_context* ctx, nn_buf dst, int byte_value, size_t bytes);
+void* nn_host_alloc(size_t bytes); /* pinned host memory for nn_buf_write / nn_buf_read */
+int nn_host_free(void* p);
+
+/* ---- quantised-weight registry: nnopt_register_int8_weight /
+ *      nnopt_register_q4_weight, src/models/lfm2-5-350m/src/utils.h:127,132
+ *      (utils.cpp:357-368, 584-595).  Keyed by the weight's device pointer; a
+ *      row-range sub-view W + r*rowbytes of a registered weight resolves too (the
+ *      reference's row tiles, utils.cpp:427-452).  Nothing is repacked. --------- */
+int nn_register_int8_weight(nn_context* ctx, nn_buf W_int8, nn_buf scale_fp16, int N, int K);
+int nn_register_q4_weight(nn_context* ctx, nn_buf W_q4, nn_buf scale_fp16, int N, int K_unpacked);
+int nn_unregister_weight(nn_context* ctx, nn_buf W);
+
+/* ---- the operator: pytorch_linear(queue, M, N, K, x, W, out),
+ *      src/models/lfm2-5-350m/src/utils.h:117-119 (utils.cpp:1263-1374);
+ *      same call in src/models/qwen2-5-0-5b/src/utils.cpp:758-826 and
+ *      src/models/smollm2-135m-instruct/src/utils.cpp:279-340.
+ *      out[M,N] = x[M,K] . W[N,K]^T.  Format is picked by registry lookup on W in
+ *      the reference's order: Q4, then int8, else fp16.  M > 1 is M independent
+ *      M = 1 results (the reference loops M = 1 for quantised weights,
+ *      src/models/lfm2-5-350m/src/model.cpp:243-251). ----------------------------- */
+int nn_linear(nn_context* ctx, int M, int N, int K, nn_buf x, nn_buf W, nn_buf out);
+
+/* residual[M,N] = half(float(residual) + x.W^T), in place: Qwen's
+ * pytorch_linear_add (src/models/qwen2-5-0-5b/src/utils.cpp:862-882) and SmolLM2's
+ * fused_oproj_residual / fused_down_residual kernels
+ * (src/models/smollm2-135m-instruct/kernels/block_fused_int8.cl:105,238;
+ *  host: src/layers/attention.cpp:771-806, src/layers/mlp.cpp:340-373). */
+int nn_linear_add(nn_context* ctx, int M, int N, int K, nn_buf x, nn_buf W, nn_buf residual_inout);
+
+/* gate_inout[n] = half(gate * sigmoid(gate) * (W3.x)[n]): pytorch_linear_silu_gate_fused,
+ * src/models/lfm2-5-350m/src/utils.h:140-142 (utils.cpp:1377-1406, kernels/mlp_fused.cl:19-73).
+ * The reference form is M = 1; M rows are accepted here. */
+int nn_linear_silu_gate_fused(nn_context* ctx, int M, int N, int K, nn_buf x, nn_buf W3, nn_buf gate_inout);
+
+/* out[M,N] = half(silu(x.Wg^T) * (x.Wu^T)): fused_gate_up_silu_m1,
+ * src/models/qwen2-5-0-5b/src/utils.cpp:478-487 and
+ * src/models/smollm2-135m-instruct/kernels/block_fused.cl:334,475,533 /
+ * block_fused_int8.cl:176-231 (host: src/layers/mlp.cpp:298-337).
+ * Wg and Wu must be of the same format. */
+int nn_fused_gate_up_silu(nn_context* ctx, int M, int N, int K, nn_buf x, nn_buf Wg, nn_buf Wu, nn_buf out);
+
+/* Three projections of the same x in one launch: fused_qkv_gemv_m1,
+ * src/models/smollm2-135m-instruct/kernels/block_fused.cl:192 (host:
+ * src/layers/attention.cpp:653-722).  q[M,Nq], k[M,Nk], v[M,Nv]; same format. */
+int nn_linear_qkv(nn_context* ctx, int M, int K, nn_buf x, nn_buf Wq, int Nq, nn_buf Wk, int Nk, nn_buf Wv, int Nv,
+                  nn_buf q, nn_buf k, nn_buf v);
+
+/* fp32 [N,K] = the dequantised weight exactly as the kernels unpack it
+ * (src/models/lfm2-5-350m/kernels/gemv_m1_q4.cl:31-40; scripts/quantize_q4.py:156-166;
+ *  scripts/quantize_weights.py:135-139).  For bit-exact checks of the unpack rule. */
+int nn_dequant(nn_context* ctx, int N, int K, nn_buf W, nn_buf out_f32);
+
+/* index of the largest fp16 logit (lowest index on ties) into a device int:
+ * argmax_block + argmax_final, src/models/lfm2-5-350m/kernels/argmax.cl:30,90
+ * (host: src/model.cpp:603-623). */
+int nn_argmax(nn_context* ctx, int n, nn_buf logits_fp16, nn_buf out_index_i32);
+
+/* ---- recorded decode step: the reference's recordable-queue replay
+ *      (src/models/smollm2-135m-instruct/src/model.cpp:104-195,312-344).
+ *      Between nn_plan_begin and nn_plan_end the operator calls above are captured
+ *      instead of run; nn_plan_launch replays them in order on the stream. -------- */
+int nn_plan_begin(nn_context* ctx);
+int nn_plan_end(nn_context* ctx, nn_plan** out_plan);
+int nn_plan_launch(nn_context* ctx, nn_plan* plan);
+int nn_plan_num_kernels(const nn_plan* plan);
+int nn_plan_free(nn_plan* plan);
+
+/* ---- class Weights, src/models/lfm2-5-350m/src/weights.h:13-51 (weights.cpp:169-297):
+ *      mmap model.{fp16,int8,q4}.bin, parse meta.json, upload a tensor on first use. - */
+int nn_weights_load(nn_context* ctx, const char* bin_path, const char* meta_path, nn_weights** out);
+int nn_weights_free(nn_weights* w);
+int nn_weights_has_tensor(const nn_weights* w, const char* key);
+nn_buf nn_weights_get_buffer(nn_weights* w, const char* key, int optional); /* NULL when missing */
+const char* nn_weights_get_dtype(const nn_weights* w, const char* key);     /* "" when missing */
+int nn_weights_get_shape(const nn_weights* w, const char* key, int* dims, int max_dims); /* returns rank */
+size_t nn_weights_get_size_bytes(const nn_weights* w, const char* key);
+size_t nn_weights_get_num_elements(const nn_weights* w, const char* key);
+int nn_weights_num_keys(const nn_weights* w);
+const char* nn_weights_key_at(const nn_weights* w, int index); /* all_keys(), sorted */
+int nn_weights_get_host_f32(const nn_weights* w, const char* key, float* out, size_t max_elems); /* get_host_vec */
+/* The NNOPT_QUANT registration walk of src/models/lfm2-5-350m/src/main.cpp:527-566:
+ * registers every int8 / q4_packed tensor that has a ".scale" sibling.
+ * Returns the number registered (>= 0) or a negative code. */
+int nn_weights_register_quantized(nn_context* ctx, nn_weights* w);
+
+/* ---- timing: the per-launch OpenCL-event profilers
+ *      (src/models/lfm2-5-350m/src/kernel_profiler.cpp:18-62) become CUDA events
+ *      on the context's stream. --------------------------------------------------- */
+int nn_event_create(void** out_event);
+int nn_event_record(nn_context* ctx, void* event);
+int nn_event_elapsed_ms(void* start, void* stop, float* out_ms); /* waits for stop */
+int nn_event_destroy(void* event);
+/* Evict L2 between timed runs by rewriting a library-owned buffer larger than L2. */
+int nn_l2_flush(nn_context* ctx);
+/* Kernels launched by this context so far (for launch accounting). */
+long long nn_launch_count(const nn_context* ctx);
+
+/* ---- row sharding across GPUs (no counterpart in the reference, which is
+ *      single-device; it extends the reference's own row tiling of large weights,
+ *      src/models/lfm2-5-350m/src/utils.cpp:427-452, from image tiles to ranks).
+ *      Rank g owns rows [g*N/G, (g+1)*N/G) of W and its scales; x is replicated;
+ *      nn_comm_all_gather concatenates the per-rank [M, N/G] blocks in rank order:
+ *      gathered layout is [G][M][N/G].  NCCL is loaded at run time (dlopen). ------ */
+int nn_comm_unique_id(void* out_id_128bytes);
+int nn_comm_init(nn_context* ctx, const void* id_128bytes, int rank, int world, nn_comm** out);
+int nn_comm_all_gather(nn_comm* comm, nn_buf send, nn_buf recv, size_t bytes_per_rank);
+int nn_comm_free(nn_comm* comm);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* NNOPT_B200_H */
