@@ -44,6 +44,8 @@ def build(force=False, verbose=False):
         cmd = [_nvcc(), *ARCH, "-lineinfo", "-O3", "-std=c++17", "-Xcompiler", "-fPIC,-Wall", "-x", "cu", "-c", src, "-o", obj]
         if verbose:
             cmd += ["-Xptxas", "-v"]
+        if os.environ.get("NNB_BUILD_TRACE"):  # debug build with per-launch phase timestamps
+            cmd += ["-DNNB_TRACE"]
         if not force and os.path.exists(obj) and all(
                 os.path.getmtime(obj) > os.path.getmtime(os.path.join(CSRC, f)) for f in os.listdir(CSRC)
                 if f.endswith((".h", ".cuh")) or os.path.join(CSRC, f) == src):

@@ -44,8 +44,10 @@ struct LinArgs {
 
 struct StreamPlan {  // launch geometry chosen on the host
     int grid;
-    int kcb;
-    int kw;
+    int kcb;     // bytes of one weight row per pipeline stage
+    int kw;      // warps splitting K of one tile
+    int warps;   // warps per block
+    int stages;  // ring depth per warp
     size_t smem;
     bool ok;
 };

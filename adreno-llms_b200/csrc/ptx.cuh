@@ -62,6 +62,19 @@ __device__ __forceinline__ void bulk_g2s(uint32_t dst, const void* src, uint32_t
         : "memory");
 }
 
+// ---- tiled 2-D tensor copy global -> shared (TMA unit, 128-byte swizzle set in the map) ----
+// x = coordinate in the innermost dimension (elements; must cover a multiple of 16 bytes),
+// y = row.  The whole box is written (out-of-range parts as zeros) and counted on the mbarrier.
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const void* tmap, int x, int y, uint32_t bar, uint64_t policy) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes.L2::cache_hint [%0], [%1, {%2, %3}], [%4], %5;" ::"r"(dst),
+        "l"(tmap), "r"(x), "r"(y), "r"(bar), "l"(policy)
+        : "memory");
+}
+__device__ __forceinline__ void prefetch_tensormap(const void* tmap) {
+    asm volatile("prefetch.tensormap [%0];" ::"l"(tmap) : "memory");
+}
+
 // ---- cp.async (per-thread, 4/16-byte) tracked by an mbarrier -------------------
 __device__ __forceinline__ void cp_async_4(uint32_t dst, const void* src) {
     asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(dst), "l"(src) : "memory");

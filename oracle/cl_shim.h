@@ -88,6 +88,8 @@ struct half {
 // ---- vectors -----------------------------------------------------------------------
 struct float4 {
     union { struct { float x, y, z, w; }; struct { float s0, s1, s2, s3; }; };
+    float4() = default;
+    float4(float v) : x(v), y(v), z(v), w(v) {}  // the literal form (float4)(v) splats
 };
 struct int4 { int x, y, z, w; };
 struct uint4 { uint x, y, z, w; };
@@ -107,8 +109,6 @@ static inline float native_exp(float x) { return expf(x); }
 static inline float native_recip(float x) { return 1.0f / x; }
 static inline int min(int a, int b) { return a < b ? a : b; }
 static inline int max(int a, int b) { return a > b ? a : b; }
-static inline float fmin(float a, float b) { return a < b ? a : b; }
-static inline float fmax(float a, float b) { return a > b ? a : b; }
 static inline int atomic_add(int* p, int v) { int o = *p; *p += v; return o; }
 
 static inline float vload_half(size_t off, const half* p) { return clshim_h2f(p[off].bits); }
@@ -117,6 +117,10 @@ static inline float4 vload_half4(size_t off, const half* p) {
     return mk4(clshim_h2f(q[0].bits), clshim_h2f(q[1].bits), clshim_h2f(q[2].bits), clshim_h2f(q[3].bits));
 }
 static inline void vstore_half(float v, size_t off, half* p) { p[off].bits = clshim_f2h(v); }
+static inline void vstore_half4(float4 v, size_t off, half* p) {
+    half* q = p + 4 * off;
+    q[0].bits = clshim_f2h(v.x); q[1].bits = clshim_f2h(v.y); q[2].bits = clshim_f2h(v.z); q[3].bits = clshim_f2h(v.w);
+}
 static inline float vload_half(size_t off, const float* p) { return p[off]; }
 
 // ---- images: a 2-D view over the row-major weight matrix ---------------------------
