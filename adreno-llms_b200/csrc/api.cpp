@@ -248,23 +248,8 @@ static int run_linear(nn_context* c, int fmt, LinArgs a, int M_total, const char
         for (int i = 0; i < a.nseg; ++i) a.seg[i].out = out0[i] + (size_t)m0 * a.seg[i].ld_out;
         cudaError_t e;
         if (stream_supported(fmt, a.M, a.K, a)) {
-            int ntiles = 0;
-            if (a.epi == EPI_SWIGLU) {
-                ntiles = (a.seg[0].N + 15) / 16;
-                a.seg[0].tile0 = 0;
-            } else {
-                for (int i = 0; i < a.nseg; ++i) {
-                    a.seg[i].tile0 = ntiles;
-                    ntiles += (a.seg[i].N + 31) / 32;
-                }
-            }
-            a.ntiles = ntiles;
-            StreamPlan p = stream_plan(fmt, a.M, a.K, ntiles, c->sm_count, c->smem_limit);
-            if (p.ok) {
-                e = launch_stream(fmt, a, p, c->stream, c->use_pdl);
-            } else {
-                e = launch_generic(fmt, a, c->stream);
-            }
+            StreamPlan p = stream_plan(fmt, a, c->sm_count, c->smem_limit);
+            e = p.ok ? launch_stream(fmt, a, p, c->stream, c->use_pdl) : launch_generic(fmt, a, c->stream);
         } else {
             e = launch_generic(fmt, a, c->stream);
         }

@@ -11,27 +11,26 @@
 // outputs fp16, all sums in fp32, int8 scale applied once after the full-K sum,
 // Q4 scale applied per 32-weight block, nibble value = nibble - 8.
 //
-// Design (HBM-bound work; the tensor cores are only there to take the FMAs off
-// the issue slots so that the dequantisation fits beside a 6+ TB/s stream):
-//   * a tile is 32 consecutive weight rows; a pipeline stage is `kcb` bytes of
-//     each of those rows.  Every lane of a warp issues ONE bulk async copy
-//     (cp.async.bulk, TMA unit) for its row into a padded shared-memory row, all
-//     32 completing on the stage's mbarrier.  Each warp runs its own ring of
-//     stages, so the SM keeps warps x (stages-1) x 32 x kcb bytes in flight and no
-//     warp ever waits for another in the main loop.
-//   * Q4 block scales travel with the stage through per-lane cp.async tracked by
-//     the same mbarrier.
-//   * weights go shared memory -> registers with ldmatrix, are converted to exact
-//     fp16 integers in registers (prmt / lop3 magic numbers, no int->float
-//     converts), and are multiplied with mma.sync m16n8k16 (fp32 accumulate)
-//     against the activations, which sit in shared memory pre-permuted so that one
-//     ldmatrix yields the B fragment matching the packed weight order.
+// Design (HBM-bound work; the tensor cores only take the FMAs off the issue slots so
+// that the dequantisation fits beside a 6+ TB/s stream):
+//   * a block = one producer warp + four consumer warps.  The producer's elected lane
+//     drives the TMA unit: per pipeline stage it issues tiled tensor copies
+//     (cp.async.bulk.tensor.2d, 128-byte swizzle) of 128 weight rows x 128-byte columns,
+//     completing on the stage's "full" mbarrier; consumers hand a stage back through its
+//     "empty" mbarrier.  Consumers never issue copies, so their issue slots go to
+//     arithmetic only.
+//   * each consumer warp owns 32 of the stage's rows (or, for operators with few rows,
+//     the four warps split K of the same 32 rows and reduce through shared memory in a
+//     fixed order).  Weights go shared memory -> registers with ldmatrix out of the
+//     swizzled boxes (conflict-free, no padding), are converted to exact fp16 integers in
+//     registers (prmt / lop3 magic numbers), and are multiplied with mma.sync m16n8k16
+//     (fp32 accumulate) against the activations, which sit in shared memory pre-permuted
+//     so that one ldmatrix yields the B fragment in the packed weight order.
 //     M = 1..8 uses one n8 tile, M = 9..16 two; rows >= M read a zero block.
-//   * small N: `kw` warps split K of one tile and reduce through shared memory in
-//     a fixed order (deterministic).
-//   * launched with programmatic dependent launch: the weight prefetch of launch
-//     i+1 (weights never depend on activations) overlaps the tail of launch i;
-//     only the activation staging waits for the prior grid.
+//   * Q4 block scales ride along through per-lane cp.async on the same full barrier.
+//   * launched with programmatic dependent launch: the producer never waits for the prior
+//     grid (weights do not depend on activations), so the weight stream of launch i+1
+//     starts under the tail of launch i; only the activation staging waits.
 #include <cuda.h>
 #include <cuda_fp16.h>
 #include <cstdio>
@@ -44,34 +43,37 @@ namespace nnb {
 
 namespace {
 
-constexpr int TILE_ROWS = 32;
-constexpr int MAX_WARPS = 8;
-constexpr int HDR_BYTES = 128;  // 64 B of zeros + room for the mbarriers' alignment
+constexpr int NCW = 4;                      // consumer warps per block
+constexpr int THREADS = (NCW + 1) * 32;     // + one producer warp
+constexpr int WARP_ROWS = 32;               // weight rows per consumer warp per tile
+constexpr int BOX_BYTES = WARP_ROWS * 128;  // one warp's 128-byte column box (4 KB)
+constexpr int CTA_BOX = NCW * BOX_BYTES;    // one column box of the whole block (16 KB)
+constexpr int HDR_BYTES = 128;              // 64 B of zeros + alignment room
 
 __host__ __device__ inline int fmt_row_bytes(int fmt, int K) { return fmt == FMT_FP16 ? K * 2 : fmt == FMT_INT8 ? K : K / 2; }
 
 struct Geo {  // shared-memory geometry, computed identically on host and device
-    int nbox;         // 128-byte column boxes per stage (each 32 rows x 128 B = 4 KB, swizzled)
+    int nbox;         // 128-byte column boxes per stage
     int sstride;      // bytes between Q4 scale rows in a stage
-    int stage_bytes;  // one stage of one warp (multiple of 1024)
+    int stage_bytes;  // one stage (multiple of 1024)
     int xstride;      // bytes between activation rows
     int off_bar, off_x, off_red, off_ring;
     int total;
 };
 
-constexpr int BOX_BYTES = TILE_ROWS * 128;
-
-__host__ __device__ inline Geo make_geo(int fmt, int M, int K, int kcb, int nwarps, int stages, int nt) {
+__host__ __device__ inline Geo make_geo(int fmt, int M, int K, int kcb, int stages, int nt) {
     Geo g;
     g.nbox = (kcb + 127) / 128;
     g.sstride = kcb / 8 + 16;
-    g.stage_bytes = g.nbox * BOX_BYTES + (fmt == FMT_Q4 ? ((TILE_ROWS * g.sstride + 1023) / 1024) * 1024 : 0);
-    g.xstride = K * 2 + 16;
-    g.off_bar = 64;
-    g.off_x = HDR_BYTES + ((nwarps * stages * 8 + 127) / 128) * 128;
-    g.off_red = g.off_x + ((M * g.xstride + 127) / 128) * 128;
-    g.off_ring = ((g.off_red + nwarps * 32 * 2 * nt * 4 * 4 + 1023) / 1024) * 1024;
-    g.total = g.off_ring + nwarps * stages * g.stage_bytes + 1024;  // slack to align the ring to 1 KB
+    g.stage_bytes = g.nbox * CTA_BOX + (fmt == FMT_Q4 ? ((NCW * WARP_ROWS * g.sstride + 1023) / 1024) * 1024 : 0);
+    // fp16 / Q4: activations as fp16 rows; int8: three 8-bit limb planes of a 24-bit
+    // fixed-point copy (row stride K + 16 bytes) followed by 64 bytes of per-row scale words
+    g.xstride = fmt == FMT_INT8 ? K + 16 : K * 2 + 16;
+    g.off_bar = 64;  // full[stages], empty[stages]
+    g.off_x = HDR_BYTES + ((stages * 16 + 127) / 128) * 128;
+    g.off_red = g.off_x + (((fmt == FMT_INT8 ? 3 * M * g.xstride + 192 : M * g.xstride) + 127) / 128) * 128;
+    g.off_ring = ((g.off_red + 2 * NCW * 32 * 2 * nt * 4 * 4 + 1023) / 1024) * 1024;  // two reduction buffers
+    g.total = g.off_ring + stages * g.stage_bytes + 1024;  // slack to align the ring to 1 KB
     return g;
 }
 
@@ -80,30 +82,78 @@ struct KArgs {
     LinArgs a;
     int stages;
     int rowbytes;
-    int nchunks;
+    int nchunks;      // K chunks of kcb bytes per row
     int evict_first;  // weights larger than L2 are streamed with an evict-first policy
 #ifdef NNB_TRACE
-    unsigned long long* trace;  // debug build only: per-launch phase timestamps
+    unsigned long long* trace;  // debug build only: per-warp phase cycle counts
     int trace_slot;
-    int dbg_mode;               // debug build only: 1 = no arithmetic, 2 = loads only, 3 = no MMA
 #endif
 };
 
-#ifdef NNB_TRACE
-__device__ __forceinline__ unsigned long long gtime() {
-    unsigned long long t;
-    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
-    return t;
+// int8 weights are multiplied on the integer tensor-core path, with no conversion of the
+// weights at all: each activation row is turned into 24-bit fixed point
+//   x_fix = rint(x * 2^p),  2^p chosen per row so that max|x| * 2^p is in [2^22, 2^23)
+// (exact for every fp16 value within 2^12 of the row's largest magnitude, otherwise rounded
+// at 2^-24 of that magnitude) and split into one signed and two unsigned 8-bit limbs.  The
+// three integer dot products are exact; they are recombined in fp32 and scaled by 2^-p and
+// the weight row's scale.  A row holding Inf or NaN is flagged and produces NaN.
+// Layout: limb planes [3][M][K + 16] (natural k order), then float 2^-p per row.
+__device__ __forceinline__ void stage_x_int8(const uint16_t* __restrict__ x, int M, int K, uint8_t* xs, int xstride, int tid,
+                                             int nthreads) {
+    unsigned int* rowmax = reinterpret_cast<unsigned int*>(xs + 3 * M * xstride);  // [16] max |x| bits, then [16] floats
+    float* rowscale = reinterpret_cast<float*>(rowmax + 16);
+    if (tid < 16) rowmax[tid] = 0u;
+    asm volatile("bar.sync 1, %0;" ::"r"(nthreads) : "memory");
+    const int per_row = K / 8;  // 16-byte pieces
+    for (int m = 0; m < M; ++m) {
+        unsigned int mx = 0u;
+        for (int p = tid; p < per_row; p += nthreads) {
+            const uint4 v = *reinterpret_cast<const uint4*>(x + (size_t)m * K + p * 8);
+            const unsigned int w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                mx = max(mx, w[i] & 0x7FFFu);
+                mx = max(mx, (w[i] >> 16) & 0x7FFFu);
+            }
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) mx = max(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+        if ((tid & 31) == 0 && mx) atomicMax(&rowmax[m], mx);
+    }
+    asm volatile("bar.sync 1, %0;" ::"r"(nthreads) : "memory");
+    for (int m = 0; m < M; ++m) {
+        const unsigned int mx = rowmax[m];
+        const bool bad = mx >= 0x7C00u;
+        // exponent of the largest magnitude: fp16 normal 2^(e-15), subnormals counted as 2^-14
+        const int e = (int)(mx >> 10) > 0 ? (int)(mx >> 10) - 15 : -14;
+        const int pw = (mx == 0u || bad) ? 0 : 22 - e;  // max|x| * 2^pw < 2^23
+        const float up = __int_as_float((127 + pw) << 23);
+        if (tid == 0) rowscale[m] = bad ? __int_as_float(0x7FC00000) : __int_as_float((127 - pw) << 23);
+        uint8_t* l0 = xs + (0 * M + m) * xstride;
+        uint8_t* l1 = xs + (1 * M + m) * xstride;
+        uint8_t* l2 = xs + (2 * M + m) * xstride;
+        for (int p = tid; p < per_row; p += nthreads) {
+            const uint4 v = *reinterpret_cast<const uint4*>(x + (size_t)m * K + p * 8);
+            const unsigned int w[4] = {v.x, v.y, v.z, v.w};
+            uint32_t hi[2] = {0, 0}, mid[2] = {0, 0}, lo[2] = {0, 0};
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+                const uint16_t hb = (uint16_t)(i & 1 ? w[i >> 1] >> 16 : w[i >> 1] & 0xFFFFu);
+                const int f = bad ? 0 : __float2int_rn(__half2float(__ushort_as_half(hb)) * up);
+                hi[i >> 2] |= (uint32_t)((f >> 16) & 0xFF) << (8 * (i & 3));
+                mid[i >> 2] |= (uint32_t)((f >> 8) & 0xFF) << (8 * (i & 3));
+                lo[i >> 2] |= (uint32_t)(f & 0xFF) << (8 * (i & 3));
+            }
+            *reinterpret_cast<uint2*>(l0 + p * 8) = make_uint2(hi[0], hi[1]);
+            *reinterpret_cast<uint2*>(l1 + p * 8) = make_uint2(mid[0], mid[1]);
+            *reinterpret_cast<uint2*>(l2 + p * 8) = make_uint2(lo[0], lo[1]);
+        }
+    }
 }
-#define TRACE(i) do { } while (0)
-#else
-#define TRACE(i) do { } while (0)
-#endif
 
 // Stage the activations [M, K] fp16 into shared memory, permuted per format so
 // that ldmatrix over 16-byte pieces yields B fragments in the weights' packed order:
 //   fp16: identity
-//   int8: per 16 k   -> [k 0,1,4,5,8,9,12,13][k 2,3,6,7,10,11,14,15]
 //   Q4  : per 32 k   -> piece j, pair t = (k 8t+j, k 8t+j+4)
 template <int FMT>
 __device__ __forceinline__ void stage_x(const uint16_t* __restrict__ x, int M, int K, uint8_t* xs, int xstride, int tid,
@@ -114,18 +164,6 @@ __device__ __forceinline__ void stage_x(const uint16_t* __restrict__ x, int M, i
             const int m = i / per_row, p = i - m * per_row;
             const uint4 v = *reinterpret_cast<const uint4*>(x + (size_t)m * K + p * 8);
             *reinterpret_cast<uint4*>(xs + m * xstride + p * 16) = v;
-        }
-    } else if (FMT == FMT_INT8) {
-        const int per_row = K / 16;
-        for (int i = tid; i < M * per_row; i += nthreads) {
-            const int m = i / per_row, p = i - m * per_row;
-            const uint4 a = *reinterpret_cast<const uint4*>(x + (size_t)m * K + p * 16);
-            const uint4 b = *reinterpret_cast<const uint4*>(x + (size_t)m * K + p * 16 + 8);
-            uint4 lo, hi;  // words are k pairs: a = (0,1)(2,3)(4,5)(6,7), b = (8,9)...(14,15)
-            lo.x = a.x; lo.y = a.z; lo.z = b.x; lo.w = b.z;
-            hi.x = a.y; hi.y = a.w; hi.z = b.y; hi.w = b.w;
-            *reinterpret_cast<uint4*>(xs + m * xstride + p * 32) = lo;
-            *reinterpret_cast<uint4*>(xs + m * xstride + p * 32 + 16) = hi;
         }
     } else {
         const int per_row = K / 32;
@@ -149,128 +187,37 @@ __device__ __forceinline__ void stage_x(const uint16_t* __restrict__ x, int M, i
 }
 
 template <int FMT, int NT, bool DUAL>
-__global__ void __launch_bounds__(MAX_WARPS * 32) linear_stream_kernel(const __grid_constant__ KArgs ka) {
+__global__ void __launch_bounds__(THREADS) linear_stream_kernel(const __grid_constant__ KArgs ka) {
     extern __shared__ __align__(128) uint8_t smem[];
     const LinArgs& a = ka.a;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    const int nwarps = blockDim.x >> 5;
-    const int stages = ka.stages;
-    const int kcb = a.kcb, kw = a.kw;
+    const int stages = ka.stages, kcb = a.kcb;
+    const bool ksplit = a.kw > 1;  // the four consumers split K of one 32-row tile
     const int rowbytes = ka.rowbytes, nchunks = ka.nchunks;
-    const Geo geo = make_geo(FMT, a.M, a.K, kcb, nwarps, stages, NT);
+    const Geo geo = make_geo(FMT, a.M, a.K, kcb, stages, NT);
+    const int warp_rows = DUAL ? 16 : WARP_ROWS;                       // rows of each weight per warp
+    const int tile_rows = ksplit ? warp_rows : NCW * warp_rows;        // rows of each weight per block tile
+    const int groups = ksplit ? (nchunks + NCW - 1) / NCW : nchunks;   // pipeline items per tile
 
     const uint32_t s_base = smem_u32(smem);
     const uint32_t zero_addr = s_base;
-    const uint32_t bar0 = s_base + geo.off_bar + warp * stages * 8;
+    const uint32_t full0 = s_base + geo.off_bar, empty0 = full0 + stages * 8;
     uint8_t* xs = smem + geo.off_x;
     float* red = reinterpret_cast<float*>(smem + geo.off_red);
-    const uint32_t ring = ((s_base + geo.off_ring + 1023u) & ~1023u) + warp * stages * geo.stage_bytes;
+    const uint32_t ring = (s_base + geo.off_ring + 1023u) & ~1023u;
 
-    TRACE(0);
     if (tid < 16) reinterpret_cast<uint32_t*>(smem)[tid] = 0u;
-    if (lane == 0) {
-        for (int s = 0; s < stages; ++s) mbar_init(bar0 + s * 8, FMT == FMT_Q4 ? 33u : 1u);
+    if (tid == 0) {
+        for (int s = 0; s < stages; ++s) {
+            mbar_init(full0 + s * 8, FMT == FMT_Q4 ? 1u + NCW * 32u : 1u);
+            mbar_init(empty0 + s * 8, (uint32_t)NCW);
+        }
         mbar_init_fence();
     }
-    __syncwarp();
+    __syncthreads();
 
-    // ---- this warp's work: tiles (slot-strided) x its share of the K chunks ----
-    const int slots = nwarps / kw;
-    const int tslot = warp / kw, kpart = warp - tslot * kw;
-    const int my_chunks = (nchunks - kpart + kw - 1) / kw;
-    const int tile_first = blockIdx.x * slots + tslot;
-    const int tile_step = gridDim.x * slots;
-    const int my_tiles = tile_first < a.ntiles ? (a.ntiles - tile_first + tile_step - 1) / tile_step : 0;
-    const int n_items = my_tiles * my_chunks;
-
-    const uint64_t policy = ka.evict_first ? l2_policy_evict_first() : l2_policy_evict_normal();
-    auto issue = [&](int it) {
-        const int ti = it / my_chunks, cj = it - ti * my_chunks;
-        const int tile = tile_first + ti * tile_step;
-        const int c = kpart + cj * kw;
-        const int stage = it % stages;
-        const uint32_t bar = bar0 + stage * 8;
-        const uint32_t dst = ring + stage * geo.stage_bytes;
-        const int cb = min(kcb, rowbytes - c * kcb);
-        // One elected lane drives the TMA unit: per 128-byte column of the chunk, one tiled
-        // tensor copy of 32 rows (two of 16 rows for the two-weight epilogue) into a
-        // 128-byte-swizzled 4 KB box.  Rows past the end of the weight arrive as zeros.
-        const int nb = (cb + 127) >> 7;
-        int sg = 0, row0;
-        if (DUAL) {
-            row0 = tile * 16;
-        } else {
-            if (a.nseg > 1 && tile >= a.seg[1].tile0) sg = 1;
-            if (a.nseg > 2 && tile >= a.seg[2].tile0) sg = 2;
-            row0 = (tile - a.seg[sg].tile0) * TILE_ROWS;
-        }
-        if (lane == 0) {
-            mbar_arrive_expect_tx(bar, (uint32_t)(nb * BOX_BYTES));
-            for (int b = 0; b < nb; ++b) {
-                if (DUAL) {
-                    tma_load_2d(dst + b * BOX_BYTES, &ka.tm[0], c * kcb + b * 128, row0, bar, policy);
-                    tma_load_2d(dst + b * BOX_BYTES + BOX_BYTES / 2, &ka.tm[3], c * kcb + b * 128, row0, bar, policy);
-                } else {
-                    tma_load_2d(dst + b * BOX_BYTES, &ka.tm[sg], c * kcb + b * 128, row0, bar, policy);
-                }
-            }
-        }
-        if (FMT == FMT_Q4) {
-            // block scales of this lane's row ride along through cp.async on the same mbarrier
-            const uint16_t* sbase;
-            int row;
-            if (DUAL) {
-                row = min(row0 + (lane & 15), a.seg[0].N - 1);
-                sbase = lane < 16 ? a.seg[0].scale : a.scale2;
-            } else {
-                row = min(row0 + lane, a.seg[sg].N - 1);
-                sbase = a.seg[sg].scale;
-            }
-            const uint8_t* ssrc = reinterpret_cast<const uint8_t*>(sbase) + ((size_t)row * (a.K / 32)) * 2 + (size_t)c * (kcb / 8);
-            const uint32_t sdst = dst + geo.nbox * BOX_BYTES + lane * geo.sstride;
-            const int sb = cb / 8;
-            if (((reinterpret_cast<uintptr_t>(ssrc) | (uintptr_t)sb) & 15) == 0) {
-                for (int o = 0; o < sb; o += 16) cp_async_16(sdst + o, ssrc + o);
-            } else {
-                for (int o = 0; o < sb; o += 4) cp_async_4(sdst + o, ssrc + o);
-            }
-            cp_async_mbar_arrive_noinc(bar);
-        }
-    };
-
-    // Weight prefetch does not depend on the previous launch: start it first.
-    const int pre = min(stages - 1, n_items);
-    for (int it = 0; it < pre; ++it) issue(it);
-
-    // ---- per-lane fragment addressing ----
-    const int g = lane >> 2, t = lane & 3;
-    // A operands live in swizzled boxes: 16-byte piece q of row r sits at
-    //   box(q / 8) + r * 128 + ((q % 8) ^ (r % 8)) * 16.
-    // fp16 / int8 ldmatrix.x4: matrices = (rows 0-7, piece q) (rows 8-15, q) (rows 0-7, q+1) (rows 8-15, q+1)
-    const uint32_t a_row_off = (uint32_t)(((lane & 7) + ((lane >> 3) & 1) * 8) * 128);
-    const uint32_t a_q_lane = (uint32_t)(lane >> 4);
-    // Q4 ldmatrix.x4: matrices = the four 8-row groups of one 16-byte piece
-    const uint32_t aq_row_off = (uint32_t)(lane * 128);
-    const uint32_t xr = (uint32_t)(lane & 7);
-    auto piece_addr = [&](uint32_t sw, uint32_t row_off, uint32_t q) {
-        return sw + (q >> 3) * BOX_BYTES + row_off + (((q & 7) ^ xr) << 4);
-    };
-    // B: matrix j = lane/8 (16-byte piece j of the 32-k step), row n = lane%8 (+8 per n tile)
-    uint32_t b_base[NT], b_step[NT];
-#pragma unroll
-    for (int nt = 0; nt < NT; ++nt) {
-        const int n = (lane & 7) + nt * 8;
-        const bool valid = n < a.M;
-        b_base[nt] = valid ? smem_u32(xs) + n * geo.xstride + (lane >> 3) * 16 : zero_addr;
-        b_step[nt] = valid ? 64u : 0u;
-    }
-
-    // Two accumulator sets per row block: consecutive k steps alternate between them so
-    // that the tensor-core results of one step are not on the critical path of the next.
-    float acc[2][2][NT][4];
-    float sc_reg[2][2];          // int8: row scales of the current tile (rows g, g+8 of each block)
-    float res_reg[2][2][NT][2];  // in-place epilogues: the values to be updated
-    bool failed = false;
+    const int my_tiles = (int)blockIdx.x < a.ntiles ? (a.ntiles - (int)blockIdx.x + (int)gridDim.x - 1) / (int)gridDim.x : 0;
+    const int n_items = my_tiles * groups;
 
     auto tile_segment = [&](int tile) {
         int si = 0;
@@ -278,52 +225,194 @@ __global__ void __launch_bounds__(MAX_WARPS * 32) linear_stream_kernel(const __g
         if (a.nseg > 2 && tile >= a.seg[2].tile0) si = 2;
         return si;
     };
+
+    // ================= producer warp: one elected lane feeds the TMA unit =================
+    if (warp == NCW) {
+        pdl_launch_dependents();
+        if (lane == 0) {
+            const uint64_t policy = ka.evict_first ? l2_policy_evict_first() : l2_policy_evict_normal();
+            int ti = 0, cg = 0, stage = 0;
+            for (int it = 0; it < n_items; ++it) {
+                const int tile = (int)blockIdx.x + ti * (int)gridDim.x;
+                if (it >= stages && !mbar_wait_bounded(empty0 + stage * 8, (uint32_t)(((it / stages) - 1) & 1))) {
+                    *reinterpret_cast<volatile int*>(a.status) = 2;
+                    break;
+                }
+                const uint32_t dst = ring + stage * geo.stage_bytes, bar = full0 + stage * 8;
+                const int sg = DUAL ? 0 : tile_segment(tile);
+                const int row0 = (tile - (DUAL ? 0 : a.seg[sg].tile0)) * tile_rows;
+                if (!ksplit) {
+                    // one copy per 128-byte column covers the rows of all four consumers
+                    const int cb = min(kcb, rowbytes - cg * kcb);
+                    const int nb = (cb + 127) >> 7;
+                    mbar_arrive_expect_tx(bar, (uint32_t)(nb * CTA_BOX));
+                    for (int b = 0; b < nb; ++b) {
+                        const int x = cg * kcb + b * 128;
+                        if (DUAL) {
+                            tma_load_2d(dst + b * CTA_BOX, &ka.tm[0], x, row0, bar, policy);
+                            tma_load_2d(dst + b * CTA_BOX + CTA_BOX / 2, &ka.tm[3], x, row0, bar, policy);
+                        } else {
+                            tma_load_2d(dst + b * CTA_BOX, &ka.tm[sg], x, row0, bar, policy);
+                        }
+                    }
+                } else {
+                    // the consumers take consecutive K chunks of the same rows
+                    uint32_t bytes = 0;
+                    for (int w = 0; w < NCW; ++w) {
+                        const int c = cg * NCW + w;
+                        if (c < nchunks) bytes += (uint32_t)(((min(kcb, rowbytes - c * kcb) + 127) >> 7) * BOX_BYTES);
+                    }
+                    mbar_arrive_expect_tx(bar, bytes);
+                    for (int w = 0; w < NCW; ++w) {
+                        const int c = cg * NCW + w;
+                        if (c >= nchunks) break;
+                        const int nb = (min(kcb, rowbytes - c * kcb) + 127) >> 7;
+                        for (int b = 0; b < nb; ++b) {
+                            const int x = c * kcb + b * 128;
+                            if (DUAL) {
+                                tma_load_2d(dst + b * CTA_BOX + w * (BOX_BYTES / 2), &ka.tm[0], x, row0, bar, policy);
+                                tma_load_2d(dst + b * CTA_BOX + CTA_BOX / 2 + w * (BOX_BYTES / 2), &ka.tm[3], x, row0, bar, policy);
+                            } else {
+                                tma_load_2d(dst + b * CTA_BOX + w * BOX_BYTES, &ka.tm[sg], x, row0, bar, policy);
+                            }
+                        }
+                    }
+                }
+                if (++cg == groups) { cg = 0; ++ti; }
+                if (++stage == stages) stage = 0;
+            }
+        }
+        return;
+    }
+
+    // ================= consumer warps =================
+    const int g = lane >> 2, t = lane & 3;
+    // This warp's two 16-row blocks inside a column box (bytes from the box start).
+    const uint32_t rb_base0 = DUAL ? (uint32_t)(warp * (BOX_BYTES / 2)) : (uint32_t)(warp * BOX_BYTES);
+    const uint32_t rb_base1 = DUAL ? (uint32_t)(CTA_BOX / 2 + warp * (BOX_BYTES / 2)) : (uint32_t)(warp * BOX_BYTES + BOX_BYTES / 2);
+    // A operands live in swizzled boxes: 16-byte piece q of row r sits at
+    //   box(q / 8) + r * 128 + ((q % 8) ^ (r % 8)) * 16.
+    // fp16 / int8 ldmatrix.x4: matrices = (rows 0-7, piece q) (rows 8-15, q) (rows 0-7, q+1) (rows 8-15, q+1)
+    const uint32_t a_row_off = (uint32_t)(((lane & 7) + ((lane >> 3) & 1) * 8) * 128);
+    const uint32_t a_q_lane = (uint32_t)(lane >> 4);
+    // Q4 ldmatrix.x4: matrices = the four 8-row groups (both row blocks) of one 16-byte piece
+    const uint32_t aq_off = ((lane >> 4) ? rb_base1 : rb_base0) + (uint32_t)((lane & 15) * 128);
+    const uint32_t xr = (uint32_t)(lane & 7);
+    auto piece_addr = [&](uint32_t sw, uint32_t off, uint32_t q) { return sw + (q >> 3) * CTA_BOX + off + (((q & 7) ^ xr) << 4); };
+    // B: matrix j = lane/8 (16-byte piece j of the 32-k step), row n = lane%8 (+8 per n tile)
+    uint32_t b_base[NT], b_step[NT], b_plane[NT];  // b_plane: int8 only, bytes between limb planes
+#pragma unroll
+    for (int nt = 0; nt < NT; ++nt) {
+        const int n = (lane & 7) + nt * 8;
+        const bool valid = n < a.M;
+        b_base[nt] = valid ? smem_u32(xs) + n * geo.xstride + (lane >> 3) * 16 : zero_addr;
+        b_step[nt] = valid ? 64u : 0u;
+        b_plane[nt] = (FMT == FMT_INT8 && valid) ? (uint32_t)(a.M * geo.xstride) : 0u;
+    }
+    const float* rowscale = reinterpret_cast<const float*>(xs + 3 * a.M * geo.xstride + 64);
+
+    // rows of this warp inside its tile, and which warp writes results
+    const int wrow_off = ksplit ? 0 : warp * warp_rows;
+    const bool writer = !ksplit || warp == 0;
+
+    float acc[2][2][NT][4];      // [accumulator set][row block][n tile][frag]
+    int iacc[FMT == FMT_INT8 ? 3 : 1][2][NT][4];  // int8: exact integer sums per activation limb
+    // Prefetched epilogue operands stay as raw fp16 bits until they are used, so that the
+    // loads' latency is not waited for where they are issued.
+    uint16_t sc_reg[2][2];          // int8: row scales of the current tile (rows g, g+8 of each block)
+    uint16_t res_reg[2][2][NT][2];  // in-place epilogues: the values to be updated
+    bool failed = false;
+
     // Per-row scales do not depend on the previous launch: fetch them ahead of use.
     auto prefetch_scales = [&](int tile) {
         if (FMT != FMT_INT8) return;
         if (DUAL) {
 #pragma unroll
             for (int i2 = 0; i2 < 2; ++i2) {
-                const int n = min(tile * 16 + g + i2 * 8, a.seg[0].N - 1);
-                sc_reg[0][i2] = __half2float(__ushort_as_half(a.seg[0].scale[n]));
-                sc_reg[1][i2] = __half2float(__ushort_as_half(a.scale2[n]));
+                const int n = min(tile * tile_rows + wrow_off + g + i2 * 8, a.seg[0].N - 1);
+                sc_reg[0][i2] = a.seg[0].scale[n];
+                sc_reg[1][i2] = a.scale2[n];
             }
         } else {
             const LinSeg& sg = a.seg[tile_segment(tile)];
-            const int row0 = (tile - sg.tile0) * TILE_ROWS;
+            const int row0 = (tile - sg.tile0) * tile_rows + wrow_off;
 #pragma unroll
             for (int rb = 0; rb < 2; ++rb)
 #pragma unroll
                 for (int i2 = 0; i2 < 2; ++i2)
-                    sc_reg[rb][i2] = __half2float(__ushort_as_half(sg.scale[min(row0 + rb * 16 + g + i2 * 8, sg.N - 1)]));
+                    sc_reg[rb][i2] = sg.scale[min(row0 + rb * 16 + g + i2 * 8, sg.N - 1)];
         }
     };
-    if (my_tiles > 0 && kpart == 0) prefetch_scales(tile_first);
+    // Q4: this lane's row of block scales for pipeline item `j` travels by cp.async and
+    // arrives on the stage's full barrier (every lane arrives for every item).
+    auto issue_scales = [&](int j) {
+        const int ti = j / groups, cg = j - ti * groups;
+        const int tile = (int)blockIdx.x + ti * (int)gridDim.x;
+        const int c = ksplit ? cg * NCW + warp : cg;
+        const int stage = j % stages;
+        const uint32_t bar = full0 + stage * 8;
+        if (c < nchunks) {
+            const uint16_t* sbase;
+            int row;
+            if (DUAL) {
+                row = min(tile * tile_rows + wrow_off + (lane & 15), a.seg[0].N - 1);
+                sbase = lane < 16 ? a.seg[0].scale : a.scale2;
+            } else {
+                const LinSeg& sg = a.seg[tile_segment(tile)];
+                row = min((tile - sg.tile0) * tile_rows + wrow_off + lane, sg.N - 1);
+                sbase = sg.scale;
+            }
+            const int cb = min(kcb, rowbytes - c * kcb);
+            const uint8_t* ssrc = reinterpret_cast<const uint8_t*>(sbase) + ((size_t)row * (a.K / 32)) * 2 + (size_t)c * (kcb / 8);
+            const uint32_t sdst = ring + stage * geo.stage_bytes + geo.nbox * CTA_BOX + (warp * WARP_ROWS + lane) * geo.sstride;
+            const int sb = cb / 8;
+            if (((reinterpret_cast<uintptr_t>(ssrc) | (uintptr_t)sb) & 15) == 0) {
+                for (int o = 0; o < sb; o += 16) cp_async_16(sdst + o, ssrc + o);
+            } else {
+                for (int o = 0; o < sb; o += 4) cp_async_4(sdst + o, ssrc + o);
+            }
+        }
+        cp_async_mbar_arrive_noinc(bar);
+    };
 
-    TRACE(1);
-    pdl_launch_dependents();
-    pdl_wait_prior_grid();
-    TRACE(2);
-    stage_x<FMT>(a.x, a.M, a.K, xs, geo.xstride, tid, blockDim.x);
-    __syncthreads();
-    TRACE(3);
-
-    const uint32_t rb_stride = 16 * 128;
+    if (FMT == FMT_Q4) {
+        const int pre = min(stages - 1, n_items);
+        for (int j = 0; j < pre; ++j) issue_scales(j);
+    }
+    if (my_tiles > 0 && writer) prefetch_scales((int)blockIdx.x);
 
 #ifdef NNB_TRACE
-    long long cyc_issue = 0, cyc_wait = 0, cyc_comp = 0, cyc_epi = 0, cyc_t0 = clock64(), cyc_a, cyc_b;
+    const long long tl_entry = clock64();
+#endif
+    pdl_launch_dependents();
+    pdl_wait_prior_grid();
+#ifdef NNB_TRACE
+    const long long tl_wait = clock64();
+#endif
+    if (FMT == FMT_INT8) stage_x_int8(a.x, a.M, a.K, xs, geo.xstride, tid, NCW * 32);
+    else stage_x<FMT>(a.x, a.M, a.K, xs, geo.xstride, tid, NCW * 32);
+    asm volatile("bar.sync 1, %0;" ::"n"(NCW * 32) : "memory");
+#ifdef NNB_TRACE
+    const long long tl_x = clock64();
+    long long tl_full = 0, tl_comp = 0;
+#endif
+
+#ifdef NNB_TRACE
+    long long cyc_wait = 0, cyc_comp = 0, cyc_t0 = clock64(), cyc_a, cyc_b;
 #define CYC_BEGIN() cyc_a = clock64()
-#define CYC_END(acc) do { cyc_b = clock64(); acc += cyc_b - cyc_a; cyc_a = cyc_b; } while (0)
+#define CYC_END(acc_) do { cyc_b = clock64(); acc_ += cyc_b - cyc_a; cyc_a = cyc_b; } while (0)
 #else
 #define CYC_BEGIN() do { } while (0)
-#define CYC_END(acc) do { } while (0)
+#define CYC_END(acc_) do { } while (0)
 #endif
+
+    int ti = 0, cg = 0, stage = 0;
+    uint32_t phase = 0;
     for (int it = 0; it < n_items; ++it) {
-        const int ti = it / my_chunks, cj = it - ti * my_chunks;
-        const int tile = tile_first + ti * tile_step;
-        const int c = kpart + cj * kw;
-        CYC_BEGIN();
-        if (cj == 0) {
+        const int tile = (int)blockIdx.x + ti * (int)gridDim.x;
+        const int c = ksplit ? cg * NCW + warp : cg;
+        const bool active = c < nchunks;
+        if (cg == 0) {
 #pragma unroll
             for (int u = 0; u < 2; ++u)
 #pragma unroll
@@ -332,11 +421,21 @@ __global__ void __launch_bounds__(MAX_WARPS * 32) linear_stream_kernel(const __g
                     for (int nt = 0; nt < NT; ++nt)
 #pragma unroll
                         for (int i = 0; i < 4; ++i) acc[u][rb][nt][i] = 0.f;
-            if (kpart == 0) {
+            if (FMT == FMT_INT8) {
+#pragma unroll
+                for (int l = 0; l < 3; ++l)
+#pragma unroll
+                    for (int rb = 0; rb < 2; ++rb)
+#pragma unroll
+                        for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+                            for (int i = 0; i < 4; ++i) iacc[l % (FMT == FMT_INT8 ? 3 : 1)][rb][nt][i] = 0;
+            }
+            if (writer) {
                 if (ti > 0) prefetch_scales(tile);
                 if (!DUAL && (a.epi == EPI_RESIDUAL || a.epi == EPI_SILU_GATE)) {
                     const LinSeg& sg = a.seg[tile_segment(tile)];
-                    const int row0 = (tile - sg.tile0) * TILE_ROWS;
+                    const int row0 = (tile - sg.tile0) * tile_rows + wrow_off;
 #pragma unroll
                     for (int rb = 0; rb < 2; ++rb)
 #pragma unroll
@@ -346,31 +445,28 @@ __global__ void __launch_bounds__(MAX_WARPS * 32) linear_stream_kernel(const __g
 #pragma unroll
                                 for (int j = 0; j < 2; ++j) {
                                     const int n = row0 + rb * 16 + g + i2 * 8, m = nt * 8 + 2 * t + j;
-                                    res_reg[rb][i2][nt][j] = (n < sg.N && m < a.M)
-                                        ? __half2float(__ushort_as_half(sg.out[(size_t)m * sg.ld_out + n])) : 0.f;
+                                    res_reg[rb][i2][nt][j] = (n < sg.N && m < a.M) ? sg.out[(size_t)m * sg.ld_out + n] : (uint16_t)0;
                                 }
                 }
             }
         }
-        __syncwarp();  // every lane is done reading the stage that is about to be refilled
-        if (it + stages - 1 < n_items) issue(it + stages - 1);
-        CYC_END(cyc_issue);
-
-        const int stage = it % stages;
+        if (FMT == FMT_Q4) {
+            __syncwarp();  // every lane is done with the scale rows that are about to be refilled
+            if (it + stages - 1 < n_items) issue_scales(it + stages - 1);
+        }
+        CYC_BEGIN();
         // A wait that runs out records an error and skips the arithmetic from then on;
         // the warp still walks its items so that the block's barriers stay matched.
-        if (!failed && !mbar_wait_bounded(bar0 + stage * 8, (uint32_t)((it / stages) & 1))) {
+        if (!failed && !mbar_wait_bounded(full0 + stage * 8, phase)) {
             failed = true;
             if (lane == 0) *reinterpret_cast<volatile int*>(a.status) = 1;
         }
-        const uint32_t sw = ring + stage * geo.stage_bytes;
-#ifdef NNB_TRACE
-        const int cb = (failed || ka.dbg_mode == 1) ? 0 : min(kcb, rowbytes - c * kcb);
-#else
-        const int cb = failed ? 0 : min(kcb, rowbytes - c * kcb);
-#endif
-        if (it == 0) TRACE(4);
         CYC_END(cyc_wait);
+#ifdef NNB_TRACE
+        if (it == 0) tl_full = clock64();
+#endif
+        const uint32_t sw = ring + stage * geo.stage_bytes;
+        const int cb = (failed || !active) ? 0 : min(kcb, rowbytes - c * kcb);
 
         if (FMT == FMT_FP16) {
             // one step = 64 bytes of each row = 32 k = two MMAs per row block
@@ -380,11 +476,11 @@ __global__ void __launch_bounds__(MAX_WARPS * 32) linear_stream_kernel(const __g
                 for (int nt = 0; nt < NT; ++nt) ldsm_x4(b_base[nt] + s * b_step[nt], b[nt][0], b[nt][1], b[nt][2], b[nt][3]);
                 uint32_t av[2][2][4];
                 const uint32_t q = (uint32_t)(s - (c * kcb) / 64) * 4 + a_q_lane;
-                const uint32_t ap0 = piece_addr(sw, a_row_off, q), ap1 = piece_addr(sw, a_row_off, q + 2);
 #pragma unroll
                 for (int rb = 0; rb < 2; ++rb) {
-                    ldsm_x4(ap0 + rb * rb_stride, av[rb][0][0], av[rb][0][1], av[rb][0][2], av[rb][0][3]);
-                    ldsm_x4(ap1 + rb * rb_stride, av[rb][1][0], av[rb][1][1], av[rb][1][2], av[rb][1][3]);
+                    const uint32_t off = (rb ? rb_base1 : rb_base0) + a_row_off;
+                    ldsm_x4(piece_addr(sw, off, q), av[rb][0][0], av[rb][0][1], av[rb][0][2], av[rb][0][3]);
+                    ldsm_x4(piece_addr(sw, off, q + 2), av[rb][1][0], av[rb][1][1], av[rb][1][2], av[rb][1][3]);
                 }
 #pragma unroll
                 for (int h = 0; h < 2; ++h)
@@ -402,61 +498,43 @@ __global__ void __launch_bounds__(MAX_WARPS * 32) linear_stream_kernel(const __g
             }
             if (s < s1) step(s, acc[0]);
         } else if (FMT == FMT_INT8) {
-            // one step = 32 bytes of each row = 32 k = two MMAs per row block
-            auto step = [&](int s, float (&ac)[2][NT][4]) {
-                uint32_t b[NT][4];
+            // one step = 64 bytes of each row = 64 k = two integer MMAs (k32) per row block and
+            // activation limb; the weights go from ldmatrix straight into the MMA
+            const int s0 = (c * kcb) / 64;
+            for (int s = 0; s < cb / 64; ++s) {
+                uint32_t b[3][NT][4];
 #pragma unroll
-                for (int nt = 0; nt < NT; ++nt) ldsm_x4(b_base[nt] + s * b_step[nt], b[nt][0], b[nt][1], b[nt][2], b[nt][3]);
-                uint32_t w[2][4];
-                const uint32_t ap = piece_addr(sw, a_row_off, (uint32_t)(s - (c * kcb) / 32) * 2 + a_q_lane);
+                for (int l = 0; l < 3; ++l)
 #pragma unroll
-                for (int rb = 0; rb < 2; ++rb) ldsm_x4(ap + rb * rb_stride, w[rb][0], w[rb][1], w[rb][2], w[rb][3]);
-#ifdef NNB_TRACE
-                if (ka.dbg_mode == 2) {
-                    ac[0][0][0] += __uint_as_float((w[0][0] ^ w[1][1] ^ b[0][0]) & 0x3f800000u);
-                    return;
-                }
-#endif
+                    for (int nt = 0; nt < NT; ++nt)
+                        ldsm_x4(b_base[nt] + l * b_plane[nt] + (s0 + s) * b_step[nt], b[l][nt][0], b[l][nt][1], b[l][nt][2], b[l][nt][3]);
 #pragma unroll
-                for (int h = 0; h < 2; ++h)
+                for (int h = 0; h < 2; ++h) {
+                    const uint32_t q = (uint32_t)s * 4 + 2 * h + a_q_lane;
 #pragma unroll
                     for (int rb = 0; rb < 2; ++rb) {
-                        uint32_t h01, h23, k01, k23;
-                        int8x4_to_half2x2(w[rb][2 * h], h01, h23);
-                        int8x4_to_half2x2(w[rb][2 * h + 1], k01, k23);
-#ifdef NNB_TRACE
-                        if (ka.dbg_mode == 3) {
-                            ac[rb][0][0] += __uint_as_float((h01 ^ k01 ^ h23 ^ k23 ^ b[0][2 * h]) & 0x3f800000u);
-                            continue;
-                        }
-#endif
+                        uint32_t w0, w1, w2, w3;
+                        ldsm_x4(piece_addr(sw, (rb ? rb_base1 : rb_base0) + a_row_off, q), w0, w1, w2, w3);
 #pragma unroll
-                        for (int nt = 0; nt < NT; ++nt) mma_16816(ac[rb][nt], h01, k01, h23, k23, b[nt][2 * h], b[nt][2 * h + 1]);
+                        for (int nt = 0; nt < NT; ++nt) {
+                            imma_16832<true>(iacc[0][rb][nt], w0, w1, w2, w3, b[0][nt][2 * h], b[0][nt][2 * h + 1]);
+                            imma_16832<false>(iacc[FMT == FMT_INT8 ? 1 : 0][rb][nt], w0, w1, w2, w3, b[1][nt][2 * h], b[1][nt][2 * h + 1]);
+                            imma_16832<false>(iacc[FMT == FMT_INT8 ? 2 : 0][rb][nt], w0, w1, w2, w3, b[2][nt][2 * h], b[2][nt][2 * h + 1]);
+                        }
                     }
-            };
-            const int s0 = (c * kcb) / 32, s1 = s0 + cb / 32;
-            int s = s0;
-            for (; s + 4 <= s1; s += 4) {
-                step(s, acc[0]);
-                step(s + 1, acc[1]);
-                step(s + 2, acc[0]);
-                step(s + 3, acc[1]);
-            }
-            for (; s < s1; ++s) {
-                if (s & 1) step(s, acc[1]);
-                else step(s, acc[0]);
+                }
             }
         } else {
             // one step = 16 bytes of each row = one 32-weight block = two MMAs per row block,
             // summed from zero and folded in with the block's scale
-            const uint8_t* sc = smem + (sw - s_base) + geo.nbox * BOX_BYTES;
+            const uint8_t* sc = smem + (sw - s_base) + geo.nbox * CTA_BOX + warp * WARP_ROWS * geo.sstride;
             const int g0 = (c * kcb) / 16;
             auto step = [&](int s, float (&ac)[2][NT][4]) {
                 uint32_t b[NT][4];
 #pragma unroll
                 for (int nt = 0; nt < NT; ++nt) ldsm_x4(b_base[nt] + s * b_step[nt], b[nt][0], b[nt][1], b[nt][2], b[nt][3]);
                 uint32_t w[4];
-                ldsm_x4(piece_addr(sw, aq_row_off, (uint32_t)(s - g0)), w[0], w[1], w[2], w[3]);
+                ldsm_x4(piece_addr(sw, aq_off, (uint32_t)(s - g0)), w[0], w[1], w[2], w[3]);
 #pragma unroll
                 for (int rb = 0; rb < 2; ++rb) {
                     uint32_t p04, p15, p26, p37, q04, q15, q26, q37;
@@ -489,11 +567,33 @@ __global__ void __launch_bounds__(MAX_WARPS * 32) linear_stream_kernel(const __g
                 else step(s, acc[0]);
             }
         }
-
         CYC_END(cyc_comp);
-        if (cj != my_chunks - 1) continue;
-        if (ti == 0) TRACE(5);
+#ifdef NNB_TRACE
+        if (it == 0) tl_comp = clock64();
+#endif
 
+        // hand the stage back to the producer
+        __syncwarp();
+        if (lane == 0) mbar_arrive(empty0 + stage * 8);
+        if (++stage == stages) { stage = 0; phase ^= 1u; }
+        const bool tile_done = (cg == groups - 1);
+        if (++cg == groups) { cg = 0; ++ti; }
+        if (!tile_done) continue;
+
+        if (FMT == FMT_INT8) {
+            // recombine the limb sums: (hi * 2^16 + mid * 2^8 + lo) * 2^-p, in fp32
+#pragma unroll
+            for (int rb = 0; rb < 2; ++rb)
+#pragma unroll
+                for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) {
+                        const int m = nt * 8 + 2 * t + (i & 1);
+                        const float v = fmaf((float)iacc[0][rb][nt][i], 65536.f,
+                                             fmaf((float)iacc[FMT == FMT_INT8 ? 1 : 0][rb][nt][i], 256.f, (float)iacc[FMT == FMT_INT8 ? 2 : 0][rb][nt][i]));
+                        acc[0][rb][nt][i] = m < a.M ? v * rowscale[m] : 0.f;
+                    }
+        }
         // ---- tile finished: fold the two accumulator sets, combine the K parts (fixed
         //      order), then the epilogue ----
 #pragma unroll
@@ -502,18 +602,23 @@ __global__ void __launch_bounds__(MAX_WARPS * 32) linear_stream_kernel(const __g
             for (int nt = 0; nt < NT; ++nt)
 #pragma unroll
                 for (int i = 0; i < 4; ++i) acc[0][rb][nt][i] += acc[1][rb][nt][i];
-        if (kw > 1) {
-            float* mine = red + (warp * 32 + lane) * (2 * NT * 4);
+        if (ksplit) {
+            // partial sums meet in shared memory; the buffer alternates between tiles so one
+            // barrier per tile is enough
+            float* buf = red + (ti & 1) * (NCW * 32 * 2 * NT * 4);
+            if (warp != 0) {
+                float* mine = buf + (warp * 32 + lane) * (2 * NT * 4);
 #pragma unroll
-            for (int rb = 0; rb < 2; ++rb)
+                for (int rb = 0; rb < 2; ++rb)
 #pragma unroll
-                for (int nt = 0; nt < NT; ++nt)
+                    for (int nt = 0; nt < NT; ++nt)
 #pragma unroll
-                    for (int i = 0; i < 4; ++i) mine[(rb * NT + nt) * 4 + i] = acc[0][rb][nt][i];
-            asm volatile("bar.sync %0, %1;" ::"r"(1 + tslot), "r"(kw * 32) : "memory");
-            if (kpart == 0) {
-                for (int p = 1; p < kw; ++p) {
-                    const float* o = red + ((warp + p) * 32 + lane) * (2 * NT * 4);
+                        for (int i = 0; i < 4; ++i) mine[(rb * NT + nt) * 4 + i] = acc[0][rb][nt][i];
+            }
+            asm volatile("bar.sync 1, %0;" ::"n"(NCW * 32) : "memory");
+            if (warp == 0) {
+                for (int p = 1; p < NCW; ++p) {
+                    const float* o = buf + (p * 32 + lane) * (2 * NT * 4);
 #pragma unroll
                     for (int rb = 0; rb < 2; ++rb)
 #pragma unroll
@@ -522,9 +627,8 @@ __global__ void __launch_bounds__(MAX_WARPS * 32) linear_stream_kernel(const __g
                             for (int i = 0; i < 4; ++i) acc[0][rb][nt][i] += o[(rb * NT + nt) * 4 + i];
                 }
             }
-            asm volatile("bar.sync %0, %1;" ::"r"(1 + tslot), "r"(kw * 32) : "memory");
         }
-        if (kpart != 0) continue;
+        if (!writer) continue;
 
         if (DUAL) {
             const LinSeg& sg = a.seg[0];
@@ -532,13 +636,13 @@ __global__ void __launch_bounds__(MAX_WARPS * 32) linear_stream_kernel(const __g
             for (int nt = 0; nt < NT; ++nt)
 #pragma unroll
                 for (int i = 0; i < 4; ++i) {
-                    const int n = tile * 16 + g + (i >> 1) * 8;
+                    const int n = tile * tile_rows + wrow_off + g + (i >> 1) * 8;
                     const int m = nt * 8 + 2 * t + (i & 1);
                     if (n < sg.N && m < a.M) {
                         float gv = acc[0][0][nt][i], uv = acc[0][1][nt][i];
                         if (FMT == FMT_INT8) {
-                            gv *= sc_reg[0][i >> 1];
-                            uv *= sc_reg[1][i >> 1];
+                            gv *= __half2float(__ushort_as_half(sc_reg[0][i >> 1]));
+                            uv *= __half2float(__ushort_as_half(sc_reg[1][i >> 1]));
                         }
                         const float r = (gv / (1.0f + expf(-gv))) * uv;
                         sg.out[(size_t)m * sg.ld_out + n] = __half_as_ushort(__float2half_rn(r));
@@ -546,7 +650,7 @@ __global__ void __launch_bounds__(MAX_WARPS * 32) linear_stream_kernel(const __g
                 }
         } else {
             const LinSeg& sg = a.seg[tile_segment(tile)];
-            const int row0 = (tile - sg.tile0) * TILE_ROWS;
+            const int row0 = (tile - sg.tile0) * tile_rows + wrow_off;
 #pragma unroll
             for (int rb = 0; rb < 2; ++rb)
 #pragma unroll
@@ -560,11 +664,11 @@ __global__ void __launch_bounds__(MAX_WARPS * 32) linear_stream_kernel(const __g
                             const int m = nt * 8 + 2 * t + j;
                             if (m >= a.M) continue;
                             float v = acc[0][rb][nt][i2 * 2 + j];
-                            if (FMT == FMT_INT8) v *= sc_reg[rb][i2];
+                            if (FMT == FMT_INT8) v *= __half2float(__ushort_as_half(sc_reg[rb][i2]));
                             if (a.epi == EPI_RESIDUAL) {
-                                v = res_reg[rb][i2][nt][j] + v;
+                                v = __half2float(__ushort_as_half(res_reg[rb][i2][nt][j])) + v;
                             } else if (a.epi == EPI_SILU_GATE) {
-                                const float gt = res_reg[rb][i2][nt][j];
+                                const float gt = __half2float(__ushort_as_half(res_reg[rb][i2][nt][j]));
                                 v = gt * (1.0f / (1.0f + expf(-gt))) * v;
                             }
                             sg.out[(size_t)m * sg.ld_out + n] = __half_as_ushort(__float2half_rn(v));
@@ -573,20 +677,24 @@ __global__ void __launch_bounds__(MAX_WARPS * 32) linear_stream_kernel(const __g
         }
     }
 #ifdef NNB_TRACE
-    cyc_epi = clock64() - cyc_t0 - cyc_issue - cyc_wait - cyc_comp;
     if (ka.trace && lane == 0 && blockIdx.x < 32) {
         unsigned long long* o = ka.trace + ((size_t)ka.trace_slot * 32 + blockIdx.x) * 8 * 8 + warp * 8;
-        o[0] = cyc_issue; o[1] = cyc_wait; o[2] = cyc_comp; o[3] = cyc_epi; o[4] = n_items; o[5] = clock64() - cyc_t0;
+        if (warp == 0) {
+            unsigned long long* tl = ka.trace + ((size_t)ka.trace_slot * 32 + blockIdx.x) * 8 * 8 + 5 * 8;
+            tl[0] = tl_wait - tl_entry; tl[1] = tl_x - tl_wait; tl[2] = tl_full - tl_x; tl[3] = tl_comp - tl_full;
+            tl[4] = clock64() - tl_comp; tl[5] = tl_entry - cyc_t0;
+        }
+        o[0] = 0; o[1] = cyc_wait; o[2] = cyc_comp; o[3] = (clock64() - cyc_t0) - cyc_wait - cyc_comp; o[4] = n_items; o[5] = clock64() - cyc_t0;
     }
 #endif
 }
 
 template <int FMT, int NT, bool DUAL>
-cudaError_t launch_t(const KArgs& ka, const StreamPlan& p, int nwarps, cudaStream_t st, bool pdl) {
+cudaError_t launch_t(const KArgs& ka, const StreamPlan& p, cudaStream_t st, bool pdl) {
     auto kern = linear_stream_kernel<FMT, NT, DUAL>;
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3((unsigned)p.grid);
-    cfg.blockDim = dim3((unsigned)(nwarps * 32));
+    cfg.blockDim = dim3((unsigned)THREADS);
     cfg.dynamicSmemBytes = p.smem;
     cfg.stream = st;
     cudaLaunchAttribute attr[1];
@@ -629,6 +737,13 @@ cudaError_t configure_one() {
     return cudaFuncSetAttribute(linear_stream_kernel<FMT, NT, DUAL>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
 }
 
+int count_tiles(const LinArgs& a, int tile_rows) {
+    if (a.epi == EPI_SWIGLU) return (a.seg[0].N + tile_rows - 1) / tile_rows;
+    int n = 0;
+    for (int i = 0; i < a.nseg; ++i) n += (a.seg[i].N + tile_rows - 1) / tile_rows;
+    return n;
+}
+
 }  // namespace
 
 cudaError_t stream_configure() {
@@ -656,7 +771,6 @@ bool stream_supported(int fmt, int M, int K, const LinArgs& a) {
     if (M < 1 || M > 16) return false;
     const int rb = fmt_row_bytes(fmt, K);
     if (rb < 128 || (rb % 64) != 0) return false;
-    if (fmt == FMT_Q4 && (K % 64) != 0) return false;
     auto al16 = [](const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; };
     for (int i = 0; i < a.nseg; ++i) {
         if (!al16(a.seg[i].W)) return false;
@@ -667,65 +781,55 @@ bool stream_supported(int fmt, int M, int K, const LinArgs& a) {
     return true;
 }
 
-// Geometry heuristics (environment overrides NNB_KCB / NNB_KW / NNB_WARPS / NNB_STAGES /
-// NNB_CTAS are for tuning runs):
-//   * kcb: the row is cut into equal chunks of at most ~512 bytes (a multiple of 64);
-//   * few tiles: the warps of a block split K (kw) so the whole operator is requested at once;
-//   * warps and stages are sized so that about three blocks fit one SM.
-StreamPlan stream_plan(int fmt, int M, int K, int ntiles, int sm_count, size_t smem_limit) {
+// Geometry heuristics (environment overrides NNB_KCB / NNB_KW / NNB_STAGES / NNB_CTAS are
+// for tuning runs):
+//   * many rows: each consumer warp owns 32 rows of a 128-row block tile, stages are
+//     256 bytes of every row;
+//   * few rows: the four consumers split K of a 32-row tile so that the whole operator is
+//     requested at once;
+//   * the grid is sized so that every block gets the same number of tiles.
+StreamPlan stream_plan(int fmt, const LinArgs& a, int sm_count, size_t smem_limit) {
     StreamPlan p = {};
+    const int M = a.M, K = a.K;
+    const bool dual = a.epi == EPI_SWIGLU;
     const int rb = fmt_row_bytes(fmt, K);
     const int nt = M > 8 ? 2 : 1;
-    // stage width: whole 128-byte columns (the TMA box width), default 256 bytes per row
-    int target = env_int("NNB_KCB", 256);
-    target = target < 128 ? 128 : target > 1024 ? 1024 : (target / 128) * 128;
-    int kcb = target;
     const int rb_cols = ((rb + 127) / 128) * 128;
-    if (kcb > rb_cols) kcb = rb_cols;
+    const int warp_rows = dual ? 16 : WARP_ROWS;
     int stages = env_int("NNB_STAGES", 2);
     if (stages < 2 || stages > 8) stages = 2;
-    int nwarps = env_int("NNB_WARPS", 0);
-    if (nwarps != 1 && nwarps != 2 && nwarps != 4 && nwarps != 8) {
-        // largest of {4, 2, 1} that lets three blocks share an SM
-        nwarps = 4;
-        while (nwarps > 1 && (size_t)make_geo(fmt, M, K, kcb, nwarps, stages, nt).total * 3 + 3072 > smem_limit) nwarps /= 2;
-    }
     int kw = env_int("NNB_KW", 0);
-    if (kw != 1 && kw != 2 && kw != 4 && kw != 8) {
-        const int want = sm_count * 8;
-        kw = 1;
-        while (kw < nwarps && ntiles * kw < want) kw *= 2;
+    if (kw != 1 && kw != NCW) kw = count_tiles(a, NCW * warp_rows) < 2 * sm_count && rb_cols >= 256 ? NCW : 1;
+    int kcb = env_int("NNB_KCB", 0);
+    if (kcb <= 0) {
+        if (kw == 1) kcb = 256;
+        else {
+            kcb = (((rb + NCW - 1) / NCW + 127) / 128) * 128;  // one chunk per consumer when the row is short
+            if (kcb > 384) kcb = 256;
+        }
     }
-    if (kw > nwarps) kw = nwarps;
-    while (kw > 1 && (rb + kcb - 1) / kcb < kw) {
-        // not enough chunks to share: cut the row finer if that is possible, else share less
-        if (kcb > 128) kcb -= 128;
-        else kw /= 2;
-    }
-    Geo g = make_geo(fmt, M, K, kcb, nwarps, stages, nt);
-    while ((size_t)g.total > smem_limit && nwarps > 1) {
-        nwarps /= 2;
-        if (kw > nwarps) kw = nwarps;
-        g = make_geo(fmt, M, K, kcb, nwarps, stages, nt);
-    }
+    kcb = kcb < 128 ? 128 : kcb > 1024 ? 1024 : (kcb / 128) * 128;
+    if (kcb > rb_cols) kcb = rb_cols;
+    Geo g = make_geo(fmt, M, K, kcb, stages, nt);
     while ((size_t)g.total > smem_limit && kcb > 128) {
         kcb -= 128;
-        g = make_geo(fmt, M, K, kcb, nwarps, stages, nt);
+        g = make_geo(fmt, M, K, kcb, stages, nt);
     }
     if ((size_t)g.total > smem_limit) { p.ok = false; return p; }
-    const int slots = nwarps / kw;
+    const int ntiles = count_tiles(a, kw == 1 ? NCW * warp_rows : warp_rows);
     int per_sm = (int)((smem_limit + 1024) / ((size_t)g.total + 1024));
     per_sm = per_sm < 1 ? 1 : per_sm > 6 ? 6 : per_sm;
     const int cap = env_int("NNB_CTAS", 0);
     if (cap > 0 && cap < per_sm) per_sm = cap;
     const int resident = sm_count * per_sm;
-    const int need = (ntiles + slots - 1) / slots;
-    p.grid = need < resident ? need : resident;
+    const int waves = (ntiles + resident - 1) / resident;
+    p.grid = waves > 0 ? (ntiles + waves - 1) / waves : 1;
     if (p.grid < 1) p.grid = 1;
     p.kcb = kcb;
     p.kw = kw;
-    p.warps = nwarps;
+    p.warps = NCW;
     p.stages = stages;
+    p.ntiles = ntiles;
     p.smem = (size_t)g.total;
     p.ok = true;
     return p;
@@ -736,26 +840,32 @@ cudaError_t launch_stream(int fmt, const LinArgs& a, const StreamPlan& p, cudaSt
     ka.a = a;
     ka.a.kcb = p.kcb;
     ka.a.kw = p.kw;
+    ka.a.ntiles = p.ntiles;
     ka.stages = p.stages;
     ka.rowbytes = fmt_row_bytes(fmt, a.K);
     ka.nchunks = (ka.rowbytes + p.kcb - 1) / p.kcb;
     size_t wbytes = 0;
     for (int i = 0; i < a.nseg; ++i) wbytes += (size_t)a.seg[i].N * ka.rowbytes;
     ka.evict_first = wbytes > ((size_t)96 << 20) ? 1 : 0;
+    const bool dual = a.epi == EPI_SWIGLU;
+    const int nt = a.M > 8 ? 2 : 1;
+    const int warp_rows = dual ? 16 : WARP_ROWS;
+    const int tile_rows = p.kw == 1 ? NCW * warp_rows : warp_rows;
+    int t0 = 0;
+    for (int i = 0; i < a.nseg; ++i) {
+        ka.a.seg[i].tile0 = t0;
+        t0 += (a.seg[i].N + tile_rows - 1) / tile_rows;
+        if (!make_weight_map(&ka.tm[i], a.seg[i].W, a.seg[i].N, ka.rowbytes, tile_rows)) return cudaErrorInvalidValue;
+    }
+    if (dual && !make_weight_map(&ka.tm[3], a.W2, a.seg[0].N, ka.rowbytes, tile_rows)) return cudaErrorInvalidValue;
 #ifdef NNB_TRACE
     ka.trace = g_trace;
     ka.trace_slot = g_trace_slots ? (g_trace_next++ % g_trace_slots) : 0;
-    ka.dbg_mode = env_int("NNB_DBG_MODE", 0);
 #endif
-    const bool dual = a.epi == EPI_SWIGLU;
-    const int nt = a.M > 8 ? 2 : 1;
-    for (int i = 0; i < a.nseg; ++i)
-        if (!make_weight_map(&ka.tm[i], a.seg[i].W, a.seg[i].N, ka.rowbytes, dual ? 16 : TILE_ROWS)) return cudaErrorInvalidValue;
-    if (dual && !make_weight_map(&ka.tm[3], a.W2, a.seg[0].N, ka.rowbytes, 16)) return cudaErrorInvalidValue;
-#define GO(F)                                                                              \
-    if (fmt == F) {                                                                        \
-        if (dual) return nt == 2 ? launch_t<F, 2, true>(ka, p, p.warps, st, pdl) : launch_t<F, 1, true>(ka, p, p.warps, st, pdl); \
-        return nt == 2 ? launch_t<F, 2, false>(ka, p, p.warps, st, pdl) : launch_t<F, 1, false>(ka, p, p.warps, st, pdl);       \
+#define GO(F)                                                                                                  \
+    if (fmt == F) {                                                                                            \
+        if (dual) return nt == 2 ? launch_t<F, 2, true>(ka, p, st, pdl) : launch_t<F, 1, true>(ka, p, st, pdl); \
+        return nt == 2 ? launch_t<F, 2, false>(ka, p, st, pdl) : launch_t<F, 1, false>(ka, p, st, pdl);         \
     }
     GO(FMT_FP16) GO(FMT_INT8) GO(FMT_Q4)
 #undef GO

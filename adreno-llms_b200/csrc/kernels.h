@@ -47,14 +47,15 @@ struct StreamPlan {  // launch geometry chosen on the host
     int kcb;     // bytes of one weight row per pipeline stage
     int kw;      // warps splitting K of one tile
     int warps;   // warps per block
-    int stages;  // ring depth per warp
+    int stages;  // ring depth
+    int ntiles;  // block tiles over all segments
     size_t smem;
     bool ok;
 };
 
 // gemv_stream.cu
 bool stream_supported(int fmt, int M, int K, const LinArgs& a);
-StreamPlan stream_plan(int fmt, int M, int K, int ntiles, int sm_count, size_t smem_limit);
+StreamPlan stream_plan(int fmt, const LinArgs& a, int sm_count, size_t smem_limit);
 cudaError_t launch_stream(int fmt, const LinArgs& a, const StreamPlan& p, cudaStream_t st, bool pdl);
 cudaError_t stream_configure();  // opt in to large dynamic shared memory, once per device
 
