@@ -102,52 +102,78 @@ __device__ __forceinline__ void stage_x_int8(const uint16_t* __restrict__ x, int
                                              int nthreads) {
     unsigned int* rowmax = reinterpret_cast<unsigned int*>(xs + 3 * M * xstride);  // [16] max |x| bits, then [16] floats
     float* rowscale = reinterpret_cast<float*>(rowmax + 16);
-    if (tid < 16) rowmax[tid] = 0u;
-    asm volatile("bar.sync 1, %0;" ::"r"(nthreads) : "memory");
     const int per_row = K / 8;  // 16-byte pieces
+    auto quantise_piece = [&](const uint4& v, bool bad, float up, uint8_t* l0, uint8_t* l1, uint8_t* l2, int p) {
+        const unsigned int w[4] = {v.x, v.y, v.z, v.w};
+        uint32_t hi[2] = {0, 0}, mid[2] = {0, 0}, lo[2] = {0, 0};
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            const uint16_t hb = (uint16_t)(i & 1 ? w[i >> 1] >> 16 : w[i >> 1] & 0xFFFFu);
+            const int f = bad ? 0 : __float2int_rn(__half2float(__ushort_as_half(hb)) * up);
+            hi[i >> 2] |= (uint32_t)((f >> 16) & 0xFF) << (8 * (i & 3));
+            mid[i >> 2] |= (uint32_t)((f >> 8) & 0xFF) << (8 * (i & 3));
+            lo[i >> 2] |= (uint32_t)(f & 0xFF) << (8 * (i & 3));
+        }
+        *reinterpret_cast<uint2*>(l0 + p * 8) = make_uint2(hi[0], hi[1]);
+        *reinterpret_cast<uint2*>(l1 + p * 8) = make_uint2(mid[0], mid[1]);
+        *reinterpret_cast<uint2*>(l2 + p * 8) = make_uint2(lo[0], lo[1]);
+    };
+    auto piece_max = [](const uint4& v) {
+        const unsigned int w[4] = {v.x, v.y, v.z, v.w};
+        unsigned int mx = 0u;
+#pragma unroll
+        for (int i = 0; i < 4; ++i) mx = max(mx, max(w[i] & 0x7FFFu, (w[i] >> 16) & 0x7FFFu));
+        return mx;
+    };
+    auto row_params = [&](int m, bool& bad, float& up) {
+        const unsigned int mx = rowmax[m];
+        bad = mx >= 0x7C00u;
+        // exponent of the largest magnitude: fp16 normal 2^(e-15), subnormals counted as 2^-14
+        const int e = (int)(mx >> 10) > 0 ? (int)(mx >> 10) - 15 : -14;
+        const int pw = (mx == 0u || bad) ? 0 : 22 - e;  // max|x| * 2^pw < 2^23
+        up = __int_as_float((127 + pw) << 23);
+        if (tid == 0) rowscale[m] = bad ? __int_as_float(0x7FC00000) : __int_as_float((127 - pw) << 23);
+    };
+    constexpr int REG_PIECES = 4;
+    if (M == 1 && per_row <= REG_PIECES * nthreads) {
+        // decode fast path: the row stays in registers between the max and the split
+        uint4 v[REG_PIECES];
+        unsigned int mx = 0u;
+#pragma unroll
+        for (int j = 0; j < REG_PIECES; ++j) {
+            const int p = tid + j * nthreads;
+            v[j] = p < per_row ? *reinterpret_cast<const uint4*>(x + p * 8) : make_uint4(0, 0, 0, 0);
+            mx = max(mx, piece_max(v[j]));
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) mx = max(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+        if ((tid & 31) == 0 && mx) atomicMax(&rowmax[0], mx);
+        asm volatile("bar.sync 1, %0;" ::"r"(nthreads) : "memory");
+        bool bad;
+        float up;
+        row_params(0, bad, up);
+#pragma unroll
+        for (int j = 0; j < REG_PIECES; ++j) {
+            const int p = tid + j * nthreads;
+            if (p < per_row) quantise_piece(v[j], bad, up, xs, xs + xstride, xs + 2 * xstride, p);
+        }
+        return;
+    }
     for (int m = 0; m < M; ++m) {
         unsigned int mx = 0u;
-        for (int p = tid; p < per_row; p += nthreads) {
-            const uint4 v = *reinterpret_cast<const uint4*>(x + (size_t)m * K + p * 8);
-            const unsigned int w[4] = {v.x, v.y, v.z, v.w};
-#pragma unroll
-            for (int i = 0; i < 4; ++i) {
-                mx = max(mx, w[i] & 0x7FFFu);
-                mx = max(mx, (w[i] >> 16) & 0x7FFFu);
-            }
-        }
+        for (int p = tid; p < per_row; p += nthreads) mx = max(mx, piece_max(*reinterpret_cast<const uint4*>(x + (size_t)m * K + p * 8)));
 #pragma unroll
         for (int o = 16; o > 0; o >>= 1) mx = max(mx, __shfl_xor_sync(0xffffffffu, mx, o));
         if ((tid & 31) == 0 && mx) atomicMax(&rowmax[m], mx);
     }
     asm volatile("bar.sync 1, %0;" ::"r"(nthreads) : "memory");
     for (int m = 0; m < M; ++m) {
-        const unsigned int mx = rowmax[m];
-        const bool bad = mx >= 0x7C00u;
-        // exponent of the largest magnitude: fp16 normal 2^(e-15), subnormals counted as 2^-14
-        const int e = (int)(mx >> 10) > 0 ? (int)(mx >> 10) - 15 : -14;
-        const int pw = (mx == 0u || bad) ? 0 : 22 - e;  // max|x| * 2^pw < 2^23
-        const float up = __int_as_float((127 + pw) << 23);
-        if (tid == 0) rowscale[m] = bad ? __int_as_float(0x7FC00000) : __int_as_float((127 - pw) << 23);
-        uint8_t* l0 = xs + (0 * M + m) * xstride;
-        uint8_t* l1 = xs + (1 * M + m) * xstride;
-        uint8_t* l2 = xs + (2 * M + m) * xstride;
-        for (int p = tid; p < per_row; p += nthreads) {
-            const uint4 v = *reinterpret_cast<const uint4*>(x + (size_t)m * K + p * 8);
-            const unsigned int w[4] = {v.x, v.y, v.z, v.w};
-            uint32_t hi[2] = {0, 0}, mid[2] = {0, 0}, lo[2] = {0, 0};
-#pragma unroll
-            for (int i = 0; i < 8; ++i) {
-                const uint16_t hb = (uint16_t)(i & 1 ? w[i >> 1] >> 16 : w[i >> 1] & 0xFFFFu);
-                const int f = bad ? 0 : __float2int_rn(__half2float(__ushort_as_half(hb)) * up);
-                hi[i >> 2] |= (uint32_t)((f >> 16) & 0xFF) << (8 * (i & 3));
-                mid[i >> 2] |= (uint32_t)((f >> 8) & 0xFF) << (8 * (i & 3));
-                lo[i >> 2] |= (uint32_t)(f & 0xFF) << (8 * (i & 3));
-            }
-            *reinterpret_cast<uint2*>(l0 + p * 8) = make_uint2(hi[0], hi[1]);
-            *reinterpret_cast<uint2*>(l1 + p * 8) = make_uint2(mid[0], mid[1]);
-            *reinterpret_cast<uint2*>(l2 + p * 8) = make_uint2(lo[0], lo[1]);
-        }
+        bool bad;
+        float up;
+        row_params(m, bad, up);
+        for (int p = tid; p < per_row; p += nthreads)
+            quantise_piece(*reinterpret_cast<const uint4*>(x + (size_t)m * K + p * 8), bad, up, xs + (0 * M + m) * xstride,
+                           xs + (1 * M + m) * xstride, xs + (2 * M + m) * xstride, p);
     }
 }
 
@@ -207,6 +233,7 @@ __global__ void __launch_bounds__(THREADS) linear_stream_kernel(const __grid_con
     const uint32_t ring = (s_base + geo.off_ring + 1023u) & ~1023u;
 
     if (tid < 16) reinterpret_cast<uint32_t*>(smem)[tid] = 0u;
+    if (FMT == FMT_INT8 && tid >= 32 && tid < 48) reinterpret_cast<uint32_t*>(xs + 3 * a.M * geo.xstride)[tid - 32] = 0u;  // per-row max words
     if (tid == 0) {
         for (int s = 0; s < stages; ++s) {
             mbar_init(full0 + s * 8, FMT == FMT_Q4 ? 1u + NCW * 32u : 1u);
@@ -320,7 +347,7 @@ __global__ void __launch_bounds__(THREADS) linear_stream_kernel(const __grid_con
     // Prefetched epilogue operands stay as raw fp16 bits until they are used, so that the
     // loads' latency is not waited for where they are issued.
     uint16_t sc_reg[2][2];          // int8: row scales of the current tile (rows g, g+8 of each block)
-    uint16_t res_reg[2][2][NT][2];  // in-place epilogues: the values to be updated
+    uint32_t res_reg[2][2][NT][2];  // in-place epilogues: the values to be updated
     bool failed = false;
 
     // Per-row scales do not depend on the previous launch: fetch them ahead of use.
@@ -375,6 +402,24 @@ __global__ void __launch_bounds__(THREADS) linear_stream_kernel(const __grid_con
         cp_async_mbar_arrive_noinc(bar);
     };
 
+    // In-place epilogues read the values they update; issued early, used at the tile's end.
+    auto prefetch_residual = [&](int tile) {
+        if (DUAL || !(a.epi == EPI_RESIDUAL || a.epi == EPI_SILU_GATE)) return;
+        const LinSeg& sg = a.seg[tile_segment(tile)];
+        const int row0 = (tile - sg.tile0) * tile_rows + wrow_off;
+#pragma unroll
+        for (int rb = 0; rb < 2; ++rb)
+#pragma unroll
+            for (int i2 = 0; i2 < 2; ++i2)
+#pragma unroll
+                for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+                    for (int j = 0; j < 2; ++j) {
+                        const int n = row0 + rb * 16 + g + i2 * 8, m = nt * 8 + 2 * t + j;
+                        res_reg[rb][i2][nt][j] = (n < sg.N && m < a.M) ? (uint32_t)sg.out[(size_t)m * sg.ld_out + n] : 0u;
+                    }
+    };
+
     if (FMT == FMT_Q4) {
         const int pre = min(stages - 1, n_items);
         for (int j = 0; j < pre; ++j) issue_scales(j);
@@ -389,6 +434,7 @@ __global__ void __launch_bounds__(THREADS) linear_stream_kernel(const __grid_con
 #ifdef NNB_TRACE
     const long long tl_wait = clock64();
 #endif
+    if (my_tiles > 0 && writer) prefetch_residual((int)blockIdx.x);
     if (FMT == FMT_INT8) stage_x_int8(a.x, a.M, a.K, xs, geo.xstride, tid, NCW * 32);
     else stage_x<FMT>(a.x, a.M, a.K, xs, geo.xstride, tid, NCW * 32);
     asm volatile("bar.sync 1, %0;" ::"n"(NCW * 32) : "memory");
@@ -433,21 +479,7 @@ __global__ void __launch_bounds__(THREADS) linear_stream_kernel(const __grid_con
             }
             if (writer) {
                 if (ti > 0) prefetch_scales(tile);
-                if (!DUAL && (a.epi == EPI_RESIDUAL || a.epi == EPI_SILU_GATE)) {
-                    const LinSeg& sg = a.seg[tile_segment(tile)];
-                    const int row0 = (tile - sg.tile0) * tile_rows + wrow_off;
-#pragma unroll
-                    for (int rb = 0; rb < 2; ++rb)
-#pragma unroll
-                        for (int i2 = 0; i2 < 2; ++i2)
-#pragma unroll
-                            for (int nt = 0; nt < NT; ++nt)
-#pragma unroll
-                                for (int j = 0; j < 2; ++j) {
-                                    const int n = row0 + rb * 16 + g + i2 * 8, m = nt * 8 + 2 * t + j;
-                                    res_reg[rb][i2][nt][j] = (n < sg.N && m < a.M) ? sg.out[(size_t)m * sg.ld_out + n] : (uint16_t)0;
-                                }
-                }
+                if (ti > 0) prefetch_residual(tile);
             }
         }
         if (FMT == FMT_Q4) {
@@ -666,9 +698,9 @@ __global__ void __launch_bounds__(THREADS) linear_stream_kernel(const __grid_con
                             float v = acc[0][rb][nt][i2 * 2 + j];
                             if (FMT == FMT_INT8) v *= __half2float(__ushort_as_half(sc_reg[rb][i2]));
                             if (a.epi == EPI_RESIDUAL) {
-                                v = __half2float(__ushort_as_half(res_reg[rb][i2][nt][j])) + v;
+                                v = __half2float(__ushort_as_half((uint16_t)res_reg[rb][i2][nt][j])) + v;
                             } else if (a.epi == EPI_SILU_GATE) {
-                                const float gt = __half2float(__ushort_as_half(res_reg[rb][i2][nt][j]));
+                                const float gt = __half2float(__ushort_as_half((uint16_t)res_reg[rb][i2][nt][j]));
                                 v = gt * (1.0f / (1.0f + expf(-gt))) * v;
                             }
                             sg.out[(size_t)m * sg.ld_out + n] = __half_as_ushort(__float2half_rn(v));
