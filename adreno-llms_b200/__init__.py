@@ -65,6 +65,7 @@ def load():
         "nn_fused_gate_up_silu": ([vp, i, i, i, vp, vp, vp, vp], i),
         "nn_linear_qkv": ([vp, i, i, vp, vp, i, vp, i, vp, i, vp, vp, vp], i),
         "nn_dequant": ([vp, i, i, vp, vp], i), "nn_argmax": ([vp, i, vp, vp], i),
+        "nn_argmax_static": ([vp, i, vp, vp], i),
         "nn_plan_begin": ([vp], i), "nn_plan_end": ([vp, pvp], i), "nn_plan_launch": ([vp, vp], i),
         "nn_plan_num_kernels": ([vp], i), "nn_plan_free": ([vp], i),
         "nn_weights_load": ([vp, cp, cp, pvp], i), "nn_weights_free": ([vp], i),

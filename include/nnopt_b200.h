@@ -126,6 +126,22 @@ int nn_dequant(nn_context* ctx, int N, int K, nn_buf W, nn_buf out_f32);
  * (host: src/model.cpp:603-623). */
 int nn_argmax(nn_context* ctx, int n, nn_buf logits_fp16, nn_buf out_index_i32);
 
+/* Arg-max for callers that are not allowed to allocate device memory (a real-time thread
+ * under a no-allocation rule, a host application that owns the whole device heap through its
+ * own pool, a service whose memory budget is frozen after start-up).  It has no counterpart
+ * in the reference; it is nn_argmax without a context: the reduction scratch is a fixed
+ * array inside the library image on every GPU that loads it (256 bytes), so nothing is ever
+ * allocated or freed.  `cuda_stream` is the cudaStream_t to order the work on (NULL = the
+ * default stream); the current device is used.
+ *   - n must be <= NN_ARGMAX_STATIC_MAX_N, otherwise NN_ERR_ARG.
+ *   - The first call on each device resolves the scratch array's device address; make that
+ *     first call before any stream capture.
+ *   - All calls on a device share the scratch.  Each call clears what it uses first, so
+ *     results never depend on earlier calls, but calls that overlap on the GPU race;
+ *     order them on one stream. */
+#define NN_ARGMAX_STATIC_MAX_N (1 << 22)
+int nn_argmax_static(void* cuda_stream, int n, nn_buf logits_fp16, nn_buf out_index_i32);
+
 /* ---- recorded decode step: the reference's recordable-queue replay
  *      (src/models/smollm2-135m-instruct/src/model.cpp:104-195,312-344).
  *      Between nn_plan_begin and nn_plan_end the operator calls above are captured
