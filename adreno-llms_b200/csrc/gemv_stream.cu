@@ -828,8 +828,6 @@ StreamPlan stream_plan(int fmt, const LinArgs& a, int sm_count, size_t smem_limi
     const int nt = M > 8 ? 2 : 1;
     const int rb_cols = ((rb + 127) / 128) * 128;
     const int warp_rows = dual ? 16 : WARP_ROWS;
-    int stages = env_int("NNB_STAGES", 2);
-    if (stages < 2 || stages > 8) stages = 2;
     int kw = env_int("NNB_KW", 0);
     if (kw != 1 && kw != NCW) kw = count_tiles(a, NCW * warp_rows) < 2 * sm_count && rb_cols >= 256 ? NCW : 1;
     int kcb = env_int("NNB_KCB", 0);
@@ -842,17 +840,33 @@ StreamPlan stream_plan(int fmt, const LinArgs& a, int sm_count, size_t smem_limi
     }
     kcb = kcb < 128 ? 128 : kcb > 1024 ? 1024 : (kcb / 128) * 128;
     if (kcb > rb_cols) kcb = rb_cols;
-    Geo g = make_geo(fmt, M, K, kcb, stages, nt);
-    while ((size_t)g.total > smem_limit && kcb > 128) {
-        kcb -= 128;
-        g = make_geo(fmt, M, K, kcb, stages, nt);
-    }
-    if ((size_t)g.total > smem_limit) { p.ok = false; return p; }
+    while ((size_t)make_geo(fmt, M, K, kcb, 2, nt).total > smem_limit && kcb > 128) kcb -= 128;
+    if ((size_t)make_geo(fmt, M, K, kcb, 2, nt).total > smem_limit) { p.ok = false; return p; }
     const int ntiles = count_tiles(a, kw == 1 ? NCW * warp_rows : warp_rows);
-    int per_sm = (int)((smem_limit + 1024) / ((size_t)g.total + 1024));
-    per_sm = per_sm < 1 ? 1 : per_sm > 6 ? 6 : per_sm;
+    const int nchunks = (rb + kcb - 1) / kcb;
+    const int groups = kw == 1 ? nchunks : (nchunks + NCW - 1) / NCW;
+    // Ring depth and blocks per SM (measured on B200): two blocks per SM with a three-stage
+    // ring stream long operators best; a block with only a few pipeline items gets a ring as
+    // deep as its item count, so that the whole operator is in flight after the first request.
+    int stages = env_int("NNB_STAGES", 0), per_sm = 0;
     const int cap = env_int("NNB_CTAS", 0);
-    if (cap > 0 && cap < per_sm) per_sm = cap;
+    for (int ps = (cap == 1 ? 1 : 2); ps >= 1 && !per_sm; --ps) {
+        const size_t budget = (smem_limit + 1024) / ps - 1024;
+        int st = stages >= 2 && stages <= 8 ? stages : (ps == 2 ? 4 : 6);
+        while (st > 2 && (size_t)make_geo(fmt, M, K, kcb, st, nt).total > budget) --st;
+        if ((size_t)make_geo(fmt, M, K, kcb, st, nt).total > budget) continue;
+        if (!(stages >= 2 && stages <= 8)) {
+            const int resident = sm_count * ps;
+            const int items = ((ntiles + resident - 1) / resident) * groups;  // pipeline items of the busiest block
+            if (items <= st) st = items < 2 ? 2 : items;
+            else if (st > 3) st = 3;
+        }
+        per_sm = ps;
+        p.stages = st;
+    }
+    if (per_sm == 0) { p.ok = false; return p; }
+    stages = p.stages;
+    Geo g = make_geo(fmt, M, K, kcb, stages, nt);
     const int resident = sm_count * per_sm;
     const int waves = (ntiles + resident - 1) / resident;
     p.grid = waves > 0 ? (ntiles + waves - 1) / waves : 1;
@@ -860,7 +874,6 @@ StreamPlan stream_plan(int fmt, const LinArgs& a, int sm_count, size_t smem_limi
     p.kcb = kcb;
     p.kw = kw;
     p.warps = NCW;
-    p.stages = stages;
     p.ntiles = ntiles;
     p.smem = (size_t)g.total;
     p.ok = true;

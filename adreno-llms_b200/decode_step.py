@@ -19,13 +19,13 @@ from . import synth
 
 class DecodeStep:
     def __init__(self, ctx, shape: synth.ModelShape, fmt: str, M: int = 1, n_sets: int = 1, seed: int = 1235,
-                 vocab_rows=None, keep_host=False):
+                 vocab_rows=None, keep_host=False, only=None):
         self.ctx, self.shape, self.fmt, self.M = ctx, shape, fmt, M
         self.vocab_lo, self.vocab_n = vocab_rows if vocab_rows else (0, shape.vocab)
         rng = np.random.default_rng(seed)
         H, F = shape.hidden, shape.ffn
         self.host = {} if keep_host else None
-        self.ops = synth.decode_step_ops(shape)
+        self.ops = [op for op in synth.decode_step_ops(shape) if only is None or op[0] == only]
         # activations (fixed inputs) and outputs
         self.x_h = self._act("x_h", M, H, rng)      # normed hidden -> QKV and gate/up
         self.x_attn = self._act("x_attn", M, shape.q_dim, rng)   # attention output -> o_proj

@@ -13,9 +13,9 @@ achieved weight-stream rate: algorithmic bytes of the step / step time, in GB/s.
             resident weight copies so that every step streams from HBM, not L2
   e2e       the same step driven from HOST buffers through the C ABI: pinned-host
             hidden vector -> device, step, logits -> pinned host, every step
-  roofline  the launch group that takes most of the step, timed alone the same way
-  cpu_baseline  the CPU oracle (port of the reference's kernel arithmetic), all host
-            cores, on a bounded sample of the same step
+  roofline  the launch group that takes most of the step, replayed alone the same way
+  cpu_baseline  the reference's own .cl kernels compiled for the CPU (oracle/_ref; the oracle
+            port when that build is absent), all host cores, on a bounded sample of the step
 
 With --gpus N > 1 (launched under torchrun) the lm_head rows are sharded across the
 ranks and all-gathered with NCCL; the per-layer projections stay replicated
@@ -143,20 +143,78 @@ def cpu_step_rate(pkg, fmt, budget_s=12.0):
 
 
 def ref_build_present():
-    return os.path.exists(os.path.join(REPO, "oracle", "_ref", "libref_cl.so"))
+    return os.path.exists(os.path.join(REPO, "oracle", "_ref", "libsmollm2_block_fused_int8.so"))
+
+
+def cpu_reference_rate(fmt, budget_s=25.0):
+    """GB/s of the reference's OWN kernels (its .cl sources compiled for the CPU,
+    oracle/_ref) on the step's launches, all host cores.  Sample: the launches of one
+    transformer layer (three QKV GEMVs, o_proj+residual, gate/up/SiLU, down+residual) and a
+    4096-row slice of the lm_head, each timed and scaled by how often it occurs in the step."""
+    sys.path.insert(0, REPO)
+    from oracle import ref_cl  # noqa: E402  (CPU-baseline leg only)
+    synth = importlib.import_module("adreno_llms_b200.synth")
+    sh = synth.SMOLLM2_135M
+    cores = os.cpu_count() or 1
+    rng = np.random.default_rng(98)
+    H, F = sh.hidden, sh.ffn
+    x_h, x_f, r = synth.activations(1, H, rng), synth.activations(1, F, rng), synth.activations(1, H, rng)
+    head_rows = 4096
+
+    def w(n, k):
+        return synth.weight(fmt, n, k, rng)
+
+    if fmt == "int8":
+        lib = "smollm2_block_fused_int8"
+        launches = [
+            (lambda W=w(sh.q_dim, H): ref_cl.gemv_scaled(lib, "gemv_m1_k576_no4_img_int8", 4, x_h, W[0], W[1], cores), sh.layers, (sh.q_dim, H)),
+            (lambda W=w(sh.kv_dim, H): ref_cl.gemv_scaled(lib, "gemv_m1_k576_no4_img_int8", 4, x_h, W[0], W[1], cores), 2 * sh.layers, (sh.kv_dim, H)),
+            (lambda W=w(H, sh.q_dim): ref_cl.residual_scaled(lib, "fused_oproj_residual_m1_no4_img_int8", x_h, W[0], W[1], r, cores), sh.layers, (H, sh.q_dim)),
+            (lambda Wg=w(F, H), Wu=w(F, H): ref_cl.swiglu_int8(x_h, Wg[0], Wg[1], Wu[0], Wu[1], cores), sh.layers, (2 * F, H)),
+            (lambda W=w(H, F): ref_cl.residual_scaled(lib, "fused_down_residual_m1_no4_img_int8", x_f, W[0], W[1], r, cores), sh.layers, (H, F)),
+            (lambda W=w(head_rows, H): ref_cl.gemv_scaled(lib, "gemv_m1_k576_no4_img_int8", 4, x_h, W[0], W[1], cores), sh.vocab / head_rows, (head_rows, H)),
+        ]
+    else:
+        lib = "smollm2_block_fused"
+        launches = [
+            (lambda W=w(sh.q_dim, H): ref_cl.gemv_fp16_img(lib, "gemv_m1_k576_no4_img", 4, x_h, W[0], cores), sh.layers, (sh.q_dim, H)),
+            (lambda W=w(sh.kv_dim, H): ref_cl.gemv_fp16_img(lib, "gemv_m1_k576_no4_img", 4, x_h, W[0], cores), 2 * sh.layers, (sh.kv_dim, H)),
+            (lambda W=w(H, sh.q_dim): ref_cl.residual_fp16_img(lib, "fused_oproj_residual_m1_no4_img", x_h, W[0], r, cores), sh.layers, (H, sh.q_dim)),
+            (lambda Wg=w(F, H), Wu=w(F, H): ref_cl.swiglu_fp16(x_h, Wg[0], Wu[0], cores), sh.layers, (2 * F, H)),
+            (lambda W=w(H, F): ref_cl.residual_fp16_img(lib, "fused_down_residual_m1_no4_img", x_f, W[0], r, cores), sh.layers, (H, F)),
+            (lambda W=w(head_rows, H): ref_cl.gemv_fp16_img(lib, "gemv_m1_k576_no4_img", 4, x_h, W[0], cores), sh.vocab / head_rows, (head_rows, H)),
+        ]
+    t_step, t_begin = 0.0, time.perf_counter()
+    for fn, count, _ in launches:
+        fn()  # warm
+        reps, t = 0, 0.0
+        while reps < 3 and (reps == 0 or time.perf_counter() - t_begin < budget_s):
+            t0 = time.perf_counter()
+            fn()
+            t += time.perf_counter() - t0
+            reps += 1
+        t_step += t / reps * count
+    return synth.decode_step_bytes(sh, fmt, 1) / t_step / 1e9, cores, t_step
+
+
+def cpu_arm(pkg, fmt, budget_s):
+    """(rate GB/s, cores, seconds per step, kind, sample text)."""
+    if ref_build_present() and fmt in ("int8", "fp16"):
+        r, cores, t = cpu_reference_rate(fmt, budget_s)
+        return r, cores, t, "reference", ("the reference's .cl kernels compiled for the CPU: the launches of one layer and a "
+                                          "4096-row lm_head slice, each timed up to 3x on all cores and scaled by its count in the step")
+    r, cores, t = cpu_step_rate(pkg, fmt, budget_s)
+    return r, cores, t, "port", "each distinct projection shape of the step timed up to 3x on all cores, scaled by its count in the step"
 
 
 def run_reference_arm(args, pkg, rank):
     if rank != 0:
         return
     fmt = args.fmt
-    kind = "port"
-    rates = []
-    for _ in range(max(1, min(args.steps, 3))):
-        r, cores, t_step = cpu_step_rate(pkg, fmt, budget_s=40.0)
-        rates.append((r, t_step))
-    r = statistics.median([a for a, _ in rates])
-    t_step = statistics.median([b for _, b in rates])
+    rates = [cpu_arm(pkg, fmt, 20.0) for _ in range(max(1, min(args.steps, 3)))]
+    r = statistics.median([a[0] for a in rates])
+    t_step = statistics.median([a[2] for a in rates])
+    _, cores, _, kind, sample = rates[0]
     synth = importlib.import_module("adreno_llms_b200.synth")
     line = {
         "impl": "reference", "metric": METRIC, "value": r, "unit": UNIT, "n_gpus": args.gpus,
@@ -165,9 +223,7 @@ def run_reference_arm(args, pkg, rank):
         "data": "synthetic",
         "config": {"workload": f"decode-step projection set, SmolLM2-135M shape, {fmt}, M=1 "
                                f"({synth.decode_step_gemvs(synth.SMOLLM2_135M)} GEMVs)"},
-        "cpu_baseline": {"value": r, "unit": UNIT, "cores": cores, "kind": kind,
-                         "sample": "each distinct projection shape of the step timed 3x on all cores, "
-                                   "scaled by its count in the step"},
+        "cpu_baseline": {"value": r, "unit": UNIT, "cores": cores, "kind": kind, "sample": sample},
         "e2e": {"value": r, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
     }
     print(json.dumps(line), flush=True)
@@ -197,6 +253,8 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--fmt", default="int8", choices=["int8", "fp16", "q4"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--only", default=None, choices=["qkv", "o_add", "gate_up", "down_add", "lm_head"],
+                    help="profiling aid: the step consists of this launch group only")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -223,9 +281,10 @@ def main():
     if shape.vocab % world:
         raise SystemExit(f"vocab {shape.vocab} is not divisible by {world} ranks")
     vrows = shape.vocab // world
-    step_bytes_full = synth.decode_step_bytes(shape, fmt, 1)
-    n_sets = max(2, math.ceil(2.0 * l2_bytes / step_bytes_full) + 1)
-    step = dstep.DecodeStep(ctx, shape, fmt, M=1, n_sets=n_sets, vocab_rows=(rank * vrows, vrows))
+    step_bytes_full = sum(synth.linear_bytes(fmt, n, k, 1) for kind, _, ws in synth.decode_step_ops(shape)
+                          if args.only in (None, kind) for n, k in ws)
+    n_sets = min(64, max(2, math.ceil(2.0 * l2_bytes / step_bytes_full) + 1))
+    step = dstep.DecodeStep(ctx, shape, fmt, M=1, n_sets=n_sets, vocab_rows=(rank * vrows, vrows), only=args.only)
 
     comm, gathered = None, None
     if world > 1:
@@ -253,7 +312,7 @@ def main():
         if comm:
             pkg._check(ctx.L.nn_comm_all_gather(comm, step.logits, gathered, vrows * 2))
 
-    kernels_per_step = step.record(with_argmax=(world == 1))
+    kernels_per_step = step.record(with_argmax=(world == 1 and args.only is None))
     for i in range(args.warmup):
         enqueue_step(i)
     barrier()
@@ -305,6 +364,10 @@ def main():
 
     # ---- roofline: each launch group of the step timed alone (same launches, rotating sets) ----
     peak, peak_src = measured_peaks()
+    traffic_tbl = {}
+    tp = os.path.join(REPO, "profiles", "dram_traffic.json")
+    if os.path.exists(tp):
+        traffic_tbl = json.load(open(tp)).get(fmt, {})
     groups = {}
     for kind, layer, ws in step.ops:
         groups.setdefault(kind, []).append(layer)
@@ -325,10 +388,18 @@ def main():
                     ctx.linear_add(M, sh.hidden, sh.ffn, step.x_act, w[0], step.resid)
                 else:
                     ctx.linear(M, step.vocab_n, sh.hidden, step.x_h, w[0], step.logits)
+        # replayed from recorded plans (one per weight copy), like the step itself
+        plans = []
+        for i in range(n_sets):
+            ctx.plan_begin()
+            run(i)
+            plans.append(ctx.plan_end())
         reps = 60
         for i in range(3):
-            run(i)
-        gms = time_group(ctx, run, reps)
+            ctx.plan_launch(plans[i % n_sets])
+        gms = time_group(ctx, lambda i: ctx.plan_launch(plans[i % n_sets]), reps)
+        for pl in plans:
+            ctx.L.nn_plan_free(pl)
         nl = len(layers)
         per_launch_us = gms * 1e3 / (reps * nl)
         ws = next(w for k2, _, w in step.ops if k2 == kind)
@@ -345,10 +416,8 @@ def main():
 
     cpu_base = None
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
-        r, cores, t_step = cpu_step_rate(pkg, fmt)
-        cpu_base = {"value": r, "unit": UNIT, "cores": cores, "kind": "port",
-                    "sample": "each distinct projection shape of the step timed up to 3x on all cores, scaled by its "
-                              f"count in the step ({t_step * 1e3:.1f} ms per step)"}
+        r, cores, t_step, kind, sample = cpu_arm(pkg, fmt, 15.0)
+        cpu_base = {"value": r, "unit": UNIT, "cores": cores, "kind": kind, "sample": f"{sample} ({t_step * 1e3:.1f} ms per step)"}
 
     if rank == 0:
         line = {
@@ -366,7 +435,7 @@ def main():
                     "d2h_bytes_per_step": shape.vocab * 2, "us_per_step": e2e_s / e2e_steps * 1e6, "steps": e2e_steps},
             "gpu_launches": launches,
             "roofline": {"bound": "hbm", "kernel": f"linear_stream_kernel [{dom['group']}]", "achieved": dom["gbps"], "peak": peak,
-                         "unit": "GB/s", "frac": dom["gbps"] / peak, "traffic": None, "peak_source": peak_src,
+                         "unit": "GB/s", "frac": dom["gbps"] / peak, "traffic": traffic_tbl.get(dom["group"]), "peak_source": peak_src,
                          "us_per_launch": dom["us_per_launch"], "bytes_per_launch": dom["bytes_per_launch"]},
             "roofline_largest_launch": {"kernel": f"linear_stream_kernel [{big['group']}]", "achieved": big["gbps"],
                                         "frac": big["gbps"] / peak, "us_per_launch": big["us_per_launch"],
