@@ -778,6 +778,18 @@ int count_tiles(const LinArgs& a, int tile_rows) {
 
 }  // namespace
 
+bool encode_tiled_2d(void* map, bool half_elems, const void* base, uint64_t dim0, uint64_t dim1, uint64_t stride1_bytes,
+                     uint32_t box0, uint32_t box1) {
+    if (!g_encode_tiled) return false;
+    const cuuint64_t dims[2] = {dim0, dim1};
+    const cuuint64_t strides[1] = {stride1_bytes};
+    const cuuint32_t box[2] = {box0, box1};
+    const cuuint32_t estr[2] = {1u, 1u};
+    return g_encode_tiled(static_cast<CUtensorMap*>(map), half_elems ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_UINT8, 2,
+                          const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                          CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
 cudaError_t stream_configure() {
     cudaError_t e;
     if (!g_encode_tiled) {
@@ -793,7 +805,7 @@ cudaError_t stream_configure() {
     CFG(FMT_INT8, 1, false) CFG(FMT_INT8, 2, false) CFG(FMT_INT8, 1, true) CFG(FMT_INT8, 2, true)
     CFG(FMT_Q4, 1, false) CFG(FMT_Q4, 2, false) CFG(FMT_Q4, 1, true) CFG(FMT_Q4, 2, true)
 #undef CFG
-    return cudaSuccess;
+    return gemm_tc_configure();
 }
 
 // Shapes the streaming kernel takes: 1 <= M <= 16, rows of at least 128 bytes whose

@@ -21,6 +21,8 @@ struct nn_context {
     int* status_host = nullptr;                // mapped pinned word written by kernels
     int* status_dev = nullptr;
     unsigned long long* argmax_slot = nullptr;
+    void* gemm_scratch = nullptr;  // fp16 copy of a quantised weight for the tensor-core path
+    size_t gemm_scratch_bytes = 0;
     void* flush_buf = nullptr;
     size_t flush_bytes = 0;
     bool use_pdl = true;

@@ -59,6 +59,18 @@ StreamPlan stream_plan(int fmt, const LinArgs& a, int sm_count, size_t smem_limi
 cudaError_t launch_stream(int fmt, const LinArgs& a, const StreamPlan& p, cudaStream_t st, bool pdl);
 cudaError_t stream_configure();  // opt in to large dynamic shared memory, once per device
 
+// 2-D tensor map helper (gemv_stream.cu): [dim1][dim0] elements, row stride in bytes, box dim0 x dim1,
+// 128-byte swizzle; fp16 elements when `half_elems`, bytes otherwise.
+bool encode_tiled_2d(void* map, bool half_elems, const void* base, uint64_t dim0, uint64_t dim1, uint64_t stride1_bytes,
+                     uint32_t box0, uint32_t box1);
+
+// gemm_tc.cu: tcgen05 / tensor-memory GEMM for M > 16
+cudaError_t gemm_tc_configure();
+bool gemm_tc_supported(int M, int N, int K, const void* x, const void* W, const void* out);
+cudaError_t launch_dequant_half(int fmt, int N, int K, const void* W, const uint16_t* scale, uint16_t* out, cudaStream_t st);
+cudaError_t launch_gemm_tc(const uint16_t* W_half, const uint16_t* row_scale, const uint16_t* x, uint16_t* out, int M, int N, int K,
+                           int ld_out, int epi, int* status, cudaStream_t st);
+
 // gemv_generic.cu: any K, any alignment (the reference's gemv_rT_fp32acc role)
 cudaError_t launch_generic(int fmt, const LinArgs& a, cudaStream_t st);
 

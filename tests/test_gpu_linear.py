@@ -257,3 +257,29 @@ def test_argmax_agreement(nnb, ctx):
         ctx.free(xb)
     assert agree >= trials - 2
     ctx.L.nn_unregister_weight(ctx.h, qw.buf)
+
+
+@pytest.mark.parametrize("fmt,N,K,M", [("fp16", 896, 896, 64), ("fp16", 4864, 896, 512), ("fp16", 1000, 1024, 100), ("fp16", 256, 4864, 17),
+                                       ("fp16", 640, 200, 48), ("int8", 1152, 896, 256), ("int8", 900, 576, 33), ("q4", 1024, 1024, 128),
+                                       ("q4", 4608, 1024, 64), ("fp16", 2048, 896, 2048)])
+def test_tensor_core_path_large_m(nnb, ctx, fmt, N, K, M):
+    """M > 16 (batched decode beyond 16 rows, prefill): the tcgen05 GEMM.  The reference is
+    M independent M = 1 results; compared here against an fp64 product of the dequantised
+    weights, which the kernel-order oracle matches to 2e-6 (tests/test_oracle_golden.py)."""
+    W, s = make_weight(fmt, N, K, 7000 + N)
+    x = make_x(M, K, 7001)
+    got = run_linear(nnb, ctx, fmt, W, s, x, N, K)
+    want = x.astype(np.float64) @ cpu.dequant(fmt, W, s).astype(np.float64).T
+    check_close(got, want, what=f"tensor-core {fmt} {N}x{K} M={M}")
+    # a few rows against the kernel-order oracle itself
+    rows = [0, M // 2, M - 1]
+    check_close(got[rows], cpu.linear(fmt, x[rows], W, s, threads=8), what="tensor-core vs oracle rows")
+
+
+def test_tensor_core_residual(nnb, ctx):
+    N, K, M = 896, 4864, 64
+    W, s = make_weight("int8", N, K, 7100)
+    x, r = make_x(M, K, 7101), make_x(M, N, 7102)
+    got = run_linear(nnb, ctx, "int8", W, s, x, N, K, call="add", extra=r)
+    want = r.astype(np.float64) + x.astype(np.float64) @ cpu.dequant("int8", W, s).astype(np.float64).T
+    check_close(got, want, what="tensor-core residual")
