@@ -6,7 +6,9 @@
 // lda = ldb = K, ldc = N, alpha 1, beta 0), and for its token-by-token loop over
 // quantised weights (src/models/lfm2-5-350m/src/model.cpp:243-251).
 //
-// One block computes a 128 (weight rows) x BN (tokens, <= 256) tile over all of K:
+// Persistent blocks (one per SM) walk 128 (weight rows) x BN (tokens, <= 256) output tiles,
+// each over all of K, with two accumulators in tensor memory so that the epilogue of one
+// tile overlaps the MMAs of the next:
 //   * warp 0, one lane: TMA producer.  Per 64-wide K block it issues two tiled tensor
 //     copies (cp.async.bulk.tensor.2d, 128-byte swizzle): 128 weight rows and BN
 //     activation rows, both K-major, completing on the stage's "full" mbarrier.
@@ -14,7 +16,7 @@
 //     four per K block) on shared-memory descriptors; the accumulator lives in tensor
 //     memory (128 lanes x BN fp32 columns).  tcgen05.commit hands each stage back through
 //     its "empty" mbarrier and signals the epilogue at the end.
-//   * all four warps: epilogue.  Warp w reads lanes 32w..32w+31 of the accumulator with
+//   * warps 2-5: epilogue.  Warp w reads lanes 32 (w % 4) .. +31 of the accumulator with
 //     tcgen05.ld (lane = weight row, column = token), applies the per-row int8 scale or
 //     the in-place residual, converts to fp16 and stores; for a fixed token the 32 lanes
 //     of a warp write 32 consecutive outputs.
@@ -35,7 +37,8 @@ namespace {
 
 constexpr int BM = 128;       // weight rows per tile (UMMA M)
 constexpr int BK = 64;        // K elements per stage = one 128-byte swizzle span of fp16
-constexpr int GEMM_THREADS = 128;
+constexpr int EPI_WARPS = 4;
+constexpr int GEMM_THREADS = (2 + EPI_WARPS) * 32;  // producer warp, MMA warp, four epilogue warps
 constexpr int A_BYTES = BM * BK * 2;  // 16 KB
 
 struct GemmK {
@@ -114,93 +117,126 @@ __global__ void __launch_bounds__(GEMM_THREADS) linear_gemm_tc_kernel(const __gr
     extern __shared__ __align__(128) uint8_t smem[];
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const uint32_t s_base = smem_u32(smem);
-    // header: full[S], empty[S], tmem_full, tmem address word
-    const uint32_t full0 = s_base, empty0 = s_base + 64, tmem_full = s_base + 128, tmem_slot = s_base + 136;
+    // header: full[S] @0, empty[S] @64, acc_full[2] @128, acc_empty[2] @144, tensor-memory address @160
+    const uint32_t full0 = s_base, empty0 = s_base + 64, acc_full0 = s_base + 128, acc_empty0 = s_base + 144, tmem_slot = s_base + 160;
     const uint32_t ring = (s_base + 1024u + 1023u) & ~1023u;
     const int b_bytes = g.bn * BK * 2;
     const int stage_bytes = A_BYTES + ((b_bytes + 1023) / 1024) * 1024;
     const int nkb = (g.K + BK - 1) / BK;
-    const int wt = blockIdx.x / g.ntok, tt = blockIdx.x - wt * g.ntok;  // weight tile, token tile
-    const int n0 = wt * BM, m0 = tt * g.bn;
+    const int ntiles = ((g.N + BM - 1) / BM) * g.ntok;
 
     if (tid == 0) {
         for (int s = 0; s < g.stages; ++s) {
             mbar_init(full0 + s * 8, 1);
             mbar_init(empty0 + s * 8, 1);
         }
-        mbar_init(tmem_full, 1);
+        for (int a = 0; a < 2; ++a) {
+            mbar_init(acc_full0 + a * 8, 1);
+            mbar_init(acc_empty0 + a * 8, EPI_WARPS);
+        }
         mbar_init_fence();
     }
-    if (warp == 1) tmem_alloc(tmem_slot, (uint32_t)g.tmem_cols);
+    if (warp == 1) tmem_alloc(tmem_slot, (uint32_t)(2 * g.tmem_cols));
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
-    const uint32_t tmem_d = *reinterpret_cast<volatile uint32_t*>(smem + 136);
-    bool failed = false;
+    const uint32_t tmem_base = *reinterpret_cast<volatile uint32_t*>(smem + 160);
 
-    if (warp == 0 && lane == 0) {
-        // ---- TMA producer ----
-        const uint64_t policy = l2_policy_evict_normal();
-        for (int kb = 0; kb < nkb; ++kb) {
-            const int s = kb % g.stages;
-            if (kb >= g.stages && !mbar_wait_bounded(empty0 + s * 8, (uint32_t)(((kb / g.stages) - 1) & 1))) {
-                *reinterpret_cast<volatile int*>(g.status) = 3;
-                break;
-            }
-            const uint32_t dst = ring + s * stage_bytes;
-            mbar_arrive_expect_tx(full0 + s * 8, (uint32_t)(A_BYTES + b_bytes));
-            tma_load_2d(dst, &g.tm_w, kb * BK, n0, full0 + s * 8, policy);
-            tma_load_2d(dst + A_BYTES, &g.tm_x, kb * BK, m0, full0 + s * 8, policy);
-        }
-    } else if (warp == 1 && lane == 0) {
-        // ---- MMA issuer ----
-        const uint32_t idesc = instr_desc_f16(g.bn);
-        for (int kb = 0; kb < nkb; ++kb) {
-            const int s = kb % g.stages;
-            if (!mbar_wait_bounded(full0 + s * 8, (uint32_t)((kb / g.stages) & 1))) {
-                *reinterpret_cast<volatile int*>(g.status) = 4;
-                break;
-            }
-            tc_fence_after();
-            const uint32_t a_addr = ring + s * stage_bytes, b_addr = a_addr + A_BYTES;
-#pragma unroll
-            for (int k = 0; k < BK / 16; ++k)
-                umma_f16(tmem_d, smem_desc_sw128(a_addr + k * 32), smem_desc_sw128(b_addr + k * 32), idesc, (uint32_t)((kb | k) != 0));
-            umma_commit(empty0 + s * 8);  // the stage is free once these MMAs have read it
-        }
-        umma_commit(tmem_full);           // accumulator complete
-    }
-    __syncwarp();
-
-    // ---- epilogue: all four warps; warp w owns accumulator lanes 32w .. 32w+31 ----
-    if (!mbar_wait_bounded(tmem_full, 0)) {
-        failed = true;
-        if (lane == 0) *reinterpret_cast<volatile int*>(g.status) = 5;
-    }
-    tc_fence_after();
-    if (!failed) {
-        const int n = n0 + warp * 32 + lane;
-        const float rs = (g.row_scale && n < g.N) ? __half2float(__ushort_as_half(g.row_scale[n])) : 1.0f;
-        for (int c = 0; c < g.bn; c += 32) {
-            uint32_t r[32];
-            tmem_ld32(tmem_d + ((uint32_t)(warp * 32) << 16) + (uint32_t)c, r);
-            if (n < g.N) {
-#pragma unroll
-                for (int j = 0; j < 32; ++j) {
-                    const int m = m0 + c + j;
-                    if (m < g.M && c + j < g.bn) {
-                        float v = __uint_as_float(r[j]) * rs;
-                        uint16_t* o = g.out + (size_t)m * g.ld_out + n;
-                        if (g.epi == EPI_RESIDUAL) v = __half2float(__ushort_as_half(*o)) + v;
-                        *o = __half_as_ushort(__float2half_rn(v));
+    if (warp == 0) {
+        // ---- TMA producer: one lane walks (tile, K block) and keeps the ring full ----
+        if (lane == 0) {
+            const uint64_t policy = l2_policy_evict_normal();
+            int it = 0;
+            bool ok = true;
+            for (int tile = blockIdx.x; tile < ntiles && ok; tile += gridDim.x) {
+                const int wt = tile / g.ntok, tt = tile - wt * g.ntok;
+                for (int kb = 0; kb < nkb; ++kb, ++it) {
+                    const int s = it % g.stages;
+                    if (it >= g.stages && !mbar_wait_bounded(empty0 + s * 8, (uint32_t)(((it / g.stages) - 1) & 1))) {
+                        *reinterpret_cast<volatile int*>(g.status) = 3;
+                        ok = false;
+                        break;
                     }
+                    const uint32_t dst = ring + s * stage_bytes;
+                    mbar_arrive_expect_tx(full0 + s * 8, (uint32_t)(A_BYTES + b_bytes));
+                    tma_load_2d(dst, &g.tm_w, kb * BK, wt * BM, full0 + s * 8, policy);
+                    tma_load_2d(dst + A_BYTES, &g.tm_x, kb * BK, tt * g.bn, full0 + s * 8, policy);
                 }
             }
         }
+    } else if (warp == 1) {
+        // ---- MMA issuer: one lane; accumulators alternate between two tensor-memory halves ----
+        if (lane == 0) {
+            const uint32_t idesc = instr_desc_f16(g.bn);
+            int it = 0, tl = 0;
+            bool ok = true;
+            for (int tile = blockIdx.x; tile < ntiles && ok; tile += gridDim.x, ++tl) {
+                const int acc = tl & 1;
+                if (tl >= 2 && !mbar_wait_bounded(acc_empty0 + acc * 8, (uint32_t)(((tl >> 1) - 1) & 1))) {
+                    *reinterpret_cast<volatile int*>(g.status) = 6;
+                    break;
+                }
+                tc_fence_after();
+                const uint32_t tmem_d = tmem_base + (uint32_t)(acc * g.tmem_cols);
+                for (int kb = 0; kb < nkb; ++kb, ++it) {
+                    const int s = it % g.stages;
+                    if (!mbar_wait_bounded(full0 + s * 8, (uint32_t)((it / g.stages) & 1))) {
+                        *reinterpret_cast<volatile int*>(g.status) = 4;
+                        ok = false;
+                        break;
+                    }
+                    tc_fence_after();
+                    const uint32_t a_addr = ring + s * stage_bytes, b_addr = a_addr + A_BYTES;
+#pragma unroll
+                    for (int k = 0; k < BK / 16; ++k)
+                        umma_f16(tmem_d, smem_desc_sw128(a_addr + k * 32), smem_desc_sw128(b_addr + k * 32), idesc, (uint32_t)((kb | k) != 0));
+                    umma_commit(empty0 + s * 8);  // the stage is free once these MMAs have read it
+                }
+                umma_commit(acc_full0 + acc * 8);  // this tile's accumulator is complete
+            }
+        }
+    } else {
+        // ---- epilogue warps: warp w owns accumulator lanes 32 (w % 4) .. +31 ----
+        const int q = warp & 3;
+        int tl = 0;
+        bool failed = false;
+        for (int tile = blockIdx.x; tile < ntiles; tile += gridDim.x, ++tl) {
+            const int wt = tile / g.ntok, tt = tile - wt * g.ntok;
+            const int n0 = wt * BM, m0 = tt * g.bn, acc = tl & 1;
+            if (!failed && !mbar_wait_bounded(acc_full0 + acc * 8, (uint32_t)((tl >> 1) & 1))) {
+                failed = true;
+                if (lane == 0) *reinterpret_cast<volatile int*>(g.status) = 5;
+            }
+            tc_fence_after();
+            if (!failed) {
+                const int n = n0 + q * 32 + lane;
+                const float rs = (g.row_scale && n < g.N) ? __half2float(__ushort_as_half(g.row_scale[n])) : 1.0f;
+                const uint32_t tmem_d = tmem_base + (uint32_t)(acc * g.tmem_cols) + ((uint32_t)(q * 32) << 16);
+                for (int c = 0; c < g.bn; c += 32) {
+                    uint32_t r[32];
+                    tmem_ld32(tmem_d + (uint32_t)c, r);
+                    if (n < g.N) {
+#pragma unroll
+                        for (int j = 0; j < 32; ++j) {
+                            const int m = m0 + c + j;
+                            if (m < g.M && c + j < g.bn) {
+                                float v = __uint_as_float(r[j]) * rs;
+                                uint16_t* o = g.out + (size_t)m * g.ld_out + n;
+                                if (g.epi == EPI_RESIDUAL) v = __half2float(__ushort_as_half(*o)) + v;
+                                *o = __half_as_ushort(__float2half_rn(v));
+                            }
+                        }
+                    }
+                }
+            }
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(acc_empty0 + acc * 8);
+        }
     }
     tc_fence_before();
     __syncthreads();
-    if (warp == 1) tmem_dealloc(tmem_d, (uint32_t)g.tmem_cols);
+    if (warp == 1) tmem_dealloc(tmem_base, (uint32_t)(2 * g.tmem_cols));
 }
 
 // fp16 copy of a quantised weight for the tensor-core path.
@@ -270,7 +306,8 @@ cudaError_t launch_gemm_tc(const uint16_t* W_half, const uint16_t* row_scale, co
     if (!encode_tiled_2d(&g.tm_w, /*fp16*/ true, W_half, (uint64_t)K, (uint64_t)N, (uint64_t)K * 2, BK, BM)) return cudaErrorInvalidValue;
     if (!encode_tiled_2d(&g.tm_x, true, x, (uint64_t)K, (uint64_t)M, (uint64_t)K * 2, BK, bn)) return cudaErrorInvalidValue;
     const size_t smem = 2048 + (size_t)stages * stage_bytes;
-    const unsigned grid = (unsigned)(((N + BM - 1) / BM) * g.ntok);
+    unsigned grid = (unsigned)(((N + BM - 1) / BM) * g.ntok);
+    if (grid > 148u) grid = 148u;  // persistent: one block per SM walks the tiles
     linear_gemm_tc_kernel<<<grid, GEMM_THREADS, smem, st>>>(g);
     return cudaGetLastError();
 }
