@@ -79,6 +79,10 @@ def load():
         "nn_l2_flush": ([vp], i), "nn_launch_count": ([vp], ctypes.c_longlong),
         "nn_comm_unique_id": ([vp], i), "nn_comm_init": ([vp, vp, i, i, pvp], i),
         "nn_comm_all_gather": ([vp, vp, vp, sz], i), "nn_comm_free": ([vp], i),
+        "nn_comm_symm_alloc": ([vp, sz, pvp], i), "nn_comm_symm_free": ([vp, vp], i),
+        "nn_linear_gather": ([vp, i, i, i, vp, vp, vp], i),
+        "nn_comm_signal": ([vp], i), "nn_comm_wait": ([vp, ctypes.c_uint], i),
+        "nn_device_count": ([], i),
     }
     for name, (args, res) in sig.items():
         if hasattr(L, name):
@@ -231,3 +235,56 @@ class QuantWeight:
             self.scale = ctx.upload(np.ascontiguousarray(scale).view(np.uint16))
             ctx.register_q4(self.buf, self.scale, self.N, self.K)
         self.nbytes = W.nbytes + (0 if scale is None else np.asarray(scale).nbytes)
+        self.ctx = ctx
+
+    def release(self):
+        """Drop the registry entry and free the device copies."""
+        if self.buf:
+            if self.scale:
+                _check(self.ctx.L.nn_unregister_weight(self.ctx.h, self.buf))
+                self.ctx.free(self.scale)
+            self.ctx.free(self.buf)
+            self.buf = self.scale = None
+
+
+class Comm:
+    """Row-sharding communicator of one rank (nn_comm_*).  `unique_id()` is called on rank 0 and
+    its 128 bytes are handed to the other ranks by whatever channel the host program has."""
+
+    @staticmethod
+    def unique_id():
+        raw = (ctypes.c_ubyte * 128)()
+        _check(load().nn_comm_unique_id(raw))
+        return bytes(raw)
+
+    def __init__(self, ctx: Context, id_bytes, rank: int, world: int):
+        self.ctx, self.rank, self.world = ctx, rank, world
+        raw = (ctypes.c_ubyte * 128)(*id_bytes) if id_bytes else None
+        h = ctypes.c_void_p()
+        _check(ctx.L.nn_comm_init(ctx.h, raw, rank, world, ctypes.byref(h)))
+        self.h = h
+
+    def all_gather(self, send, recv, bytes_per_rank):
+        _check(self.ctx.L.nn_comm_all_gather(self.h, send, recv, bytes_per_rank))
+
+    def symm_alloc(self, nbytes):
+        p = ctypes.c_void_p()
+        _check(self.ctx.L.nn_comm_symm_alloc(self.h, nbytes, ctypes.byref(p)))
+        return p.value
+
+    def symm_free(self, buf):
+        _check(self.ctx.L.nn_comm_symm_free(self.h, buf))
+
+    def linear_gather(self, M, n_local, K, x, W, gathered):
+        _check(self.ctx.L.nn_linear_gather(self.h, M, n_local, K, x, W, gathered))
+
+    def signal(self):
+        _check(self.ctx.L.nn_comm_signal(self.h))
+
+    def wait(self, timeout_ms=2000):
+        _check(self.ctx.L.nn_comm_wait(self.h, timeout_ms))
+
+    def close(self):
+        if self.h:
+            self.ctx.L.nn_comm_free(self.h)
+            self.h = None

@@ -102,6 +102,11 @@ extern "C" int nn_shutdown(nn_context* c) {
     return NN_OK;
 }
 
+extern "C" int nn_device_count(void) {
+    int n = 0;
+    return cudaGetDeviceCount(&n) == cudaSuccess ? n : 0;
+}
+
 extern "C" void* nn_stream(nn_context* c) { return c ? (void*)c->stream : nullptr; }
 
 extern "C" int nn_sync(nn_context* c) {
@@ -266,7 +271,7 @@ static int run_gemm_tc(nn_context* c, int fmt, const LinArgs& a, int M, const ch
         Wh = (const uint16_t*)c->gemm_scratch;
         if (fmt == FMT_INT8) row_scale = sg.scale;
     }
-    cudaError_t e = launch_gemm_tc(Wh, row_scale, a.x, sg.out, M, sg.N, a.K, sg.ld_out, a.epi, a.status, c->stream);
+    cudaError_t e = launch_gemm_tc(Wh, row_scale, a.x, sg.out, M, sg.N, a.K, sg.ld_out, a.epi, a.status, a.peer_out, a.npeer, c->stream);
     if (e != cudaSuccess) return NN_FAIL(NN_ERR_CUDA, "%s: tensor-core launch failed: %s (M=%d N=%d K=%d)", who, cudaGetErrorString(e), M, sg.N, a.K);
     c->launches++;
     *done = true;
@@ -282,15 +287,21 @@ static int run_linear(nn_context* c, int fmt, LinArgs a, int M_total, const char
     // M > 16 is walked in slices of 16 activation rows (each slice re-streams the weights).
     const uint16_t* x0 = a.x;
     uint16_t* out0[3] = {a.seg[0].out, a.seg[1].out, a.seg[2].out};
+    uint16_t* peer0[7];
+    for (int p = 0; p < 7; ++p) peer0[p] = a.peer_out[p];
     for (int m0 = 0; m0 < M_total; m0 += 16) {
         a.M = M_total - m0 < 16 ? M_total - m0 : 16;
         a.x = x0 + (size_t)m0 * a.K;
         for (int i = 0; i < a.nseg; ++i) a.seg[i].out = out0[i] + (size_t)m0 * a.seg[i].ld_out;
+        for (int p = 0; p < a.npeer; ++p) a.peer_out[p] = peer0[p] + (size_t)m0 * a.seg[0].ld_out;
         cudaError_t e;
-        if (stream_supported(fmt, a.M, a.K, a)) {
-            StreamPlan p = stream_plan(fmt, a, c->sm_count, c->smem_limit);
-            e = p.ok ? launch_stream(fmt, a, p, c->stream, c->use_pdl) : launch_generic(fmt, a, c->stream);
+        StreamPlan p = {};
+        if (stream_supported(fmt, a.M, a.K, a)) p = stream_plan(fmt, a, c->sm_count, c->smem_limit);
+        if (p.ok) {
+            e = launch_stream(fmt, a, p, c->stream, c->use_pdl);
         } else {
+            if (a.npeer > 0)
+                return NN_FAIL(NN_ERR_UNSUPPORTED, "%s: this shape takes the any-shape kernel, which does not write to peer ranks (K=%d)", who, a.K);
             e = launch_generic(fmt, a, c->stream);
         }
         if (e != cudaSuccess) return NN_FAIL(NN_ERR_CUDA, "%s: launch failed: %s (M=%d K=%d)", who, cudaGetErrorString(e), a.M, a.K);
@@ -306,7 +317,8 @@ static int check_common(nn_context* c, int M, int N, int K, const void* x, const
     return NN_OK;
 }
 
-static int one_weight(nn_context* c, int M, int N, int K, nn_buf x, nn_buf W, nn_buf out, int epi, const char* who) {
+static int one_weight(nn_context* c, int M, int N, int K, nn_buf x, nn_buf W, nn_buf out, int epi, const char* who,
+                      uint16_t* const* peers = nullptr, int npeer = 0) {
     int rc = check_common(c, M, N, K, x, W, out, who);
     if (rc) return rc;
     if (M == 0) return NN_OK;
@@ -326,7 +338,15 @@ static int one_weight(nn_context* c, int M, int N, int K, nn_buf x, nn_buf W, nn
     a.K = K;
     a.epi = epi;
     a.status = c->status_dev;
+    if (npeer < 0 || npeer > 7) return NN_FAIL(NN_ERR_ARG, "%s: %d peers", who, npeer);
+    a.npeer = npeer;
+    for (int p = 0; p < npeer; ++p) a.peer_out[p] = peers[p];
     return run_linear(c, r.fmt, a, M, who);
+}
+
+int nnb::linear_to_peers(nn_context* c, int M, int N, int K, nn_buf x, nn_buf W, nn_buf out, uint16_t* const* peers, int npeer,
+                         const char* who) {
+    return one_weight(c, M, N, K, x, W, out, EPI_STORE, who, peers, npeer);
 }
 
 extern "C" int nn_linear(nn_context* c, int M, int N, int K, nn_buf x, nn_buf W, nn_buf out) {

@@ -10,9 +10,11 @@
 
 #include <cstdlib>
 #include <cstring>
+#include <vector>
 
 #include "../../include/nnopt_b200.h"
 #include "internal.h"
+#include "kernels.h"
 
 namespace {
 
@@ -59,11 +61,78 @@ const char* nccl_err(int rc) { return g_nccl.error_string ? g_nccl.error_string(
 
 }  // namespace
 
+// One buffer of the same size on every rank, each rank holding peer mappings of the others'.
+struct SymmAlloc {
+    void* base[8] = {};  // base[rank] is this rank's own allocation, the rest are peer mappings
+    size_t bytes = 0;
+};
+
 struct nn_comm {
     nn_context* ctx = nullptr;
     void* comm = nullptr;
     int rank = 0, world = 1;
+    std::vector<SymmAlloc> symm;
+    unsigned* flags = nullptr;   // symmetric: word g is written by rank g's signal kernel
+    unsigned* epochs = nullptr;  // local: [0] signals sent, [1] waits done
 };
+
+#define COMM_CUDA(call)                                                                                   \
+    do {                                                                                                  \
+        cudaError_t e_ = (call);                                                                          \
+        if (e_ != cudaSuccess) return NN_FAIL(NN_ERR_CUDA, "%s: %s", #call, cudaGetErrorString(e_));      \
+    } while (0)
+
+namespace {
+
+// Allocates `bytes` on this rank, exchanges CUDA IPC handles through the communicator and maps the
+// other ranks' allocations.  Collective: every rank calls it with the same size, in the same order.
+int symm_alloc(nn_comm* c, size_t bytes, SymmAlloc* out) {
+    SymmAlloc sa;
+    sa.bytes = bytes;
+    cudaSetDevice(c->ctx->device);
+    void* local = nullptr;
+    COMM_CUDA(cudaMalloc(&local, bytes));
+    COMM_CUDA(cudaMemsetAsync(local, 0, bytes, c->ctx->stream));
+    sa.base[c->rank] = local;
+    if (c->world > 1) {
+        cudaIpcMemHandle_t mine;
+        COMM_CUDA(cudaIpcGetMemHandle(&mine, local));
+        const size_t hb = sizeof(cudaIpcMemHandle_t);
+        std::vector<cudaIpcMemHandle_t> all((size_t)c->world);
+        void* dev = nullptr;
+        COMM_CUDA(cudaMalloc(&dev, hb * c->world));
+        COMM_CUDA(cudaMemcpyAsync((char*)dev + hb * c->rank, &mine, hb, cudaMemcpyHostToDevice, c->ctx->stream));
+        const int rc = g_nccl.all_gather((char*)dev + hb * c->rank, dev, hb, /*ncclInt8*/ 0, c->comm, c->ctx->stream);
+        if (rc != 0) return NN_FAIL(NN_ERR_COMM, "ncclAllGather (handle exchange): %s", nccl_err(rc));
+        COMM_CUDA(cudaMemcpyAsync(all.data(), dev, hb * c->world, cudaMemcpyDeviceToHost, c->ctx->stream));
+        COMM_CUDA(cudaStreamSynchronize(c->ctx->stream));
+        COMM_CUDA(cudaFree(dev));
+        for (int g = 0; g < c->world; ++g) {
+            if (g == c->rank) continue;
+            void* p = nullptr;
+            cudaError_t e = cudaIpcOpenMemHandle(&p, all[(size_t)g], cudaIpcMemLazyEnablePeerAccess);
+            if (e != cudaSuccess)
+                return NN_FAIL(NN_ERR_COMM, "rank %d cannot map rank %d's buffer (cudaIpcOpenMemHandle: %s); peer access is required",
+                               c->rank, g, cudaGetErrorString(e));
+            sa.base[g] = p;
+        }
+    } else {
+        COMM_CUDA(cudaStreamSynchronize(c->ctx->stream));
+    }
+    *out = sa;
+    return NN_OK;
+}
+
+void symm_release(nn_comm* c, SymmAlloc& sa) {
+    for (int g = 0; g < c->world; ++g) {
+        if (!sa.base[g]) continue;
+        if (g == c->rank) cudaFree(sa.base[g]);
+        else cudaIpcCloseMemHandle(sa.base[g]);
+        sa.base[g] = nullptr;
+    }
+}
+
+}  // namespace
 
 extern "C" int nn_comm_unique_id(void* out) {
     if (!out) return NN_FAIL(NN_ERR_ARG, "nn_comm_unique_id: null argument");
@@ -96,6 +165,79 @@ extern "C" int nn_comm_init(nn_context* ctx, const void* id_bytes, int rank, int
     return NN_OK;
 }
 
+extern "C" int nn_comm_symm_alloc(nn_comm* c, size_t bytes, nn_buf* out) {
+    if (!c || !out || bytes == 0) return NN_FAIL(NN_ERR_ARG, "nn_comm_symm_alloc: null argument or zero size");
+    *out = nullptr;
+    if (c->world > 8) return NN_FAIL(NN_ERR_UNSUPPORTED, "nn_comm_symm_alloc: at most 8 ranks (one NVSwitch domain)");
+    if (!c->flags) {
+        // first use: the flag words (symmetric) and the two local epoch counters
+        SymmAlloc fl;
+        int rc = symm_alloc(c, 256, &fl);
+        if (rc) return rc;
+        c->symm.push_back(fl);
+        c->flags = (unsigned*)fl.base[c->rank];
+        COMM_CUDA(cudaMalloc((void**)&c->epochs, 64));
+        COMM_CUDA(cudaMemset(c->epochs, 0, 64));
+    }
+    SymmAlloc sa;
+    int rc = symm_alloc(c, bytes, &sa);
+    if (rc) return rc;
+    c->symm.push_back(sa);
+    *out = sa.base[c->rank];
+    return NN_OK;
+}
+
+extern "C" int nn_comm_symm_free(nn_comm* c, nn_buf buf) {
+    if (!c || !buf) return NN_OK;
+    for (size_t i = 0; i < c->symm.size(); ++i)
+        if (c->symm[i].base[c->rank] == buf && buf != (void*)c->flags) {
+            symm_release(c, c->symm[i]);
+            c->symm.erase(c->symm.begin() + (long)i);
+            return NN_OK;
+        }
+    return NN_FAIL(NN_ERR_ARG, "nn_comm_symm_free: %p is not a symmetric buffer of this communicator", buf);
+}
+
+extern "C" int nn_comm_signal(nn_comm* c) {
+    if (!c || !c->flags) return NN_FAIL(NN_ERR_ARG, "nn_comm_signal: no symmetric buffer has been allocated on this communicator");
+    nnb::PeerFlags pf = {};
+    pf.world = c->world;
+    pf.rank = c->rank;
+    for (int g = 0; g < c->world; ++g) pf.flags[g] = (unsigned*)c->symm[0].base[g];
+    COMM_CUDA(nnb::launch_comm_signal(pf, c->epochs, c->ctx->stream));
+    c->ctx->launches++;
+    return NN_OK;
+}
+
+extern "C" int nn_comm_wait(nn_comm* c, unsigned timeout_ms) {
+    if (!c || !c->flags) return NN_FAIL(NN_ERR_ARG, "nn_comm_wait: no symmetric buffer has been allocated on this communicator");
+    if (timeout_ms == 0 || timeout_ms > 10000) return NN_FAIL(NN_ERR_ARG, "nn_comm_wait: timeout %u ms outside 1..10000", timeout_ms);
+    COMM_CUDA(nnb::launch_comm_wait(c->flags, c->world, c->epochs + 1, timeout_ms, c->ctx->status_dev, c->ctx->stream));
+    c->ctx->launches++;
+    return NN_OK;
+}
+
+extern "C" int nn_linear_gather(nn_comm* c, int M, int n_local, int K, nn_buf x, nn_buf W, nn_buf gathered) {
+    if (!c || !gathered) return NN_FAIL(NN_ERR_ARG, "nn_linear_gather: null argument");
+    if (M <= 0 || n_local <= 0) return NN_FAIL(NN_ERR_ARG, "nn_linear_gather: bad shape M=%d n_local=%d", M, n_local);
+    const SymmAlloc* sa = nullptr;
+    for (const SymmAlloc& s : c->symm)
+        if (s.base[c->rank] == gathered) sa = &s;
+    if (!sa) return NN_FAIL(NN_ERR_ARG, "nn_linear_gather: %p was not returned by nn_comm_symm_alloc on this communicator", gathered);
+    const size_t block = (size_t)M * n_local * 2;
+    if (block * c->world > sa->bytes)
+        return NN_FAIL(NN_ERR_ARG, "nn_linear_gather: %d blocks of %zu bytes exceed the %zu-byte gather buffer", c->world, block, sa->bytes);
+    uint16_t* peers[7];
+    int np = 0;
+    for (int g = 0; g < c->world; ++g)
+        if (g != c->rank) peers[np++] = (uint16_t*)((char*)sa->base[g] + block * c->rank);
+    int rc = nnb::linear_to_peers(c->ctx, M, n_local, K, x, W, (char*)gathered + block * c->rank, peers, np, "nn_linear_gather");
+    if (rc) return rc;
+    rc = nn_comm_signal(c);
+    if (rc) return rc;
+    return nn_comm_wait(c, 2000);
+}
+
 extern "C" int nn_comm_all_gather(nn_comm* c, nn_buf send, nn_buf recv, size_t bytes) {
     if (!c || !send || !recv) return NN_FAIL(NN_ERR_ARG, "nn_comm_all_gather: null argument");
     if (c->world == 1) {
@@ -112,6 +254,10 @@ extern "C" int nn_comm_all_gather(nn_comm* c, nn_buf send, nn_buf recv, size_t b
 
 extern "C" int nn_comm_free(nn_comm* c) {
     if (!c) return NN_OK;
+    cudaSetDevice(c->ctx->device);
+    cudaStreamSynchronize(c->ctx->stream);
+    for (SymmAlloc& sa : c->symm) symm_release(c, sa);
+    if (c->epochs) cudaFree(c->epochs);
     if (c->comm && g_nccl.comm_destroy) g_nccl.comm_destroy(c->comm);
     delete c;
     return NN_OK;

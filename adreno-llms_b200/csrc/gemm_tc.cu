@@ -53,6 +53,8 @@ struct GemmK {
     int tmem_cols; // power of two >= bn
     int epi;       // EPI_STORE or EPI_RESIDUAL
     int* status;
+    uint16_t* peer_out[7];  // the same output block in the other ranks' gather buffers
+    int npeer;
 };
 
 // ---- tcgen05 wrappers -------------------------------------------------------------------
@@ -223,7 +225,9 @@ __global__ void __launch_bounds__(GEMM_THREADS) linear_gemm_tc_kernel(const __gr
                                 float v = __uint_as_float(r[j]) * rs;
                                 uint16_t* o = g.out + (size_t)m * g.ld_out + n;
                                 if (g.epi == EPI_RESIDUAL) v = __half2float(__ushort_as_half(*o)) + v;
-                                *o = __half_as_ushort(__float2half_rn(v));
+                                const uint16_t hv = __half_as_ushort(__float2half_rn(v));
+                                *o = hv;
+                                for (int p = 0; p < g.npeer; ++p) g.peer_out[p][(size_t)m * g.ld_out + n] = hv;
                             }
                         }
                     }
@@ -285,8 +289,11 @@ cudaError_t launch_dequant_half(int fmt, int N, int K, const void* W, const uint
 }
 
 cudaError_t launch_gemm_tc(const uint16_t* W_half, const uint16_t* row_scale, const uint16_t* x, uint16_t* out, int M, int N, int K,
-                           int ld_out, int epi, int* status, cudaStream_t st) {
+                           int ld_out, int epi, int* status, uint16_t* const* peer_out, int npeer, cudaStream_t st) {
     GemmK g;
+    if (npeer < 0 || npeer > 7) return cudaErrorInvalidValue;
+    g.npeer = npeer;
+    for (int p = 0; p < 7; ++p) g.peer_out[p] = p < npeer ? peer_out[p] : nullptr;
     int bn = M >= 256 ? 256 : ((M + 15) / 16) * 16;
     g.bn = bn;
     g.ntok = (M + bn - 1) / bn;

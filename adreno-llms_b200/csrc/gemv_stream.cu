@@ -703,7 +703,9 @@ __global__ void __launch_bounds__(THREADS) linear_stream_kernel(const __grid_con
                                 const float gt = __half2float(__ushort_as_half((uint16_t)res_reg[rb][i2][nt][j]));
                                 v = gt * (1.0f / (1.0f + expf(-gt))) * v;
                             }
-                            sg.out[(size_t)m * sg.ld_out + n] = __half_as_ushort(__float2half_rn(v));
+                            const uint16_t hv = __half_as_ushort(__float2half_rn(v));
+                            sg.out[(size_t)m * sg.ld_out + n] = hv;
+                            for (int p = 0; p < a.npeer; ++p) a.peer_out[p][(size_t)m * sg.ld_out + n] = hv;
                         }
                 }
         }

@@ -39,6 +39,10 @@ struct ResolvedW {
 };
 bool resolve_weight(const nn_context* c, const void* W, int K, ResolvedW* out);
 
+// nn_linear that also stores every output at the same offset of `npeer` peer-mapped buffers
+// (the row-sharded gather); api.cpp
+int linear_to_peers(nn_context* c, int M, int N, int K, void* x, void* W, void* out, uint16_t* const* peers, int npeer, const char* who);
+
 int fail(int code, const char* file, int line, const char* fmt, ...) __attribute__((format(printf, 4, 5)));
 
 }  // namespace nnb

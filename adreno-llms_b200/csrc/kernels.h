@@ -40,6 +40,10 @@ struct LinArgs {
     int* status;     // device word: non-zero when a bounded wait ran out
     // optional fused arg-max over the stored fp16 values of seg[0] (M == 1)
     unsigned long long* argmax_slot;  // packed (ordered value << 32 | ~index), atomicMax
+    // row-sharded gather: the same block of seg[0].out in the other ranks' gather buffers
+    // (peer-mapped device pointers); every stored value is also written there
+    uint16_t* peer_out[7];
+    int npeer;
 };
 
 struct StreamPlan {  // launch geometry chosen on the host
@@ -69,10 +73,18 @@ cudaError_t gemm_tc_configure();
 bool gemm_tc_supported(int M, int N, int K, const void* x, const void* W, const void* out);
 cudaError_t launch_dequant_half(int fmt, int N, int K, const void* W, const uint16_t* scale, uint16_t* out, cudaStream_t st);
 cudaError_t launch_gemm_tc(const uint16_t* W_half, const uint16_t* row_scale, const uint16_t* x, uint16_t* out, int M, int N, int K,
-                           int ld_out, int epi, int* status, cudaStream_t st);
+                           int ld_out, int epi, int* status, uint16_t* const* peer_out, int npeer, cudaStream_t st);
 
 // gemv_generic.cu: any K, any alignment (the reference's gemv_rT_fp32acc role)
 cudaError_t launch_generic(int fmt, const LinArgs& a, cudaStream_t st);
+
+// comm_kernels.cu: cross-rank flags in peer-mapped memory
+struct PeerFlags {
+    unsigned* flags[8];  // flags[g] = base of rank g's flag array (peer-mapped for g != rank)
+    int world, rank;
+};
+cudaError_t launch_comm_signal(const PeerFlags& pf, unsigned* epoch_sent, cudaStream_t st);
+cudaError_t launch_comm_wait(const unsigned* my_flags, int world, unsigned* epoch_waited, unsigned timeout_ms, int* status, cudaStream_t st);
 
 // misc.cu
 cudaError_t launch_dequant(int fmt, int N, int K, const void* W, const uint16_t* scale, float* out, cudaStream_t st);

@@ -245,6 +245,65 @@ def time_group(ctx, fn, reps):
     return ms
 
 
+def sharded_projections(pkg, ctx, synth, comm, rank, world, dist, reps=12):
+    """The scaled-up row-sharded projections: int8 lm_head 151936 x 896 at M=256 and a Q4 FFN
+    matrix 28672 x 8192 at M in {1, 8, 32, 128}.  Rank g owns rows [g N/G, (g+1) N/G), writes its
+    [M, N/G] block straight into slot g of the gather buffer, and an in-place all-gather fills
+    the other slots (layout [G][M][N/G]).  Device-timed per operator with L2 flushed before each
+    launch; the projection and the all-gather are reported separately, max over ranks."""
+    rows = []
+    cases = [("int8", 151936, 896, 256)] + [("q4", 28672, 8192, m) for m in (1, 8, 32, 128)]
+    cache = {}
+    for fmt, N, K, M in cases:
+        n = N // world
+        if (fmt, N, K) not in cache:
+            for old in cache.values():
+                old.release()
+            cache.clear()
+            # timing does not depend on the values: quantise a block of rows and repeat it
+            blk = min(n, 1024)
+            W, sc = synth.weight(fmt, blk, K, np.random.default_rng(77 + rank))
+            rep = (n + blk - 1) // blk
+            W = np.tile(W, (rep, 1))[:n]
+            sc = np.tile(sc, (rep, 1) if sc.ndim == 2 else rep)[:n]
+            cache[(fmt, N, K)] = pkg.QuantWeight(ctx, fmt, W, sc)
+        qw = cache[(fmt, N, K)]
+        x = ctx.upload(synth.activations(M, K, np.random.default_rng(78)).view(np.uint16))
+        gathered = ctx.alloc(M * N * 2)
+        mine = gathered + rank * M * n * 2
+        ev = [ctx.event() for _ in range(3)]
+        t_lin = t_ag = 0.0
+        for i in range(reps + 2):
+            ctx.l2_flush()
+            ctx.record(ev[0])
+            ctx.linear(M, n, K, x, qw.buf, mine)
+            ctx.record(ev[1])
+            if comm:
+                pkg._check(ctx.L.nn_comm_all_gather(comm, mine, gathered, M * n * 2))
+            ctx.record(ev[2])
+            ctx.sync()
+            if i >= 2:
+                t_lin += ctx.elapsed_ms(ev[0], ev[1])
+                t_ag += ctx.elapsed_ms(ev[1], ev[2])
+        t = [t_lin / reps * 1e3, t_ag / reps * 1e3]
+        if dist:
+            import torch
+            tt = torch.tensor(t, dtype=torch.float64)
+            dist.all_reduce(tt, op=dist.ReduceOp.MAX)
+            t = tt.tolist()
+        b = synth.linear_bytes(fmt, N, K, M)
+        rows.append({"fmt": fmt, "N": N, "K": K, "M": M, "rows_per_rank": n, "linear_us": t[0], "all_gather_us": t[1],
+                     "gbps_aggregate": b / ((t[0] + t[1]) * 1e-6) / 1e9,
+                     "tflops_aggregate": 2.0 * M * N * K / ((t[0] + t[1]) * 1e-6) / 1e12})
+        for e in ev:
+            ctx.L.nn_event_destroy(e)
+        ctx.free(gathered)
+        ctx.free(x)
+    for old in cache.values():
+        old.release()
+    return rows
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -412,6 +471,7 @@ def main():
         g["share_of_step"] = g["share_of_step"] / tot
     dom = max(group_rows, key=lambda g: g["share_of_step"])
     big = max(group_rows, key=lambda g: g["bytes_per_launch"])
+    sharded = sharded_projections(pkg, ctx, synth, comm, rank, world, dist) if args.only is None else None
     clocks = sampler.stop()
 
     cpu_base = None
@@ -441,6 +501,7 @@ def main():
                                         "frac": big["gbps"] / peak, "us_per_launch": big["us_per_launch"],
                                         "bytes_per_launch": big["bytes_per_launch"]},
             "launch_groups": group_rows,
+            "sharded_projections": sharded,
             "clocks": clocks,
         }
         if cpu_base:

@@ -193,6 +193,33 @@ int nn_comm_init(nn_context* ctx, const void* id_128bytes, int rank, int world, 
 int nn_comm_all_gather(nn_comm* comm, nn_buf send, nn_buf recv, size_t bytes_per_rank);
 int nn_comm_free(nn_comm* comm);
 
+/* Projection fused with its gather, over peer-mapped memory (NVLink / NVSwitch):
+ *   nn_comm_symm_alloc  collective; every rank passes the same size and gets a zeroed local
+ *                       buffer whose twins on the other ranks are mapped here (CUDA IPC; needs
+ *                       peer access between the GPUs, at most 8 ranks).  Freed with
+ *                       nn_comm_symm_free (collective, after all ranks have synchronised) or
+ *                       by nn_comm_free.
+ *   nn_linear_gather    out block = x[M,K] . W[n_local,K]^T like nn_linear, where W holds this
+ *                       rank's rows.  The kernel stores each output into block `rank` of the
+ *                       gather buffer ([G][M][n_local] fp16) on EVERY rank, then the ranks
+ *                       exchange completion flags; when the call's work has run in stream
+ *                       order, all G blocks of this rank's `gathered` are complete.  `gathered`
+ *                       must be a pointer returned by nn_comm_symm_alloc.  A peer may start
+ *                       writing the next call's block into the same buffer while this rank
+ *                       still reads it: alternate between two gather buffers.
+ *   nn_comm_signal      publish "my stream has reached this point" to every rank;
+ *   nn_comm_wait        hold the stream until every rank's signal count has reached this
+ *                       rank's wait count, at most timeout_ms (1..10000); when the wait runs
+ *                       out the next nn_sync returns NN_ERR_TIMEOUT and the context stays usable.
+ * No counterpart in the reference. */
+int nn_comm_symm_alloc(nn_comm* comm, size_t bytes, nn_buf* out);
+int nn_comm_symm_free(nn_comm* comm, nn_buf buf);
+int nn_linear_gather(nn_comm* comm, int M, int n_local, int K, nn_buf x, nn_buf W, nn_buf gathered);
+int nn_comm_signal(nn_comm* comm);
+int nn_comm_wait(nn_comm* comm, unsigned timeout_ms);
+/* Number of CUDA devices visible to the process (0 when there is none). */
+int nn_device_count(void);
+
 #ifdef __cplusplus
 }
 #endif

@@ -1,0 +1,99 @@
+"""One rank of the multi-GPU parity check (launched by test_gpu_multi.py through
+torch.distributed.run, one process per GPU).
+
+Every rank builds the same seeded weight, keeps its row block, and runs the projection twice:
+  * nn_linear + NCCL all-gather (in place in the gather buffer), and
+  * nn_linear_gather, whose kernel stores into every rank's gather buffer over peer memory.
+Both gathered results must be bit-identical, and, reassembled to [M, N], must match the CPU
+oracle on the unsharded weight within the path's tolerance.
+"""
+import os
+import sys
+
+import numpy as np
+
+REPO = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+sys.path.insert(0, REPO)
+sys.path.insert(0, os.path.join(REPO, "tests"))
+
+CASES = [  # fmt, N, K, M
+    ("int8", 4096, 576, 1),
+    ("q4", 2048, 1024, 8),
+    ("fp16", 1536, 896, 16),
+    ("fp16", 2048, 512, 64),    # tensor-core path
+    ("int8", 3072, 896, 256),   # tensor-core path, quantised weight
+    ("q4", 1024, 2048, 40),
+]
+
+
+def main():
+    import torch
+    import torch.distributed as dist
+    from conftest import load_package
+    from helpers import TOL, make_weight, make_x
+    from oracle import cpu
+    import importlib
+    pkg = load_package()
+    sharding = importlib.import_module("adreno_llms_b200.sharding")
+
+    rank, world, local = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"]), int(os.environ["LOCAL_RANK"])
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    ctx = pkg.Context(local)
+    idt = torch.zeros(128, dtype=torch.uint8)
+    if rank == 0:
+        idt = torch.tensor(list(pkg.Comm.unique_id()), dtype=torch.uint8)
+    dist.broadcast(idt, 0)
+    comm = pkg.Comm(ctx, bytes(idt.tolist()), rank, world)
+
+    failures = []
+    for fmt, N, K, M in CASES:
+        W, s = make_weight(fmt, N, K, 9000 + N)
+        x = make_x(M, K, 9001 + K)
+        Wl, sl = sharding.shard_weight(fmt, W, s, world, rank)
+        lo, n = sharding.shard_rows(N, world, rank)
+        qw = pkg.QuantWeight(ctx, fmt, Wl, sl)
+        dx = ctx.upload(x.view(np.uint16))
+        block = M * n * 2
+        # (1) NCCL, in place
+        g1 = ctx.alloc(block * world)
+        ctx.linear(M, n, K, dx, qw.buf, g1 + rank * block)
+        comm.all_gather(g1 + rank * block, g1, block)
+        r1 = ctx.download(g1, (world, M, n), np.uint16)
+        # (2) fused: peer stores + flags, twice into alternating buffers (epochs advance)
+        bufs = [comm.symm_alloc(block * world) for _ in range(2)]
+        outs = []
+        for rep in range(4):
+            comm.linear_gather(M, n, K, dx, qw.buf, bufs[rep & 1])
+            outs.append(ctx.download(bufs[rep & 1], (world, M, n), np.uint16))
+        for rep, r2 in enumerate(outs):
+            if not np.array_equal(r1, r2):
+                failures.append(f"{fmt} N={N} K={K} M={M} rep {rep}: fused gather differs from NCCL gather in "
+                                f"{int((r1 != r2).sum())} of {r1.size} values")
+        full = sharding.gathered_to_row_major(outs[-1], world, M, N).view(np.float16)
+        want = cpu.linear(fmt, x, W, s, order=2)
+        err = cpu.rel_l2(full, want)
+        if not err <= TOL:
+            failures.append(f"{fmt} N={N} K={K} M={M}: relative L2 {err:.3e} against the oracle")
+        ctx.sync()
+        dist.barrier()   # nobody frees a buffer a peer may still write
+        for b in bufs:
+            comm.symm_free(b)
+        qw.release()
+        ctx.free(g1)
+        ctx.free(dx)
+    ctx.sync()
+    dist.barrier()
+    comm.close()
+    ctx.close()
+    ok = torch.tensor([0 if failures else 1])
+    dist.all_reduce(ok, op=dist.ReduceOp.MIN)
+    for f in failures:
+        print(f"rank {rank}: {f}", flush=True)
+    if rank == 0:
+        print("MULTI_GPU_OK" if int(ok.item()) == 1 else "MULTI_GPU_FAIL", flush=True)
+    dist.destroy_process_group()
+    return 0 if int(ok.item()) == 1 else 1
+
+
+if __name__ == "__main__":
+    sys.exit(main())

@@ -1,0 +1,104 @@
+"""Multi-GPU parity of the row-sharded projections (needs at least two GPUs; skipped otherwise)
+and the single-rank behaviour of the gather entry points, including a wait that runs out."""
+import os
+import socket
+import subprocess
+import sys
+
+import numpy as np
+import pytest
+
+from helpers import TOL, make_weight, make_x
+from oracle import cpu
+
+REPO = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+pytestmark = pytest.mark.gpu
+
+
+def _free_port():
+    s = socket.socket()
+    s.bind(("127.0.0.1", 0))
+    p = s.getsockname()[1]
+    s.close()
+    return p
+
+
+def test_two_rank_gather_matches_nccl_and_oracle(nnb, built_lib):
+    n = built_lib.nn_device_count()
+    if n < 2:
+        pytest.skip(f"{n} GPU visible; the two-rank check needs two")
+    env = dict(os.environ, NCCL_DEBUG="WARN")
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", "2", "--master-addr", "127.0.0.1",
+           "--master-port", str(_free_port()), os.path.join(REPO, "tests", "multi_gpu_worker.py")]
+    r = subprocess.run(cmd, cwd=REPO, env=env, capture_output=True, text=True, timeout=600)
+    assert r.returncode == 0 and "MULTI_GPU_OK" in r.stdout, (r.stdout[-3000:], r.stderr[-3000:])
+
+
+@pytest.mark.parametrize("fmt,N,K,M", [("int8", 1536, 576, 1), ("q4", 512, 1024, 8), ("fp16", 1024, 512, 48)])
+def test_single_rank_gather_is_linear(nnb, ctx, fmt, N, K, M):
+    comm = nnb.Comm(ctx, None, 0, 1)
+    try:
+        W, s = make_weight(fmt, N, K, 31)
+        x = make_x(M, K, 32)
+        qw = nnb.QuantWeight(ctx, fmt, W, s)
+        dx = ctx.upload(x.view(np.uint16))
+        g = comm.symm_alloc(M * N * 2)
+        comm.linear_gather(M, N, K, dx, qw.buf, g)
+        got = ctx.download(g, (M, N), np.uint16).view(np.float16)
+        out = ctx.alloc(M * N * 2)
+        ctx.linear(M, N, K, dx, qw.buf, out)
+        ref = ctx.download(out, (M, N), np.uint16).view(np.float16)
+        assert np.array_equal(got.view(np.uint16), ref.view(np.uint16))
+        assert cpu.rel_l2(got, cpu.linear(fmt, x, W, s, order=2)) <= TOL
+        qw.release()
+        ctx.free(dx)
+        ctx.free(out)
+    finally:
+        ctx.sync()
+        comm.close()
+
+
+def test_gather_rejects_foreign_buffer(nnb, ctx):
+    comm = nnb.Comm(ctx, None, 0, 1)
+    try:
+        g = comm.symm_alloc(4096)
+        plain = ctx.alloc(4096)
+        W, _ = make_weight("fp16", 128, 64, 1)
+        dw = ctx.upload(W.view(np.uint16))
+        dx = ctx.upload(make_x(1, 64, 2).view(np.uint16))
+        with pytest.raises(nnb.NNError):
+            comm.linear_gather(1, 128, 64, dx, dw, plain)          # not a symmetric buffer
+        with pytest.raises(nnb.NNError):
+            comm.linear_gather(64, 128, 64, dx, dw, g)             # 64 * 128 * 2 bytes > 4096
+        for b in (plain, dw, dx):
+            ctx.free(b)
+    finally:
+        ctx.sync()
+        comm.close()
+
+
+def test_wait_that_nothing_signals_times_out_and_context_survives(nnb, ctx):
+    """A wait whose flag is never written must return after its limit, report NN_ERR_TIMEOUT
+    through nn_sync, and leave the context usable."""
+    comm = nnb.Comm(ctx, None, 0, 1)
+    try:
+        comm.symm_alloc(256)
+        comm.wait(timeout_ms=50)            # no signal has been sent: the flag stays at 0
+        with pytest.raises(nnb.NNError) as ei:
+            ctx.sync()
+        assert ei.value.code == nnb.NN_ERR_TIMEOUT
+        # the context still works, and a matched signal / wait pair passes
+        comm.signal()                       # brings the sent count level with the wait count
+        comm.signal()
+        comm.wait(timeout_ms=1000)
+        ctx.sync()
+        W, _ = make_weight("fp16", 256, 128, 5)
+        x = make_x(1, 128, 6)
+        dw, dx, out = ctx.upload(W.view(np.uint16)), ctx.upload(x.view(np.uint16)), ctx.alloc(512)
+        ctx.linear(1, 256, 128, dx, dw, out)
+        got = ctx.download(out, (1, 256), np.uint16).view(np.float16)
+        assert cpu.rel_l2(got, cpu.linear("fp16", x, W, None, order=2)) <= TOL
+        for b in (dw, dx, out):
+            ctx.free(b)
+    finally:
+        comm.close()
