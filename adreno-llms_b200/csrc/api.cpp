@@ -79,6 +79,12 @@ extern "C" int nn_init(int device, nn_context** out) {
         delete c;
         return NN_FAIL(NN_ERR_CUDA, "nn_init: cudaMalloc failed");
     }
+    if (cudaMalloc((void**)&c->sk_scratch, SK_SCRATCH_BYTES) != cudaSuccess ||
+        cudaMalloc((void**)&c->sk_flags, SK_MAX_BLOCKS * sizeof(unsigned)) != cudaSuccess ||
+        cudaMemset(c->sk_flags, 0, SK_MAX_BLOCKS * sizeof(unsigned)) != cudaSuccess) {
+        delete c;
+        return NN_FAIL(NN_ERR_CUDA, "nn_init: cudaMalloc failed");
+    }
     if ((e = stream_configure()) != cudaSuccess) {
         delete c;
         return NN_FAIL(NN_ERR_CUDA, "nn_init: kernel configuration failed: %s", cudaGetErrorString(e));
@@ -96,6 +102,8 @@ extern "C" int nn_shutdown(nn_context* c) {
     if (c->gemm_scratch) cudaFree(c->gemm_scratch);
     if (c->flush_buf) cudaFree(c->flush_buf);
     if (c->argmax_slot) cudaFree(c->argmax_slot);
+    if (c->sk_scratch) cudaFree(c->sk_scratch);
+    if (c->sk_flags) cudaFree(c->sk_flags);
     if (c->status_host) cudaFreeHost(c->status_host);
     cudaStreamDestroy(c->stream);
     delete c;
@@ -271,7 +279,7 @@ static int run_gemm_tc(nn_context* c, int fmt, const LinArgs& a, int M, const ch
         Wh = (const uint16_t*)c->gemm_scratch;
         if (fmt == FMT_INT8) row_scale = sg.scale;
     }
-    cudaError_t e = launch_gemm_tc(Wh, row_scale, a.x, sg.out, M, sg.N, a.K, sg.ld_out, a.epi, a.status, a.peer_out, a.npeer, c->stream);
+    cudaError_t e = launch_gemm_tc(Wh, row_scale, a.x, sg.out, M, sg.N, a.K, sg.ld_out, a.epi, a.status, a.peer_out, a.npeer, &a.sig, c->stream);
     if (e != cudaSuccess) return NN_FAIL(NN_ERR_CUDA, "%s: tensor-core launch failed: %s (M=%d N=%d K=%d)", who, cudaGetErrorString(e), M, sg.N, a.K);
     c->launches++;
     *done = true;
@@ -279,6 +287,8 @@ static int run_gemm_tc(nn_context* c, int fmt, const LinArgs& a, int M, const ch
 }
 
 static int run_linear(nn_context* c, int fmt, LinArgs a, int M_total, const char* who) {
+    a.sk_scratch = c->sk_scratch;
+    a.sk_flags = c->sk_flags;
     if (M_total > 16) {
         bool done = false;
         const int rc = run_gemm_tc(c, fmt, a, M_total, who, &done);
@@ -289,7 +299,10 @@ static int run_linear(nn_context* c, int fmt, LinArgs a, int M_total, const char
     uint16_t* out0[3] = {a.seg[0].out, a.seg[1].out, a.seg[2].out};
     uint16_t* peer0[7];
     for (int p = 0; p < 7; ++p) peer0[p] = a.peer_out[p];
+    const GatherSignal sig0 = a.sig;
     for (int m0 = 0; m0 < M_total; m0 += 16) {
+        a.sig = sig0;
+        if (m0 + 16 < M_total) a.sig.world = 0;  // the last slice sends the gather's signal
         a.M = M_total - m0 < 16 ? M_total - m0 : 16;
         a.x = x0 + (size_t)m0 * a.K;
         for (int i = 0; i < a.nseg; ++i) a.seg[i].out = out0[i] + (size_t)m0 * a.seg[i].ld_out;
@@ -318,7 +331,7 @@ static int check_common(nn_context* c, int M, int N, int K, const void* x, const
 }
 
 static int one_weight(nn_context* c, int M, int N, int K, nn_buf x, nn_buf W, nn_buf out, int epi, const char* who,
-                      uint16_t* const* peers = nullptr, int npeer = 0) {
+                      uint16_t* const* peers = nullptr, int npeer = 0, const GatherSignal* sig = nullptr) {
     int rc = check_common(c, M, N, K, x, W, out, who);
     if (rc) return rc;
     if (M == 0) return NN_OK;
@@ -341,12 +354,13 @@ static int one_weight(nn_context* c, int M, int N, int K, nn_buf x, nn_buf W, nn
     if (npeer < 0 || npeer > 7) return NN_FAIL(NN_ERR_ARG, "%s: %d peers", who, npeer);
     a.npeer = npeer;
     for (int p = 0; p < npeer; ++p) a.peer_out[p] = peers[p];
+    if (sig) a.sig = *sig;
     return run_linear(c, r.fmt, a, M, who);
 }
 
 int nnb::linear_to_peers(nn_context* c, int M, int N, int K, nn_buf x, nn_buf W, nn_buf out, uint16_t* const* peers, int npeer,
-                         const char* who) {
-    return one_weight(c, M, N, K, x, W, out, EPI_STORE, who, peers, npeer);
+                         const GatherSignal* sig, const char* who) {
+    return one_weight(c, M, N, K, x, W, out, EPI_STORE, who, peers, npeer, sig);
 }
 
 extern "C" int nn_linear(nn_context* c, int M, int N, int K, nn_buf x, nn_buf W, nn_buf out) {

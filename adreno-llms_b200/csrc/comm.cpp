@@ -212,7 +212,7 @@ extern "C" int nn_comm_signal(nn_comm* c) {
 extern "C" int nn_comm_wait(nn_comm* c, unsigned timeout_ms) {
     if (!c || !c->flags) return NN_FAIL(NN_ERR_ARG, "nn_comm_wait: no symmetric buffer has been allocated on this communicator");
     if (timeout_ms == 0 || timeout_ms > 10000) return NN_FAIL(NN_ERR_ARG, "nn_comm_wait: timeout %u ms outside 1..10000", timeout_ms);
-    COMM_CUDA(nnb::launch_comm_wait(c->flags, c->world, c->epochs + 1, timeout_ms, c->ctx->status_dev, c->ctx->stream));
+    COMM_CUDA(nnb::launch_comm_wait(c->flags, c->world, c->epochs + 1, timeout_ms, c->ctx->status_dev, false, c->ctx->stream));
     c->ctx->launches++;
     return NN_OK;
 }
@@ -231,11 +231,19 @@ extern "C" int nn_linear_gather(nn_comm* c, int M, int n_local, int K, nn_buf x,
     int np = 0;
     for (int g = 0; g < c->world; ++g)
         if (g != c->rank) peers[np++] = (uint16_t*)((char*)sa->base[g] + block * c->rank);
-    int rc = nnb::linear_to_peers(c->ctx, M, n_local, K, x, W, (char*)gathered + block * c->rank, peers, np, "nn_linear_gather");
+    // the projection kernel's last block sends this rank's signal; the wait kernel is launched
+    // so that it is already spinning when that happens
+    nnb::GatherSignal sig = {};
+    sig.world = c->world;
+    sig.rank = c->rank;
+    for (int g = 0; g < c->world; ++g) sig.flags[g] = (unsigned*)c->symm[0].base[g];
+    sig.epoch = c->epochs;
+    sig.done = c->epochs + 2;
+    int rc = nnb::linear_to_peers(c->ctx, M, n_local, K, x, W, (char*)gathered + block * c->rank, peers, np, &sig, "nn_linear_gather");
     if (rc) return rc;
-    rc = nn_comm_signal(c);
-    if (rc) return rc;
-    return nn_comm_wait(c, 2000);
+    COMM_CUDA(nnb::launch_comm_wait(c->flags, c->world, c->epochs + 1, 2000, c->ctx->status_dev, c->ctx->use_pdl, c->ctx->stream));
+    c->ctx->launches++;
+    return NN_OK;
 }
 
 extern "C" int nn_comm_all_gather(nn_comm* c, nn_buf send, nn_buf recv, size_t bytes) {

@@ -31,7 +31,6 @@ __global__ void comm_signal_kernel(PeerFlags pf, unsigned* epoch_sent) {
     }
     __syncthreads();
     // the stores of the kernels before this one in the stream are ordered before the flag
-    __threadfence_system();
     if ((int)threadIdx.x < pf.world) {
         unsigned* dst = pf.flags[threadIdx.x] + pf.rank;
         asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(dst), "r"(e) : "memory");
@@ -51,16 +50,18 @@ __global__ void comm_wait_kernel(const unsigned* my_flags, int world, unsigned* 
         const unsigned* src = my_flags + threadIdx.x;
         for (;;) {
             unsigned v;
-            asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(src) : "memory");
+            asm volatile("ld.relaxed.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(src) : "memory");
             if ((int)(v - e) >= 0) break;
             if (global_ns() - t0 > limit) {
                 *reinterpret_cast<volatile int*>(status) = 7;
                 break;
             }
-            __nanosleep(64);
+            __nanosleep(32);
         }
     }
-    __threadfence_system();
+    // one acquire for all the flags read above: what the signalling ranks stored before their
+    // flags is visible to the kernels that follow in this stream
+    asm volatile("fence.acq_rel.sys;" ::: "memory");
 }
 
 }  // namespace
@@ -70,9 +71,21 @@ cudaError_t launch_comm_signal(const PeerFlags& pf, unsigned* epoch_sent, cudaSt
     return cudaGetLastError();
 }
 
-cudaError_t launch_comm_wait(const unsigned* my_flags, int world, unsigned* epoch_waited, unsigned timeout_ms, int* status, cudaStream_t st) {
-    comm_wait_kernel<<<1, 32, 0, st>>>(my_flags, world, epoch_waited, timeout_ms, status);
-    return cudaGetLastError();
+cudaError_t launch_comm_wait(const unsigned* my_flags, int world, unsigned* epoch_waited, unsigned timeout_ms, int* status, bool overlap,
+                             cudaStream_t st) {
+    // With `overlap` the kernel does not wait for the grid before it (it never executes
+    // griddepcontrol.wait): its own rank's flag, which that grid sets when its last block has
+    // stored and fenced its outputs, is among the flags it spins on.
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(1);
+    cfg.blockDim = dim3(32);
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = overlap ? 1 : 0;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    return cudaLaunchKernelEx(&cfg, comm_wait_kernel, my_flags, world, epoch_waited, timeout_ms, status);
 }
 
 }  // namespace nnb

@@ -55,6 +55,7 @@ struct GemmK {
     int* status;
     uint16_t* peer_out[7];  // the same output block in the other ranks' gather buffers
     int npeer;
+    GatherSignal sig;       // completion signal of the gather (world == 0: none)
 };
 
 // ---- tcgen05 wrappers -------------------------------------------------------------------
@@ -241,6 +242,7 @@ __global__ void __launch_bounds__(GEMM_THREADS) linear_gemm_tc_kernel(const __gr
     tc_fence_before();
     __syncthreads();
     if (warp == 1) tmem_dealloc(tmem_base, (uint32_t)(2 * g.tmem_cols));
+    if (tid == 0 && g.sig.world > 0) gather_signal_block_done(g.sig);
 }
 
 // fp16 copy of a quantised weight for the tensor-core path.
@@ -289,8 +291,10 @@ cudaError_t launch_dequant_half(int fmt, int N, int K, const void* W, const uint
 }
 
 cudaError_t launch_gemm_tc(const uint16_t* W_half, const uint16_t* row_scale, const uint16_t* x, uint16_t* out, int M, int N, int K,
-                           int ld_out, int epi, int* status, uint16_t* const* peer_out, int npeer, cudaStream_t st) {
+                           int ld_out, int epi, int* status, uint16_t* const* peer_out, int npeer, const GatherSignal* sig, cudaStream_t st) {
     GemmK g;
+    g.sig = GatherSignal{};
+    if (sig) g.sig = *sig;
     if (npeer < 0 || npeer > 7) return cudaErrorInvalidValue;
     g.npeer = npeer;
     for (int p = 0; p < 7; ++p) g.peer_out[p] = p < npeer ? peer_out[p] : nullptr;

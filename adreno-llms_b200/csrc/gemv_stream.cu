@@ -27,7 +27,8 @@
 //     (fp32 accumulate) against the activations, which sit in shared memory pre-permuted
 //     so that one ldmatrix yields the B fragment in the packed weight order.
 //     M = 1..8 uses one n8 tile, M = 9..16 two; rows >= M read a zero block.
-//   * Q4 block scales ride along through per-lane cp.async on the same full barrier.
+//   * Q4 block scales ride along on the same full barrier: one dense tensor copy per stage when
+//     the scale rows keep a 16-byte pitch (K a multiple of 256), per-lane cp.async otherwise.
 //   * launched with programmatic dependent launch: the producer never waits for the prior
 //     grid (weights do not depend on activations), so the weight stream of launch i+1
 //     starts under the tail of launch i; only the activation staging waits.
@@ -84,6 +85,8 @@ struct KArgs {
     int rowbytes;
     int nchunks;      // K chunks of kcb bytes per row
     int evict_first;  // weights larger than L2 are streamed with an evict-first policy
+    int scale_tma;    // Q4: block scales arrive by tensor copies (tm_s) instead of per-lane cp.async
+    alignas(64) CUtensorMap tm_s[4];  // Q4 scale views [N][K/16 bytes]: seg[0..2], and scale2
 #ifdef NNB_TRACE
     unsigned long long* trace;  // debug build only: per-warp phase cycle counts
     int trace_slot;
@@ -236,15 +239,31 @@ __global__ void __launch_bounds__(THREADS) linear_stream_kernel(const __grid_con
     if (FMT == FMT_INT8 && tid >= 32 && tid < 48) reinterpret_cast<uint32_t*>(xs + 3 * a.M * geo.xstride)[tid - 32] = 0u;  // per-row max words
     if (tid == 0) {
         for (int s = 0; s < stages; ++s) {
-            mbar_init(full0 + s * 8, FMT == FMT_Q4 ? 1u + NCW * 32u : 1u);
+            mbar_init(full0 + s * 8, (FMT == FMT_Q4 && !ka.scale_tma) ? 1u + NCW * 32u : 1u);
             mbar_init(empty0 + s * 8, (uint32_t)NCW);
         }
         mbar_init_fence();
     }
     __syncthreads();
 
-    const int my_tiles = (int)blockIdx.x < a.ntiles ? (a.ntiles - (int)blockIdx.x + (int)gridDim.x - 1) / (int)gridDim.x : 0;
-    const int n_items = my_tiles * groups;
+    // Pipeline items of this block.  Plain: whole tiles b, b + G, ... .  Balanced: a contiguous
+    // share of the launch's tiles x groups items, which may begin and end inside a tile.
+    const bool sk = a.streamk != 0;
+    const long long sk_total = (long long)a.ntiles * groups;
+    int n_items, tile_first, cg_first;
+    if (sk) {
+        const long long i0 = (long long)blockIdx.x * sk_total / (long long)gridDim.x;
+        const long long i1 = (long long)(blockIdx.x + 1) * sk_total / (long long)gridDim.x;
+        n_items = (int)(i1 - i0);
+        tile_first = (int)(i0 / groups);
+        cg_first = (int)(i0 - (long long)tile_first * groups);
+    } else {
+        const int my_tiles = (int)blockIdx.x < a.ntiles ? (a.ntiles - (int)blockIdx.x + (int)gridDim.x - 1) / (int)gridDim.x : 0;
+        n_items = my_tiles * groups;
+        tile_first = (int)blockIdx.x;
+        cg_first = 0;
+    }
+    const int tile_step = sk ? 1 : (int)gridDim.x;
 
     auto tile_segment = [&](int tile) {
         int si = 0;
@@ -258,9 +277,9 @@ __global__ void __launch_bounds__(THREADS) linear_stream_kernel(const __grid_con
         pdl_launch_dependents();
         if (lane == 0) {
             const uint64_t policy = ka.evict_first ? l2_policy_evict_first() : l2_policy_evict_normal();
-            int ti = 0, cg = 0, stage = 0;
+            int tile_s = tile_first, cg = cg_first, stage = 0;
             for (int it = 0; it < n_items; ++it) {
-                const int tile = (int)blockIdx.x + ti * (int)gridDim.x;
+                const int tile = tile_s;
                 if (it >= stages && !mbar_wait_bounded(empty0 + stage * 8, (uint32_t)(((it / stages) - 1) & 1))) {
                     *reinterpret_cast<volatile int*>(a.status) = 2;
                     break;
@@ -272,7 +291,18 @@ __global__ void __launch_bounds__(THREADS) linear_stream_kernel(const __grid_con
                     // one copy per 128-byte column covers the rows of all four consumers
                     const int cb = min(kcb, rowbytes - cg * kcb);
                     const int nb = (cb + 127) >> 7;
-                    mbar_arrive_expect_tx(bar, (uint32_t)(nb * CTA_BOX));
+                    const bool stma = FMT == FMT_Q4 && ka.scale_tma;
+                    const int bw = kcb / 8;  // bytes of block scales per row and stage
+                    mbar_arrive_expect_tx(bar, (uint32_t)(nb * CTA_BOX + (stma ? NCW * WARP_ROWS * bw : 0)));
+                    if (stma) {
+                        const uint32_t sdst = dst + geo.nbox * CTA_BOX;
+                        if (DUAL) {
+                            tma_load_2d(sdst, &ka.tm_s[0], cg * bw, row0, bar, policy);
+                            tma_load_2d(sdst + (NCW * WARP_ROWS / 2) * bw, &ka.tm_s[3], cg * bw, row0, bar, policy);
+                        } else {
+                            tma_load_2d(sdst, &ka.tm_s[sg], cg * bw, row0, bar, policy);
+                        }
+                    }
                     for (int b = 0; b < nb; ++b) {
                         const int x = cg * kcb + b * 128;
                         if (DUAL) {
@@ -284,15 +314,26 @@ __global__ void __launch_bounds__(THREADS) linear_stream_kernel(const __grid_con
                     }
                 } else {
                     // the consumers take consecutive K chunks of the same rows
+                    const bool stma = FMT == FMT_Q4 && ka.scale_tma;
+                    const int bw = kcb / 8;
                     uint32_t bytes = 0;
                     for (int w = 0; w < NCW; ++w) {
                         const int c = cg * NCW + w;
-                        if (c < nchunks) bytes += (uint32_t)(((min(kcb, rowbytes - c * kcb) + 127) >> 7) * BOX_BYTES);
+                        if (c < nchunks) bytes += (uint32_t)(((min(kcb, rowbytes - c * kcb) + 127) >> 7) * BOX_BYTES + (stma ? WARP_ROWS * bw : 0));
                     }
                     mbar_arrive_expect_tx(bar, bytes);
                     for (int w = 0; w < NCW; ++w) {
                         const int c = cg * NCW + w;
                         if (c >= nchunks) break;
+                        if (stma) {
+                            const uint32_t sdst = dst + geo.nbox * CTA_BOX;
+                            if (DUAL) {
+                                tma_load_2d(sdst + w * (WARP_ROWS / 2) * bw, &ka.tm_s[0], c * bw, row0, bar, policy);
+                                tma_load_2d(sdst + (NCW * WARP_ROWS / 2 + w * (WARP_ROWS / 2)) * bw, &ka.tm_s[3], c * bw, row0, bar, policy);
+                            } else {
+                                tma_load_2d(sdst + w * WARP_ROWS * bw, &ka.tm_s[sg], c * bw, row0, bar, policy);
+                            }
+                        }
                         const int nb = (min(kcb, rowbytes - c * kcb) + 127) >> 7;
                         for (int b = 0; b < nb; ++b) {
                             const int x = c * kcb + b * 128;
@@ -305,7 +346,7 @@ __global__ void __launch_bounds__(THREADS) linear_stream_kernel(const __grid_con
                         }
                     }
                 }
-                if (++cg == groups) { cg = 0; ++ti; }
+                if (++cg == groups) { cg = 0; tile_s += tile_step; }
                 if (++stage == stages) stage = 0;
             }
         }
@@ -373,8 +414,8 @@ __global__ void __launch_bounds__(THREADS) linear_stream_kernel(const __grid_con
     // Q4: this lane's row of block scales for pipeline item `j` travels by cp.async and
     // arrives on the stage's full barrier (every lane arrives for every item).
     auto issue_scales = [&](int j) {
-        const int ti = j / groups, cg = j - ti * groups;
-        const int tile = (int)blockIdx.x + ti * (int)gridDim.x;
+        const int lin = cg_first + j, ti = lin / groups, cg = lin - ti * groups;
+        const int tile = tile_first + ti * tile_step;
         const int c = ksplit ? cg * NCW + warp : cg;
         const int stage = j % stages;
         const uint32_t bar = full0 + stage * 8;
@@ -420,11 +461,11 @@ __global__ void __launch_bounds__(THREADS) linear_stream_kernel(const __grid_con
                     }
     };
 
-    if (FMT == FMT_Q4) {
+    if (FMT == FMT_Q4 && !ka.scale_tma) {
         const int pre = min(stages - 1, n_items);
         for (int j = 0; j < pre; ++j) issue_scales(j);
     }
-    if (my_tiles > 0 && writer) prefetch_scales((int)blockIdx.x);
+    if (n_items > 0 && writer) prefetch_scales(tile_first);
 
 #ifdef NNB_TRACE
     const long long tl_entry = clock64();
@@ -434,7 +475,7 @@ __global__ void __launch_bounds__(THREADS) linear_stream_kernel(const __grid_con
 #ifdef NNB_TRACE
     const long long tl_wait = clock64();
 #endif
-    if (my_tiles > 0 && writer) prefetch_residual((int)blockIdx.x);
+    if (n_items > 0 && writer) prefetch_residual(tile_first);
     if (FMT == FMT_INT8) stage_x_int8(a.x, a.M, a.K, xs, geo.xstride, tid, NCW * 32);
     else stage_x<FMT>(a.x, a.M, a.K, xs, geo.xstride, tid, NCW * 32);
     asm volatile("bar.sync 1, %0;" ::"n"(NCW * 32) : "memory");
@@ -444,7 +485,7 @@ __global__ void __launch_bounds__(THREADS) linear_stream_kernel(const __grid_con
 #endif
 
 #ifdef NNB_TRACE
-    long long cyc_wait = 0, cyc_comp = 0, cyc_t0 = clock64(), cyc_a, cyc_b;
+    long long cyc_wait = 0, cyc_comp = 0, cyc_iss = 0, cyc_t0 = clock64(), cyc_a, cyc_b;
 #define CYC_BEGIN() cyc_a = clock64()
 #define CYC_END(acc_) do { cyc_b = clock64(); acc_ += cyc_b - cyc_a; cyc_a = cyc_b; } while (0)
 #else
@@ -452,13 +493,15 @@ __global__ void __launch_bounds__(THREADS) linear_stream_kernel(const __grid_con
 #define CYC_END(acc_) do { } while (0)
 #endif
 
-    int ti = 0, cg = 0, stage = 0;
+    int tile_s = tile_first, cg = cg_first, ti = 0, stage = 0;
     uint32_t phase = 0;
+    bool seg_has_head = true;  // the running sums began at the first K item of their tile
     for (int it = 0; it < n_items; ++it) {
-        const int tile = (int)blockIdx.x + ti * (int)gridDim.x;
+        const int tile = tile_s;
         const int c = ksplit ? cg * NCW + warp : cg;
         const bool active = c < nchunks;
-        if (cg == 0) {
+        if (cg == 0 || it == 0) {
+            seg_has_head = (cg == 0);
 #pragma unroll
             for (int u = 0; u < 2; ++u)
 #pragma unroll
@@ -477,16 +520,17 @@ __global__ void __launch_bounds__(THREADS) linear_stream_kernel(const __grid_con
 #pragma unroll
                             for (int i = 0; i < 4; ++i) iacc[l % (FMT == FMT_INT8 ? 3 : 1)][rb][nt][i] = 0;
             }
-            if (writer) {
-                if (ti > 0) prefetch_scales(tile);
-                if (ti > 0) prefetch_residual(tile);
+            if (writer && it > 0) {
+                prefetch_scales(tile);
+                prefetch_residual(tile);
             }
         }
-        if (FMT == FMT_Q4) {
+        CYC_BEGIN();
+        if (FMT == FMT_Q4 && !ka.scale_tma) {
             __syncwarp();  // every lane is done with the scale rows that are about to be refilled
             if (it + stages - 1 < n_items) issue_scales(it + stages - 1);
         }
-        CYC_BEGIN();
+        CYC_END(cyc_iss);
         // A wait that runs out records an error and skips the arithmetic from then on;
         // the warp still walks its items so that the block's barriers stay matched.
         if (!failed && !mbar_wait_bounded(full0 + stage * 8, phase)) {
@@ -559,7 +603,14 @@ __global__ void __launch_bounds__(THREADS) linear_stream_kernel(const __grid_con
         } else {
             // one step = 16 bytes of each row = one 32-weight block = two MMAs per row block,
             // summed from zero and folded in with the block's scale
-            const uint8_t* sc = smem + (sw - s_base) + geo.nbox * CTA_BOX + warp * WARP_ROWS * geo.sstride;
+            // scale rows of this warp's two row blocks inside the stage's scale region: the
+            // cp.async path keeps each warp's 32 rows together; tensor copies land whole boxes,
+            // which for two weights means all gate rows first, then all up rows
+            const int sstr = ka.scale_tma ? kcb / 8 : geo.sstride;
+            const int srow0 = (ka.scale_tma && DUAL) ? warp * (WARP_ROWS / 2) : warp * WARP_ROWS;
+            const int srow1 = (ka.scale_tma && DUAL) ? NCW * WARP_ROWS / 2 + warp * (WARP_ROWS / 2) : warp * WARP_ROWS + 16;
+            const uint8_t* scb = smem + (sw - s_base) + geo.nbox * CTA_BOX;
+            const uint8_t* sc_rb[2] = {scb + (srow0 + g) * sstr, scb + (srow1 + g) * sstr};
             const int g0 = (c * kcb) / 16;
             auto step = [&](int s, float (&ac)[2][NT][4]) {
                 uint32_t b[NT][4];
@@ -572,8 +623,8 @@ __global__ void __launch_bounds__(THREADS) linear_stream_kernel(const __grid_con
                     uint32_t p04, p15, p26, p37, q04, q15, q26, q37;
                     q4x8_to_half2x4(w[rb * 2], p04, p15, p26, p37);
                     q4x8_to_half2x4(w[rb * 2 + 1], q04, q15, q26, q37);
-                    const float s_lo = __half2float(__ushort_as_half(*reinterpret_cast<const uint16_t*>(sc + (rb * 16 + g) * geo.sstride + (s - g0) * 2)));
-                    const float s_hi = __half2float(__ushort_as_half(*reinterpret_cast<const uint16_t*>(sc + (rb * 16 + g + 8) * geo.sstride + (s - g0) * 2)));
+                    const float s_lo = __half2float(__ushort_as_half(*reinterpret_cast<const uint16_t*>(sc_rb[rb] + (s - g0) * 2)));
+                    const float s_hi = __half2float(__ushort_as_half(*reinterpret_cast<const uint16_t*>(sc_rb[rb] + 8 * sstr + (s - g0) * 2)));
 #pragma unroll
                     for (int nt = 0; nt < NT; ++nt) {
                         float d[4] = {0.f, 0.f, 0.f, 0.f};
@@ -608,9 +659,11 @@ __global__ void __launch_bounds__(THREADS) linear_stream_kernel(const __grid_con
         __syncwarp();
         if (lane == 0) mbar_arrive(empty0 + stage * 8);
         if (++stage == stages) { stage = 0; phase ^= 1u; }
-        const bool tile_done = (cg == groups - 1);
-        if (++cg == groups) { cg = 0; ++ti; }
-        if (!tile_done) continue;
+        const bool has_tail = (cg == groups - 1);              // this item ends its tile
+        const bool seg_end = has_tail || it == n_items - 1;    // ... or this block's share of it
+        if (++cg == groups) { cg = 0; tile_s += tile_step; }
+        if (!seg_end) continue;
+        ++ti;
 
         if (FMT == FMT_INT8) {
             // recombine the limb sums: (hi * 2^16 + mid * 2^8 + lo) * 2^-p, in fp32
@@ -657,6 +710,58 @@ __global__ void __launch_bounds__(THREADS) linear_stream_kernel(const __grid_con
                         for (int nt = 0; nt < NT; ++nt)
 #pragma unroll
                             for (int i = 0; i < 4; ++i) acc[0][rb][nt][i] += o[(rb * NT + nt) * 4 + i];
+                }
+            }
+        }
+        if (sk && !(seg_has_head && has_tail)) {
+            float* part = a.sk_scratch + ((size_t)blockIdx.x * (NCW * 32) + (size_t)(warp * 32 + lane)) * (2 * NT * 4);
+            if (!seg_has_head) {
+                // the tile began in an earlier block: hand the sums over to it
+                if (writer) {
+#pragma unroll
+                    for (int rb = 0; rb < 2; ++rb)
+#pragma unroll
+                        for (int nt = 0; nt < NT; ++nt)
+                            *reinterpret_cast<float4*>(part + (rb * NT + nt) * 4) =
+                                make_float4(acc[0][rb][nt][0], acc[0][rb][nt][1], acc[0][rb][nt][2], acc[0][rb][nt][3]);
+                }
+                __threadfence();
+                asm volatile("bar.sync 1, %0;" ::"n"(NCW * 32) : "memory");
+                if (tid == 0) asm volatile("st.release.gpu.global.u32 [%0], %1;" ::"l"(a.sk_flags + blockIdx.x), "r"(1u) : "memory");
+                continue;
+            }
+            // this block owns the tile but not its last K items: add the partial sums of the
+            // blocks that follow, in block order (they produce theirs first thing)
+            const long long tile_end = (long long)(tile + 1) * groups;
+            for (int nb = (int)blockIdx.x + 1; nb < (int)gridDim.x; ++nb) {
+                if ((long long)nb * sk_total / (long long)gridDim.x >= tile_end) break;
+                if (tid == 0 && !failed) {
+                    const long long t0 = clock64();
+                    for (;;) {
+                        unsigned v;
+                        asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(a.sk_flags + nb) : "memory");
+                        if (v) break;
+                        if (clock64() - t0 > 400000000ll) {
+                            *reinterpret_cast<volatile int*>(a.status) = 8;
+                            break;
+                        }
+                        __nanosleep(40);
+                    }
+                    a.sk_flags[nb] = 0u;  // consumed; the flag is clear again for the next launch
+                }
+                asm volatile("bar.sync 1, %0;" ::"n"(NCW * 32) : "memory");
+                if (writer) {
+                    const float* o = a.sk_scratch + ((size_t)nb * (NCW * 32) + (size_t)(warp * 32 + lane)) * (2 * NT * 4);
+#pragma unroll
+                    for (int rb = 0; rb < 2; ++rb)
+#pragma unroll
+                        for (int nt = 0; nt < NT; ++nt) {
+                            const float4 v = __ldcg(reinterpret_cast<const float4*>(o + (rb * NT + nt) * 4));
+                            acc[0][rb][nt][0] += v.x;
+                            acc[0][rb][nt][1] += v.y;
+                            acc[0][rb][nt][2] += v.z;
+                            acc[0][rb][nt][3] += v.w;
+                        }
                 }
             }
         }
@@ -710,6 +815,11 @@ __global__ void __launch_bounds__(THREADS) linear_stream_kernel(const __grid_con
                 }
         }
     }
+    if (a.sig.world > 0) {
+        // row-sharded gather: all of this block's outputs are stored; count the block in
+        asm volatile("bar.sync 1, %0;" ::"n"(NCW * 32) : "memory");
+        if (tid == 0) gather_signal_block_done(a.sig);
+    }
 #ifdef NNB_TRACE
     if (ka.trace && lane == 0 && blockIdx.x < 32) {
         unsigned long long* o = ka.trace + ((size_t)ka.trace_slot * 32 + blockIdx.x) * 8 * 8 + warp * 8;
@@ -718,7 +828,7 @@ __global__ void __launch_bounds__(THREADS) linear_stream_kernel(const __grid_con
             tl[0] = tl_wait - tl_entry; tl[1] = tl_x - tl_wait; tl[2] = tl_full - tl_x; tl[3] = tl_comp - tl_full;
             tl[4] = clock64() - tl_comp; tl[5] = tl_entry - cyc_t0;
         }
-        o[0] = 0; o[1] = cyc_wait; o[2] = cyc_comp; o[3] = (clock64() - cyc_t0) - cyc_wait - cyc_comp; o[4] = n_items; o[5] = clock64() - cyc_t0;
+        o[0] = cyc_iss; o[1] = cyc_wait; o[2] = cyc_comp; o[3] = (clock64() - cyc_t0) - cyc_wait - cyc_comp - cyc_iss; o[4] = n_items; o[5] = clock64() - cyc_t0;
     }
 #endif
 }
@@ -763,6 +873,18 @@ bool make_weight_map(CUtensorMap* m, const void* W, int rows, int rowbytes, int 
     const cuuint32_t estr[2] = {1u, 1u};
     return g_encode_tiled(m, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(W), dims, strides, box, estr,
                           CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                          CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+// 2-D byte view of a Q4 scale tensor: [rows][rowbytes], dense box of box_bytes x box_rows.
+bool make_scale_map(CUtensorMap* m, const void* S, int rows, int rowbytes, int box_bytes, int box_rows) {
+    if (!g_encode_tiled || box_bytes % 16 || box_bytes > 256 || box_rows > 256) return false;
+    const cuuint64_t dims[2] = {(cuuint64_t)rowbytes, (cuuint64_t)rows};
+    const cuuint64_t strides[1] = {(cuuint64_t)rowbytes};
+    const cuuint32_t box[2] = {(cuuint32_t)box_bytes, (cuuint32_t)box_rows};
+    const cuuint32_t estr[2] = {1u, 1u};
+    return g_encode_tiled(m, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(S), dims, strides, box, estr,
+                          CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
                           CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
@@ -864,9 +986,12 @@ StreamPlan stream_plan(int fmt, const LinArgs& a, int sm_count, size_t smem_limi
     // deep as its item count, so that the whole operator is in flight after the first request.
     int stages = env_int("NNB_STAGES", 0), per_sm = 0;
     const int cap = env_int("NNB_CTAS", 0);
-    for (int ps = (cap == 1 ? 1 : 2); ps >= 1 && !per_sm; --ps) {
+    int ps_first = env_int("NNB_PS", 0);
+    if (ps_first < 1 || ps_first > 4) ps_first = 2;
+    if (cap == 1) ps_first = 1;
+    for (int ps = ps_first; ps >= 1 && !per_sm; --ps) {
         const size_t budget = (smem_limit + 1024) / ps - 1024;
-        int st = stages >= 2 && stages <= 8 ? stages : (ps == 2 ? 4 : 6);
+        int st = stages >= 2 && stages <= 8 ? stages : (ps >= 2 ? 4 : 6);
         while (st > 2 && (size_t)make_geo(fmt, M, K, kcb, st, nt).total > budget) --st;
         if ((size_t)make_geo(fmt, M, K, kcb, st, nt).total > budget) continue;
         if (!(stages >= 2 && stages <= 8)) {
@@ -885,6 +1010,26 @@ StreamPlan stream_plan(int fmt, const LinArgs& a, int sm_count, size_t smem_limi
     const int waves = (ntiles + resident - 1) / resident;
     p.grid = waves > 0 ? (ntiles + waves - 1) / waves : 1;
     if (p.grid < 1) p.grid = 1;
+    // Whole tiles leave SMs idle when the tile count is an awkward multiple of the SM count
+    // (224 tiles on 148 SMs: some SMs run two blocks, some one).  For operators large enough
+    // that the fix-up's latency does not matter, deal the items out evenly instead.
+    {
+        size_t wbytes = 0;
+        for (int i = 0; i < a.nseg; ++i) wbytes += (size_t)a.seg[i].N * rb;
+        const int sm_blocks = (p.grid + sm_count - 1) / sm_count;
+        const double plain_eff = (double)ntiles / ((double)sm_count * sm_blocks * (waves > 0 ? waves : 1));
+        const long long total = (long long)ntiles * groups;
+        const long long per_block = (total + resident - 1) / resident;
+        const double sk_eff = (double)total / ((double)resident * (double)per_block);
+        int want = env_int("NNB_SK", -1);
+        // (measured: it pays for the instruction-bound Q4 kernel with long rows; the int8 and fp16
+        // kernels are HBM-bound, idle SM slots cost them nothing and the fix-up only adds latency)
+        if (want < 0) want = (fmt == FMT_Q4 && wbytes >= ((size_t)8 << 20) && plain_eff < 0.9 && sk_eff > plain_eff + 0.05 && per_block >= 8) ? 1 : 0;
+        if (want && a.sk_scratch && a.sk_flags && resident <= SK_MAX_BLOCKS && total >= resident) {
+            p.streamk = true;
+            p.grid = resident;
+        }
+    }
     p.kcb = kcb;
     p.kw = kw;
     p.warps = NCW;
@@ -900,6 +1045,7 @@ cudaError_t launch_stream(int fmt, const LinArgs& a, const StreamPlan& p, cudaSt
     ka.a.kcb = p.kcb;
     ka.a.kw = p.kw;
     ka.a.ntiles = p.ntiles;
+    ka.a.streamk = p.streamk ? 1 : 0;
     ka.stages = p.stages;
     ka.rowbytes = fmt_row_bytes(fmt, a.K);
     ka.nchunks = (ka.rowbytes + p.kcb - 1) / p.kcb;
@@ -917,6 +1063,18 @@ cudaError_t launch_stream(int fmt, const LinArgs& a, const StreamPlan& p, cudaSt
         if (!make_weight_map(&ka.tm[i], a.seg[i].W, a.seg[i].N, ka.rowbytes, tile_rows)) return cudaErrorInvalidValue;
     }
     if (dual && !make_weight_map(&ka.tm[3], a.W2, a.seg[0].N, ka.rowbytes, tile_rows)) return cudaErrorInvalidValue;
+    // Q4 block scales by tensor copy: the scale rows (K / 16 bytes each) must keep 16-byte
+    // pitch and alignment; otherwise the consumers fetch them with cp.async
+    ka.scale_tma = 0;
+    if (fmt == FMT_Q4 && a.K % 256 == 0 && env_int("NNB_SCALE_TMA", 1) != 0) {
+        bool ok = true;
+        for (int i = 0; i < a.nseg; ++i) ok = ok && (reinterpret_cast<uintptr_t>(a.seg[i].scale) & 15) == 0;
+        if (dual) ok = ok && (reinterpret_cast<uintptr_t>(a.scale2) & 15) == 0;
+        const int srow = a.K / 16, bw = p.kcb / 8;
+        for (int i = 0; ok && i < a.nseg; ++i) ok = make_scale_map(&ka.tm_s[i], a.seg[i].scale, a.seg[i].N, srow, bw, tile_rows);
+        if (ok && dual) ok = make_scale_map(&ka.tm_s[3], a.scale2, a.seg[0].N, srow, bw, tile_rows);
+        ka.scale_tma = ok ? 1 : 0;
+    }
 #ifdef NNB_TRACE
     ka.trace = g_trace;
     ka.trace_slot = g_trace_slots ? (g_trace_next++ % g_trace_slots) : 0;

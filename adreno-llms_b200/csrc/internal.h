@@ -23,6 +23,8 @@ struct nn_context {
     unsigned long long* argmax_slot = nullptr;
     void* gemm_scratch = nullptr;  // fp16 copy of a quantised weight for the tensor-core path
     size_t gemm_scratch_bytes = 0;
+    float* sk_scratch = nullptr;   // partial sums of blocks that share a tile (balanced K-streaming)
+    unsigned* sk_flags = nullptr;
     void* flush_buf = nullptr;
     size_t flush_bytes = 0;
     bool use_pdl = true;
@@ -39,9 +41,11 @@ struct ResolvedW {
 };
 bool resolve_weight(const nn_context* c, const void* W, int K, ResolvedW* out);
 
-// nn_linear that also stores every output at the same offset of `npeer` peer-mapped buffers
-// (the row-sharded gather); api.cpp
-int linear_to_peers(nn_context* c, int M, int N, int K, void* x, void* W, void* out, uint16_t* const* peers, int npeer, const char* who);
+// nn_linear that also stores every output at the same offset of `npeer` peer-mapped buffers and,
+// with `sig`, sends the gather's completion signal from the (last) kernel itself; api.cpp
+struct GatherSignal;
+int linear_to_peers(nn_context* c, int M, int N, int K, void* x, void* W, void* out, uint16_t* const* peers, int npeer,
+                    const GatherSignal* sig, const char* who);
 
 int fail(int code, const char* file, int line, const char* fmt, ...) __attribute__((format(printf, 4, 5)));
 

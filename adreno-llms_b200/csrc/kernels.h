@@ -17,6 +17,15 @@ enum Epi : int {
     EPI_SILU_GATE = 3,  // out = half(out * sigmoid(out) * acc)       (in place)
 };
 
+// Completion signal of a row-sharded gather, sent by the projection kernel itself: the last
+// block to finish publishes the next epoch number in word `rank` of every rank's flag array.
+struct GatherSignal {
+    unsigned* flags[8];  // flags[g] = rank g's flag array (peer-mapped for g != rank)
+    unsigned* epoch;     // local: signals sent so far
+    unsigned* done;      // local: blocks of the current launch that have finished (returns to 0)
+    int world, rank;     // world == 0: no signal
+};
+
 struct LinSeg {
     const uint8_t* W;       // [N, rowbytes] row-major, on-disk layout
     const uint16_t* scale;  // int8: [N]; Q4: [N, K/32]; fp16: null
@@ -44,6 +53,13 @@ struct LinArgs {
     // (peer-mapped device pointers); every stored value is also written there
     uint16_t* peer_out[7];
     int npeer;
+    GatherSignal sig;
+    // balanced K-streaming: block b takes pipeline items [b T / G, (b+1) T / G) of the launch's
+    // T = tiles x K-groups items, so a tile may be shared by neighbouring blocks; the block that
+    // holds the head of a tile adds the others' fp32 partial sums (fixed order) and stores it
+    float* sk_scratch;    // [blocks][consumer threads][2 * NT * 4] partial sums
+    unsigned* sk_flags;   // [blocks] "partial written", consumed and cleared by the tile's owner
+    int streamk;
 };
 
 struct StreamPlan {  // launch geometry chosen on the host
@@ -55,9 +71,12 @@ struct StreamPlan {  // launch geometry chosen on the host
     int ntiles;  // block tiles over all segments
     size_t smem;
     bool ok;
+    bool streamk;  // items are dealt out evenly across the grid instead of whole tiles
 };
 
 // gemv_stream.cu
+constexpr int SK_MAX_BLOCKS = 148 * 4;                      // grid limit of a balanced launch
+constexpr size_t SK_SCRATCH_BYTES = (size_t)SK_MAX_BLOCKS * 128 * 16 * sizeof(float);
 bool stream_supported(int fmt, int M, int K, const LinArgs& a);
 StreamPlan stream_plan(int fmt, const LinArgs& a, int sm_count, size_t smem_limit);
 cudaError_t launch_stream(int fmt, const LinArgs& a, const StreamPlan& p, cudaStream_t st, bool pdl);
@@ -73,7 +92,7 @@ cudaError_t gemm_tc_configure();
 bool gemm_tc_supported(int M, int N, int K, const void* x, const void* W, const void* out);
 cudaError_t launch_dequant_half(int fmt, int N, int K, const void* W, const uint16_t* scale, uint16_t* out, cudaStream_t st);
 cudaError_t launch_gemm_tc(const uint16_t* W_half, const uint16_t* row_scale, const uint16_t* x, uint16_t* out, int M, int N, int K,
-                           int ld_out, int epi, int* status, uint16_t* const* peer_out, int npeer, cudaStream_t st);
+                           int ld_out, int epi, int* status, uint16_t* const* peer_out, int npeer, const GatherSignal* sig, cudaStream_t st);
 
 // gemv_generic.cu: any K, any alignment (the reference's gemv_rT_fp32acc role)
 cudaError_t launch_generic(int fmt, const LinArgs& a, cudaStream_t st);
@@ -84,7 +103,10 @@ struct PeerFlags {
     int world, rank;
 };
 cudaError_t launch_comm_signal(const PeerFlags& pf, unsigned* epoch_sent, cudaStream_t st);
-cudaError_t launch_comm_wait(const unsigned* my_flags, int world, unsigned* epoch_waited, unsigned timeout_ms, int* status, cudaStream_t st);
+// `overlap`: launch with programmatic stream serialisation so that the wait starts spinning while
+// the kernel before it still runs (valid when that kernel sends this rank's own signal).
+cudaError_t launch_comm_wait(const unsigned* my_flags, int world, unsigned* epoch_waited, unsigned timeout_ms, int* status, bool overlap,
+                             cudaStream_t st);
 
 // misc.cu
 cudaError_t launch_dequant(int fmt, int N, int K, const void* W, const uint16_t* scale, float* out, cudaStream_t st);

@@ -5,6 +5,8 @@
 #include <cuda_fp16.h>
 #include <stdint.h>
 
+#include "kernels.h"
+
 namespace nnb {
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
@@ -157,6 +159,26 @@ __device__ __forceinline__ void q4x8_to_half2x4(uint32_t w, uint32_t& p04, uint3
     p15 = *reinterpret_cast<uint32_t*>(&r1);
     p26 = *reinterpret_cast<uint32_t*>(&r2);
     p37 = *reinterpret_cast<uint32_t*>(&r3);
+}
+
+// Called by one thread of every block after a barrier that covers the block's output stores
+// (kernels.h: GatherSignal).  Every block orders its stores, local and to peers, before its
+// count with a device-scope fence; the block that completes the count publishes the epoch with
+// one system-scope release, which is cumulative over what the counts it observed had ordered.
+// System-scope fences cost microseconds each, so there is exactly one on this path.
+__device__ __forceinline__ void gather_signal_block_done(const nnb::GatherSignal& s) {
+    __threadfence();
+    const unsigned prev = atomicAdd(s.done, 1u);
+    if (prev == gridDim.x - 1u) {
+        *reinterpret_cast<volatile unsigned*>(s.done) = 0u;
+        const unsigned e = *reinterpret_cast<volatile unsigned*>(s.epoch) + 1u;
+        *reinterpret_cast<volatile unsigned*>(s.epoch) = e;
+        asm volatile("fence.acq_rel.sys;" ::: "memory");
+        for (int g = 0; g < s.world; ++g) {
+            unsigned* dst = s.flags[g] + s.rank;
+            asm volatile("st.relaxed.sys.global.u32 [%0], %1;" ::"l"(dst), "r"(e) : "memory");
+        }
+    }
 }
 
 }  // namespace nnb

@@ -19,8 +19,13 @@ from . import synth
 
 class DecodeStep:
     def __init__(self, ctx, shape: synth.ModelShape, fmt: str, M: int = 1, n_sets: int = 1, seed: int = 1235,
-                 vocab_rows=None, keep_host=False, only=None):
+                 vocab_rows=None, keep_host=False, only=None, comm=None):
         self.ctx, self.shape, self.fmt, self.M = ctx, shape, fmt, M
+        # with a communicator the lm_head rows are this rank's shard and the projection
+        # stores into every rank's gather buffer (one buffer per weight set, so that
+        # consecutive steps never share one)
+        self.comm = comm
+        self.gathered = [comm.symm_alloc(M * shape.vocab * 2) for _ in range(n_sets)] if comm else None
         self.vocab_lo, self.vocab_n = vocab_rows if vocab_rows else (0, shape.vocab)
         rng = np.random.default_rng(seed)
         H, F = shape.hidden, shape.ffn
@@ -87,10 +92,15 @@ class DecodeStep:
                 c.fused_gate_up_silu(M, sh.ffn, sh.hidden, self.x_h, w[0], w[1], self.act)
             elif kind == "down_add":
                 c.linear_add(M, sh.hidden, sh.ffn, self.x_act, w[0], self.resid)
+            elif self.comm:
+                self.comm.linear_gather(M, self.vocab_n, sh.hidden, self.x_h, w[0], self.gathered[set_index])
             else:
                 c.linear(M, self.vocab_n, sh.hidden, self.x_h, w[0], self.logits)
         if with_argmax and M == 1:
-            c.argmax(self.vocab_n, self.logits, self.token)
+            if self.comm:   # [G][1][V/G] is the full logits vector
+                c.argmax(sh.vocab, self.gathered[set_index], self.token)
+            else:
+                c.argmax(self.vocab_n, self.logits, self.token)
 
     def record(self, with_argmax=True):
         """Record one plan per weight set (the reference's recorded-queue replay)."""

@@ -41,6 +41,21 @@ METRIC = "int8/Q4 GEMV achieved HBM GB/s (decode-step projection set)"
 UNIT = "GB/s"
 
 
+class StdoutToStderr:
+    """Send file descriptor 1 to stderr for a while: NCCL prints its version banner on stdout
+    when a communicator is first made, and the bench prints exactly one JSON line there."""
+
+    def __enter__(self):
+        sys.stdout.flush()
+        self.saved = os.dup(1)
+        os.dup2(2, 1)
+
+    def __exit__(self, *a):
+        sys.stdout.flush()
+        os.dup2(self.saved, 1)
+        os.close(self.saved)
+
+
 def load_pkg():
     name = "adreno_llms_b200"
     if name in sys.modules:
@@ -275,26 +290,49 @@ def sharded_projections(pkg, ctx, synth, comm, rank, world, dist, reps=12):
         t_lin = t_ag = 0.0
         for i in range(reps + 2):
             ctx.l2_flush()
+            if comm:   # line the ranks up on the device before the timed launches
+                comm.signal()
+                comm.wait()
             ctx.record(ev[0])
             ctx.linear(M, n, K, x, qw.buf, mine)
             ctx.record(ev[1])
             if comm:
-                pkg._check(ctx.L.nn_comm_all_gather(comm, mine, gathered, M * n * 2))
+                comm.all_gather(mine, gathered, M * n * 2)
             ctx.record(ev[2])
             ctx.sync()
             if i >= 2:
                 t_lin += ctx.elapsed_ms(ev[0], ev[1])
                 t_ag += ctx.elapsed_ms(ev[1], ev[2])
-        t = [t_lin / reps * 1e3, t_ag / reps * 1e3]
+        t_fused = 0.0
+        if comm:
+            sym = [comm.symm_alloc(M * N * 2) for _ in range(2)]
+            for i in range(reps + 2):
+                ctx.l2_flush()
+                comm.signal()
+                comm.wait()
+                ctx.record(ev[0])
+                comm.linear_gather(M, n, K, x, qw.buf, sym[i & 1])
+                ctx.record(ev[1])
+                ctx.sync()
+                if i >= 2:
+                    t_fused += ctx.elapsed_ms(ev[0], ev[1])
+            if dist:
+                dist.barrier()
+            for b in sym:
+                comm.symm_free(b)
+        else:
+            t_fused = t_lin + t_ag
+        t = [t_lin / reps * 1e3, t_ag / reps * 1e3, t_fused / reps * 1e3]
         if dist:
             import torch
             tt = torch.tensor(t, dtype=torch.float64)
             dist.all_reduce(tt, op=dist.ReduceOp.MAX)
             t = tt.tolist()
         b = synth.linear_bytes(fmt, N, K, M)
-        rows.append({"fmt": fmt, "N": N, "K": K, "M": M, "rows_per_rank": n, "linear_us": t[0], "all_gather_us": t[1],
-                     "gbps_aggregate": b / ((t[0] + t[1]) * 1e-6) / 1e9,
-                     "tflops_aggregate": 2.0 * M * N * K / ((t[0] + t[1]) * 1e-6) / 1e12})
+        rows.append({"fmt": fmt, "N": N, "K": K, "M": M, "rows_per_rank": n, "linear_us": t[0], "nccl_all_gather_us": t[1],
+                     "fused_gather_us": t[2],   # projection with peer stores + flag exchange, one call
+                     "gbps_aggregate": b / (t[2] * 1e-6) / 1e9,
+                     "tflops_aggregate": 2.0 * M * N * K / (t[2] * 1e-6) / 1e12})
         for e in ev:
             ctx.L.nn_event_destroy(e)
         ctx.free(gathered)
@@ -343,22 +381,17 @@ def main():
     step_bytes_full = sum(synth.linear_bytes(fmt, n, k, 1) for kind, _, ws in synth.decode_step_ops(shape)
                           if args.only in (None, kind) for n, k in ws)
     n_sets = min(64, max(2, math.ceil(2.0 * l2_bytes / step_bytes_full) + 1))
-    step = dstep.DecodeStep(ctx, shape, fmt, M=1, n_sets=n_sets, vocab_rows=(rank * vrows, vrows), only=args.only)
-
-    comm, gathered = None, None
+    comm = None
     if world > 1:
         import torch
         idbuf = torch.zeros(128, dtype=torch.uint8)
         if rank == 0:
-            raw = (128 * __import__("ctypes").c_ubyte)()
-            pkg._check(ctx.L.nn_comm_unique_id(raw))
-            idbuf = torch.tensor(list(raw), dtype=torch.uint8)
+            idbuf = torch.tensor(list(pkg.Comm.unique_id()), dtype=torch.uint8)
         dist.broadcast(idbuf, 0)
-        raw = (__import__("ctypes").c_ubyte * 128)(*idbuf.tolist())
-        h = __import__("ctypes").c_void_p()
-        pkg._check(ctx.L.nn_comm_init(ctx.h, raw, rank, world, __import__("ctypes").byref(h)))
-        comm = h
-        gathered = ctx.alloc(shape.vocab * 2)
+        with StdoutToStderr():
+            comm = pkg.Comm(ctx, bytes(idbuf.tolist()), rank, world)
+            comm.symm_free(comm.symm_alloc(256))   # first collective on the communicator
+    step = dstep.DecodeStep(ctx, shape, fmt, M=1, n_sets=n_sets, vocab_rows=(rank * vrows, vrows), only=args.only, comm=comm)
 
     def barrier():
         ctx.sync()
@@ -366,12 +399,11 @@ def main():
             dist.barrier()
 
     def enqueue_step(i, with_argmax=True):
-        """One step: recorded plan of the projections (+ all-gather of the logits shards)."""
+        """One step: the recorded plan of the projections.  With several ranks the lm_head
+        kernel of each rank stores its rows into every rank's gather buffer."""
         step.launch(i % n_sets)
-        if comm:
-            pkg._check(ctx.L.nn_comm_all_gather(comm, step.logits, gathered, vrows * 2))
 
-    kernels_per_step = step.record(with_argmax=(world == 1 and args.only is None))
+    kernels_per_step = step.record(with_argmax=(args.only is None))
     for i in range(args.warmup):
         enqueue_step(i)
     barrier()
@@ -399,11 +431,11 @@ def main():
     hl = pkg.load().nn_host_alloc(shape.vocab * 2)
     import ctypes
     ctypes.memmove(hx, synth.activations(1, shape.hidden, np.random.default_rng(5)).ctypes.data, shape.hidden * 2)
-    out_buf = gathered if comm else step.logits
 
     def e2e_step(i):
         pkg._check(ctx.L.nn_buf_write(ctx.h, step.x_h, 0, hx, shape.hidden * 2))
         enqueue_step(i)
+        out_buf = step.gathered[i % n_sets] if comm else step.logits
         pkg._check(ctx.L.nn_buf_read(ctx.h, hl, out_buf, 0, shape.vocab * 2))
         ctx.sync()
 
@@ -445,6 +477,8 @@ def main():
                     ctx.fused_gate_up_silu(M, sh.ffn, sh.hidden, step.x_h, w[0], w[1], step.act)
                 elif kind == "down_add":
                     ctx.linear_add(M, sh.hidden, sh.ffn, step.x_act, w[0], step.resid)
+                elif comm:
+                    comm.linear_gather(M, step.vocab_n, sh.hidden, step.x_h, w[0], step.gathered[i % n_sets])
                 else:
                     ctx.linear(M, step.vocab_n, sh.hidden, step.x_h, w[0], step.logits)
         # replayed from recorded plans (one per weight copy), like the step itself
@@ -490,7 +524,8 @@ def main():
                        "algorithmic_bytes_per_step": step_bytes_full,
                        "l2": f"{n_sets} resident weight copies rotated step to step "
                              f"({n_sets * step.weight_bytes / 1e6:.0f} MB > L2 {l2_bytes / 1e6:.0f} MB)",
-                       "sharding": "none" if world == 1 else f"lm_head rows / {world} ranks + NCCL all-gather; layers replicated"},
+                       "sharding": "none" if world == 1 else f"lm_head rows / {world} ranks, each rank's kernel stores into every rank's "
+                                                                    "gather buffer over NVLink peer memory; layers replicated"},
             "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": shape.hidden * 2,
                     "d2h_bytes_per_step": shape.vocab * 2, "us_per_step": e2e_s / e2e_steps * 1e6, "steps": e2e_steps},
             "gpu_launches": launches,

@@ -82,7 +82,9 @@ def test_batched_decode(nnb, ctx, fmt, M):
     check_close(got, want, what=f"{fmt} M={M}")
     # row m of the batch equals the M = 1 call on row m
     one = run_linear(nnb, ctx, fmt, W, s, x[M - 1:M], N, K)
-    check_close(got[M - 1:M], one, tol=2e-4, what="batch row vs single")
+    # (above 16 rows a Q4 weight goes to the tensor cores as fp16(code * scale), one rounding of
+    # 2^-12 per weight that the M <= 16 kernel, which scales exact block sums, does not make)
+    check_close(got[M - 1:M], one, tol=5e-4 if (fmt == "q4" and M > 16) else 2e-4, what="batch row vs single")
 
 
 @pytest.mark.parametrize("fmt", FMTS)
