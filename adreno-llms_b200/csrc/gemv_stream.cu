@@ -58,7 +58,7 @@ struct Geo {  // shared-memory geometry, computed identically on host and device
     int sstride;      // bytes between Q4 scale rows in a stage
     int stage_bytes;  // one stage (multiple of 1024)
     int xstride;      // bytes between activation rows
-    int off_bar, off_x, off_red, off_ring;
+    int off_bar, off_x, off_ctab, off_red, off_ring;
     int total;
 };
 
@@ -72,7 +72,10 @@ __host__ __device__ inline Geo make_geo(int fmt, int M, int K, int kcb, int stag
     g.xstride = fmt == FMT_INT8 ? K + 16 : K * 2 + 16;
     g.off_bar = 64;  // full[stages], empty[stages]
     g.off_x = HDR_BYTES + ((stages * 16 + 127) / 128) * 128;
-    g.off_red = g.off_x + (((fmt == FMT_INT8 ? 3 * M * g.xstride + 192 : M * g.xstride) + 127) / 128) * 128;
+    // Q4: per 32-weight block and token pair one float4 (c0, c1, c0, c1) with c = -72 * (sum of
+    // the block's activations), the value the block's accumulator starts from
+    g.off_ctab = g.off_x + (((fmt == FMT_INT8 ? 3 * M * g.xstride + 192 : M * g.xstride) + 127) / 128) * 128;
+    g.off_red = g.off_ctab + (fmt == FMT_Q4 ? (K / 32) * ((M + 1) / 2) * 16 : 0);
     g.off_ring = ((g.off_red + 2 * NCW * 32 * 2 * nt * 4 * 4 + 1023) / 1024) * 1024;  // two reduction buffers
     g.total = g.off_ring + stages * g.stage_bytes + 1024;  // slack to align the ring to 1 KB
     return g;
@@ -185,7 +188,7 @@ __device__ __forceinline__ void stage_x_int8(const uint16_t* __restrict__ x, int
 //   fp16: identity
 //   Q4  : per 32 k   -> piece j, pair t = (k 8t+j, k 8t+j+4)
 template <int FMT>
-__device__ __forceinline__ void stage_x(const uint16_t* __restrict__ x, int M, int K, uint8_t* xs, int xstride, int tid,
+__device__ __forceinline__ void stage_x(const uint16_t* __restrict__ x, int M, int K, uint8_t* xs, int xstride, float* ctab, int tid,
                                         int nthreads) {
     if (FMT == FMT_FP16) {
         const int per_row = K / 8;  // 16-byte pieces
@@ -200,9 +203,17 @@ __device__ __forceinline__ void stage_x(const uint16_t* __restrict__ x, int M, i
             const int m = i / per_row, p = i - m * per_row;
             const uint4* src = reinterpret_cast<const uint4*>(x + (size_t)m * K + p * 32);
             uint32_t o[4][4];
+            float bsum = 0.f;
 #pragma unroll
             for (int t = 0; t < 4; ++t) {
                 const uint4 v = src[t];  // k 8t .. 8t+7 as pairs (0,1)(2,3)(4,5)(6,7)
+                const uint32_t vv[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+                for (int q = 0; q < 4; ++q) {
+                    const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&vv[q]));
+                    bsum += f.x;
+                    bsum += f.y;
+                }
                 o[0][t] = __byte_perm(v.x, v.z, 0x5410);  // (k0, k4)
                 o[1][t] = __byte_perm(v.x, v.z, 0x7632);  // (k1, k5)
                 o[2][t] = __byte_perm(v.y, v.w, 0x5410);  // (k2, k6)
@@ -211,6 +222,15 @@ __device__ __forceinline__ void stage_x(const uint16_t* __restrict__ x, int M, i
 #pragma unroll
             for (int j = 0; j < 4; ++j)
                 *reinterpret_cast<uint4*>(xs + m * xstride + p * 64 + j * 16) = make_uint4(o[j][0], o[j][1], o[j][2], o[j][3]);
+            // accumulator start of block p, token m: (c0, c1, c0, c1) per token pair
+            float* cq = ctab + ((size_t)p * ((M + 1) / 2) + (m >> 1)) * 4 + (m & 1);
+            const float nc = -Q4_BIAS * bsum;
+            cq[0] = nc;
+            cq[2] = nc;
+            if (m == M - 1 && !(m & 1)) {  // odd token count: the pair's second column is unused
+                cq[1] = 0.f;
+                cq[3] = 0.f;
+            }
         }
     }
 }
@@ -377,6 +397,12 @@ __global__ void __launch_bounds__(THREADS) linear_stream_kernel(const __grid_con
         b_step[nt] = valid ? 64u : 0u;
         b_plane[nt] = (FMT == FMT_INT8 && valid) ? (uint32_t)(a.M * geo.xstride) : 0u;
     }
+    // Q4: this lane's accumulator-start quads (token pair t of each n tile), one per 32-weight block
+    const int npair = (a.M + 1) / 2;
+    const int ctab_step = npair * 16;
+    const uint8_t* ctab_lane[NT];
+#pragma unroll
+    for (int nt = 0; nt < NT; ++nt) ctab_lane[nt] = smem + geo.off_ctab + min(t + 4 * nt, npair - 1) * 16;
     const float* rowscale = reinterpret_cast<const float*>(xs + 3 * a.M * geo.xstride + 64);
 
     // rows of this warp inside its tile, and which warp writes results
@@ -477,7 +503,7 @@ __global__ void __launch_bounds__(THREADS) linear_stream_kernel(const __grid_con
 #endif
     if (n_items > 0 && writer) prefetch_residual(tile_first);
     if (FMT == FMT_INT8) stage_x_int8(a.x, a.M, a.K, xs, geo.xstride, tid, NCW * 32);
-    else stage_x<FMT>(a.x, a.M, a.K, xs, geo.xstride, tid, NCW * 32);
+    else stage_x<FMT>(a.x, a.M, a.K, xs, geo.xstride, reinterpret_cast<float*>(smem + geo.off_ctab), tid, NCW * 32);
     asm volatile("bar.sync 1, %0;" ::"n"(NCW * 32) : "memory");
 #ifdef NNB_TRACE
     const long long tl_x = clock64();
@@ -485,7 +511,7 @@ __global__ void __launch_bounds__(THREADS) linear_stream_kernel(const __grid_con
 #endif
 
 #ifdef NNB_TRACE
-    long long cyc_wait = 0, cyc_comp = 0, cyc_iss = 0, cyc_t0 = clock64(), cyc_a, cyc_b;
+    long long cyc_wait = 0, cyc_comp = 0, cyc_iss = 0, cyc_rel = 0, cyc_epi = 0, cyc_t0 = clock64(), cyc_a, cyc_b;
 #define CYC_BEGIN() cyc_a = clock64()
 #define CYC_END(acc_) do { cyc_b = clock64(); acc_ += cyc_b - cyc_a; cyc_a = cyc_b; } while (0)
 #else
@@ -601,8 +627,9 @@ __global__ void __launch_bounds__(THREADS) linear_stream_kernel(const __grid_con
                 }
             }
         } else {
-            // one step = 16 bytes of each row = one 32-weight block = two MMAs per row block,
-            // summed from zero and folded in with the block's scale
+            // one step = 16 bytes of each row = one 32-weight block = two MMAs per row block on
+            // the biased codes (64 + nibble), started from -72 * sum(x) of the block so that the
+            // result is sum((nibble - 8) x), then folded in with the block's scale
             // scale rows of this warp's two row blocks inside the stage's scale region: the
             // cp.async path keeps each warp's 32 rows together; tensor copies land whole boxes,
             // which for two weights means all gate rows first, then all up rows
@@ -614,21 +641,25 @@ __global__ void __launch_bounds__(THREADS) linear_stream_kernel(const __grid_con
             const int g0 = (c * kcb) / 16;
             auto step = [&](int s, float (&ac)[2][NT][4]) {
                 uint32_t b[NT][4];
+                float4 cq[NT];
 #pragma unroll
-                for (int nt = 0; nt < NT; ++nt) ldsm_x4(b_base[nt] + s * b_step[nt], b[nt][0], b[nt][1], b[nt][2], b[nt][3]);
+                for (int nt = 0; nt < NT; ++nt) {
+                    ldsm_x4(b_base[nt] + s * b_step[nt], b[nt][0], b[nt][1], b[nt][2], b[nt][3]);
+                    cq[nt] = *reinterpret_cast<const float4*>(ctab_lane[nt] + (size_t)s * ctab_step);
+                }
                 uint32_t w[4];
                 ldsm_x4(piece_addr(sw, aq_off, (uint32_t)(s - g0)), w[0], w[1], w[2], w[3]);
 #pragma unroll
                 for (int rb = 0; rb < 2; ++rb) {
                     uint32_t p04, p15, p26, p37, q04, q15, q26, q37;
-                    q4x8_to_half2x4(w[rb * 2], p04, p15, p26, p37);
-                    q4x8_to_half2x4(w[rb * 2 + 1], q04, q15, q26, q37);
+                    q4x8_to_half2x4_biased(w[rb * 2], p04, p15, p26, p37);
+                    q4x8_to_half2x4_biased(w[rb * 2 + 1], q04, q15, q26, q37);
                     const float s_lo = __half2float(__ushort_as_half(*reinterpret_cast<const uint16_t*>(sc_rb[rb] + (s - g0) * 2)));
                     const float s_hi = __half2float(__ushort_as_half(*reinterpret_cast<const uint16_t*>(sc_rb[rb] + 8 * sstr + (s - g0) * 2)));
 #pragma unroll
                     for (int nt = 0; nt < NT; ++nt) {
-                        float d[4] = {0.f, 0.f, 0.f, 0.f};
-                        mma_16816(d, p04, q04, p15, q15, b[nt][0], b[nt][1]);
+                        float d[4];
+                        mma_16816_c(d, p04, q04, p15, q15, b[nt][0], b[nt][1], cq[nt]);  // starts at -72 * sum(x)
                         mma_16816(d, p26, q26, p37, q37, b[nt][2], b[nt][3]);
                         ac[rb][nt][0] = fmaf(d[0], s_lo, ac[rb][nt][0]);
                         ac[rb][nt][1] = fmaf(d[1], s_lo, ac[rb][nt][1]);
@@ -658,6 +689,7 @@ __global__ void __launch_bounds__(THREADS) linear_stream_kernel(const __grid_con
         // hand the stage back to the producer
         __syncwarp();
         if (lane == 0) mbar_arrive(empty0 + stage * 8);
+        CYC_END(cyc_rel);
         if (++stage == stages) { stage = 0; phase ^= 1u; }
         const bool has_tail = (cg == groups - 1);              // this item ends its tile
         const bool seg_end = has_tail || it == n_items - 1;    // ... or this block's share of it
@@ -828,7 +860,7 @@ __global__ void __launch_bounds__(THREADS) linear_stream_kernel(const __grid_con
             tl[0] = tl_wait - tl_entry; tl[1] = tl_x - tl_wait; tl[2] = tl_full - tl_x; tl[3] = tl_comp - tl_full;
             tl[4] = clock64() - tl_comp; tl[5] = tl_entry - cyc_t0;
         }
-        o[0] = cyc_iss; o[1] = cyc_wait; o[2] = cyc_comp; o[3] = (clock64() - cyc_t0) - cyc_wait - cyc_comp - cyc_iss; o[4] = n_items; o[5] = clock64() - cyc_t0;
+        o[0] = cyc_iss; o[6] = cyc_rel; o[1] = cyc_wait; o[2] = cyc_comp; o[3] = (clock64() - cyc_t0) - cyc_wait - cyc_comp - cyc_iss - cyc_rel; o[4] = n_items; o[5] = clock64() - cyc_t0;
     }
 #endif
 }

@@ -106,6 +106,15 @@ __device__ __forceinline__ void mma_16816(float (&d)[4], uint32_t a0, uint32_t a
         : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
 
+// D = A * B + C with C in registers of its own (the accumulator starts from a given value)
+__device__ __forceinline__ void mma_16816_c(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1,
+                                            const float4& c) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%11,%12,%13};"
+        : "=f"(d[0]), "=f"(d[1]), "=f"(d[2]), "=f"(d[3])
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "f"(c.x), "f"(c.y), "f"(c.z), "f"(c.w));
+}
+
 // D(16x8,s32) += A(16x32,s8,row) * B(32x8,col); B is signed or unsigned 8-bit
 template <bool B_SIGNED>
 __device__ __forceinline__ void imma_16832(int (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
@@ -159,6 +168,20 @@ __device__ __forceinline__ void q4x8_to_half2x4(uint32_t w, uint32_t& p04, uint3
     p15 = *reinterpret_cast<uint32_t*>(&r1);
     p26 = *reinterpret_cast<uint32_t*>(&r2);
     p37 = *reinterpret_cast<uint32_t*>(&r3);
+}
+
+// 8 nibbles in one word -> four half2 of (64 + nibble), exact, paired as
+// (n0,n4) (n1,n5) (n2,n6) (n3,n7): each nibble is moved to mantissa bits 4..7 of 64.0h.
+// The common offset 64 + 8 is taken out of the 32-weight block sum afterwards
+// (sum (64 + n) x - 72 sum x = sum (n - 8) x), so no subtraction is spent per weight.
+constexpr float Q4_BIAS = 72.0f;
+__device__ __forceinline__ void q4x8_to_half2x4_biased(uint32_t w, uint32_t& p04, uint32_t& p15, uint32_t& p26, uint32_t& p37) {
+    const uint32_t MASK = 0x00F000F0u, MAGIC = 0x54005400u;  // 64.0h in both lanes
+    const uint32_t wl4 = w << 4, wr4 = w >> 4, wr8 = w >> 8;
+    asm("lop3.b32 %0, %1, %2, %3, 0xEA;" : "=r"(p04) : "r"(wl4), "r"(MASK), "r"(MAGIC));
+    asm("lop3.b32 %0, %1, %2, %3, 0xEA;" : "=r"(p15) : "r"(w), "r"(MASK), "r"(MAGIC));
+    asm("lop3.b32 %0, %1, %2, %3, 0xEA;" : "=r"(p26) : "r"(wr4), "r"(MASK), "r"(MAGIC));
+    asm("lop3.b32 %0, %1, %2, %3, 0xEA;" : "=r"(p37) : "r"(wr8), "r"(MASK), "r"(MAGIC));
 }
 
 // Called by one thread of every block after a barrier that covers the block's output stores
