@@ -66,6 +66,7 @@ def load():
         "nn_linear_qkv": ([vp, i, i, vp, vp, i, vp, i, vp, i, vp, vp, vp], i),
         "nn_dequant": ([vp, i, i, vp, vp], i), "nn_argmax": ([vp, i, vp, vp], i),
         "nn_argmax_static": ([vp, i, vp, vp], i),
+        "nn_linear_argmax": ([vp, i, i, vp, vp, vp, vp], i),
         "nn_plan_begin": ([vp], i), "nn_plan_end": ([vp, pvp], i), "nn_plan_launch": ([vp, vp], i),
         "nn_plan_num_kernels": ([vp], i), "nn_plan_free": ([vp], i),
         "nn_weights_load": ([vp, cp, cp, pvp], i), "nn_weights_free": ([vp], i),
@@ -185,6 +186,9 @@ class Context:
 
     def argmax(self, n, logits, out_idx):
         _check(self.L.nn_argmax(self.h, n, logits, out_idx))
+
+    def linear_argmax(self, N, K, x, W, logits, out_idx):
+        _check(self.L.nn_linear_argmax(self.h, N, K, x, W, logits, out_idx))
 
     def l2_flush(self):
         _check(self.L.nn_l2_flush(self.h))

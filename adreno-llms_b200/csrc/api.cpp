@@ -75,7 +75,8 @@ extern "C" int nn_init(int device, nn_context** out) {
         return NN_FAIL(NN_ERR_CUDA, "nn_init: status word allocation failed");
     }
     *c->status_host = 0;
-    if (cudaMalloc((void**)&c->argmax_slot, 8) != cudaSuccess) {
+    // [0] nn_argmax's reduction word, [1] the fused arg-max's word, [2] its block counter
+    if (cudaMalloc((void**)&c->argmax_slot, 32) != cudaSuccess || cudaMemset(c->argmax_slot, 0, 32) != cudaSuccess) {
         delete c;
         return NN_FAIL(NN_ERR_CUDA, "nn_init: cudaMalloc failed");
     }
@@ -123,6 +124,8 @@ extern "C" int nn_sync(nn_context* c) {
     if (*c->status_host != 0) {
         const int s = *c->status_host;
         *c->status_host = 0;
+        cudaMemsetAsync(c->argmax_slot, 0, 32, c->stream);  // a cut-short launch may have left its words set
+        cudaMemsetAsync(c->sk_flags, 0, SK_MAX_BLOCKS * sizeof(unsigned), c->stream);
         return NN_FAIL(NN_ERR_TIMEOUT, "a device-side bounded wait ran out (status %d); results of the last calls are invalid", s);
     }
     return NN_OK;
@@ -440,6 +443,47 @@ extern "C" int nn_dequant(nn_context* c, int N, int K, nn_buf W, nn_buf out) {
     if (!resolve_weight(c, W, K, &r)) return NN_FAIL(NN_ERR_ARG, "nn_dequant: registration does not match K=%d", K);
     if (r.rows_avail >= 0 && N > r.rows_avail) return NN_FAIL(NN_ERR_ARG, "nn_dequant: N exceeds the registered rows");
     CUDA_TRY(launch_dequant(r.fmt, N, K, W, r.scale, (float*)out, c->stream));
+    c->launches++;
+    return NN_OK;
+}
+
+extern "C" int nn_linear_argmax(nn_context* c, int N, int K, nn_buf x, nn_buf W, nn_buf logits, nn_buf out_idx) {
+    int rc = check_common(c, 1, N, K, x, W, out_idx, "nn_linear_argmax");
+    if (rc) return rc;
+    ResolvedW r;
+    if (!resolve_weight(c, W, K, &r))
+        return NN_FAIL(NN_ERR_ARG, "nn_linear_argmax: W points into a registered quantised weight but K=%d or the row offset does not match", K);
+    if (r.rows_avail >= 0 && N > r.rows_avail)
+        return NN_FAIL(NN_ERR_ARG, "nn_linear_argmax: N=%d exceeds the %d rows registered for this weight", N, r.rows_avail);
+    LinArgs a = {};
+    a.nseg = 1;
+    a.seg[0].W = (const uint8_t*)W;
+    a.seg[0].scale = r.scale;
+    a.seg[0].out = (uint16_t*)logits;
+    a.seg[0].N = N;
+    a.seg[0].ld_out = N;
+    a.x = (const uint16_t*)x;
+    a.M = 1;
+    a.K = K;
+    a.epi = EPI_STORE;
+    a.status = c->status_dev;
+    a.sk_scratch = c->sk_scratch;
+    a.sk_flags = c->sk_flags;
+    StreamPlan p = {};
+    if (stream_supported(r.fmt, 1, K, a)) p = stream_plan(r.fmt, a, c->sm_count, c->smem_limit);
+    if (!p.ok) {
+        // shapes the streaming kernel does not take: projection, then the separate arg-max
+        if (!logits) return NN_FAIL(NN_ERR_UNSUPPORTED, "nn_linear_argmax: this shape (K=%d) needs a logits buffer", K);
+        rc = one_weight(c, 1, N, K, x, W, logits, EPI_STORE, "nn_linear_argmax");
+        if (rc) return rc;
+        return nn_argmax(c, N, logits, out_idx);
+    }
+    a.argmax_slot = c->argmax_slot + 1;
+    a.argmax_done = reinterpret_cast<unsigned*>(c->argmax_slot + 2);
+    a.argmax_out = (int*)out_idx;
+    a.argmax_base = 0;
+    cudaError_t e = launch_stream(r.fmt, a, p, c->stream, c->use_pdl);
+    if (e != cudaSuccess) return NN_FAIL(NN_ERR_CUDA, "nn_linear_argmax: launch failed: %s (N=%d K=%d)", cudaGetErrorString(e), N, K);
     c->launches++;
     return NN_OK;
 }

@@ -88,13 +88,21 @@ struct KArgs {
     int rowbytes;
     int nchunks;      // K chunks of kcb bytes per row
     int evict_first;  // weights larger than L2 are streamed with an evict-first policy
-    int scale_tma;    // Q4: block scales arrive by tensor copies (tm_s) instead of per-lane cp.async
-    alignas(64) CUtensorMap tm_s[4];  // Q4 scale views [N][K/16 bytes]: seg[0..2], and scale2
+    int scale_tma;    // Q4: block scales arrive by tensor copies (KArgsQ4::tm_s) instead of per-lane cp.async
 #ifdef NNB_TRACE
     unsigned long long* trace;  // debug build only: per-warp phase cycle counts
     int trace_slot;
 #endif
 };
+// Only the Q4 kernels carry the scale views: kernel parameters are read by every block of every
+// launch, and the small per-layer operators are launch-latency-bound.
+struct KArgsQ4 : KArgs {
+    alignas(64) CUtensorMap tm_s[4];  // Q4 scale views [N][K/16 bytes]: seg[0..2], and scale2
+};
+template <int FMT> struct KArgsFor { typedef KArgs type; };
+template <> struct KArgsFor<FMT_Q4> { typedef KArgsQ4 type; };
+__device__ __forceinline__ const CUtensorMap* scale_map(const KArgs&, int) { return nullptr; }
+__device__ __forceinline__ const CUtensorMap* scale_map(const KArgsQ4& ka, int i) { return &ka.tm_s[i]; }
 
 // int8 weights are multiplied on the integer tensor-core path, with no conversion of the
 // weights at all: each activation row is turned into 24-bit fixed point
@@ -235,8 +243,12 @@ __device__ __forceinline__ void stage_x(const uint16_t* __restrict__ x, int M, i
     }
 }
 
-template <int FMT, int NT, bool DUAL>
-__global__ void __launch_bounds__(THREADS) linear_stream_kernel(const __grid_constant__ KArgs ka) {
+// EXT: the launch uses one of the rarer features (balanced item dealing, peer stores, the
+// gather signal, the fused arg-max).  The plain instantiation carries none of that code: the
+// per-layer operators are launch-latency-bound and every instruction-cache line their blocks
+// have to fetch shows up in the step time.
+template <int FMT, int NT, bool DUAL, bool EXT>
+__global__ void __launch_bounds__(THREADS) linear_stream_kernel(const __grid_constant__ typename KArgsFor<FMT>::type ka) {
     extern __shared__ __align__(128) uint8_t smem[];
     const LinArgs& a = ka.a;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -268,7 +280,7 @@ __global__ void __launch_bounds__(THREADS) linear_stream_kernel(const __grid_con
 
     // Pipeline items of this block.  Plain: whole tiles b, b + G, ... .  Balanced: a contiguous
     // share of the launch's tiles x groups items, which may begin and end inside a tile.
-    const bool sk = a.streamk != 0;
+    const bool sk = EXT && a.streamk != 0;
     const long long sk_total = (long long)a.ntiles * groups;
     int n_items, tile_first, cg_first;
     if (sk) {
@@ -317,10 +329,10 @@ __global__ void __launch_bounds__(THREADS) linear_stream_kernel(const __grid_con
                     if (stma) {
                         const uint32_t sdst = dst + geo.nbox * CTA_BOX;
                         if (DUAL) {
-                            tma_load_2d(sdst, &ka.tm_s[0], cg * bw, row0, bar, policy);
-                            tma_load_2d(sdst + (NCW * WARP_ROWS / 2) * bw, &ka.tm_s[3], cg * bw, row0, bar, policy);
+                            tma_load_2d(sdst, scale_map(ka, 0), cg * bw, row0, bar, policy);
+                            tma_load_2d(sdst + (NCW * WARP_ROWS / 2) * bw, scale_map(ka, 3), cg * bw, row0, bar, policy);
                         } else {
-                            tma_load_2d(sdst, &ka.tm_s[sg], cg * bw, row0, bar, policy);
+                            tma_load_2d(sdst, scale_map(ka, sg), cg * bw, row0, bar, policy);
                         }
                     }
                     for (int b = 0; b < nb; ++b) {
@@ -348,10 +360,10 @@ __global__ void __launch_bounds__(THREADS) linear_stream_kernel(const __grid_con
                         if (stma) {
                             const uint32_t sdst = dst + geo.nbox * CTA_BOX;
                             if (DUAL) {
-                                tma_load_2d(sdst + w * (WARP_ROWS / 2) * bw, &ka.tm_s[0], c * bw, row0, bar, policy);
-                                tma_load_2d(sdst + (NCW * WARP_ROWS / 2 + w * (WARP_ROWS / 2)) * bw, &ka.tm_s[3], c * bw, row0, bar, policy);
+                                tma_load_2d(sdst + w * (WARP_ROWS / 2) * bw, scale_map(ka, 0), c * bw, row0, bar, policy);
+                                tma_load_2d(sdst + (NCW * WARP_ROWS / 2 + w * (WARP_ROWS / 2)) * bw, scale_map(ka, 3), c * bw, row0, bar, policy);
                             } else {
-                                tma_load_2d(sdst + w * WARP_ROWS * bw, &ka.tm_s[sg], c * bw, row0, bar, policy);
+                                tma_load_2d(sdst + w * WARP_ROWS * bw, scale_map(ka, sg), c * bw, row0, bar, policy);
                             }
                         }
                         const int nb = (min(kcb, rowbytes - c * kcb) + 127) >> 7;
@@ -416,6 +428,7 @@ __global__ void __launch_bounds__(THREADS) linear_stream_kernel(const __grid_con
     uint16_t sc_reg[2][2];          // int8: row scales of the current tile (rows g, g+8 of each block)
     uint32_t res_reg[2][2][NT][2];  // in-place epilogues: the values to be updated
     bool failed = false;
+    unsigned long long am_best = 0ull;  // fused arg-max: best key among this thread's rows
 
     // Per-row scales do not depend on the previous launch: fetch them ahead of use.
     auto prefetch_scales = [&](int tile) {
@@ -841,13 +854,39 @@ __global__ void __launch_bounds__(THREADS) linear_stream_kernel(const __grid_con
                                 v = gt * (1.0f / (1.0f + expf(-gt))) * v;
                             }
                             const uint16_t hv = __half_as_ushort(__float2half_rn(v));
-                            sg.out[(size_t)m * sg.ld_out + n] = hv;
-                            for (int p = 0; p < a.npeer; ++p) a.peer_out[p][(size_t)m * sg.ld_out + n] = hv;
+                            if (!EXT || sg.out) sg.out[(size_t)m * sg.ld_out + n] = hv;
+                            if (EXT)
+                                for (int p = 0; p < a.npeer; ++p) a.peer_out[p][(size_t)m * sg.ld_out + n] = hv;
+                            if (EXT && a.argmax_slot && m == 0 && (hv & 0x7FFFu) <= 0x7C00u) {  // NaNs never win
+                                const unsigned long long key = argmax_key_half(hv, a.argmax_base + n);
+                                am_best = key > am_best ? key : am_best;
+                            }
                         }
                 }
         }
     }
-    if (a.sig.world > 0) {
+    if (EXT && a.argmax_slot) {
+        // fused arg-max: one atomic per warp, then the last block to finish publishes the index
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            const unsigned long long other = __shfl_xor_sync(0xffffffffu, am_best, o);
+            am_best = other > am_best ? other : am_best;
+        }
+        if (lane == 0 && am_best) atomicMax(a.argmax_slot, am_best);
+        __threadfence();
+        asm volatile("bar.sync 1, %0;" ::"n"(NCW * 32) : "memory");
+        if (tid == 0) {
+            const unsigned prev = atomicAdd(a.argmax_done, 1u);
+            if (prev == gridDim.x - 1u) {
+                __threadfence();
+                const unsigned long long k = *reinterpret_cast<volatile unsigned long long*>(a.argmax_slot);
+                *a.argmax_out = k ? (int)(0xFFFFFFFFu - (unsigned int)(k & 0xFFFFFFFFull)) : -1;
+                *reinterpret_cast<volatile unsigned long long*>(a.argmax_slot) = 0ull;
+                *reinterpret_cast<volatile unsigned*>(a.argmax_done) = 0u;
+            }
+        }
+    }
+    if (EXT && a.sig.world > 0) {
         // row-sharded gather: all of this block's outputs are stored; count the block in
         asm volatile("bar.sync 1, %0;" ::"n"(NCW * 32) : "memory");
         if (tid == 0) gather_signal_block_done(a.sig);
@@ -865,9 +904,9 @@ __global__ void __launch_bounds__(THREADS) linear_stream_kernel(const __grid_con
 #endif
 }
 
-template <int FMT, int NT, bool DUAL>
-cudaError_t launch_t(const KArgs& ka, const StreamPlan& p, cudaStream_t st, bool pdl) {
-    auto kern = linear_stream_kernel<FMT, NT, DUAL>;
+template <int FMT, int NT, bool DUAL, bool EXT>
+cudaError_t launch_e(const typename KArgsFor<FMT>::type& ka, const StreamPlan& p, cudaStream_t st, bool pdl) {
+    auto kern = linear_stream_kernel<FMT, NT, DUAL, EXT>;
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3((unsigned)p.grid);
     cfg.blockDim = dim3((unsigned)THREADS);
@@ -879,6 +918,13 @@ cudaError_t launch_t(const KArgs& ka, const StreamPlan& p, cudaStream_t st, bool
     cfg.attrs = attr;
     cfg.numAttrs = 1;
     return cudaLaunchKernelEx(&cfg, kern, ka);
+}
+
+template <int FMT, int NT, bool DUAL>
+cudaError_t launch_t(const typename KArgsFor<FMT>::type& ka, const StreamPlan& p, cudaStream_t st, bool pdl) {
+    const LinArgs& a = ka.a;
+    const bool ext = a.streamk || a.npeer > 0 || a.sig.world > 0 || a.argmax_slot != nullptr || a.seg[0].out == nullptr;
+    return ext ? launch_e<FMT, NT, DUAL, true>(ka, p, st, pdl) : launch_e<FMT, NT, DUAL, false>(ka, p, st, pdl);
 }
 
 int env_int(const char* name, int dflt) {
@@ -922,7 +968,9 @@ bool make_scale_map(CUtensorMap* m, const void* S, int rows, int rowbytes, int b
 
 template <int FMT, int NT, bool DUAL>
 cudaError_t configure_one() {
-    return cudaFuncSetAttribute(linear_stream_kernel<FMT, NT, DUAL>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+    cudaError_t e = cudaFuncSetAttribute(linear_stream_kernel<FMT, NT, DUAL, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+    if (e != cudaSuccess) return e;
+    return cudaFuncSetAttribute(linear_stream_kernel<FMT, NT, DUAL, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
 }
 
 int count_tiles(const LinArgs& a, int tile_rows) {
@@ -1072,7 +1120,7 @@ StreamPlan stream_plan(int fmt, const LinArgs& a, int sm_count, size_t smem_limi
 }
 
 cudaError_t launch_stream(int fmt, const LinArgs& a, const StreamPlan& p, cudaStream_t st, bool pdl) {
-    KArgs ka;
+    KArgsQ4 ka;  // sliced to KArgs for the formats without block scales
     ka.a = a;
     ka.a.kcb = p.kcb;
     ka.a.kw = p.kw;

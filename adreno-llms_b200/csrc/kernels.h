@@ -47,8 +47,14 @@ struct LinArgs {
     int kcb;         // bytes of one weight row moved per pipeline stage
     int kw;          // warps that split K of one tile (1, 2 or 4)
     int* status;     // device word: non-zero when a bounded wait ran out
-    // optional fused arg-max over the stored fp16 values of seg[0] (M == 1)
-    unsigned long long* argmax_slot;  // packed (ordered value << 32 | ~index), atomicMax
+    // optional fused arg-max over the fp16 values of seg[0] (M == 1, one segment): every block
+    // folds its rows into argmax_slot (packed ordered value << 32 | ~index, atomicMax, 0 before
+    // and after the launch); the block that finishes last writes the index and clears the words.
+    // seg[0].out may then be null (the logits are not stored).
+    unsigned long long* argmax_slot;
+    unsigned* argmax_done;   // blocks finished (returns to 0)
+    int* argmax_out;         // device int: winning row + argmax_base, -1 when every value is NaN
+    int argmax_base;
     // row-sharded gather: the same block of seg[0].out in the other ranks' gather buffers
     // (peer-mapped device pointers); every stored value is also written there
     uint16_t* peer_out[7];

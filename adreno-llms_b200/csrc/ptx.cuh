@@ -184,6 +184,13 @@ __device__ __forceinline__ void q4x8_to_half2x4_biased(uint32_t w, uint32_t& p04
     asm("lop3.b32 %0, %1, %2, %3, 0xEA;" : "=r"(p37) : "r"(wr8), "r"(MASK), "r"(MAGIC));
 }
 
+// Order-preserving arg-max key of an fp16 value: larger value wins, then the LOWER index.
+__device__ __forceinline__ unsigned long long argmax_key_half(uint16_t h, int idx) {
+    unsigned int b = __float_as_uint(__half2float(__ushort_as_half(h)));
+    b = (b & 0x80000000u) ? ~b : (b | 0x80000000u);
+    return ((unsigned long long)b << 32) | (unsigned long long)(0xFFFFFFFFu - (unsigned int)idx);
+}
+
 // Called by one thread of every block after a barrier that covers the block's output stores
 // (kernels.h: GatherSignal).  Every block orders its stores, local and to peers, before its
 // count with a device-scope fence; the block that completes the count publishes the epoch with

@@ -94,13 +94,13 @@ class DecodeStep:
                 c.linear_add(M, sh.hidden, sh.ffn, self.x_act, w[0], self.resid)
             elif self.comm:
                 self.comm.linear_gather(M, self.vocab_n, sh.hidden, self.x_h, w[0], self.gathered[set_index])
+                if with_argmax and M == 1:   # [G][1][V/G] is the full logits vector
+                    c.argmax(sh.vocab, self.gathered[set_index], self.token)
+            elif with_argmax and M == 1:
+                # lm_head and the greedy pick in one launch (the logits are still stored)
+                c.linear_argmax(self.vocab_n, sh.hidden, self.x_h, w[0], self.logits, self.token)
             else:
                 c.linear(M, self.vocab_n, sh.hidden, self.x_h, w[0], self.logits)
-        if with_argmax and M == 1:
-            if self.comm:   # [G][1][V/G] is the full logits vector
-                c.argmax(sh.vocab, self.gathered[set_index], self.token)
-            else:
-                c.argmax(self.vocab_n, self.logits, self.token)
 
     def record(self, with_argmax=True):
         """Record one plan per weight set (the reference's recorded-queue replay)."""

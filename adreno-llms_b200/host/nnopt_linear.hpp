@@ -47,6 +47,12 @@ inline bool fused_qkv_gemv_m1(nn_context* queue, int K, nn_buf x, nn_buf Wq, int
     return nn_linear_qkv(queue, 1, K, x, Wq, Nq, Wk, Nk, Wv, Nv, q, k, v) == NN_OK;
 }
 
+// src/models/smollm2-135m-instruct/src/layers/lm_head.cpp:36-67 followed by the GPU arg-max of
+// src/model.cpp:603-623, as one launch; `logits` may be nullptr (they are then never written).
+inline bool lm_head_argmax_m1(nn_context* queue, int vocab, int hidden, nn_buf x, nn_buf W, nn_buf logits, nn_buf token_out) {
+    return nn_linear_argmax(queue, vocab, hidden, x, W, logits, token_out) == NN_OK;
+}
+
 // class Weights (weights.h:13-51).  load() takes the context the buffers are created in.
 class Weights {
 public:

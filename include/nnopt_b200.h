@@ -126,6 +126,14 @@ int nn_dequant(nn_context* ctx, int N, int K, nn_buf W, nn_buf out_f32);
  * (host: src/model.cpp:603-623). */
 int nn_argmax(nn_context* ctx, int n, nn_buf logits_fp16, nn_buf out_index_i32);
 
+/* lm_head and greedy pick in one launch (M = 1): out_index = arg-max over n of
+ * fp16( x[K] . W[n,K] ), the index nn_linear followed by nn_argmax would give.  `logits_fp16`
+ * may be NULL, in which case the N logits are never written (the reference's profile names the
+ * logits write as the lm_head's bottleneck, src/models/smollm2-135m-instruct/BENCHMARK.md:549-551).
+ * Replaces the pair LmHead::forward + argmax_block/argmax_final
+ * (src/models/smollm2-135m-instruct/src/layers/lm_head.cpp:36-67, kernels/argmax.cl:33,80). */
+int nn_linear_argmax(nn_context* ctx, int N, int K, nn_buf x, nn_buf W, nn_buf logits_fp16, nn_buf out_index_i32);
+
 /* Arg-max for callers that are not allowed to allocate device memory (a real-time thread
  * under a no-allocation rule, a host application that owns the whole device heap through its
  * own pool, a service whose memory budget is frozen after start-up).  It has no counterpart

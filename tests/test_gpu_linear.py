@@ -285,3 +285,40 @@ def test_tensor_core_residual(nnb, ctx):
     got = run_linear(nnb, ctx, "int8", W, s, x, N, K, call="add", extra=r)
     want = r.astype(np.float64) + x.astype(np.float64) @ cpu.dequant("int8", W, s).astype(np.float64).T
     check_close(got, want, what="tensor-core residual")
+
+
+@pytest.mark.parametrize("fmt,N,K", [("int8", 49152, 576), ("fp16", 4101, 576), ("q4", 8192, 1024), ("q4", 4608, 8192), ("int8", 1000, 200)])
+def test_linear_argmax_matches_linear_then_argmax(nnb, ctx, fmt, N, K):
+    """The fused lm_head + greedy pick returns the index nn_linear + nn_argmax returns, with and
+    without a logits buffer, launch after launch (its reduction words clear themselves)."""
+    if fmt == "q4" and K % 32:
+        pytest.skip("Q4 needs K % 32 == 0")
+    W, s = make_weight(fmt, N, K, 71)
+    qw = nnb.QuantWeight(ctx, fmt, W, s)
+    logits, logits2, idx, idx2 = ctx.alloc(N * 2), ctx.alloc(N * 2), ctx.alloc(4), ctx.alloc(4)
+    for rep in range(3):
+        x = make_x(1, K, 72 + rep)
+        dx = ctx.upload(x.view(np.uint16))
+        ctx.linear(1, N, K, dx, qw.buf, logits)
+        ctx.argmax(N, logits, idx)
+        ctx.linear_argmax(N, K, dx, qw.buf, logits2, idx2)
+        want = int(ctx.download(idx, (1,), np.int32)[0])
+        got = int(ctx.download(idx2, (1,), np.int32)[0])
+        a = ctx.download(logits, (N,), np.uint16)
+        b = ctx.download(logits2, (N,), np.uint16)
+        assert np.array_equal(a, b)
+        assert got == want == int(np.argmax(a.view(np.float16).astype(np.float32)))
+        if K % 64 == 0:
+            ctx.linear_argmax(N, K, dx, qw.buf, None, idx2)      # logits never written
+            assert int(ctx.download(idx2, (1,), np.int32)[0]) == want
+        else:
+            with pytest.raises(nnb.NNError):                     # the any-shape kernel needs the buffer
+                ctx.linear_argmax(N, K, dx, qw.buf, None, idx2)
+        # greedy-token agreement with the oracle: its logit at the chosen row is its maximum
+        # up to the path's tolerance
+        ref = cpu.linear(fmt, x, W, s).astype(np.float32)[0]
+        assert ref[got] >= ref.max() - 2e-3 * np.abs(ref).max()
+        ctx.free(dx)
+    qw.release()
+    for b_ in (logits, logits2, idx, idx2):
+        ctx.free(b_)
