@@ -520,7 +520,7 @@ __global__ void __launch_bounds__(THREADS) linear_stream_kernel(const __grid_con
     asm volatile("bar.sync 1, %0;" ::"n"(NCW * 32) : "memory");
 #ifdef NNB_TRACE
     const long long tl_x = clock64();
-    long long tl_full = 0, tl_comp = 0;
+    long long tl_full = 0, tl_comp = 0, tl_red = 0, tl_epi = 0, tl_e0 = 0, tl_e1 = 0, tl_q[4] = {0, 0, 0, 0};
 #endif
 
 #ifdef NNB_TRACE
@@ -758,6 +758,9 @@ __global__ void __launch_bounds__(THREADS) linear_stream_kernel(const __grid_con
                 }
             }
         }
+#ifdef NNB_TRACE
+        if (ti == 1) tl_red = clock64();
+#endif
         if (sk && !(seg_has_head && has_tail)) {
             float* part = a.sk_scratch + ((size_t)blockIdx.x * (NCW * 32) + (size_t)(warp * 32 + lane)) * (2 * NT * 4);
             if (!seg_has_head) {
@@ -813,58 +816,88 @@ __global__ void __launch_bounds__(THREADS) linear_stream_kernel(const __grid_con
         if (!writer) continue;
 
         if (DUAL) {
-            const LinSeg& sg = a.seg[0];
+            const int seg_n = a.seg[0].N, seg_ld = a.seg[0].ld_out, m_count = a.M;
+            uint16_t* const seg_out = a.seg[0].out;
 #pragma unroll
             for (int nt = 0; nt < NT; ++nt)
 #pragma unroll
                 for (int i = 0; i < 4; ++i) {
                     const int n = tile * tile_rows + wrow_off + g + (i >> 1) * 8;
                     const int m = nt * 8 + 2 * t + (i & 1);
-                    if (n < sg.N && m < a.M) {
+                    if (n < seg_n && m < m_count) {
                         float gv = acc[0][0][nt][i], uv = acc[0][1][nt][i];
                         if (FMT == FMT_INT8) {
                             gv *= __half2float(__ushort_as_half(sc_reg[0][i >> 1]));
                             uv *= __half2float(__ushort_as_half(sc_reg[1][i >> 1]));
                         }
                         const float r = (gv / (1.0f + expf(-gv))) * uv;
-                        sg.out[(size_t)m * sg.ld_out + n] = __half_as_ushort(__float2half_rn(r));
+                        seg_out[(size_t)m * seg_ld + n] = __half_as_ushort(__float2half_rn(r));
                     }
                 }
         } else {
-            const LinSeg& sg = a.seg[tile_segment(tile)];
-            const int row0 = (tile - sg.tile0) * tile_rows + wrow_off;
+#ifdef NNB_TRACE
+            if (ti == 1) tl_e0 = clock64();
+#endif
+            // Everything the store loop needs is copied into registers first: the segment lives in
+            // kernel-parameter memory reached through a run-time index, and a 16-bit store may alias
+            // it as far as the compiler can tell, so every field read after a store would be a fresh
+            // (slow) load.
+            const int si = tile_segment(tile);
+            const int seg_n = a.seg[si].N, seg_ld = a.seg[si].ld_out, seg_tile0 = a.seg[si].tile0;
+            uint16_t* const seg_out = a.seg[si].out;
+            const int m_count = a.M, epi = a.epi;
+            const int npeer = EXT ? a.npeer : 0;
+            unsigned long long* const am_slot = EXT ? a.argmax_slot : nullptr;
+            const int am_base = EXT ? a.argmax_base : 0;
+            uint16_t* peer[7];
+#pragma unroll
+            for (int p = 0; p < 7; ++p) peer[p] = (EXT && p < npeer) ? a.peer_out[p] : nullptr;
+            const int row0 = (tile - seg_tile0) * tile_rows + wrow_off;
+#ifdef NNB_TRACE
+            if (ti == 1 && row0 >= 0) tl_e1 = clock64();
+#endif
 #pragma unroll
             for (int rb = 0; rb < 2; ++rb)
 #pragma unroll
                 for (int i2 = 0; i2 < 2; ++i2) {
                     const int n = row0 + rb * 16 + g + i2 * 8;
-                    if (n >= sg.N) continue;
+                    if (n >= seg_n) continue;
 #pragma unroll
                     for (int nt = 0; nt < NT; ++nt)
 #pragma unroll
                         for (int j = 0; j < 2; ++j) {
                             const int m = nt * 8 + 2 * t + j;
-                            if (m >= a.M) continue;
+                            if (m >= m_count) continue;
                             float v = acc[0][rb][nt][i2 * 2 + j];
                             if (FMT == FMT_INT8) v *= __half2float(__ushort_as_half(sc_reg[rb][i2]));
-                            if (a.epi == EPI_RESIDUAL) {
+                            if (epi == EPI_RESIDUAL) {
                                 v = __half2float(__ushort_as_half((uint16_t)res_reg[rb][i2][nt][j])) + v;
-                            } else if (a.epi == EPI_SILU_GATE) {
+                            } else if (epi == EPI_SILU_GATE) {
                                 const float gt = __half2float(__ushort_as_half((uint16_t)res_reg[rb][i2][nt][j]));
                                 v = gt * (1.0f / (1.0f + expf(-gt))) * v;
                             }
                             const uint16_t hv = __half_as_ushort(__float2half_rn(v));
-                            if (!EXT || sg.out) sg.out[(size_t)m * sg.ld_out + n] = hv;
-                            if (EXT)
-                                for (int p = 0; p < a.npeer; ++p) a.peer_out[p][(size_t)m * sg.ld_out + n] = hv;
-                            if (EXT && a.argmax_slot && m == 0 && (hv & 0x7FFFu) <= 0x7C00u) {  // NaNs never win
-                                const unsigned long long key = argmax_key_half(hv, a.argmax_base + n);
+                            const size_t o = (size_t)m * seg_ld + n;
+                            if (!EXT || seg_out) seg_out[o] = hv;
+                            if (EXT) {
+#pragma unroll
+                                for (int p = 0; p < 7; ++p)
+                                    if (p < npeer) peer[p][o] = hv;
+                            }
+                            if (EXT && am_slot && m == 0 && (hv & 0x7FFFu) <= 0x7C00u) {  // NaNs never win
+                                const unsigned long long key = argmax_key_half(hv, am_base + n);
                                 am_best = key > am_best ? key : am_best;
                             }
                         }
+#ifdef NNB_TRACE
+                    if (ti == 1) tl_q[rb * 2 + i2] = clock64();
+#endif
                 }
         }
     }
+#ifdef NNB_TRACE
+    tl_epi = clock64();
+#endif
     if (EXT && a.argmax_slot) {
         // fused arg-max: one atomic per warp, then the last block to finish publishes the index
 #pragma unroll
@@ -897,7 +930,7 @@ __global__ void __launch_bounds__(THREADS) linear_stream_kernel(const __grid_con
         if (warp == 0) {
             unsigned long long* tl = ka.trace + ((size_t)ka.trace_slot * 32 + blockIdx.x) * 8 * 8 + 5 * 8;
             tl[0] = tl_wait - tl_entry; tl[1] = tl_x - tl_wait; tl[2] = tl_full - tl_x; tl[3] = tl_comp - tl_full;
-            tl[4] = clock64() - tl_comp; tl[5] = tl_entry - cyc_t0;
+            tl[4] = clock64() - tl_comp; tl[5] = tl_entry - cyc_t0; tl[6] = tl_e0 - tl_red; tl[7] = tl_e1 - tl_e0; tl[5] = tl_epi - tl_e1; tl[0] = tl_q[0] - tl_e1; tl[1] = tl_q[1] - tl_e1; tl[2] = tl_q[2] - tl_e1; tl[3] = tl_q[3] - tl_e1;
         }
         o[0] = cyc_iss; o[6] = cyc_rel; o[1] = cyc_wait; o[2] = cyc_comp; o[3] = (clock64() - cyc_t0) - cyc_wait - cyc_comp - cyc_iss - cyc_rel; o[4] = n_items; o[5] = clock64() - cyc_t0;
     }
