@@ -303,6 +303,16 @@ __global__ void __launch_bounds__(THREADS) linear_stream_kernel(const __grid_con
         if (a.nseg > 2 && tile >= a.seg[2].tile0) si = 2;
         return si;
     };
+    // A segment's fields by value.  The three cases index the parameter block with constants:
+    // a run-time index would turn every field access into a generic-address load of a few
+    // hundred cycles instead of a constant-bank read.
+    auto seg_at = [&](int si) {
+        LinSeg r;
+        if (si == 0) r = a.seg[0];
+        else if (si == 1) r = a.seg[1];
+        else r = a.seg[2];
+        return r;
+    };
 
     // ================= producer warp: one elected lane feeds the TMA unit =================
     if (warp == NCW) {
@@ -318,7 +328,7 @@ __global__ void __launch_bounds__(THREADS) linear_stream_kernel(const __grid_con
                 }
                 const uint32_t dst = ring + stage * geo.stage_bytes, bar = full0 + stage * 8;
                 const int sg = DUAL ? 0 : tile_segment(tile);
-                const int row0 = (tile - (DUAL ? 0 : a.seg[sg].tile0)) * tile_rows;
+                const int row0 = (tile - (DUAL ? 0 : seg_at(sg).tile0)) * tile_rows;
                 if (!ksplit) {
                     // one copy per 128-byte column covers the rows of all four consumers
                     const int cb = min(kcb, rowbytes - cg * kcb);
@@ -441,7 +451,7 @@ __global__ void __launch_bounds__(THREADS) linear_stream_kernel(const __grid_con
                 sc_reg[1][i2] = a.scale2[n];
             }
         } else {
-            const LinSeg& sg = a.seg[tile_segment(tile)];
+            const LinSeg sg = seg_at(tile_segment(tile));
             const int row0 = (tile - sg.tile0) * tile_rows + wrow_off;
 #pragma unroll
             for (int rb = 0; rb < 2; ++rb)
@@ -465,7 +475,7 @@ __global__ void __launch_bounds__(THREADS) linear_stream_kernel(const __grid_con
                 row = min(tile * tile_rows + wrow_off + (lane & 15), a.seg[0].N - 1);
                 sbase = lane < 16 ? a.seg[0].scale : a.scale2;
             } else {
-                const LinSeg& sg = a.seg[tile_segment(tile)];
+                const LinSeg sg = seg_at(tile_segment(tile));
                 row = min((tile - sg.tile0) * tile_rows + wrow_off + lane, sg.N - 1);
                 sbase = sg.scale;
             }
@@ -485,7 +495,7 @@ __global__ void __launch_bounds__(THREADS) linear_stream_kernel(const __grid_con
     // In-place epilogues read the values they update; issued early, used at the tile's end.
     auto prefetch_residual = [&](int tile) {
         if (DUAL || !(a.epi == EPI_RESIDUAL || a.epi == EPI_SILU_GATE)) return;
-        const LinSeg& sg = a.seg[tile_segment(tile)];
+        const LinSeg sg = seg_at(tile_segment(tile));
         const int row0 = (tile - sg.tile0) * tile_rows + wrow_off;
 #pragma unroll
         for (int rb = 0; rb < 2; ++rb)
@@ -842,9 +852,9 @@ __global__ void __launch_bounds__(THREADS) linear_stream_kernel(const __grid_con
             // kernel-parameter memory reached through a run-time index, and a 16-bit store may alias
             // it as far as the compiler can tell, so every field read after a store would be a fresh
             // (slow) load.
-            const int si = tile_segment(tile);
-            const int seg_n = a.seg[si].N, seg_ld = a.seg[si].ld_out, seg_tile0 = a.seg[si].tile0;
-            uint16_t* const seg_out = a.seg[si].out;
+            const LinSeg sg = seg_at(tile_segment(tile));
+            const int seg_n = sg.N, seg_ld = sg.ld_out, seg_tile0 = sg.tile0;
+            uint16_t* const seg_out = sg.out;
             const int m_count = a.M, epi = a.epi;
             const int npeer = EXT ? a.npeer : 0;
             unsigned long long* const am_slot = EXT ? a.argmax_slot : nullptr;
