@@ -44,6 +44,8 @@ constexpr int A_BYTES = BM * BK * 2;  // 16 KB
 struct GemmK {
     alignas(64) CUtensorMap tm_w;  // [N][K] fp16, box 64 x 128
     alignas(64) CUtensorMap tm_x;  // [M][K] fp16, box 64 x BN
+    alignas(64) CUtensorMap tm_out;  // [M][ld_out] fp16, box 128 x BN (dense), when tma_store
+    int tma_store;                   // plain-store epilogue through shared memory and one tensor store per tile
     uint16_t* out;                 // [M][ld_out]
     const uint16_t* row_scale;     // int8 weights: fp16 scale per weight row, else null
     int M, N, K, ld_out;
@@ -92,6 +94,16 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
     asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 }
 
+// ---- tensor store (shared -> global) ------------------------------------------------------
+__device__ __forceinline__ void tma_store_2d(const void* tmap, uint32_t src, int x, int y) {
+    asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];" ::"l"(tmap), "r"(src), "r"(x), "r"(y)
+                 : "memory");
+    asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+}
+__device__ __forceinline__ void bulk_wait_read0() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
+__device__ __forceinline__ void bulk_wait0() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
+__device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+
 // Shared-memory matrix descriptor, K-major operand in 128-byte-swizzled rows of 128 bytes:
 // start address >> 4, stride between 8-row groups = 1024 bytes, descriptor version 1,
 // layout type 2 (128-byte swizzle).  The leading-dimension offset is not used by this layout.
@@ -120,16 +132,27 @@ __global__ void __launch_bounds__(GEMM_THREADS) linear_gemm_tc_kernel(const __gr
     extern __shared__ __align__(128) uint8_t smem[];
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const uint32_t s_base = smem_u32(smem);
+    // Scalars are read from the parameter block once: its address is taken (tensor maps), so a
+    // field read after a store would be a fresh load each time, and the epilogue stores a lot.
+    const int gM = g.M, gN = g.N, g_ld = g.ld_out, g_bn = g.bn, g_ntok = g.ntok, g_stages = g.stages, g_cols = g.tmem_cols;
+    const int g_epi = g.epi, g_npeer = g.npeer, g_tma_store = g.tma_store;
+    uint16_t* const g_out = g.out;
+    const uint16_t* const g_rs = g.row_scale;
+    int* const g_status = g.status;
+    uint16_t* g_peer[7];
+#pragma unroll
+    for (int p = 0; p < 7; ++p) g_peer[p] = p < g_npeer ? g.peer_out[p] : nullptr;
     // header: full[S] @0, empty[S] @64, acc_full[2] @128, acc_empty[2] @144, tensor-memory address @160
     const uint32_t full0 = s_base, empty0 = s_base + 64, acc_full0 = s_base + 128, acc_empty0 = s_base + 144, tmem_slot = s_base + 160;
     const uint32_t ring = (s_base + 1024u + 1023u) & ~1023u;
-    const int b_bytes = g.bn * BK * 2;
+    const int b_bytes = g_bn * BK * 2;
     const int stage_bytes = A_BYTES + ((b_bytes + 1023) / 1024) * 1024;
     const int nkb = (g.K + BK - 1) / BK;
-    const int ntiles = ((g.N + BM - 1) / BM) * g.ntok;
+    const uint32_t out_stage = ring + (uint32_t)(g_stages * stage_bytes);  // [BN][128] fp16 staging of one output tile
+    const int ntiles = ((gN + BM - 1) / BM) * g_ntok;
 
     if (tid == 0) {
-        for (int s = 0; s < g.stages; ++s) {
+        for (int s = 0; s < g_stages; ++s) {
             mbar_init(full0 + s * 8, 1);
             mbar_init(empty0 + s * 8, 1);
         }
@@ -139,7 +162,7 @@ __global__ void __launch_bounds__(GEMM_THREADS) linear_gemm_tc_kernel(const __gr
         }
         mbar_init_fence();
     }
-    if (warp == 1) tmem_alloc(tmem_slot, (uint32_t)(2 * g.tmem_cols));
+    if (warp == 1) tmem_alloc(tmem_slot, (uint32_t)(2 * g_cols));
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
@@ -152,39 +175,39 @@ __global__ void __launch_bounds__(GEMM_THREADS) linear_gemm_tc_kernel(const __gr
             int it = 0;
             bool ok = true;
             for (int tile = blockIdx.x; tile < ntiles && ok; tile += gridDim.x) {
-                const int wt = tile / g.ntok, tt = tile - wt * g.ntok;
+                const int wt = tile / g_ntok, tt = tile - wt * g_ntok;
                 for (int kb = 0; kb < nkb; ++kb, ++it) {
-                    const int s = it % g.stages;
-                    if (it >= g.stages && !mbar_wait_bounded(empty0 + s * 8, (uint32_t)(((it / g.stages) - 1) & 1))) {
-                        *reinterpret_cast<volatile int*>(g.status) = 3;
+                    const int s = it % g_stages;
+                    if (it >= g_stages && !mbar_wait_bounded(empty0 + s * 8, (uint32_t)(((it / g_stages) - 1) & 1))) {
+                        *reinterpret_cast<volatile int*>(g_status) = 3;
                         ok = false;
                         break;
                     }
                     const uint32_t dst = ring + s * stage_bytes;
                     mbar_arrive_expect_tx(full0 + s * 8, (uint32_t)(A_BYTES + b_bytes));
                     tma_load_2d(dst, &g.tm_w, kb * BK, wt * BM, full0 + s * 8, policy);
-                    tma_load_2d(dst + A_BYTES, &g.tm_x, kb * BK, tt * g.bn, full0 + s * 8, policy);
+                    tma_load_2d(dst + A_BYTES, &g.tm_x, kb * BK, tt * g_bn, full0 + s * 8, policy);
                 }
             }
         }
     } else if (warp == 1) {
         // ---- MMA issuer: one lane; accumulators alternate between two tensor-memory halves ----
         if (lane == 0) {
-            const uint32_t idesc = instr_desc_f16(g.bn);
+            const uint32_t idesc = instr_desc_f16(g_bn);
             int it = 0, tl = 0;
             bool ok = true;
             for (int tile = blockIdx.x; tile < ntiles && ok; tile += gridDim.x, ++tl) {
                 const int acc = tl & 1;
                 if (tl >= 2 && !mbar_wait_bounded(acc_empty0 + acc * 8, (uint32_t)(((tl >> 1) - 1) & 1))) {
-                    *reinterpret_cast<volatile int*>(g.status) = 6;
+                    *reinterpret_cast<volatile int*>(g_status) = 6;
                     break;
                 }
                 tc_fence_after();
-                const uint32_t tmem_d = tmem_base + (uint32_t)(acc * g.tmem_cols);
+                const uint32_t tmem_d = tmem_base + (uint32_t)(acc * g_cols);
                 for (int kb = 0; kb < nkb; ++kb, ++it) {
-                    const int s = it % g.stages;
-                    if (!mbar_wait_bounded(full0 + s * 8, (uint32_t)((it / g.stages) & 1))) {
-                        *reinterpret_cast<volatile int*>(g.status) = 4;
+                    const int s = it % g_stages;
+                    if (!mbar_wait_bounded(full0 + s * 8, (uint32_t)((it / g_stages) & 1))) {
+                        *reinterpret_cast<volatile int*>(g_status) = 4;
                         ok = false;
                         break;
                     }
@@ -204,31 +227,64 @@ __global__ void __launch_bounds__(GEMM_THREADS) linear_gemm_tc_kernel(const __gr
         int tl = 0;
         bool failed = false;
         for (int tile = blockIdx.x; tile < ntiles; tile += gridDim.x, ++tl) {
-            const int wt = tile / g.ntok, tt = tile - wt * g.ntok;
-            const int n0 = wt * BM, m0 = tt * g.bn, acc = tl & 1;
+            const int wt = tile / g_ntok, tt = tile - wt * g_ntok;
+            const int n0 = wt * BM, m0 = tt * g_bn, acc = tl & 1;
             if (!failed && !mbar_wait_bounded(acc_full0 + acc * 8, (uint32_t)((tl >> 1) & 1))) {
                 failed = true;
-                if (lane == 0) *reinterpret_cast<volatile int*>(g.status) = 5;
+                if (lane == 0) *reinterpret_cast<volatile int*>(g_status) = 5;
             }
             tc_fence_after();
-            if (!failed) {
+            if (!failed && g_tma_store) {
+                // fast path: scale and convert, lay the tile out as [token][weight row] in shared
+                // memory (a warp writes 64 contiguous bytes per token) and let one tensor store
+                // write it; the tensor map clips the rows and columns past M and N
                 const int n = n0 + q * 32 + lane;
-                const float rs = (g.row_scale && n < g.N) ? __half2float(__ushort_as_half(g.row_scale[n])) : 1.0f;
-                const uint32_t tmem_d = tmem_base + (uint32_t)(acc * g.tmem_cols) + ((uint32_t)(q * 32) << 16);
-                for (int c = 0; c < g.bn; c += 32) {
+                const float rs = (g_rs && n < gN) ? __half2float(__ushort_as_half(g_rs[n])) : 1.0f;
+                const uint32_t tmem_d = tmem_base + (uint32_t)(acc * g_cols) + ((uint32_t)(q * 32) << 16);
+                if (tl > 0) {
+                    // the previous tile's store must have finished reading the staging buffer
+                    if (warp == 2 && lane == 0) bulk_wait_read0();
+                    asm volatile("bar.sync 2, %0;" ::"n"(EPI_WARPS * 32) : "memory");
+                }
+                const uint32_t dst0 = out_stage + (uint32_t)((q * 32 + lane) * 2);
+                for (int c = 0; c < g_bn; c += 32) {
                     uint32_t r[32];
                     tmem_ld32(tmem_d + (uint32_t)c, r);
-                    if (n < g.N) {
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) {
+                        const uint16_t hv = __half_as_ushort(__float2half_rn(__uint_as_float(r[j]) * rs));
+                        asm volatile("st.shared.u16 [%0], %1;" ::"r"(dst0 + (uint32_t)((c + j) * (BM * 2))), "h"(hv) : "memory");
+                    }
+                }
+                // the accumulator is free as soon as it has been read
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(acc_empty0 + acc * 8);
+                fence_async_smem();
+                asm volatile("bar.sync 2, %0;" ::"n"(EPI_WARPS * 32) : "memory");
+                if (warp == 2 && lane == 0) tma_store_2d(&g.tm_out, out_stage, n0, m0);
+                continue;
+            }
+            if (!failed) {
+                const int n = n0 + q * 32 + lane;
+                const float rs = (g_rs && n < gN) ? __half2float(__ushort_as_half(g_rs[n])) : 1.0f;
+                const uint32_t tmem_d = tmem_base + (uint32_t)(acc * g_cols) + ((uint32_t)(q * 32) << 16);
+                for (int c = 0; c < g_bn; c += 32) {
+                    uint32_t r[32];
+                    tmem_ld32(tmem_d + (uint32_t)c, r);
+                    if (n < gN) {
 #pragma unroll
                         for (int j = 0; j < 32; ++j) {
                             const int m = m0 + c + j;
-                            if (m < g.M && c + j < g.bn) {
+                            if (m < gM && c + j < g_bn) {
                                 float v = __uint_as_float(r[j]) * rs;
-                                uint16_t* o = g.out + (size_t)m * g.ld_out + n;
-                                if (g.epi == EPI_RESIDUAL) v = __half2float(__ushort_as_half(*o)) + v;
+                                uint16_t* o = g_out + (size_t)m * g_ld + n;
+                                if (g_epi == EPI_RESIDUAL) v = __half2float(__ushort_as_half(*o)) + v;
                                 const uint16_t hv = __half_as_ushort(__float2half_rn(v));
                                 *o = hv;
-                                for (int p = 0; p < g.npeer; ++p) g.peer_out[p][(size_t)m * g.ld_out + n] = hv;
+                                #pragma unroll
+                                for (int p = 0; p < 7; ++p)
+                                    if (p < g_npeer) g_peer[p][(size_t)m * g_ld + n] = hv;
                             }
                         }
                     }
@@ -239,9 +295,10 @@ __global__ void __launch_bounds__(GEMM_THREADS) linear_gemm_tc_kernel(const __gr
             if (lane == 0) mbar_arrive(acc_empty0 + acc * 8);
         }
     }
+    if (g_tma_store && warp == 2 && lane == 0) bulk_wait0();  // all of this block's tensor stores have landed
     tc_fence_before();
     __syncthreads();
-    if (warp == 1) tmem_dealloc(tmem_base, (uint32_t)(2 * g.tmem_cols));
+    if (warp == 1) tmem_dealloc(tmem_base, (uint32_t)(2 * g_cols));
     if (tid == 0 && g.sig.world > 0) gather_signal_block_done(g.sig);
 }
 
@@ -305,7 +362,11 @@ cudaError_t launch_gemm_tc(const uint16_t* W_half, const uint16_t* row_scale, co
     while (g.tmem_cols < bn) g.tmem_cols *= 2;
     const int b_bytes = ((bn * BK * 2 + 1023) / 1024) * 1024;
     const int stage_bytes = A_BYTES + b_bytes;
-    int stages = (227 * 1024 - 2048) / stage_bytes;
+    // Plain stores go out through a staging tile in shared memory and one tensor store per tile,
+    // when the output rows keep 16-byte pitch and alignment and no peer copies are asked for.
+    g.tma_store = (epi == EPI_STORE && npeer == 0 && (ld_out % 8) == 0 && (reinterpret_cast<uintptr_t>(out) & 15) == 0) ? 1 : 0;
+    const int out_bytes = g.tma_store ? ((bn + 31) / 32) * 32 * BM * 2 : 0;  // the epilogue reads 32 columns at a time
+    int stages = (227 * 1024 - 2048 - out_bytes) / stage_bytes;
     if (stages > 6) stages = 6;
     if (stages < 2) return cudaErrorInvalidValue;
     g.stages = stages;
@@ -316,7 +377,9 @@ cudaError_t launch_gemm_tc(const uint16_t* W_half, const uint16_t* row_scale, co
     g.status = status;
     if (!encode_tiled_2d(&g.tm_w, /*fp16*/ true, W_half, (uint64_t)K, (uint64_t)N, (uint64_t)K * 2, BK, BM)) return cudaErrorInvalidValue;
     if (!encode_tiled_2d(&g.tm_x, true, x, (uint64_t)K, (uint64_t)M, (uint64_t)K * 2, BK, bn)) return cudaErrorInvalidValue;
-    const size_t smem = 2048 + (size_t)stages * stage_bytes;
+    if (g.tma_store && !encode_tiled_2d(&g.tm_out, true, out, (uint64_t)N, (uint64_t)M, (uint64_t)ld_out * 2, BM, bn, /*swizzle128=*/false))
+        return cudaErrorInvalidValue;
+    const size_t smem = 2048 + (size_t)stages * stage_bytes + out_bytes;
     unsigned grid = (unsigned)(((N + BM - 1) / BM) * g.ntok);
     if (grid > 148u) grid = 148u;  // persistent: one block per SM walks the tiles
     linear_gemm_tc_kernel<<<grid, GEMM_THREADS, smem, st>>>(g);

@@ -252,10 +252,16 @@ __global__ void __launch_bounds__(THREADS) linear_stream_kernel(const __grid_con
     extern __shared__ __align__(128) uint8_t smem[];
     const LinArgs& a = ka.a;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    // Scalars used all over the kernel are read from the parameter block once.  The block's
+    // address is taken (the tensor maps in it are handed to the TMA unit), so the compiler must
+    // assume that any store may change it and would otherwise re-read a field after every store.
+    const int aM = a.M, aK = a.K, a_epi = a.epi, a_nseg = a.nseg;
+    int* const a_status = a.status;
+    const int seg1_tile0 = a.seg[1].tile0, seg2_tile0 = a.seg[2].tile0;
     const int stages = ka.stages, kcb = a.kcb;
     const bool ksplit = a.kw > 1;  // the four consumers split K of one 32-row tile
     const int rowbytes = ka.rowbytes, nchunks = ka.nchunks;
-    const Geo geo = make_geo(FMT, a.M, a.K, kcb, stages, NT);
+    const Geo geo = make_geo(FMT, aM, aK, kcb, stages, NT);
     const int warp_rows = DUAL ? 16 : WARP_ROWS;                       // rows of each weight per warp
     const int tile_rows = ksplit ? warp_rows : NCW * warp_rows;        // rows of each weight per block tile
     const int groups = ksplit ? (nchunks + NCW - 1) / NCW : nchunks;   // pipeline items per tile
@@ -268,7 +274,7 @@ __global__ void __launch_bounds__(THREADS) linear_stream_kernel(const __grid_con
     const uint32_t ring = (s_base + geo.off_ring + 1023u) & ~1023u;
 
     if (tid < 16) reinterpret_cast<uint32_t*>(smem)[tid] = 0u;
-    if (FMT == FMT_INT8 && tid >= 32 && tid < 48) reinterpret_cast<uint32_t*>(xs + 3 * a.M * geo.xstride)[tid - 32] = 0u;  // per-row max words
+    if (FMT == FMT_INT8 && tid >= 32 && tid < 48) reinterpret_cast<uint32_t*>(xs + 3 * aM * geo.xstride)[tid - 32] = 0u;  // per-row max words
     if (tid == 0) {
         for (int s = 0; s < stages; ++s) {
             mbar_init(full0 + s * 8, (FMT == FMT_Q4 && !ka.scale_tma) ? 1u + NCW * 32u : 1u);
@@ -299,8 +305,8 @@ __global__ void __launch_bounds__(THREADS) linear_stream_kernel(const __grid_con
 
     auto tile_segment = [&](int tile) {
         int si = 0;
-        if (a.nseg > 1 && tile >= a.seg[1].tile0) si = 1;
-        if (a.nseg > 2 && tile >= a.seg[2].tile0) si = 2;
+        if (a_nseg > 1 && tile >= seg1_tile0) si = 1;
+        if (a_nseg > 2 && tile >= seg2_tile0) si = 2;
         return si;
     };
     // A segment's fields by value.  The three cases index the parameter block with constants:
@@ -323,7 +329,7 @@ __global__ void __launch_bounds__(THREADS) linear_stream_kernel(const __grid_con
             for (int it = 0; it < n_items; ++it) {
                 const int tile = tile_s;
                 if (it >= stages && !mbar_wait_bounded(empty0 + stage * 8, (uint32_t)(((it / stages) - 1) & 1))) {
-                    *reinterpret_cast<volatile int*>(a.status) = 2;
+                    *reinterpret_cast<volatile int*>(a_status) = 2;
                     break;
                 }
                 const uint32_t dst = ring + stage * geo.stage_bytes, bar = full0 + stage * 8;
@@ -414,18 +420,18 @@ __global__ void __launch_bounds__(THREADS) linear_stream_kernel(const __grid_con
 #pragma unroll
     for (int nt = 0; nt < NT; ++nt) {
         const int n = (lane & 7) + nt * 8;
-        const bool valid = n < a.M;
+        const bool valid = n < aM;
         b_base[nt] = valid ? smem_u32(xs) + n * geo.xstride + (lane >> 3) * 16 : zero_addr;
         b_step[nt] = valid ? 64u : 0u;
-        b_plane[nt] = (FMT == FMT_INT8 && valid) ? (uint32_t)(a.M * geo.xstride) : 0u;
+        b_plane[nt] = (FMT == FMT_INT8 && valid) ? (uint32_t)(aM * geo.xstride) : 0u;
     }
     // Q4: this lane's accumulator-start quads (token pair t of each n tile), one per 32-weight block
-    const int npair = (a.M + 1) / 2;
+    const int npair = (aM + 1) / 2;
     const int ctab_step = npair * 16;
     const uint8_t* ctab_lane[NT];
 #pragma unroll
     for (int nt = 0; nt < NT; ++nt) ctab_lane[nt] = smem + geo.off_ctab + min(t + 4 * nt, npair - 1) * 16;
-    const float* rowscale = reinterpret_cast<const float*>(xs + 3 * a.M * geo.xstride + 64);
+    const float* rowscale = reinterpret_cast<const float*>(xs + 3 * aM * geo.xstride + 64);
 
     // rows of this warp inside its tile, and which warp writes results
     const int wrow_off = ksplit ? 0 : warp * warp_rows;
@@ -480,7 +486,7 @@ __global__ void __launch_bounds__(THREADS) linear_stream_kernel(const __grid_con
                 sbase = sg.scale;
             }
             const int cb = min(kcb, rowbytes - c * kcb);
-            const uint8_t* ssrc = reinterpret_cast<const uint8_t*>(sbase) + ((size_t)row * (a.K / 32)) * 2 + (size_t)c * (kcb / 8);
+            const uint8_t* ssrc = reinterpret_cast<const uint8_t*>(sbase) + ((size_t)row * (aK / 32)) * 2 + (size_t)c * (kcb / 8);
             const uint32_t sdst = ring + stage * geo.stage_bytes + geo.nbox * CTA_BOX + (warp * WARP_ROWS + lane) * geo.sstride;
             const int sb = cb / 8;
             if (((reinterpret_cast<uintptr_t>(ssrc) | (uintptr_t)sb) & 15) == 0) {
@@ -494,7 +500,7 @@ __global__ void __launch_bounds__(THREADS) linear_stream_kernel(const __grid_con
 
     // In-place epilogues read the values they update; issued early, used at the tile's end.
     auto prefetch_residual = [&](int tile) {
-        if (DUAL || !(a.epi == EPI_RESIDUAL || a.epi == EPI_SILU_GATE)) return;
+        if (DUAL || !(a_epi == EPI_RESIDUAL || a_epi == EPI_SILU_GATE)) return;
         const LinSeg sg = seg_at(tile_segment(tile));
         const int row0 = (tile - sg.tile0) * tile_rows + wrow_off;
 #pragma unroll
@@ -506,7 +512,7 @@ __global__ void __launch_bounds__(THREADS) linear_stream_kernel(const __grid_con
 #pragma unroll
                     for (int j = 0; j < 2; ++j) {
                         const int n = row0 + rb * 16 + g + i2 * 8, m = nt * 8 + 2 * t + j;
-                        res_reg[rb][i2][nt][j] = (n < sg.N && m < a.M) ? (uint32_t)sg.out[(size_t)m * sg.ld_out + n] : 0u;
+                        res_reg[rb][i2][nt][j] = (n < sg.N && m < aM) ? (uint32_t)sg.out[(size_t)m * sg.ld_out + n] : 0u;
                     }
     };
 
@@ -525,8 +531,8 @@ __global__ void __launch_bounds__(THREADS) linear_stream_kernel(const __grid_con
     const long long tl_wait = clock64();
 #endif
     if (n_items > 0 && writer) prefetch_residual(tile_first);
-    if (FMT == FMT_INT8) stage_x_int8(a.x, a.M, a.K, xs, geo.xstride, tid, NCW * 32);
-    else stage_x<FMT>(a.x, a.M, a.K, xs, geo.xstride, reinterpret_cast<float*>(smem + geo.off_ctab), tid, NCW * 32);
+    if (FMT == FMT_INT8) stage_x_int8(a.x, aM, aK, xs, geo.xstride, tid, NCW * 32);
+    else stage_x<FMT>(a.x, aM, aK, xs, geo.xstride, reinterpret_cast<float*>(smem + geo.off_ctab), tid, NCW * 32);
     asm volatile("bar.sync 1, %0;" ::"n"(NCW * 32) : "memory");
 #ifdef NNB_TRACE
     const long long tl_x = clock64();
@@ -584,7 +590,7 @@ __global__ void __launch_bounds__(THREADS) linear_stream_kernel(const __grid_con
         // the warp still walks its items so that the block's barriers stay matched.
         if (!failed && !mbar_wait_bounded(full0 + stage * 8, phase)) {
             failed = true;
-            if (lane == 0) *reinterpret_cast<volatile int*>(a.status) = 1;
+            if (lane == 0) *reinterpret_cast<volatile int*>(a_status) = 1;
         }
         CYC_END(cyc_wait);
 #ifdef NNB_TRACE
@@ -731,7 +737,7 @@ __global__ void __launch_bounds__(THREADS) linear_stream_kernel(const __grid_con
                         const int m = nt * 8 + 2 * t + (i & 1);
                         const float v = fmaf((float)iacc[0][rb][nt][i], 65536.f,
                                              fmaf((float)iacc[FMT == FMT_INT8 ? 1 : 0][rb][nt][i], 256.f, (float)iacc[FMT == FMT_INT8 ? 2 : 0][rb][nt][i]));
-                        acc[0][rb][nt][i] = m < a.M ? v * rowscale[m] : 0.f;
+                        acc[0][rb][nt][i] = m < aM ? v * rowscale[m] : 0.f;
                     }
         }
         // ---- tile finished: fold the two accumulator sets, combine the K parts (fixed
@@ -800,7 +806,7 @@ __global__ void __launch_bounds__(THREADS) linear_stream_kernel(const __grid_con
                         asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(a.sk_flags + nb) : "memory");
                         if (v) break;
                         if (clock64() - t0 > 400000000ll) {
-                            *reinterpret_cast<volatile int*>(a.status) = 8;
+                            *reinterpret_cast<volatile int*>(a_status) = 8;
                             break;
                         }
                         __nanosleep(40);
@@ -826,7 +832,7 @@ __global__ void __launch_bounds__(THREADS) linear_stream_kernel(const __grid_con
         if (!writer) continue;
 
         if (DUAL) {
-            const int seg_n = a.seg[0].N, seg_ld = a.seg[0].ld_out, m_count = a.M;
+            const int seg_n = a.seg[0].N, seg_ld = a.seg[0].ld_out, m_count = aM;
             uint16_t* const seg_out = a.seg[0].out;
 #pragma unroll
             for (int nt = 0; nt < NT; ++nt)
@@ -855,7 +861,7 @@ __global__ void __launch_bounds__(THREADS) linear_stream_kernel(const __grid_con
             const LinSeg sg = seg_at(tile_segment(tile));
             const int seg_n = sg.N, seg_ld = sg.ld_out, seg_tile0 = sg.tile0;
             uint16_t* const seg_out = sg.out;
-            const int m_count = a.M, epi = a.epi;
+            const int m_count = aM, epi = a_epi;
             const int npeer = EXT ? a.npeer : 0;
             unsigned long long* const am_slot = EXT ? a.argmax_slot : nullptr;
             const int am_base = EXT ? a.argmax_base : 0;
@@ -1026,14 +1032,15 @@ int count_tiles(const LinArgs& a, int tile_rows) {
 }  // namespace
 
 bool encode_tiled_2d(void* map, bool half_elems, const void* base, uint64_t dim0, uint64_t dim1, uint64_t stride1_bytes,
-                     uint32_t box0, uint32_t box1) {
+                     uint32_t box0, uint32_t box1, bool swizzle128) {
     if (!g_encode_tiled) return false;
     const cuuint64_t dims[2] = {dim0, dim1};
     const cuuint64_t strides[1] = {stride1_bytes};
     const cuuint32_t box[2] = {box0, box1};
     const cuuint32_t estr[2] = {1u, 1u};
     return g_encode_tiled(static_cast<CUtensorMap*>(map), half_elems ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_UINT8, 2,
-                          const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                          const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                          swizzle128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE,
                           CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 

@@ -89,9 +89,9 @@ cudaError_t launch_stream(int fmt, const LinArgs& a, const StreamPlan& p, cudaSt
 cudaError_t stream_configure();  // opt in to large dynamic shared memory, once per device
 
 // 2-D tensor map helper (gemv_stream.cu): [dim1][dim0] elements, row stride in bytes, box dim0 x dim1,
-// 128-byte swizzle; fp16 elements when `half_elems`, bytes otherwise.
+// 128-byte swizzle (or none); fp16 elements when `half_elems`, bytes otherwise.
 bool encode_tiled_2d(void* map, bool half_elems, const void* base, uint64_t dim0, uint64_t dim1, uint64_t stride1_bytes,
-                     uint32_t box0, uint32_t box1);
+                     uint32_t box0, uint32_t box1, bool swizzle128 = true);
 
 // gemm_tc.cu: tcgen05 / tensor-memory GEMM for M > 16
 cudaError_t gemm_tc_configure();
