@@ -142,8 +142,10 @@ __global__ void __launch_bounds__(GEMM_THREADS) linear_gemm_tc_kernel(const __gr
     uint16_t* g_peer[7];
 #pragma unroll
     for (int p = 0; p < 7; ++p) g_peer[p] = p < g_npeer ? g.peer_out[p] : nullptr;
-    // header: full[S] @0, empty[S] @64, acc_full[2] @128, acc_empty[2] @144, tensor-memory address @160
+    // header: full[S] @0, empty[S] @64, acc_full[2] @128, acc_empty[2] @144, tensor-memory address @160,
+    // residual-tile barrier @176
     const uint32_t full0 = s_base, empty0 = s_base + 64, acc_full0 = s_base + 128, acc_empty0 = s_base + 144, tmem_slot = s_base + 160;
+    const uint32_t res_bar = s_base + 176;
     const uint32_t ring = (s_base + 1024u + 1023u) & ~1023u;
     const int b_bytes = g_bn * BK * 2;
     const int stage_bytes = A_BYTES + ((b_bytes + 1023) / 1024) * 1024;
@@ -160,6 +162,7 @@ __global__ void __launch_bounds__(GEMM_THREADS) linear_gemm_tc_kernel(const __gr
             mbar_init(acc_full0 + a * 8, 1);
             mbar_init(acc_empty0 + a * 8, EPI_WARPS);
         }
+        mbar_init(res_bar, 1);
         mbar_init_fence();
     }
     if (warp == 1) tmem_alloc(tmem_slot, (uint32_t)(2 * g_cols));
@@ -237,7 +240,9 @@ __global__ void __launch_bounds__(GEMM_THREADS) linear_gemm_tc_kernel(const __gr
             if (!failed && g_tma_store) {
                 // fast path: scale and convert, lay the tile out as [token][weight row] in shared
                 // memory (a warp writes 64 contiguous bytes per token) and let one tensor store
-                // write it; the tensor map clips the rows and columns past M and N
+                // write it; the tensor map clips the rows and columns past M and N.  For the
+                // in-place residual the tile's current values are fetched into the same buffer
+                // first; for a row-sharded gather the finished tile is also copied to the peers.
                 const int n = n0 + q * 32 + lane;
                 const float rs = (g_rs && n < gN) ? __half2float(__ushort_as_half(g_rs[n])) : 1.0f;
                 const uint32_t tmem_d = tmem_base + (uint32_t)(acc * g_cols) + ((uint32_t)(q * 32) << 16);
@@ -246,14 +251,31 @@ __global__ void __launch_bounds__(GEMM_THREADS) linear_gemm_tc_kernel(const __gr
                     if (warp == 2 && lane == 0) bulk_wait_read0();
                     asm volatile("bar.sync 2, %0;" ::"n"(EPI_WARPS * 32) : "memory");
                 }
+                if (g_epi == EPI_RESIDUAL) {
+                    if (warp == 2 && lane == 0) {
+                        mbar_arrive_expect_tx(res_bar, (uint32_t)(g_bn * BM * 2));
+                        tma_load_2d(out_stage, &g.tm_out, n0, m0, res_bar, l2_policy_evict_normal());
+                    }
+                    if (!mbar_wait_bounded(res_bar, (uint32_t)(tl & 1))) {
+                        failed = true;
+                        if (lane == 0) *reinterpret_cast<volatile int*>(g_status) = 9;
+                    }
+                }
                 const uint32_t dst0 = out_stage + (uint32_t)((q * 32 + lane) * 2);
                 for (int c = 0; c < g_bn; c += 32) {
                     uint32_t r[32];
                     tmem_ld32(tmem_d + (uint32_t)c, r);
 #pragma unroll
                     for (int j = 0; j < 32; ++j) {
-                        const uint16_t hv = __half_as_ushort(__float2half_rn(__uint_as_float(r[j]) * rs));
-                        asm volatile("st.shared.u16 [%0], %1;" ::"r"(dst0 + (uint32_t)((c + j) * (BM * 2))), "h"(hv) : "memory");
+                        float v = __uint_as_float(r[j]) * rs;
+                        const uint32_t addr = dst0 + (uint32_t)((c + j) * (BM * 2));
+                        if (g_epi == EPI_RESIDUAL) {
+                            uint16_t old;
+                            asm volatile("ld.shared.u16 %0, [%1];" : "=h"(old) : "r"(addr) : "memory");
+                            v = __half2float(__ushort_as_half(old)) + v;
+                        }
+                        const uint16_t hv = __half_as_ushort(__float2half_rn(v));
+                        asm volatile("st.shared.u16 [%0], %1;" ::"r"(addr), "h"(hv) : "memory");
                     }
                 }
                 // the accumulator is free as soon as it has been read
@@ -263,6 +285,22 @@ __global__ void __launch_bounds__(GEMM_THREADS) linear_gemm_tc_kernel(const __gr
                 fence_async_smem();
                 asm volatile("bar.sync 2, %0;" ::"n"(EPI_WARPS * 32) : "memory");
                 if (warp == 2 && lane == 0) tma_store_2d(&g.tm_out, out_stage, n0, m0);
+                if (g_npeer > 0) {
+                    // peers get the tile in 16-byte pieces, 256 contiguous bytes per token row
+                    const int et = (warp - 2) * 32 + lane;
+                    const int rows = min(g_bn, gM - m0);
+                    for (int i = et; i < rows * 16; i += EPI_WARPS * 32) {
+                        const int mr = i >> 4, ch = i & 15;
+                        if (n0 + ch * 8 >= gN) continue;
+                        uint4 v;
+                        asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+                                     : "r"(out_stage + (uint32_t)(mr * (BM * 2) + ch * 16)) : "memory");
+                        const size_t o = (size_t)(m0 + mr) * g_ld + n0 + ch * 8;
+#pragma unroll
+                        for (int p = 0; p < 7; ++p)
+                            if (p < g_npeer) *reinterpret_cast<uint4*>(g_peer[p] + o) = v;
+                    }
+                }
                 continue;
             }
             if (!failed) {
@@ -362,9 +400,11 @@ cudaError_t launch_gemm_tc(const uint16_t* W_half, const uint16_t* row_scale, co
     while (g.tmem_cols < bn) g.tmem_cols *= 2;
     const int b_bytes = ((bn * BK * 2 + 1023) / 1024) * 1024;
     const int stage_bytes = A_BYTES + b_bytes;
-    // Plain stores go out through a staging tile in shared memory and one tensor store per tile,
-    // when the output rows keep 16-byte pitch and alignment and no peer copies are asked for.
-    g.tma_store = (epi == EPI_STORE && npeer == 0 && (ld_out % 8) == 0 && (reinterpret_cast<uintptr_t>(out) & 15) == 0) ? 1 : 0;
+    // The epilogue goes through a staging tile in shared memory and one tensor store per tile
+    // when the output rows keep 16-byte pitch and alignment (lane-by-lane stores otherwise).
+    bool aligned = (ld_out % 8) == 0 && (reinterpret_cast<uintptr_t>(out) & 15) == 0;
+    for (int p = 0; p < npeer; ++p) aligned = aligned && (reinterpret_cast<uintptr_t>(peer_out[p]) & 15) == 0;
+    g.tma_store = aligned ? 1 : 0;
     const int out_bytes = g.tma_store ? ((bn + 31) / 32) * 32 * BM * 2 : 0;  // the epilogue reads 32 columns at a time
     int stages = (227 * 1024 - 2048 - out_bytes) / stage_bytes;
     if (stages > 6) stages = 6;
