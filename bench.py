@@ -5,7 +5,8 @@
 
 A step is one pass over every projection of a SmolLM2-135M-shaped decode step
 (30 x {QKV, o_proj+residual, gate/up/SiLU, down+residual} + tied lm_head; 211 GEMVs
-issued as 121 fused launches) at M = 1 on seeded synthetic weights.  The metric is the
+issued as 121 fused launches, the last of which also takes the greedy token) at M = 1 on
+seeded synthetic weights.  The metric is the
 achieved weight-stream rate: algorithmic bytes of the step / step time, in GB/s.
 
   value     steps replayed from a recorded plan, operands resident in HBM, timed with
@@ -17,8 +18,13 @@ achieved weight-stream rate: algorithmic bytes of the step / step time, in GB/s.
   cpu_baseline  the reference's own .cl kernels compiled for the CPU (oracle/_ref; the oracle
             port when that build is absent), all host cores, on a bounded sample of the step
 
+  sharded_projections, prefill_gemm   the scaled-up operators of the other BASELINE configs
+            (row-sharded int8 lm_head at M = 256, Q4 FFN matrix at M = 1..128; fp16 lm_head
+            at M = 512 / 2048 on the tensor-core path), each timed alone
+
 With --gpus N > 1 (launched under torchrun) the lm_head rows are sharded across the
-ranks and all-gathered with NCCL; the per-layer projections stay replicated
+ranks and every rank's lm_head kernel stores its rows into every rank's gather buffer
+over NVLink peer memory; the per-layer projections stay replicated
 (north star: only the large row-sharded projections are partitioned).
 --impl reference times the reference's own CPU implementation of the path
 (oracle/_ref when it was built, else the oracle port) on the host cores.
@@ -74,6 +80,45 @@ def measured_peaks():
         d = json.load(open(p))
         return float(d["hbm_gbs"]), "measured (MEASURED_PEAKS.json hbm_gbs)"
     return 6650.0, "fallback (6.65 TB/s, earlier measurement on this pool)"
+
+
+def measured_tensor_peak():
+    p = os.path.join(REPO, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        d = json.load(open(p))
+        return float(d["bf16_tflops"]), "measured (MEASURED_PEAKS.json bf16_tflops, burst)"
+    return 1590.0, "fallback (1.59 PFLOP/s, earlier measurement on this pool)"
+
+
+def prefill_gemm(pkg, ctx, synth, reps=6):
+    """The prefill shapes of the Qwen-shaped lm_head (151936 x 896, fp16) on the tensor-core path:
+    TFLOP/s = 2 M N K / device time, each launch timed alone with CUDA events (the 272 MB weight
+    and the M x N output are larger than L2)."""
+    peak, src = measured_tensor_peak()
+    N, K = 151936, 896
+    W, _ = synth.weight("fp16", 2048, K, np.random.default_rng(91))
+    qw = pkg.QuantWeight(ctx, "fp16", np.tile(W, (N // 2048 + 1, 1))[:N], None)
+    rows = []
+    for M in (512, 2048):
+        x = ctx.upload(synth.activations(M, K, np.random.default_rng(92)).view(np.uint16))
+        out = ctx.alloc(M * N * 2)
+        a, b = ctx.event(), ctx.event()
+        best = []
+        for i in range(reps + 2):
+            ctx.record(a)
+            ctx.linear(M, N, K, x, qw.buf, out)
+            ctx.record(b)
+            ctx.sync()
+            if i >= 2:
+                best.append(ctx.elapsed_ms(a, b))
+        us = float(np.mean(best)) * 1e3
+        tf = 2.0 * M * N * K / (us * 1e-6) / 1e12
+        rows.append({"kernel": "linear_gemm_tc_kernel", "fmt": "fp16", "N": N, "K": K, "M": M, "us": us, "tflops": tf,
+                     "peak_tflops": peak, "frac": tf / peak, "peak_source": src})
+        ctx.free(out)
+        ctx.free(x)
+    qw.release()
+    return rows
 
 
 class ClockSampler:
@@ -506,6 +551,7 @@ def main():
     dom = max(group_rows, key=lambda g: g["share_of_step"])
     big = max(group_rows, key=lambda g: g["bytes_per_launch"])
     sharded = sharded_projections(pkg, ctx, synth, comm, rank, world, dist) if args.only is None else None
+    prefill = prefill_gemm(pkg, ctx, synth) if (args.only is None and world == 1) else None
     clocks = sampler.stop()
 
     cpu_base = None
@@ -537,6 +583,7 @@ def main():
                                         "bytes_per_launch": big["bytes_per_launch"]},
             "launch_groups": group_rows,
             "sharded_projections": sharded,
+            "prefill_gemm": prefill,
             "clocks": clocks,
         }
         if cpu_base:
