@@ -100,7 +100,6 @@ extern "C" int nn_shutdown(nn_context* c) {
     if (!c) return NN_OK;
     cudaSetDevice(c->device);
     cudaStreamSynchronize(c->stream);
-    if (c->gemm_scratch) cudaFree(c->gemm_scratch);
     if (c->flush_buf) cudaFree(c->flush_buf);
     if (c->argmax_slot) cudaFree(c->argmax_slot);
     if (c->sk_scratch) cudaFree(c->sk_scratch);
@@ -255,34 +254,15 @@ bool nnb::resolve_weight(const nn_context* c, const void* W, int K, ResolvedW* o
 // ---------------------------------------------------------------------------------
 // operator dispatch
 // ---------------------------------------------------------------------------------
-// M > 16 with one weight and a plain or residual epilogue: tensor-core GEMM.  Quantised
-// weights go through an fp16 copy in context scratch (grown outside graph capture only).
+// M > 16 with one weight and a plain or residual epilogue: tensor-core GEMM (quantised weights
+// are expanded to fp16 inside the kernel, stage by stage).
 static int run_gemm_tc(nn_context* c, int fmt, const LinArgs& a, int M, const char* who, bool* done) {
     *done = false;
     if (a.nseg != 1 || !(a.epi == EPI_STORE || a.epi == EPI_RESIDUAL)) return NN_OK;
     const LinSeg& sg = a.seg[0];
-    if (!gemm_tc_supported(M, sg.N, a.K, a.x, sg.W, sg.out)) return NN_OK;
+    if (!gemm_tc_supported(fmt, M, sg.N, a.K, a.x, sg.W, sg.out)) return NN_OK;
     if (getenv("NNB_NO_TC")) return NN_OK;
-    const uint16_t* Wh = (const uint16_t*)sg.W;
-    const uint16_t* row_scale = nullptr;
-    if (fmt != FMT_FP16) {
-        const size_t need = (size_t)sg.N * a.K * 2;
-        if (need > c->gemm_scratch_bytes) {
-            if (c->capturing) return NN_OK;  // cannot allocate while recording: the sliced path takes over
-            cudaSetDevice(c->device);
-            CUDA_TRY(cudaStreamSynchronize(c->stream));
-            if (c->gemm_scratch) CUDA_TRY(cudaFree(c->gemm_scratch));
-            c->gemm_scratch = nullptr;
-            c->gemm_scratch_bytes = 0;
-            CUDA_TRY(cudaMalloc(&c->gemm_scratch, need));
-            c->gemm_scratch_bytes = need;
-        }
-        CUDA_TRY(launch_dequant_half(fmt, sg.N, a.K, sg.W, sg.scale, (uint16_t*)c->gemm_scratch, c->stream));
-        c->launches++;
-        Wh = (const uint16_t*)c->gemm_scratch;
-        if (fmt == FMT_INT8) row_scale = sg.scale;
-    }
-    cudaError_t e = launch_gemm_tc(Wh, row_scale, a.x, sg.out, M, sg.N, a.K, sg.ld_out, a.epi, a.status, a.peer_out, a.npeer, &a.sig, c->stream);
+    cudaError_t e = launch_gemm_tc(fmt, sg.W, sg.scale, a.x, sg.out, M, sg.N, a.K, sg.ld_out, a.epi, a.status, a.peer_out, a.npeer, &a.sig, c->stream);
     if (e != cudaSuccess) return NN_FAIL(NN_ERR_CUDA, "%s: tensor-core launch failed: %s (M=%d N=%d K=%d)", who, cudaGetErrorString(e), M, sg.N, a.K);
     c->launches++;
     *done = true;

@@ -23,9 +23,9 @@
 // Blocks that share a weight tile (different token tiles) are adjacent in launch order, so
 // the tile is fetched from HBM once and re-read from L2.
 //
-// int8 / Q4 weights take this path through an fp16 copy made by dequant_half_kernel
-// (int8 codes are exact in fp16 and the per-row scale is applied in the epilogue, after
-// the full-K sum, like the GEMV; Q4 stores code x block-scale rounded to fp16).
+// int8 / Q4 weights are streamed packed, once: four more warps expand each stage into the fp16
+// operand inside shared memory (int8 codes are exact in fp16 and the per-row scale is applied in
+// the epilogue, after the full-K sum, like the GEMV; Q4 becomes code x block-scale rounded to fp16).
 #include <cuda.h>
 #include <cuda_fp16.h>
 
@@ -38,11 +38,16 @@ namespace {
 constexpr int BM = 128;       // weight rows per tile (UMMA M)
 constexpr int BK = 64;        // K elements per stage = one 128-byte swizzle span of fp16
 constexpr int EPI_WARPS = 4;
-constexpr int GEMM_THREADS = (2 + EPI_WARPS) * 32;  // producer warp, MMA warp, four epilogue warps
+constexpr int DQ_WARPS = 8;   // quantised weights only: warps that turn the raw stage into the fp16 operand
+constexpr int GEMM_THREADS = (2 + EPI_WARPS) * 32;            // producer warp, MMA warp, four epilogue warps
+constexpr int GEMM_THREADS_Q = GEMM_THREADS + DQ_WARPS * 32 + 32;  // ... plus the expanding warps and the packed-weight producer
 constexpr int A_BYTES = BM * BK * 2;  // 16 KB
+constexpr int OUT_ROWS = 128;         // tokens per output slab (staging buffer: OUT_ROWS x 128 fp16 = 32 KB)
 
 struct GemmK {
-    alignas(64) CUtensorMap tm_w;  // [N][K] fp16, box 64 x 128
+    alignas(64) CUtensorMap tm_w;  // fp16: [N][K] half, box 64 x 128; int8: [N][K] bytes, Q4: [N][K/2] bytes, box 128 B x 128
+                                   // (all with the 128-byte swizzle)
+    const uint16_t* q4_scale;      // Q4: [N][K/32] fp16 block scales (read by the dequantising warps)
     alignas(64) CUtensorMap tm_x;  // [M][K] fp16, box 64 x BN
     alignas(64) CUtensorMap tm_out;  // [M][ld_out] fp16, box 128 x BN (dense), when tma_store
     int tma_store;                   // plain-store epilogue through shared memory and one tensor store per tile
@@ -52,6 +57,7 @@ struct GemmK {
     int bn;        // tokens per tile (multiple of 16, <= 256)
     int ntok;      // token tiles
     int stages;
+    int raw_stages;  // packed weights: depth of their own, deeper ring (covers the HBM latency)
     int tmem_cols; // power of two >= bn
     int epi;       // EPI_STORE or EPI_RESIDUAL
     int* status;
@@ -128,7 +134,12 @@ __device__ __forceinline__ uint32_t instr_desc_f16(int bn) {
     return d;
 }
 
-__global__ void __launch_bounds__(GEMM_THREADS) linear_gemm_tc_kernel(const __grid_constant__ GemmK g) {
+// WFMT = FMT_FP16: the weight operand is loaded by TMA as it is.  FMT_INT8 / FMT_Q4: TMA brings the
+// packed rows of a stage, four more warps expand them to fp16 straight into the MMA's swizzled
+// operand layout (int8 codes are exact in fp16 and the row scale is applied in the epilogue; a Q4
+// weight becomes fp16(code * block scale)), so a quantised weight is read from HBM once, packed.
+template <int WFMT>
+__global__ void __launch_bounds__(WFMT == FMT_FP16 ? GEMM_THREADS : GEMM_THREADS_Q) linear_gemm_tc_kernel(const __grid_constant__ GemmK g) {
     extern __shared__ __align__(128) uint8_t smem[];
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const uint32_t s_base = smem_u32(smem);
@@ -145,18 +156,28 @@ __global__ void __launch_bounds__(GEMM_THREADS) linear_gemm_tc_kernel(const __gr
     // header: full[S] @0, empty[S] @64, acc_full[2] @128, acc_empty[2] @144, tensor-memory address @160,
     // residual-tile barrier @176
     const uint32_t full0 = s_base, empty0 = s_base + 64, acc_full0 = s_base + 128, acc_empty0 = s_base + 144, tmem_slot = s_base + 160;
-    const uint32_t res_bar = s_base + 176;
+    const uint32_t res_bar = s_base + 176, raw_full0 = s_base + 192, raw_empty0 = s_base + 256;  // up to 8 packed stages
     const uint32_t ring = (s_base + 1024u + 1023u) & ~1023u;
     const int b_bytes = g_bn * BK * 2;
+    // Packed weights arrive in spans of 128 bytes per row (int8: two K blocks, Q4: four), so that the
+    // HBM reads are 128-byte pieces rather than 32- or 64-byte ones; 128-byte swizzle, like the operands.
+    constexpr int RAW_SPAN = WFMT == FMT_INT8 ? 2 : 4;       // K blocks per packed stage
+    constexpr int RAW_BYTES = WFMT == FMT_FP16 ? 0 : BM * 128;
     const int stage_bytes = A_BYTES + ((b_bytes + 1023) / 1024) * 1024;
+    const int g_raw_stages = g.raw_stages;
     const int nkb = (g.K + BK - 1) / BK;
-    const uint32_t out_stage = ring + (uint32_t)(g_stages * stage_bytes);  // [BN][128] fp16 staging of one output tile
+    const uint32_t raw_ring = ring + (uint32_t)(g_stages * stage_bytes);        // packed weight stages
+    const uint32_t out_stage = raw_ring + (uint32_t)(g_raw_stages * RAW_BYTES);  // fp16 staging of one output slab
     const int ntiles = ((gN + BM - 1) / BM) * g_ntok;
 
     if (tid == 0) {
         for (int s = 0; s < g_stages; ++s) {
-            mbar_init(full0 + s * 8, 1);
+            mbar_init(full0 + s * 8, WFMT == FMT_FP16 ? 1 : 1 + DQ_WARPS);  // operands ready: TMA bytes (+ the expanding warps)
             mbar_init(empty0 + s * 8, 1);
+        }
+        for (int r = 0; r < g_raw_stages; ++r) {
+            mbar_init(raw_full0 + r * 8, 1);
+            mbar_init(raw_empty0 + r * 8, DQ_WARPS);
         }
         for (int a = 0; a < 2; ++a) {
             mbar_init(acc_full0 + a * 8, 1);
@@ -187,8 +208,12 @@ __global__ void __launch_bounds__(GEMM_THREADS) linear_gemm_tc_kernel(const __gr
                         break;
                     }
                     const uint32_t dst = ring + s * stage_bytes;
-                    mbar_arrive_expect_tx(full0 + s * 8, (uint32_t)(A_BYTES + b_bytes));
-                    tma_load_2d(dst, &g.tm_w, kb * BK, wt * BM, full0 + s * 8, policy);
+                    if (WFMT == FMT_FP16) {
+                        mbar_arrive_expect_tx(full0 + s * 8, (uint32_t)(A_BYTES + b_bytes));
+                        tma_load_2d(dst, &g.tm_w, kb * BK, wt * BM, full0 + s * 8, policy);
+                    } else {
+                        mbar_arrive_expect_tx(full0 + s * 8, (uint32_t)b_bytes);  // the weight half comes from the expanding warps
+                    }
                     tma_load_2d(dst + A_BYTES, &g.tm_x, kb * BK, tt * g_bn, full0 + s * 8, policy);
                 }
             }
@@ -224,11 +249,138 @@ __global__ void __launch_bounds__(GEMM_THREADS) linear_gemm_tc_kernel(const __gr
                 umma_commit(acc_full0 + acc * 8);  // this tile's accumulator is complete
             }
         }
+    } else if (WFMT != FMT_FP16 && warp == 2 + EPI_WARPS + DQ_WARPS) {
+        // ---- packed-weight producer: runs g_raw_stages ahead of the expanding warps ----
+        if (lane == 0) {
+            const uint64_t policy = l2_policy_evict_first();
+            int it = 0;
+            bool ok = true;
+            for (int tile = blockIdx.x; tile < ntiles && ok; tile += gridDim.x) {
+                const int wt = tile / g_ntok;
+                for (int sp = 0; sp * RAW_SPAN < nkb; ++sp, ++it) {
+                    const int r = it % g_raw_stages;
+                    if (it >= g_raw_stages && !mbar_wait_bounded(raw_empty0 + r * 8, (uint32_t)(((it / g_raw_stages) - 1) & 1))) {
+                        *reinterpret_cast<volatile int*>(g_status) = 11;
+                        ok = false;
+                        break;
+                    }
+                    mbar_arrive_expect_tx(raw_full0 + r * 8, (uint32_t)RAW_BYTES);
+                    tma_load_2d(raw_ring + r * RAW_BYTES, &g.tm_w, sp * 128, wt * BM, raw_full0 + r * 8, policy);
+                }
+            }
+        }
+    } else if (WFMT != FMT_FP16 && warp >= 2 + EPI_WARPS) {
+        // ---- expanding warps: packed stage -> fp16 rows in the operand's swizzled layout ----
+        // Operand layout (K-major, 128-byte swizzle): row r of the stage at (r / 8) * 1024 + (r % 8) * 128,
+        // its 16-byte piece c at ((c ^ (r % 8)) * 16).
+        const int dt = tid - (2 + EPI_WARPS) * 32;   // 0 .. DQ_WARPS * 32 - 1
+        constexpr int DQ_THREADS = DQ_WARPS * 32;
+        const int K32 = g.K / 32;
+        const uint16_t* const q4s = g.q4_scale;
+        int it = 0, rit = 0;   // operand stages and packed spans consumed so far
+        bool ok = true;
+        constexpr int Q4_PASSES = BM * 2 / DQ_THREADS, I8_PASSES = BM * 4 / DQ_THREADS;
+        // Q4: a thread expands the same weight row and the same half (blk) of every stage, so its
+        // block scales are every other entry of the row's scale vector: one aligned 16-byte load
+        // brings the eight scales of four stages, fetched four stages ahead of their use
+        // (rows whose scale vector is not a multiple of 16 bytes take two-byte loads).
+        static_assert(Q4_PASSES == 1 || WFMT != FMT_Q4, "one Q4 task per thread and stage");
+        const int q_row_in_tile = dt >> 1, q_blk = dt & 1;
+        const bool q4_vec = (K32 % 8) == 0 && (reinterpret_cast<uintptr_t>(q4s) & 15) == 0;
+        uint4 sv_cur = make_uint4(0, 0, 0, 0), sv_next = make_uint4(0, 0, 0, 0);
+        auto load_group = [&](int tile, int grp) {   // scales 8 grp .. 8 grp + 7 of this thread's row
+            const int row = (tile / g_ntok) * BM + q_row_in_tile;
+            if (tile < ntiles && row < gN && grp * 8 < K32) return *reinterpret_cast<const uint4*>(q4s + (size_t)row * K32 + grp * 8);
+            return make_uint4(0, 0, 0, 0);
+        };
+        if (WFMT == FMT_Q4 && q4_vec) sv_next = load_group(blockIdx.x, 0);
+        for (int tile = blockIdx.x; tile < ntiles && ok; tile += gridDim.x) {
+            for (int kb = 0; kb < nkb; ++kb, ++it) {
+                const int s = it % g_stages;
+                uint16_t sc[1] = {0};
+                if (WFMT == FMT_Q4) {
+                    if (q4_vec) {
+                        if ((kb & 3) == 0) {
+                            sv_cur = sv_next;
+                            sv_next = (kb + 4 < nkb) ? load_group(tile, (kb >> 2) + 1) : load_group(tile + (int)gridDim.x, 0);
+                        }
+                        const int e = (kb & 3) * 2 + q_blk;   // entry of the current group
+                        const uint32_t w32 = e < 2 ? sv_cur.x : e < 4 ? sv_cur.y : e < 6 ? sv_cur.z : sv_cur.w;
+                        sc[0] = (uint16_t)((e & 1) ? (w32 >> 16) : (w32 & 0xFFFFu));
+                    } else {
+                        const int row = (tile / g_ntok) * BM + q_row_in_tile, blk = kb * 2 + q_blk;
+                        if (row < gN && blk < K32) sc[0] = q4s[(size_t)row * K32 + blk];
+                    }
+                }
+                const int r = rit % g_raw_stages, jspan = kb % RAW_SPAN;
+                // the packed span has landed (first K block of the span), and the MMAs that read this
+                // operand slot last are done
+                if ((jspan == 0 && !mbar_wait_bounded(raw_full0 + r * 8, (uint32_t)((rit / g_raw_stages) & 1))) ||
+                    (it >= g_stages && !mbar_wait_bounded(empty0 + s * 8, (uint32_t)(((it / g_stages) - 1) & 1)))) {
+                    if (lane == 0) *reinterpret_cast<volatile int*>(g_status) = 10;
+                    ok = false;
+                    break;
+                }
+                const uint32_t a_addr = ring + s * stage_bytes, raw = raw_ring + r * RAW_BYTES;
+                if (WFMT == FMT_INT8) {
+#pragma unroll
+                    for (int ps = 0; ps < I8_PASSES; ++ps) {
+                        const int task = ps * DQ_THREADS + dt, row = task >> 2, ch = task & 3;  // 16 codes = 16 k
+                        uint32_t w0, w1, w2, w3;
+                        asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(w0), "=r"(w1), "=r"(w2), "=r"(w3) : "r"(raw + (uint32_t)((row >> 3) * 1024 + (row & 7) * 128) + (((uint32_t)(jspan * 4 + ch) ^ (uint32_t)(row & 7)) << 4)));
+                        uint32_t h[8];
+                        int8x4_to_half2x2(w0, h[0], h[1]);
+                        int8x4_to_half2x2(w1, h[2], h[3]);
+                        int8x4_to_half2x2(w2, h[4], h[5]);
+                        int8x4_to_half2x2(w3, h[6], h[7]);
+                        const uint32_t rbase = a_addr + (uint32_t)((row >> 3) * 1024 + (row & 7) * 128);
+                        const uint32_t x7 = (uint32_t)(row & 7);
+                        asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(rbase + (((uint32_t)(2 * ch) ^ x7) << 4)), "r"(h[0]), "r"(h[1]), "r"(h[2]), "r"(h[3]) : "memory");
+                        asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(rbase + (((uint32_t)(2 * ch + 1) ^ x7) << 4)), "r"(h[4]), "r"(h[5]), "r"(h[6]), "r"(h[7]) : "memory");
+                    }
+                } else {
+#pragma unroll
+                    for (int ps = 0; ps < Q4_PASSES; ++ps) {
+                        const int task = ps * DQ_THREADS + dt, row = task >> 1, blk = task & 1;  // 32 nibbles = one scale block
+                        uint32_t w[4];
+                        asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(w[0]), "=r"(w[1]), "=r"(w[2]), "=r"(w[3]) : "r"(raw + (uint32_t)((row >> 3) * 1024 + (row & 7) * 128) + (((uint32_t)(jspan * 2 + blk) ^ (uint32_t)(row & 7)) << 4)));
+                        const __half sh = __ushort_as_half(sc[ps]);
+                        const __half2 s2 = __halves2half2(sh, sh);
+                        const uint32_t rbase = a_addr + (uint32_t)((row >> 3) * 1024 + (row & 7) * 128);
+                        const uint32_t x7 = (uint32_t)(row & 7);
+#pragma unroll
+                        for (int j = 0; j < 4; ++j) {
+                            uint32_t p04, p15, p26, p37;
+                            q4x8_to_half2x4(w[j], p04, p15, p26, p37);   // (n0,n4) (n1,n5) (n2,n6) (n3,n7), exact codes
+                            uint32_t o[4];
+                            asm("prmt.b32 %0, %1, %2, 0x5410;" : "=r"(o[0]) : "r"(p04), "r"(p15));  // (n0, n1)
+                            asm("prmt.b32 %0, %1, %2, 0x5410;" : "=r"(o[1]) : "r"(p26), "r"(p37));  // (n2, n3)
+                            asm("prmt.b32 %0, %1, %2, 0x7632;" : "=r"(o[2]) : "r"(p04), "r"(p15));  // (n4, n5)
+                            asm("prmt.b32 %0, %1, %2, 0x7632;" : "=r"(o[3]) : "r"(p26), "r"(p37));  // (n6, n7)
+#pragma unroll
+                            for (int e = 0; e < 4; ++e) {
+                                const __half2 v = __hmul2(*reinterpret_cast<const __half2*>(&o[e]), s2);  // fp16(code * scale)
+                                o[e] = *reinterpret_cast<const uint32_t*>(&v);
+                            }
+                            asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(rbase + (((uint32_t)(4 * blk + j) ^ x7) << 4)), "r"(o[0]), "r"(o[1]), "r"(o[2]), "r"(o[3]) : "memory");
+                        }
+                    }
+                }
+                fence_async_smem();   // the MMA reads the operand through the async proxy
+                __syncwarp();
+                if (lane == 0) mbar_arrive(full0 + s * 8);
+                if (jspan == RAW_SPAN - 1 || kb == nkb - 1) {   // last K block of the span: hand it back
+                    if (lane == 0) mbar_arrive(raw_empty0 + r * 8);
+                    ++rit;
+                }
+            }
+        }
     } else {
         // ---- epilogue warps: warp w owns accumulator lanes 32 (w % 4) .. +31 ----
         const int q = warp & 3;
-        int tl = 0;
+        int tl = 0, n_stores = 0;
         bool failed = false;
+        const int g_out_box = min(g_bn, OUT_ROWS);
         for (int tile = blockIdx.x; tile < ntiles; tile += gridDim.x, ++tl) {
             const int wt = tile / g_ntok, tt = tile - wt * g_ntok;
             const int n0 = wt * BM, m0 = tt * g_bn, acc = tl & 1;
@@ -246,59 +398,66 @@ __global__ void __launch_bounds__(GEMM_THREADS) linear_gemm_tc_kernel(const __gr
                 const int n = n0 + q * 32 + lane;
                 const float rs = (g_rs && n < gN) ? __half2float(__ushort_as_half(g_rs[n])) : 1.0f;
                 const uint32_t tmem_d = tmem_base + (uint32_t)(acc * g_cols) + ((uint32_t)(q * 32) << 16);
-                if (tl > 0) {
-                    // the previous tile's store must have finished reading the staging buffer
-                    if (warp == 2 && lane == 0) bulk_wait_read0();
-                    asm volatile("bar.sync 2, %0;" ::"n"(EPI_WARPS * 32) : "memory");
-                }
-                if (g_epi == EPI_RESIDUAL) {
-                    if (warp == 2 && lane == 0) {
-                        mbar_arrive_expect_tx(res_bar, (uint32_t)(g_bn * BM * 2));
-                        tma_load_2d(out_stage, &g.tm_out, n0, m0, res_bar, l2_policy_evict_normal());
-                    }
-                    if (!mbar_wait_bounded(res_bar, (uint32_t)(tl & 1))) {
-                        failed = true;
-                        if (lane == 0) *reinterpret_cast<volatile int*>(g_status) = 9;
-                    }
-                }
                 const uint32_t dst0 = out_stage + (uint32_t)((q * 32 + lane) * 2);
-                for (int c = 0; c < g_bn; c += 32) {
-                    uint32_t r[32];
-                    tmem_ld32(tmem_d + (uint32_t)c, r);
-#pragma unroll
-                    for (int j = 0; j < 32; ++j) {
-                        float v = __uint_as_float(r[j]) * rs;
-                        const uint32_t addr = dst0 + (uint32_t)((c + j) * (BM * 2));
-                        if (g_epi == EPI_RESIDUAL) {
-                            uint16_t old;
-                            asm volatile("ld.shared.u16 %0, [%1];" : "=h"(old) : "r"(addr) : "memory");
-                            v = __half2float(__ushort_as_half(old)) + v;
-                        }
-                        const uint16_t hv = __half_as_ushort(__float2half_rn(v));
-                        asm volatile("st.shared.u16 [%0], %1;" ::"r"(addr), "h"(hv) : "memory");
+                // the tile leaves in slabs of at most OUT_ROWS tokens (the staging buffer's height)
+                for (int h0 = 0; h0 < g_bn; h0 += OUT_ROWS) {
+                    const int hrows = min(OUT_ROWS, g_bn - h0);
+                    if (n_stores > 0) {
+                        // the previous slab's store must have finished reading the staging buffer
+                        if (warp == 2 && lane == 0) bulk_wait_read0();
+                        asm volatile("bar.sync 2, %0;" ::"n"(EPI_WARPS * 32) : "memory");
                     }
-                }
-                // the accumulator is free as soon as it has been read
-                tc_fence_before();
-                __syncwarp();
-                if (lane == 0) mbar_arrive(acc_empty0 + acc * 8);
-                fence_async_smem();
-                asm volatile("bar.sync 2, %0;" ::"n"(EPI_WARPS * 32) : "memory");
-                if (warp == 2 && lane == 0) tma_store_2d(&g.tm_out, out_stage, n0, m0);
-                if (g_npeer > 0) {
-                    // peers get the tile in 16-byte pieces, 256 contiguous bytes per token row
-                    const int et = (warp - 2) * 32 + lane;
-                    const int rows = min(g_bn, gM - m0);
-                    for (int i = et; i < rows * 16; i += EPI_WARPS * 32) {
-                        const int mr = i >> 4, ch = i & 15;
-                        if (n0 + ch * 8 >= gN) continue;
-                        uint4 v;
-                        asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
-                                     : "r"(out_stage + (uint32_t)(mr * (BM * 2) + ch * 16)) : "memory");
-                        const size_t o = (size_t)(m0 + mr) * g_ld + n0 + ch * 8;
+                    if (g_epi == EPI_RESIDUAL) {
+                        if (warp == 2 && lane == 0) {
+                            mbar_arrive_expect_tx(res_bar, (uint32_t)(g_out_box * BM * 2));
+                            tma_load_2d(out_stage, &g.tm_out, n0, m0 + h0, res_bar, l2_policy_evict_normal());
+                        }
+                        if (!mbar_wait_bounded(res_bar, (uint32_t)(n_stores & 1))) {
+                            failed = true;
+                            if (lane == 0) *reinterpret_cast<volatile int*>(g_status) = 9;
+                        }
+                    }
+                    for (int c = 0; c < hrows; c += 32) {
+                        uint32_t r[32];
+                        tmem_ld32(tmem_d + (uint32_t)(h0 + c), r);
 #pragma unroll
-                        for (int p = 0; p < 7; ++p)
-                            if (p < g_npeer) *reinterpret_cast<uint4*>(g_peer[p] + o) = v;
+                        for (int j = 0; j < 32; ++j) {
+                            float v = __uint_as_float(r[j]) * rs;
+                            const uint32_t addr = dst0 + (uint32_t)((c + j) * (BM * 2));
+                            if (g_epi == EPI_RESIDUAL) {
+                                uint16_t old;
+                                asm volatile("ld.shared.u16 %0, [%1];" : "=h"(old) : "r"(addr) : "memory");
+                                v = __half2float(__ushort_as_half(old)) + v;
+                            }
+                            const uint16_t hv = __half_as_ushort(__float2half_rn(v));
+                            asm volatile("st.shared.u16 [%0], %1;" ::"r"(addr), "h"(hv) : "memory");
+                        }
+                    }
+                    if (h0 + OUT_ROWS >= g_bn) {
+                        // the accumulator is free as soon as its last columns have been read
+                        tc_fence_before();
+                        __syncwarp();
+                        if (lane == 0) mbar_arrive(acc_empty0 + acc * 8);
+                    }
+                    fence_async_smem();
+                    asm volatile("bar.sync 2, %0;" ::"n"(EPI_WARPS * 32) : "memory");
+                    if (warp == 2 && lane == 0) tma_store_2d(&g.tm_out, out_stage, n0, m0 + h0);
+                    ++n_stores;
+                    if (g_npeer > 0) {
+                        // peers get the slab in 16-byte pieces, 256 contiguous bytes per token row
+                        const int et = (warp - 2) * 32 + lane;
+                        const int rows = min(hrows, gM - m0 - h0);
+                        for (int i = et; i < rows * 16; i += EPI_WARPS * 32) {
+                            const int mr = i >> 4, ch = i & 15;
+                            if (n0 + ch * 8 >= gN) continue;
+                            uint4 v;
+                            asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+                                         : "r"(out_stage + (uint32_t)(mr * (BM * 2) + ch * 16)) : "memory");
+                            const size_t o = (size_t)(m0 + h0 + mr) * g_ld + n0 + ch * 8;
+#pragma unroll
+                            for (int p = 0; p < 7; ++p)
+                                if (p < g_npeer) *reinterpret_cast<uint4*>(g_peer[p] + o) = v;
+                        }
                     }
                 }
                 continue;
@@ -340,73 +499,58 @@ __global__ void __launch_bounds__(GEMM_THREADS) linear_gemm_tc_kernel(const __gr
     if (tid == 0 && g.sig.world > 0) gather_signal_block_done(g.sig);
 }
 
-// fp16 copy of a quantised weight for the tensor-core path.
-template <int FMT>
-__global__ void dequant_half_kernel(const uint8_t* __restrict__ W, const uint16_t* __restrict__ scale, uint16_t* __restrict__ out, int N, int K) {
-    const size_t total = (size_t)N * K / 8;  // 8 outputs per thread step
-    for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
-        const size_t e = i * 8, n = e / K;
-        const int k = (int)(e - n * K);
-        uint16_t h[8];
-        if (FMT == FMT_INT8) {
-            const uint2 v = *reinterpret_cast<const uint2*>(W + e);
-            const int8_t* q = reinterpret_cast<const int8_t*>(&v);
-#pragma unroll
-            for (int j = 0; j < 8; ++j) h[j] = __half_as_ushort(__int2half_rn((int)q[j]));  // exact; scale goes to the epilogue
-        } else {
-            const uint32_t v = *reinterpret_cast<const uint32_t*>(W + n * (size_t)(K / 2) + (k >> 1));
-            const float s = __half2float(__ushort_as_half(scale[n * (size_t)(K / 32) + (k >> 5)]));
-#pragma unroll
-            for (int j = 0; j < 8; ++j) h[j] = __half_as_ushort(__float2half_rn((float)((int)((v >> (4 * j)) & 0xF) - 8) * s));
-        }
-        *reinterpret_cast<uint4*>(out + e) = *reinterpret_cast<const uint4*>(h);
-    }
-}
-
 }  // namespace
 
 cudaError_t gemm_tc_configure() {
-    return cudaFuncSetAttribute(linear_gemm_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+    cudaError_t e = cudaFuncSetAttribute(linear_gemm_tc_kernel<FMT_FP16>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+    if (e != cudaSuccess) return e;
+    e = cudaFuncSetAttribute(linear_gemm_tc_kernel<FMT_INT8>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+    if (e != cudaSuccess) return e;
+    return cudaFuncSetAttribute(linear_gemm_tc_kernel<FMT_Q4>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
 }
 
-bool gemm_tc_supported(int M, int N, int K, const void* x, const void* W, const void* out) {
+bool gemm_tc_supported(int fmt, int M, int N, int K, const void* x, const void* W, const void* out) {
     if (M <= 16 || N < 1 || K < 64 || (K % 8) != 0) return false;
+    if (fmt == FMT_INT8 && (K % 16) != 0) return false;   // packed rows keep a 16-byte pitch for the tensor copies
+    if (fmt == FMT_Q4 && (K % 32) != 0) return false;
     auto al16 = [](const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; };
     return al16(x) && al16(W) && out != nullptr;
 }
 
-cudaError_t launch_dequant_half(int fmt, int N, int K, const void* W, const uint16_t* scale, uint16_t* out, cudaStream_t st) {
-    const size_t total = (size_t)N * K / 8;
-    size_t blocks = (total + 255) / 256;
-    if (blocks > 148 * 16) blocks = 148 * 16;
-    if (blocks < 1) blocks = 1;
-    if (fmt == FMT_INT8) dequant_half_kernel<FMT_INT8><<<(unsigned)blocks, 256, 0, st>>>((const uint8_t*)W, scale, out, N, K);
-    else dequant_half_kernel<FMT_Q4><<<(unsigned)blocks, 256, 0, st>>>((const uint8_t*)W, scale, out, N, K);
-    return cudaGetLastError();
-}
-
-cudaError_t launch_gemm_tc(const uint16_t* W_half, const uint16_t* row_scale, const uint16_t* x, uint16_t* out, int M, int N, int K,
+cudaError_t launch_gemm_tc(int fmt, const void* W, const uint16_t* scale, const uint16_t* x, uint16_t* out, int M, int N, int K,
                            int ld_out, int epi, int* status, uint16_t* const* peer_out, int npeer, const GatherSignal* sig, cudaStream_t st) {
     GemmK g;
+    const uint16_t* row_scale = fmt == FMT_INT8 ? scale : nullptr;
+    g.q4_scale = fmt == FMT_Q4 ? scale : nullptr;
     g.sig = GatherSignal{};
     if (sig) g.sig = *sig;
     if (npeer < 0 || npeer > 7) return cudaErrorInvalidValue;
     g.npeer = npeer;
     for (int p = 0; p < 7; ++p) g.peer_out[p] = p < npeer ? peer_out[p] : nullptr;
-    int bn = M >= 256 ? 256 : ((M + 15) / 16) * 16;
+    const int bn_max = 256;
+    int bn = M >= bn_max ? bn_max : ((M + 15) / 16) * 16;
     g.bn = bn;
     g.ntok = (M + bn - 1) / bn;
     g.tmem_cols = 32;
     while (g.tmem_cols < bn) g.tmem_cols *= 2;
     const int b_bytes = ((bn * BK * 2 + 1023) / 1024) * 1024;
+    const int raw_bytes = fmt == FMT_FP16 ? 0 : BM * 128;  // packed spans: 128 bytes of each of the tile's rows
     const int stage_bytes = A_BYTES + b_bytes;
     // The epilogue goes through a staging tile in shared memory and one tensor store per tile
     // when the output rows keep 16-byte pitch and alignment (lane-by-lane stores otherwise).
     bool aligned = (ld_out % 8) == 0 && (reinterpret_cast<uintptr_t>(out) & 15) == 0;
     for (int p = 0; p < npeer; ++p) aligned = aligned && (reinterpret_cast<uintptr_t>(peer_out[p]) & 15) == 0;
     g.tma_store = aligned ? 1 : 0;
-    const int out_bytes = g.tma_store ? ((bn + 31) / 32) * 32 * BM * 2 : 0;  // the epilogue reads 32 columns at a time
-    int stages = (227 * 1024 - 2048 - out_bytes) / stage_bytes;
+    const int out_rows = bn < OUT_ROWS ? ((bn + 31) / 32) * 32 : OUT_ROWS;  // the epilogue reads 32 columns at a time
+    const int out_bytes = g.tma_store ? out_rows * BM * 2 : 0;
+    // packed weights get a ring of their own, deep enough to cover the HBM latency
+    int raw_stages = 0;
+    if (raw_bytes) {
+        raw_stages = 4;
+        while (raw_stages > 2 && (227 * 1024 - 2048 - out_bytes - raw_stages * raw_bytes) / stage_bytes < 3) --raw_stages;
+    }
+    g.raw_stages = raw_stages;
+    int stages = (227 * 1024 - 2048 - out_bytes - raw_stages * raw_bytes) / stage_bytes;
     if (stages > 6) stages = 6;
     if (stages < 2) return cudaErrorInvalidValue;
     g.stages = stages;
@@ -415,14 +559,20 @@ cudaError_t launch_gemm_tc(const uint16_t* W_half, const uint16_t* row_scale, co
     g.M = M; g.N = N; g.K = K; g.ld_out = ld_out;
     g.epi = epi;
     g.status = status;
-    if (!encode_tiled_2d(&g.tm_w, /*fp16*/ true, W_half, (uint64_t)K, (uint64_t)N, (uint64_t)K * 2, BK, BM)) return cudaErrorInvalidValue;
+    bool okw;
+    if (fmt == FMT_FP16) okw = encode_tiled_2d(&g.tm_w, /*fp16*/ true, W, (uint64_t)K, (uint64_t)N, (uint64_t)K * 2, BK, BM);
+    else if (fmt == FMT_INT8) okw = encode_tiled_2d(&g.tm_w, false, W, (uint64_t)K, (uint64_t)N, (uint64_t)K, 128, BM);
+    else okw = encode_tiled_2d(&g.tm_w, false, W, (uint64_t)K / 2, (uint64_t)N, (uint64_t)K / 2, 128, BM);
+    if (!okw) return cudaErrorInvalidValue;
     if (!encode_tiled_2d(&g.tm_x, true, x, (uint64_t)K, (uint64_t)M, (uint64_t)K * 2, BK, bn)) return cudaErrorInvalidValue;
-    if (g.tma_store && !encode_tiled_2d(&g.tm_out, true, out, (uint64_t)N, (uint64_t)M, (uint64_t)ld_out * 2, BM, bn, /*swizzle128=*/false))
+    if (g.tma_store && !encode_tiled_2d(&g.tm_out, true, out, (uint64_t)N, (uint64_t)M, (uint64_t)ld_out * 2, BM, bn < OUT_ROWS ? bn : OUT_ROWS, /*swizzle128=*/false))
         return cudaErrorInvalidValue;
-    const size_t smem = 2048 + (size_t)stages * stage_bytes + out_bytes;
+    const size_t smem = 2048 + (size_t)stages * stage_bytes + (size_t)raw_stages * raw_bytes + out_bytes;
     unsigned grid = (unsigned)(((N + BM - 1) / BM) * g.ntok);
     if (grid > 148u) grid = 148u;  // persistent: one block per SM walks the tiles
-    linear_gemm_tc_kernel<<<grid, GEMM_THREADS, smem, st>>>(g);
+    if (fmt == FMT_FP16) linear_gemm_tc_kernel<FMT_FP16><<<grid, GEMM_THREADS, smem, st>>>(g);
+    else if (fmt == FMT_INT8) linear_gemm_tc_kernel<FMT_INT8><<<grid, GEMM_THREADS_Q, smem, st>>>(g);
+    else linear_gemm_tc_kernel<FMT_Q4><<<grid, GEMM_THREADS_Q, smem, st>>>(g);
     return cudaGetLastError();
 }
 

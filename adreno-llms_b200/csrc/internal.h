@@ -21,8 +21,6 @@ struct nn_context {
     int* status_host = nullptr;                // mapped pinned word written by kernels
     int* status_dev = nullptr;
     unsigned long long* argmax_slot = nullptr;
-    void* gemm_scratch = nullptr;  // fp16 copy of a quantised weight for the tensor-core path
-    size_t gemm_scratch_bytes = 0;
     float* sk_scratch = nullptr;   // partial sums of blocks that share a tile (balanced K-streaming)
     unsigned* sk_flags = nullptr;
     void* flush_buf = nullptr;

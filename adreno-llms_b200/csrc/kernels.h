@@ -95,9 +95,9 @@ bool encode_tiled_2d(void* map, bool half_elems, const void* base, uint64_t dim0
 
 // gemm_tc.cu: tcgen05 / tensor-memory GEMM for M > 16
 cudaError_t gemm_tc_configure();
-bool gemm_tc_supported(int M, int N, int K, const void* x, const void* W, const void* out);
-cudaError_t launch_dequant_half(int fmt, int N, int K, const void* W, const uint16_t* scale, uint16_t* out, cudaStream_t st);
-cudaError_t launch_gemm_tc(const uint16_t* W_half, const uint16_t* row_scale, const uint16_t* x, uint16_t* out, int M, int N, int K,
+bool gemm_tc_supported(int fmt, int M, int N, int K, const void* x, const void* W, const void* out);
+// W in its registered format; scale = int8 row scales / Q4 block scales / null
+cudaError_t launch_gemm_tc(int fmt, const void* W, const uint16_t* scale, const uint16_t* x, uint16_t* out, int M, int N, int K,
                            int ld_out, int epi, int* status, uint16_t* const* peer_out, int npeer, const GatherSignal* sig, cudaStream_t st);
 
 // gemv_generic.cu: any K, any alignment (the reference's gemv_rT_fp32acc role)
