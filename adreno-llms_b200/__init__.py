@@ -67,6 +67,10 @@ def load():
         "nn_dequant": ([vp, i, i, vp, vp], i), "nn_argmax": ([vp, i, vp, vp], i),
         "nn_argmax_static": ([vp, i, vp, vp], i),
         "nn_linear_argmax": ([vp, i, i, vp, vp, vp, vp], i),
+        "nn_rmsnorm": ([vp, i, i, vp, vp, ctypes.c_float, vp], i),
+        "nn_rmsnorm_linear": ([vp, i, i, i, vp, vp, ctypes.c_float, vp, vp], i),
+        "nn_rmsnorm_linear_qkv": ([vp, i, i, vp, vp, ctypes.c_float, vp, i, vp, i, vp, i, vp, vp, vp], i),
+        "nn_rmsnorm_gate_up_silu": ([vp, i, i, i, vp, vp, ctypes.c_float, vp, vp, vp], i),
         "nn_plan_begin": ([vp], i), "nn_plan_end": ([vp, pvp], i), "nn_plan_launch": ([vp, vp], i),
         "nn_plan_num_kernels": ([vp], i), "nn_plan_free": ([vp], i),
         "nn_weights_load": ([vp, cp, cp, pvp], i), "nn_weights_free": ([vp], i),
@@ -189,6 +193,18 @@ class Context:
 
     def linear_argmax(self, N, K, x, W, logits, out_idx):
         _check(self.L.nn_linear_argmax(self.h, N, K, x, W, logits, out_idx))
+
+    def rmsnorm(self, rows, cols, x, weight, eps, out):
+        _check(self.L.nn_rmsnorm(self.h, rows, cols, x, weight, eps, out))
+
+    def rmsnorm_linear(self, M, N, K, x, gamma, eps, W, out):
+        _check(self.L.nn_rmsnorm_linear(self.h, M, N, K, x, gamma, eps, W, out))
+
+    def rmsnorm_linear_qkv(self, M, K, x, gamma, eps, Wq, Nq, Wk, Nk, Wv, Nv, q, k, v):
+        _check(self.L.nn_rmsnorm_linear_qkv(self.h, M, K, x, gamma, eps, Wq, Nq, Wk, Nk, Wv, Nv, q, k, v))
+
+    def rmsnorm_gate_up_silu(self, M, N, K, x, gamma, eps, Wg, Wu, out):
+        _check(self.L.nn_rmsnorm_gate_up_silu(self.h, M, N, K, x, gamma, eps, Wg, Wu, out))
 
     def l2_flush(self):
         _check(self.L.nn_l2_flush(self.h))

@@ -102,6 +102,7 @@ extern "C" int nn_shutdown(nn_context* c) {
     cudaStreamSynchronize(c->stream);
     if (c->flush_buf) cudaFree(c->flush_buf);
     if (c->argmax_slot) cudaFree(c->argmax_slot);
+    if (c->norm_scratch) cudaFree(c->norm_scratch);
     if (c->sk_scratch) cudaFree(c->sk_scratch);
     if (c->sk_flags) cudaFree(c->sk_flags);
     if (c->status_host) cudaFreeHost(c->status_host);
@@ -269,9 +270,42 @@ static int run_gemm_tc(nn_context* c, int fmt, const LinArgs& a, int M, const ch
     return NN_OK;
 }
 
+// The nn_rmsnorm_* entry points are the plain ones with a norm to apply first; they leave it
+// here for run_linear to pick up (one host thread drives a context).
+static thread_local const uint16_t* t_norm_w = nullptr;
+static thread_local float t_norm_eps = 0.f;
+
 static int run_linear(nn_context* c, int fmt, LinArgs a, int M_total, const char* who) {
     a.sk_scratch = c->sk_scratch;
     a.sk_flags = c->sk_flags;
+    a.norm_w = t_norm_w;
+    a.norm_eps = t_norm_eps;
+    t_norm_w = nullptr;
+    if (a.norm_w) {
+        // the prologue is fused into the streaming kernel; every other route normalises into
+        // context scratch first
+        LinArgs probe = a;
+        probe.M = M_total;
+        bool fused = M_total <= 16 && stream_supported(fmt, M_total, a.K, probe);
+        if (fused) fused = stream_plan(fmt, probe, c->sm_count, c->smem_limit).ok;
+        if (!fused) {
+            const size_t need = (size_t)M_total * a.K * 2;
+            if (need > c->norm_scratch_bytes) {
+                if (c->capturing) return NN_FAIL(NN_ERR_UNSUPPORTED, "%s: the norm scratch cannot grow while a plan is being recorded; run the call once before recording", who);
+                cudaSetDevice(c->device);
+                CUDA_TRY(cudaStreamSynchronize(c->stream));
+                if (c->norm_scratch) CUDA_TRY(cudaFree(c->norm_scratch));
+                c->norm_scratch = nullptr;
+                c->norm_scratch_bytes = 0;
+                CUDA_TRY(cudaMalloc(&c->norm_scratch, need));
+                c->norm_scratch_bytes = need;
+            }
+            CUDA_TRY(launch_rmsnorm(a.x, a.norm_w, (uint16_t*)c->norm_scratch, M_total, a.K, a.norm_eps, c->stream));
+            c->launches++;
+            a.x = (const uint16_t*)c->norm_scratch;
+            a.norm_w = nullptr;
+        }
+    }
     if (M_total > 16) {
         bool done = false;
         const int rc = run_gemm_tc(c, fmt, a, M_total, who, &done);
@@ -414,6 +448,44 @@ extern "C" int nn_linear_qkv(nn_context* c, int M, int K, nn_buf x, nn_buf Wq, i
     a.epi = EPI_STORE;
     a.status = c->status_dev;
     return run_linear(c, fmt, a, M, who);
+}
+
+extern "C" int nn_rmsnorm(nn_context* c, int rows, int cols, nn_buf x, nn_buf weight, float eps, nn_buf out) {
+    if (!c || !x || !weight || !out) return NN_FAIL(NN_ERR_ARG, "nn_rmsnorm: null argument");
+    if (rows < 0 || cols <= 0) return NN_FAIL(NN_ERR_ARG, "nn_rmsnorm: bad shape rows=%d cols=%d", rows, cols);
+    if (rows == 0) return NN_OK;
+    CUDA_TRY(launch_rmsnorm((const uint16_t*)x, (const uint16_t*)weight, (uint16_t*)out, rows, cols, eps, c->stream));
+    c->launches++;
+    return NN_OK;
+}
+
+static int with_norm(nn_buf gamma, float eps, const char* who) {
+    if (!gamma) return NN_FAIL(NN_ERR_ARG, "%s: null norm weight", who);
+    t_norm_w = (const uint16_t*)gamma;
+    t_norm_eps = eps;
+    return NN_OK;
+}
+
+extern "C" int nn_rmsnorm_linear(nn_context* c, int M, int N, int K, nn_buf x, nn_buf gamma, float eps, nn_buf W, nn_buf out) {
+    int rc = with_norm(gamma, eps, "nn_rmsnorm_linear");
+    if (rc == NN_OK) rc = one_weight(c, M, N, K, x, W, out, EPI_STORE, "nn_rmsnorm_linear");
+    t_norm_w = nullptr;
+    return rc;
+}
+
+extern "C" int nn_rmsnorm_linear_qkv(nn_context* c, int M, int K, nn_buf x, nn_buf gamma, float eps, nn_buf Wq, int Nq, nn_buf Wk, int Nk,
+                                     nn_buf Wv, int Nv, nn_buf q, nn_buf k, nn_buf v) {
+    int rc = with_norm(gamma, eps, "nn_rmsnorm_linear_qkv");
+    if (rc == NN_OK) rc = nn_linear_qkv(c, M, K, x, Wq, Nq, Wk, Nk, Wv, Nv, q, k, v);
+    t_norm_w = nullptr;
+    return rc;
+}
+
+extern "C" int nn_rmsnorm_gate_up_silu(nn_context* c, int M, int N, int K, nn_buf x, nn_buf gamma, float eps, nn_buf Wg, nn_buf Wu, nn_buf out) {
+    int rc = with_norm(gamma, eps, "nn_rmsnorm_gate_up_silu");
+    if (rc == NN_OK) rc = nn_fused_gate_up_silu(c, M, N, K, x, Wg, Wu, out);
+    t_norm_w = nullptr;
+    return rc;
 }
 
 extern "C" int nn_dequant(nn_context* c, int N, int K, nn_buf W, nn_buf out) {

@@ -58,11 +58,11 @@ struct Geo {  // shared-memory geometry, computed identically on host and device
     int sstride;      // bytes between Q4 scale rows in a stage
     int stage_bytes;  // one stage (multiple of 1024)
     int xstride;      // bytes between activation rows
-    int off_bar, off_x, off_ctab, off_red, off_ring;
+    int off_bar, off_x, off_ctab, off_norm, off_red, off_ring;
     int total;
 };
 
-__host__ __device__ inline Geo make_geo(int fmt, int M, int K, int kcb, int stages, int nt) {
+__host__ __device__ inline Geo make_geo(int fmt, int M, int K, int kcb, int stages, int nt, bool norm) {
     Geo g;
     g.nbox = (kcb + 127) / 128;
     g.sstride = kcb / 8 + 16;
@@ -75,7 +75,9 @@ __host__ __device__ inline Geo make_geo(int fmt, int M, int K, int kcb, int stag
     // Q4: per 32-weight block and token pair one float4 (c0, c1, c0, c1) with c = -72 * (sum of
     // the block's activations), the value the block's accumulator starts from
     g.off_ctab = g.off_x + (((fmt == FMT_INT8 ? 3 * M * g.xstride + 192 : M * g.xstride) + 127) / 128) * 128;
-    g.off_red = g.off_ctab + (fmt == FMT_Q4 ? (K / 32) * ((M + 1) / 2) * 16 : 0);
+    // fused RMSNorm: the normalised fp16 activations [M][K], from which the staging then reads
+    g.off_norm = g.off_ctab + (fmt == FMT_Q4 ? (K / 32) * ((M + 1) / 2) * 16 : 0);
+    g.off_red = g.off_norm + (norm ? ((M * K * 2 + 127) / 128) * 128 : 0);
     g.off_ring = ((g.off_red + 2 * NCW * 32 * 2 * nt * 4 * 4 + 1023) / 1024) * 1024;  // two reduction buffers
     g.total = g.off_ring + stages * g.stage_bytes + 1024;  // slack to align the ring to 1 KB
     return g;
@@ -261,7 +263,8 @@ __global__ void __launch_bounds__(THREADS) linear_stream_kernel(const __grid_con
     const int stages = ka.stages, kcb = a.kcb;
     const bool ksplit = a.kw > 1;  // the four consumers split K of one 32-row tile
     const int rowbytes = ka.rowbytes, nchunks = ka.nchunks;
-    const Geo geo = make_geo(FMT, aM, aK, kcb, stages, NT);
+    const bool a_norm = EXT && a.norm_w != nullptr;
+    const Geo geo = make_geo(FMT, aM, aK, kcb, stages, NT, a_norm);
     const int warp_rows = DUAL ? 16 : WARP_ROWS;                       // rows of each weight per warp
     const int tile_rows = ksplit ? warp_rows : NCW * warp_rows;        // rows of each weight per block tile
     const int groups = ksplit ? (nchunks + NCW - 1) / NCW : nchunks;   // pipeline items per tile
@@ -531,8 +534,57 @@ __global__ void __launch_bounds__(THREADS) linear_stream_kernel(const __grid_con
     const long long tl_wait = clock64();
 #endif
     if (n_items > 0 && writer) prefetch_residual(tile_first);
-    if (FMT == FMT_INT8) stage_x_int8(a.x, aM, aK, xs, geo.xstride, tid, NCW * 32);
-    else stage_x<FMT>(a.x, aM, aK, xs, geo.xstride, reinterpret_cast<float*>(smem + geo.off_ctab), tid, NCW * 32);
+    const uint16_t* x_src = a.x;
+    if (a_norm) {
+        // RMSNorm prologue (src/models/smollm2-135m-instruct/kernels/rmsnorm.cl:27-104 fused into the
+        // projection that reads its output): sum of squares per row, then the normalised fp16 row
+        // goes to shared memory and the staging below reads it from there.
+        uint16_t* xn = reinterpret_cast<uint16_t*>(smem + geo.off_norm);
+        const uint16_t* gw = a.norm_w;
+        const float n_eps = a.norm_eps;
+        const int per_row = aK / 8;
+        for (int m = 0; m < aM; ++m) {
+            float ss = 0.f;
+            for (int p = tid; p < per_row; p += NCW * 32) {
+                const uint4 v = *reinterpret_cast<const uint4*>(a.x + (size_t)m * aK + p * 8);
+                const uint32_t wv[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+                for (int q = 0; q < 4; ++q) {
+                    const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&wv[q]));
+                    ss += f.x * f.x;
+                    ss += f.y * f.y;
+                }
+            }
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+            if (lane == 0) red[warp * 16 + m] = ss;
+        }
+        asm volatile("bar.sync 1, %0;" ::"n"(NCW * 32) : "memory");
+        for (int m = 0; m < aM; ++m) {
+            float tot = 0.f;
+#pragma unroll
+            for (int w2 = 0; w2 < NCW; ++w2) tot += red[w2 * 16 + m];
+            const float inv = 1.0f / sqrtf(tot / (float)aK + n_eps);
+            for (int p = tid; p < per_row; p += NCW * 32) {
+                const uint4 v = *reinterpret_cast<const uint4*>(a.x + (size_t)m * aK + p * 8);
+                const uint4 g4 = *reinterpret_cast<const uint4*>(gw + p * 8);
+                const uint32_t xv[4] = {v.x, v.y, v.z, v.w}, gv[4] = {g4.x, g4.y, g4.z, g4.w};
+                uint32_t o4[4];
+#pragma unroll
+                for (int q = 0; q < 4; ++q) {
+                    const float2 fx = __half22float2(*reinterpret_cast<const __half2*>(&xv[q]));
+                    const float2 fg = __half22float2(*reinterpret_cast<const __half2*>(&gv[q]));
+                    const __half2 h = __floats2half2_rn((fx.x * inv) * fg.x, (fx.y * inv) * fg.y);
+                    o4[q] = *reinterpret_cast<const uint32_t*>(&h);
+                }
+                *reinterpret_cast<uint4*>(xn + (size_t)m * aK + p * 8) = make_uint4(o4[0], o4[1], o4[2], o4[3]);
+            }
+        }
+        asm volatile("bar.sync 1, %0;" ::"n"(NCW * 32) : "memory");
+        x_src = xn;
+    }
+    if (FMT == FMT_INT8) stage_x_int8(x_src, aM, aK, xs, geo.xstride, tid, NCW * 32);
+    else stage_x<FMT>(x_src, aM, aK, xs, geo.xstride, reinterpret_cast<float*>(smem + geo.off_ctab), tid, NCW * 32);
     asm volatile("bar.sync 1, %0;" ::"n"(NCW * 32) : "memory");
 #ifdef NNB_TRACE
     const long long tl_x = clock64();
@@ -972,7 +1024,7 @@ cudaError_t launch_e(const typename KArgsFor<FMT>::type& ka, const StreamPlan& p
 template <int FMT, int NT, bool DUAL>
 cudaError_t launch_t(const typename KArgsFor<FMT>::type& ka, const StreamPlan& p, cudaStream_t st, bool pdl) {
     const LinArgs& a = ka.a;
-    const bool ext = a.streamk || a.npeer > 0 || a.sig.world > 0 || a.argmax_slot != nullptr || a.seg[0].out == nullptr;
+    const bool ext = a.streamk || a.npeer > 0 || a.sig.world > 0 || a.argmax_slot != nullptr || a.seg[0].out == nullptr || a.norm_w != nullptr;
     return ext ? launch_e<FMT, NT, DUAL, true>(ka, p, st, pdl) : launch_e<FMT, NT, DUAL, false>(ka, p, st, pdl);
 }
 
@@ -1076,6 +1128,7 @@ bool stream_supported(int fmt, int M, int K, const LinArgs& a) {
     }
     if (a.epi == EPI_SWIGLU && (!al16(a.W2) || (fmt == FMT_Q4 && (reinterpret_cast<uintptr_t>(a.scale2) & 3)))) return false;
     if (!al16(a.x)) return false;
+    if (a.norm_w && !al16(a.norm_w)) return false;
     return true;
 }
 
@@ -1089,7 +1142,7 @@ bool stream_supported(int fmt, int M, int K, const LinArgs& a) {
 StreamPlan stream_plan(int fmt, const LinArgs& a, int sm_count, size_t smem_limit) {
     StreamPlan p = {};
     const int M = a.M, K = a.K;
-    const bool dual = a.epi == EPI_SWIGLU;
+    const bool dual = a.epi == EPI_SWIGLU, norm = a.norm_w != nullptr;
     const int rb = fmt_row_bytes(fmt, K);
     const int nt = M > 8 ? 2 : 1;
     const int rb_cols = ((rb + 127) / 128) * 128;
@@ -1106,8 +1159,8 @@ StreamPlan stream_plan(int fmt, const LinArgs& a, int sm_count, size_t smem_limi
     }
     kcb = kcb < 128 ? 128 : kcb > 1024 ? 1024 : (kcb / 128) * 128;
     if (kcb > rb_cols) kcb = rb_cols;
-    while ((size_t)make_geo(fmt, M, K, kcb, 2, nt).total > smem_limit && kcb > 128) kcb -= 128;
-    if ((size_t)make_geo(fmt, M, K, kcb, 2, nt).total > smem_limit) { p.ok = false; return p; }
+    while ((size_t)make_geo(fmt, M, K, kcb, 2, nt, norm).total > smem_limit && kcb > 128) kcb -= 128;
+    if ((size_t)make_geo(fmt, M, K, kcb, 2, nt, norm).total > smem_limit) { p.ok = false; return p; }
     const int ntiles = count_tiles(a, kw == 1 ? NCW * warp_rows : warp_rows);
     const int nchunks = (rb + kcb - 1) / kcb;
     const int groups = kw == 1 ? nchunks : (nchunks + NCW - 1) / NCW;
@@ -1122,8 +1175,8 @@ StreamPlan stream_plan(int fmt, const LinArgs& a, int sm_count, size_t smem_limi
     for (int ps = ps_first; ps >= 1 && !per_sm; --ps) {
         const size_t budget = (smem_limit + 1024) / ps - 1024;
         int st = stages >= 2 && stages <= 8 ? stages : (ps >= 2 ? 4 : 6);
-        while (st > 2 && (size_t)make_geo(fmt, M, K, kcb, st, nt).total > budget) --st;
-        if ((size_t)make_geo(fmt, M, K, kcb, st, nt).total > budget) continue;
+        while (st > 2 && (size_t)make_geo(fmt, M, K, kcb, st, nt, norm).total > budget) --st;
+        if ((size_t)make_geo(fmt, M, K, kcb, st, nt, norm).total > budget) continue;
         if (!(stages >= 2 && stages <= 8)) {
             const int resident = sm_count * ps;
             const int items = ((ntiles + resident - 1) / resident) * groups;  // pipeline items of the busiest block
@@ -1135,7 +1188,7 @@ StreamPlan stream_plan(int fmt, const LinArgs& a, int sm_count, size_t smem_limi
     }
     if (per_sm == 0) { p.ok = false; return p; }
     stages = p.stages;
-    Geo g = make_geo(fmt, M, K, kcb, stages, nt);
+    Geo g = make_geo(fmt, M, K, kcb, stages, nt, norm);
     const int resident = sm_count * per_sm;
     const int waves = (ntiles + resident - 1) / resident;
     p.grid = waves > 0 ? (ntiles + waves - 1) / waves : 1;

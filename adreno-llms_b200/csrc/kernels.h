@@ -63,6 +63,10 @@ struct LinArgs {
     // balanced K-streaming: block b takes pipeline items [b T / G, (b+1) T / G) of the launch's
     // T = tiles x K-groups items, so a tile may be shared by neighbouring blocks; the block that
     // holds the head of a tile adds the others' fp32 partial sums (fixed order) and stores it
+    // optional RMSNorm of the activations before the projection (fused prologue):
+    // x_used[m][k] = half((x[m][k] * rsqrt(mean_k x[m]^2 + eps)) * norm_w[k])
+    const uint16_t* norm_w;  // fp16 [K], null = no norm
+    float norm_eps;
     float* sk_scratch;    // [blocks][consumer threads][2 * NT * 4] partial sums
     unsigned* sk_flags;   // [blocks] "partial written", consumed and cleared by the tile's owner
     int streamk;
@@ -120,5 +124,6 @@ cudaError_t launch_argmax_half(const uint16_t* v, int n, int* out_idx, unsigned 
 cudaError_t launch_fill_u64(unsigned long long* p, unsigned long long v, cudaStream_t st);
 cudaError_t launch_argmax_finish(const unsigned long long* slot, int* out_idx, cudaStream_t st);
 cudaError_t launch_l2_flush(void* buf, size_t bytes, cudaStream_t st);
+cudaError_t launch_rmsnorm(const uint16_t* x, const uint16_t* w, uint16_t* out, int rows, int cols, float eps, cudaStream_t st);
 
 }  // namespace nnb

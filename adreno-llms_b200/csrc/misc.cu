@@ -76,6 +76,27 @@ __global__ void argmax_finish_kernel(const unsigned long long* slot, int* out_id
     *out_idx = k ? (int)(0xFFFFFFFFu - (unsigned int)(k & 0xFFFFFFFFull)) : -1;
 }
 
+// RMSNorm on fp16 storage, one block per row: out = half((x * rsqrt(mean(x^2) + eps)) * weight)
+// (src/models/smollm2-135m-instruct/kernels/rmsnorm.cl:27-104; fp32 sums, a different but fixed order).
+__global__ void rmsnorm_kernel(const uint16_t* __restrict__ x, const uint16_t* __restrict__ w, uint16_t* __restrict__ out, int cols, float eps) {
+    const uint16_t* xr = x + (size_t)blockIdx.x * cols;
+    uint16_t* orow = out + (size_t)blockIdx.x * cols;
+    float ss = 0.f;
+    for (int c = threadIdx.x; c < cols; c += blockDim.x) {
+        const float v = h2f(xr[c]);
+        ss += v * v;
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+    __shared__ float part[32];
+    if ((threadIdx.x & 31) == 0) part[threadIdx.x >> 5] = ss;
+    __syncthreads();
+    float tot = 0.f;
+    for (int i = 0; i < (int)(blockDim.x >> 5); ++i) tot += part[i];
+    const float inv = 1.0f / sqrtf(tot / (float)cols + eps);
+    for (int c = threadIdx.x; c < cols; c += blockDim.x) orow[c] = __half_as_ushort(__float2half_rn((h2f(xr[c]) * inv) * h2f(w[c])));
+}
+
 __global__ void l2_flush_kernel(uint4* buf, size_t n16) {
     for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < n16; i += (size_t)gridDim.x * blockDim.x) {
         uint4 v = buf[i];
@@ -119,6 +140,12 @@ cudaError_t launch_argmax_half(const uint16_t* v, int n, int* out_idx, unsigned 
         if ((e = cudaGetLastError()) != cudaSuccess) return e;
     }
     return launch_argmax_finish(slot, out_idx, st);
+}
+
+cudaError_t launch_rmsnorm(const uint16_t* x, const uint16_t* w, uint16_t* out, int rows, int cols, float eps, cudaStream_t st) {
+    if (rows <= 0 || cols <= 0) return cudaSuccess;
+    rmsnorm_kernel<<<(unsigned)rows, 256, 0, st>>>(x, w, out, cols, eps);
+    return cudaGetLastError();
 }
 
 cudaError_t launch_l2_flush(void* buf, size_t bytes, cudaStream_t st) {

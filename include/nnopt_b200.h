@@ -116,6 +116,20 @@ int nn_fused_gate_up_silu(nn_context* ctx, int M, int N, int K, nn_buf x, nn_buf
 int nn_linear_qkv(nn_context* ctx, int M, int K, nn_buf x, nn_buf Wq, int Nq, nn_buf Wk, int Nk, nn_buf Wv, int Nv,
                   nn_buf q, nn_buf k, nn_buf v);
 
+/* RMSNorm on fp16 storage: out[r,c] = half( (x[r,c] * rsqrt(mean_c x[r,c]^2 + eps)) * weight[c] )
+ * (rmsnorm_forward, src/models/smollm2-135m-instruct/kernels/rmsnorm.cl:27-104; host
+ * src/layers/layer_norm.cpp:76-126).  The three nn_rmsnorm_* forms below are nn_linear,
+ * nn_linear_qkv and nn_fused_gate_up_silu applied to that normalised row, the pairs
+ * input_layernorm -> QKV and post_attention_layernorm -> gate/up of a decoder layer: for
+ * M <= 16 the norm is the prologue of the projection kernel (no launch, no round trip of the
+ * normalised row through memory); otherwise it runs as a launch of its own into context scratch
+ * (which can only grow outside a recording). */
+int nn_rmsnorm(nn_context* ctx, int rows, int cols, nn_buf x, nn_buf weight_fp16, float eps, nn_buf out);
+int nn_rmsnorm_linear(nn_context* ctx, int M, int N, int K, nn_buf x, nn_buf norm_weight, float eps, nn_buf W, nn_buf out);
+int nn_rmsnorm_linear_qkv(nn_context* ctx, int M, int K, nn_buf x, nn_buf norm_weight, float eps, nn_buf Wq, int Nq, nn_buf Wk, int Nk,
+                          nn_buf Wv, int Nv, nn_buf q, nn_buf k, nn_buf v);
+int nn_rmsnorm_gate_up_silu(nn_context* ctx, int M, int N, int K, nn_buf x, nn_buf norm_weight, float eps, nn_buf Wg, nn_buf Wu, nn_buf out);
+
 /* fp32 [N,K] = the dequantised weight exactly as the kernels unpack it
  * (src/models/lfm2-5-350m/kernels/gemv_m1_q4.cl:31-40; scripts/quantize_q4.py:156-166;
  *  scripts/quantize_weights.py:135-139).  For bit-exact checks of the unpack rule. */

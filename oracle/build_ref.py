@@ -32,6 +32,7 @@ CL_FILES = [
     ("smollm2_block_fused", "src/models/smollm2-135m-instruct/kernels/block_fused.cl"),
     ("smollm2_block_fused_int8", "src/models/smollm2-135m-instruct/kernels/block_fused_int8.cl"),
     ("qwen_gemv_m1", "src/models/qwen2-5-0-5b/kernels/gemv_m1.cl"),
+    ("smollm2_rmsnorm", "src/models/smollm2-135m-instruct/kernels/rmsnorm.cl"),
 ]
 
 _KERNEL_RE = re.compile(r"__kernel\b(?P<attrs>(?:\s*__attribute__\s*\(\((?:[^()]|\([^()]*\))*\)\))*)\s*void\s+(?P<name>\w+)\s*\((?P<params>[^{]*?)\)\s*\{", re.S)
@@ -43,7 +44,7 @@ def strip_comments(text):
 
 
 def parse_kernels(text):
-    """-> [(name, work_group_size_token, [(kind, ctype)])], kind in ptr/image/int/local."""
+    """-> [(name, work_group_size_token, [(kind, ctype)])], kind in ptr/image/int/float/local."""
     out = []
     for m in _KERNEL_RE.finditer(strip_comments(text)):
         wg = re.search(r"reqd_work_group_size\s*\(\s*([\w]+)", m.group("attrs") or "")
@@ -59,6 +60,8 @@ def parse_kernels(text):
                 base = re.sub(r"\b(__global|__constant|__local|const|restrict)\b", "", p)
                 base = base[: base.index("*")].strip()
                 params.append(("local" if is_local else "ptr", base))
+            elif re.search(r"\bfloat\b", p):
+                params.append(("float", "float"))
             else:
                 params.append(("int", "int"))
         out.append((m.group("name"), wg.group(1) if wg else "64", params))
@@ -77,6 +80,8 @@ def dispatcher(kernels):
                 args.append(f"*(image2d_t*)argv[{i}]")
             elif kind == "ptr":
                 args.append(f"({ctype}*)argv[{i}]")
+            elif kind == "float":
+                args.append(f"*(float*)argv[{i}]")
             else:
                 args.append(f"*(int*)argv[{i}]")
         call = f"{name}({', '.join(args)});"

@@ -107,6 +107,7 @@ static inline float4 convert_float4(float4 v) { return v; }
 static inline float dot(float4 a, float4 b) { return ((a.x * b.x + a.y * b.y) + a.z * b.z) + a.w * b.w; }
 static inline float native_exp(float x) { return expf(x); }
 static inline float native_recip(float x) { return 1.0f / x; }
+static inline float native_rsqrt(float x) { return 1.0f / sqrtf(x); }
 static inline int min(int a, int b) { return a < b ? a : b; }
 static inline int max(int a, int b) { return a > b ? a : b; }
 static inline int atomic_add(int* p, int v) { int o = *p; *p += v; return o; }

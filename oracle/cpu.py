@@ -125,6 +125,19 @@ def linear_silu_gate(fmt, x, W3, s3, gate, order=ORDER_KERNEL) -> np.ndarray:
     return g.view(np.float16)
 
 
+def rmsnorm(x, weight, eps) -> np.ndarray:
+    """fp16 [rows, cols] = the reference's rmsnorm_forward on fp16 storage."""
+    x = _c(x, np.uint16)
+    if x.ndim == 1:
+        x = x[None, :]
+    w = _c(weight, np.uint16)
+    out = np.empty(x.shape, dtype=np.uint16)
+    L = lib()
+    L.oracle_rmsnorm_half.argtypes = [ctypes.c_int, ctypes.c_int, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_float, ctypes.c_void_p]
+    L.oracle_rmsnorm_half(x.shape[0], x.shape[1], _p(x), _p(w), float(eps), _p(out))
+    return out.view(np.float16)
+
+
 def argmax_half(v) -> int:
     v = _c(v, np.uint16).reshape(-1)
     return int(lib().oracle_argmax_half(v.size, _p(v)))

@@ -290,8 +290,39 @@ void oracle_store_silu_gate(size_t n, const float* acc, uint16_t* gate) {
     }
 }
 
-/* arg-max over fp16 logits, first index wins on ties
- * (src/models/lfm2-5-350m/kernels/argmax.cl:30-120 keeps the lower index). */
+/* ---- RMSNorm feeding the projections --------------------------------------
+ * src/models/smollm2-135m-instruct/kernels/rmsnorm.cl:27-104 (USE_FP16 path): one work-group
+ * of 64 per row; lane t sums dot(v, v) over the vec4 columns c4 = t, t + 64, ... (then a scalar
+ * tail), a binary tree reduces the 64 partials, inv = rsqrt(sum / cols + eps), and every element
+ * is stored as half((x * inv) * weight). */
+void oracle_rmsnorm_half(int rows, int cols, const uint16_t* x, const uint16_t* weight, float eps, uint16_t* out) {
+    const int C4 = cols >> 2;
+    for (int r = 0; r < rows; ++r) {
+        const uint16_t* xr = x + (size_t)r * cols;
+        float p[64];
+        for (int t = 0; t < 64; ++t) {
+            float acc = 0.0f;
+            for (int c4 = t; c4 < C4; c4 += 64) {
+                float v[4];
+                for (int i = 0; i < 4; ++i) v[i] = oracle_f16_to_f32(xr[c4 * 4 + i]);
+                acc += ((v[0] * v[0] + v[1] * v[1]) + v[2] * v[2]) + v[3] * v[3];
+            }
+            for (int c = C4 * 4 + t; c < cols; c += 64) {
+                float v = oracle_f16_to_f32(xr[c]);
+                acc += v * v;
+            }
+            p[t] = acc;
+        }
+        for (int s2 = 32; s2 > 0; s2 >>= 1)
+            for (int t = 0; t < s2; ++t) p[t] += p[t + s2];
+        const float inv = 1.0f / sqrtf(p[0] / (float)cols + eps);
+        for (int c = 0; c < cols; ++c)
+            out[(size_t)r * cols + c] = oracle_f32_to_f16((oracle_f16_to_f32(xr[c]) * inv) * oracle_f16_to_f32(weight[c]));
+    }
+}
+
+/* arg-max over fp16 logits; the first index wins on ties (the reference's
+ * src/models/lfm2-5-350m/kernels/argmax.cl:30-120 resolves ties by work-item order). */
 int oracle_argmax_half(size_t n, const uint16_t* v) {
     size_t best = 0;
     float bv = -INFINITY;

@@ -37,7 +37,7 @@ class _Image(ctypes.Structure):
 
 
 def run(tag, kernel, args, n_groups, threads=1):
-    """args: list of ("ptr", ndarray) | ("img", ndarray 2-D, row-major weight) | ("int", value).
+    """args: list of ("ptr", ndarray) | ("img", ndarray 2-D, row-major weight) | ("int", value) | ("float", value).
     Arrays are used in place (outputs are written into them)."""
     keep, argv = [], (ctypes.c_void_p * len(args))()
     for i, a in enumerate(args):
@@ -50,6 +50,10 @@ def run(tag, kernel, args, n_groups, threads=1):
             im = _Image(w.ctypes.data, w.strides[0])
             keep.append(im)
             argv[i] = ctypes.addressof(im)
+        elif a[0] == "float":
+            v = ctypes.c_float(float(a[1]))
+            keep.append(v)
+            argv[i] = ctypes.addressof(v)
         else:
             v = ctypes.c_int(int(a[1]))
             keep.append(v)
@@ -126,6 +130,30 @@ def generic_fp16(x, W, threads=1):
     out = np.zeros(N, np.uint16)
     run("lfm2_gemv_m1", "gemv_m1_generic", [("ptr", _h(x)), ("ptr", _h(W)), ("ptr", out), ("int", K), ("int", N)], N, threads)
     return out.view(np.float16)
+
+
+def rmsnorm_fp16(x, weight, eps, threads=1):
+    """rmsnorm_forward of the SmolLM2 port: one work-group per row."""
+    xx, ww = _h(x), _h(weight)
+    rows, cols = xx.shape
+    out = np.zeros((rows, cols), np.uint16)
+    run("smollm2_rmsnorm", "rmsnorm_forward", [("ptr", xx), ("ptr", ww), ("ptr", out), ("int", rows), ("int", cols), ("float", eps)], rows, threads)
+    return out.view(np.float16)
+
+
+def write_golden_rmsnorm(path):
+    rng = np.random.default_rng(515151)
+    data, cases = {}, []
+    for i, (rows, cols, eps) in enumerate(((1, 576, 1e-5), (3, 1024, 1e-5), (2, 896, 1e-6), (1, 70, 1e-5), (4, 1536, 1e-5))):
+        x = (rng.standard_normal((rows, cols)) * (0.3 + i)).astype(np.float32).astype(np.float16)
+        w = (1.0 + 0.1 * rng.standard_normal(cols)).astype(np.float32).astype(np.float16)
+        tag = f"rms{i}"
+        data[tag + "_x"], data[tag + "_w"], data[tag + "_y"] = _h(x), _h(w), _h(rmsnorm_fp16(x, w, eps))
+        cases.append({"tag": tag, "rows": rows, "cols": cols, "eps": eps})
+    import json
+    data["cases"] = np.frombuffer(json.dumps(cases).encode(), dtype=np.uint8)
+    np.savez_compressed(path, **data)
+    return cases
 
 
 # ---- fixture generation ------------------------------------------------------------------

@@ -15,6 +15,7 @@ What it produces
   bundle_smollm2/  model.{fp16,int8}.bin + .meta.json, same with the SmolLM2 script
   kernels_ref.npz  (only when oracle/_ref is built) outputs of the reference's
                    unmodified .cl kernels run on the CPU for seeded inputs
+  rmsnorm_ref.npz  (same condition) outputs of the reference's rmsnorm_forward kernel
 """
 import importlib.util
 import json
@@ -168,6 +169,7 @@ def make_kernels_ref():
         print("oracle/_ref not built, kernels_ref.npz not regenerated")
         return
     ref_cl.write_golden(os.path.join(HERE, "kernels_ref.npz"))
+    ref_cl.write_golden_rmsnorm(os.path.join(HERE, "rmsnorm_ref.npz"))
 
 
 if __name__ == "__main__":
