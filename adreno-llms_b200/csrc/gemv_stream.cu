@@ -245,12 +245,14 @@ __device__ __forceinline__ void stage_x(const uint16_t* __restrict__ x, int M, i
     }
 }
 
-// EXT: the launch uses one of the rarer features (balanced item dealing, peer stores, the
-// gather signal, the fused arg-max).  The plain instantiation carries none of that code: the
-// per-layer operators are launch-latency-bound and every instruction-cache line their blocks
-// have to fetch shows up in the step time.
-template <int FMT, int NT, bool DUAL, bool EXT>
+// VAR selects how much of the kernel is compiled in: 0 = the plain projection, 1 = plus the RMSNorm
+// prologue, 2 = plus the rarer features (balanced item dealing, peer stores, the gather signal,
+// the fused arg-max).  The plain instantiation carries none of that code: the per-layer operators
+// are launch-latency-bound, and every instruction-cache line their blocks have to fetch shows up
+// in the step time (the full variant is 0.5 us slower per small launch with nothing switched on).
+template <int FMT, int NT, bool DUAL, int VAR>
 __global__ void __launch_bounds__(THREADS) linear_stream_kernel(const __grid_constant__ typename KArgsFor<FMT>::type ka) {
+    constexpr bool EXT = VAR == 2;
     extern __shared__ __align__(128) uint8_t smem[];
     const LinArgs& a = ka.a;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -263,7 +265,7 @@ __global__ void __launch_bounds__(THREADS) linear_stream_kernel(const __grid_con
     const int stages = ka.stages, kcb = a.kcb;
     const bool ksplit = a.kw > 1;  // the four consumers split K of one 32-row tile
     const int rowbytes = ka.rowbytes, nchunks = ka.nchunks;
-    const bool a_norm = EXT && a.norm_w != nullptr;
+    const bool a_norm = VAR >= 1 && a.norm_w != nullptr;
     const Geo geo = make_geo(FMT, aM, aK, kcb, stages, NT, a_norm);
     const int warp_rows = DUAL ? 16 : WARP_ROWS;                       // rows of each weight per warp
     const int tile_rows = ksplit ? warp_rows : NCW * warp_rows;        // rows of each weight per block tile
@@ -445,6 +447,10 @@ __global__ void __launch_bounds__(THREADS) linear_stream_kernel(const __grid_con
     // Prefetched epilogue operands stay as raw fp16 bits until they are used, so that the
     // loads' latency is not waited for where they are issued.
     uint16_t sc_reg[2][2];          // int8: row scales of the current tile (rows g, g+8 of each block)
+    // Single-token launches (one weight): lane L of a warp finishes row L of the warp's 32 rows, so
+    // it prefetches one scale and one residual value and the tile leaves in one 64-byte store.
+    const bool lane_rows = !DUAL && aM == 1;
+    uint16_t sc1 = 0, res1 = 0;
     uint32_t res_reg[2][2][NT][2];  // in-place epilogues: the values to be updated
     bool failed = false;
     unsigned long long am_best = 0ull;  // fused arg-max: best key among this thread's rows
@@ -462,6 +468,10 @@ __global__ void __launch_bounds__(THREADS) linear_stream_kernel(const __grid_con
         } else {
             const LinSeg sg = seg_at(tile_segment(tile));
             const int row0 = (tile - sg.tile0) * tile_rows + wrow_off;
+            if (lane_rows) {
+                sc1 = sg.scale[min(row0 + lane, sg.N - 1)];
+                return;
+            }
 #pragma unroll
             for (int rb = 0; rb < 2; ++rb)
 #pragma unroll
@@ -506,6 +516,10 @@ __global__ void __launch_bounds__(THREADS) linear_stream_kernel(const __grid_con
         if (DUAL || !(a_epi == EPI_RESIDUAL || a_epi == EPI_SILU_GATE)) return;
         const LinSeg sg = seg_at(tile_segment(tile));
         const int row0 = (tile - sg.tile0) * tile_rows + wrow_off;
+        if (lane_rows) {
+            res1 = (row0 + lane < sg.N) ? sg.out[row0 + lane] : (uint16_t)0;
+            return;
+        }
 #pragma unroll
         for (int rb = 0; rb < 2; ++rb)
 #pragma unroll
@@ -543,6 +557,51 @@ __global__ void __launch_bounds__(THREADS) linear_stream_kernel(const __grid_con
         const uint16_t* gw = a.norm_w;
         const float n_eps = a.norm_eps;
         const int per_row = aK / 8;
+        constexpr int NREG = 4;
+        if (aM == 1 && per_row <= NREG * NCW * 32) {
+            // decode fast path: the row and the norm weight are read once and stay in registers
+            uint4 xv4[NREG], gv4[NREG];
+            float ss = 0.f;
+#pragma unroll
+            for (int j = 0; j < NREG; ++j) {
+                const int p = tid + j * NCW * 32;
+                xv4[j] = p < per_row ? *reinterpret_cast<const uint4*>(a.x + p * 8) : make_uint4(0, 0, 0, 0);
+                gv4[j] = p < per_row ? *reinterpret_cast<const uint4*>(gw + p * 8) : make_uint4(0, 0, 0, 0);
+            }
+#pragma unroll
+            for (int j = 0; j < NREG; ++j) {
+                const uint32_t wv[4] = {xv4[j].x, xv4[j].y, xv4[j].z, xv4[j].w};
+#pragma unroll
+                for (int q = 0; q < 4; ++q) {
+                    const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&wv[q]));
+                    ss += f.x * f.x;
+                    ss += f.y * f.y;
+                }
+            }
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+            if (lane == 0) red[warp * 16] = ss;
+            asm volatile("bar.sync 1, %0;" ::"n"(NCW * 32) : "memory");
+            float tot = 0.f;
+#pragma unroll
+            for (int w2 = 0; w2 < NCW; ++w2) tot += red[w2 * 16];
+            const float inv = 1.0f / sqrtf(tot / (float)aK + n_eps);
+#pragma unroll
+            for (int j = 0; j < NREG; ++j) {
+                const int p = tid + j * NCW * 32;
+                if (p >= per_row) continue;
+                const uint32_t xv[4] = {xv4[j].x, xv4[j].y, xv4[j].z, xv4[j].w}, gv[4] = {gv4[j].x, gv4[j].y, gv4[j].z, gv4[j].w};
+                uint32_t o4[4];
+#pragma unroll
+                for (int q = 0; q < 4; ++q) {
+                    const float2 fx = __half22float2(*reinterpret_cast<const __half2*>(&xv[q]));
+                    const float2 fg = __half22float2(*reinterpret_cast<const __half2*>(&gv[q]));
+                    const __half2 h = __floats2half2_rn((fx.x * inv) * fg.x, (fx.y * inv) * fg.y);
+                    o4[q] = *reinterpret_cast<const uint32_t*>(&h);
+                }
+                *reinterpret_cast<uint4*>(xn + p * 8) = make_uint4(o4[0], o4[1], o4[2], o4[3]);
+            }
+        } else {
         for (int m = 0; m < aM; ++m) {
             float ss = 0.f;
             for (int p = tid; p < per_row; p += NCW * 32) {
@@ -579,6 +638,7 @@ __global__ void __launch_bounds__(THREADS) linear_stream_kernel(const __grid_con
                 }
                 *reinterpret_cast<uint4*>(xn + (size_t)m * aK + p * 8) = make_uint4(o4[0], o4[1], o4[2], o4[3]);
             }
+        }
         }
         asm volatile("bar.sync 1, %0;" ::"n"(NCW * 32) : "memory");
         x_src = xn;
@@ -924,6 +984,36 @@ __global__ void __launch_bounds__(THREADS) linear_stream_kernel(const __grid_con
 #ifdef NNB_TRACE
             if (ti == 1 && row0 >= 0) tl_e1 = clock64();
 #endif
+            if (lane_rows) {
+                // the token's 32 results sit in lanes 0, 4, .. 28 (rows g, g + 8 of each row block):
+                // bring row L to lane L, finish it there and store the 32 rows with one instruction
+                const int src = (lane & 7) * 4, sel = lane >> 3;
+                const float v00 = __shfl_sync(0xffffffffu, acc[0][0][0][0], src), v01 = __shfl_sync(0xffffffffu, acc[0][0][0][2], src);
+                const float v10 = __shfl_sync(0xffffffffu, acc[0][1][0][0], src), v11 = __shfl_sync(0xffffffffu, acc[0][1][0][2], src);
+                float v = sel == 0 ? v00 : sel == 1 ? v01 : sel == 2 ? v10 : v11;
+                const int n = row0 + lane;
+                if (n < seg_n) {
+                    if (FMT == FMT_INT8) v *= __half2float(__ushort_as_half(sc1));
+                    if (epi == EPI_RESIDUAL) {
+                        v = __half2float(__ushort_as_half(res1)) + v;
+                    } else if (epi == EPI_SILU_GATE) {
+                        const float gt = __half2float(__ushort_as_half(res1));
+                        v = gt * (1.0f / (1.0f + expf(-gt))) * v;
+                    }
+                    const uint16_t hv = __half_as_ushort(__float2half_rn(v));
+                    if (!EXT || seg_out) seg_out[n] = hv;
+                    if (EXT) {
+#pragma unroll
+                        for (int p = 0; p < 7; ++p)
+                            if (p < npeer) peer[p][n] = hv;
+                    }
+                    if (EXT && am_slot && (hv & 0x7FFFu) <= 0x7C00u) {  // NaNs never win
+                        const unsigned long long key = argmax_key_half(hv, am_base + n);
+                        am_best = key > am_best ? key : am_best;
+                    }
+                }
+                continue;
+            }
 #pragma unroll
             for (int rb = 0; rb < 2; ++rb)
 #pragma unroll
@@ -1005,9 +1095,14 @@ __global__ void __launch_bounds__(THREADS) linear_stream_kernel(const __grid_con
 #endif
 }
 
-template <int FMT, int NT, bool DUAL, bool EXT>
+int env_int(const char* name, int dflt) {
+    const char* v = getenv(name);
+    return v && *v ? atoi(v) : dflt;
+}
+
+template <int FMT, int NT, bool DUAL, int VAR>
 cudaError_t launch_e(const typename KArgsFor<FMT>::type& ka, const StreamPlan& p, cudaStream_t st, bool pdl) {
-    auto kern = linear_stream_kernel<FMT, NT, DUAL, EXT>;
+    auto kern = linear_stream_kernel<FMT, NT, DUAL, VAR>;
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3((unsigned)p.grid);
     cfg.blockDim = dim3((unsigned)THREADS);
@@ -1024,13 +1119,11 @@ cudaError_t launch_e(const typename KArgsFor<FMT>::type& ka, const StreamPlan& p
 template <int FMT, int NT, bool DUAL>
 cudaError_t launch_t(const typename KArgsFor<FMT>::type& ka, const StreamPlan& p, cudaStream_t st, bool pdl) {
     const LinArgs& a = ka.a;
-    const bool ext = a.streamk || a.npeer > 0 || a.sig.world > 0 || a.argmax_slot != nullptr || a.seg[0].out == nullptr || a.norm_w != nullptr;
-    return ext ? launch_e<FMT, NT, DUAL, true>(ka, p, st, pdl) : launch_e<FMT, NT, DUAL, false>(ka, p, st, pdl);
-}
-
-int env_int(const char* name, int dflt) {
-    const char* v = getenv(name);
-    return v && *v ? atoi(v) : dflt;
+    const bool ext = a.streamk || a.npeer > 0 || a.sig.world > 0 || a.argmax_slot != nullptr || a.seg[0].out == nullptr;
+    static const bool force_ext = env_int("NNB_FORCE_EXT", 0) != 0;  // tuning aid
+    if (ext || force_ext) return launch_e<FMT, NT, DUAL, 2>(ka, p, st, pdl);
+    if (a.norm_w) return launch_e<FMT, NT, DUAL, 1>(ka, p, st, pdl);
+    return launch_e<FMT, NT, DUAL, 0>(ka, p, st, pdl);
 }
 
 #ifdef NNB_TRACE
@@ -1069,9 +1162,11 @@ bool make_scale_map(CUtensorMap* m, const void* S, int rows, int rowbytes, int b
 
 template <int FMT, int NT, bool DUAL>
 cudaError_t configure_one() {
-    cudaError_t e = cudaFuncSetAttribute(linear_stream_kernel<FMT, NT, DUAL, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+    cudaError_t e = cudaFuncSetAttribute(linear_stream_kernel<FMT, NT, DUAL, 0>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
     if (e != cudaSuccess) return e;
-    return cudaFuncSetAttribute(linear_stream_kernel<FMT, NT, DUAL, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+    e = cudaFuncSetAttribute(linear_stream_kernel<FMT, NT, DUAL, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+    if (e != cudaSuccess) return e;
+    return cudaFuncSetAttribute(linear_stream_kernel<FMT, NT, DUAL, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
 }
 
 int count_tiles(const LinArgs& a, int tile_rows) {

@@ -19,7 +19,7 @@ from . import synth
 
 class DecodeStep:
     def __init__(self, ctx, shape: synth.ModelShape, fmt: str, M: int = 1, n_sets: int = 1, seed: int = 1235,
-                 vocab_rows=None, keep_host=False, only=None, comm=None):
+                 vocab_rows=None, keep_host=False, only=None, comm=None, norm=False):
         self.ctx, self.shape, self.fmt, self.M = ctx, shape, fmt, M
         # with a communicator the lm_head rows are this rank's shard and the projection
         # stores into every rank's gather buffer (one buffer per weight set, so that
@@ -33,6 +33,16 @@ class DecodeStep:
         self.ops = [op for op in synth.decode_step_ops(shape) if only is None or op[0] == only]
         # activations (fixed inputs) and outputs
         self.x_h = self._act("x_h", M, H, rng)      # normed hidden -> QKV and gate/up
+        # norm=True: the layer norms are part of the step, fused into the projections that read
+        # them: QKV and gate/up take the residual stream itself through an RMSNorm prologue
+        # (input_layernorm / post_attention_layernorm of the decoder layer)
+        self.norm = norm
+        self.eps = 1e-5
+        if norm:
+            g = (1.0 + 0.1 * rng.standard_normal(H)).astype(np.float32).astype(np.float16)
+            self.gamma = ctx.upload(g.view(np.uint16))
+            if self.host is not None:
+                self.host["gamma"] = g
         self.x_attn = self._act("x_attn", M, shape.q_dim, rng)   # attention output -> o_proj
         self.x_act = self._act("x_act", M, F, rng)  # SwiGLU output -> down_proj
         self.resid0 = synth.activations(M, H, rng)
@@ -84,7 +94,12 @@ class DecodeStep:
         c, s, M, sh = self.ctx, self.sets[set_index], self.M, self.shape
         for kind, layer, ws in self.ops:
             w = [s[f"{kind}.{layer}.{j}"].buf for j in range(len(ws))]
-            if kind == "qkv":
+            if kind == "qkv" and self.norm:
+                c.rmsnorm_linear_qkv(M, sh.hidden, self.resid, self.gamma, self.eps, w[0], sh.q_dim, w[1], sh.kv_dim, w[2], sh.kv_dim,
+                                     self.q, self.k, self.v)
+            elif kind == "gate_up" and self.norm:
+                c.rmsnorm_gate_up_silu(M, sh.ffn, sh.hidden, self.resid, self.gamma, self.eps, w[0], w[1], self.act)
+            elif kind == "qkv":
                 c.linear_qkv(M, sh.hidden, self.x_h, w[0], sh.q_dim, w[1], sh.kv_dim, w[2], sh.kv_dim, self.q, self.k, self.v)
             elif kind == "o_add":
                 c.linear_add(M, sh.hidden, sh.q_dim, self.x_attn, w[0], self.resid)

@@ -53,6 +53,19 @@ inline bool lm_head_argmax_m1(nn_context* queue, int vocab, int hidden, nn_buf x
     return nn_linear_argmax(queue, vocab, hidden, x, W, logits, token_out) == NN_OK;
 }
 
+// RMSNorm::forward (src/models/smollm2-135m-instruct/src/layers/layer_norm.cpp:76-126) and the norm fused
+// into the projection that consumes it.
+inline bool rmsnorm_forward(nn_context* queue, int rows, int cols, nn_buf x, nn_buf weight, float eps, nn_buf out) {
+    return nn_rmsnorm(queue, rows, cols, x, weight, eps, out) == NN_OK;
+}
+inline bool rmsnorm_qkv_m1(nn_context* queue, int K, nn_buf x, nn_buf norm_weight, float eps, nn_buf Wq, int Nq, nn_buf Wk, int Nk, nn_buf Wv,
+                           int Nv, nn_buf q, nn_buf k, nn_buf v) {
+    return nn_rmsnorm_linear_qkv(queue, 1, K, x, norm_weight, eps, Wq, Nq, Wk, Nk, Wv, Nv, q, k, v) == NN_OK;
+}
+inline bool rmsnorm_gate_up_silu_m1(nn_context* queue, int N, int K, nn_buf x, nn_buf norm_weight, float eps, nn_buf Wg, nn_buf Wu, nn_buf out) {
+    return nn_rmsnorm_gate_up_silu(queue, 1, N, K, x, norm_weight, eps, Wg, Wu, out) == NN_OK;
+}
+
 // class Weights (weights.h:13-51).  load() takes the context the buffers are created in.
 class Weights {
 public:

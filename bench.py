@@ -552,6 +552,18 @@ def main():
     big = max(group_rows, key=lambda g: g["bytes_per_launch"])
     sharded = sharded_projections(pkg, ctx, synth, comm, rank, world, dist) if args.only is None else None
     prefill = prefill_gemm(pkg, ctx, synth) if (args.only is None and world == 1) else None
+    # the same step with the two layer norms of every layer fused into the projections that read
+    # them (QKV and gate/up read the residual stream through an RMSNorm prologue): 60 norms more
+    # work per step, no launch more
+    norm_step_us = None
+    if args.only is None and world == 1:
+        nstep = dstep.DecodeStep(ctx, shape, fmt, M=1, n_sets=min(n_sets, 3), norm=True)
+        nstep.record(with_argmax=True)
+        for i in range(5):
+            nstep.launch(i % len(nstep.sets))
+        nreps = 300
+        nms = time_group(ctx, lambda i: nstep.launch(i % len(nstep.sets)), nreps)
+        norm_step_us = nms * 1e3 / nreps
     clocks = sampler.stop()
 
     cpu_base = None
@@ -584,6 +596,7 @@ def main():
             "launch_groups": group_rows,
             "sharded_projections": sharded,
             "prefill_gemm": prefill,
+            "decode_step_with_fused_rmsnorm_us": norm_step_us,
             "clocks": clocks,
         }
         if cpu_base:

@@ -85,3 +85,31 @@ def test_recorded_step_equals_eager(nnb, ctx):
             r = cpu.linear_residual(fmt, step.host["x_act"], Wd, sd, r)
         got = ctx.download(step.resid, (1, shape.hidden), np.uint16).view(np.float16)
         check_close(got, r, what=f"step residual {fmt}")
+
+
+@pytest.mark.parametrize("fmt", ["int8", "fp16", "q4"])
+def test_step_with_fused_rmsnorm_follows_the_oracle_chain(nnb, ctx, fmt):
+    """With the layer norms fused into QKV and gate/up the residual stream feeds the projections:
+    follow two layers on the CPU (oracle RMSNorm -> oracle projections) and compare what the
+    recorded step leaves in the q / act buffers of the last layer and in the residual stream."""
+    import importlib
+    synth = importlib.import_module("adreno_llms_b200.synth")
+    dstep = importlib.import_module("adreno_llms_b200.decode_step")
+    shape = synth.ModelShape("tiny-norm", 1024, 2, 1024, 512, 4608, 2048)
+    step = dstep.DecodeStep(ctx, shape, fmt, M=1, n_sets=1, keep_host=True, norm=True)
+    n = step.record()
+    assert n == 4 * shape.layers + 1          # the norms add no launch
+    step.launch(0)
+    ctx.sync()
+    h = step.host
+    r = step.resid0.copy()
+    for layer in range(shape.layers):
+        xn = cpu.rmsnorm(r, h["gamma"], step.eps)
+        q = cpu.linear(fmt, xn, *h[f"qkv.{layer}.0"])
+        r = cpu.linear_residual(fmt, h["x_attn"], *h[f"o_add.{layer}.0"], r)
+        xn2 = cpu.rmsnorm(r, h["gamma"], step.eps)
+        act = cpu.linear_swiglu(fmt, xn2, *h[f"gate_up.{layer}.0"], *h[f"gate_up.{layer}.1"])
+        r = cpu.linear_residual(fmt, h["x_act"], *h[f"down_add.{layer}.0"], r)
+    check_close(ctx.download(step.q, (1, shape.q_dim), np.uint16).view(np.float16), q, tol=2e-3, what=f"q after norm {fmt}")
+    check_close(ctx.download(step.act, (1, shape.ffn), np.uint16).view(np.float16), act, tol=2e-3, what=f"act after norm {fmt}")
+    check_close(ctx.download(step.resid, (1, shape.hidden), np.uint16).view(np.float16), r, what=f"residual {fmt}")
