@@ -459,6 +459,12 @@ __global__ void __launch_bounds__(THREADS) linear_stream_kernel(const __grid_con
     auto prefetch_scales = [&](int tile) {
         if (FMT != FMT_INT8) return;
         if (DUAL) {
+            if (aM == 1) {   // lane L (< 16) finishes row L of the warp's 16 rows
+                const int n = min(tile * tile_rows + wrow_off + (lane & 15), a.seg[0].N - 1);
+                sc1 = a.seg[0].scale[n];
+                res1 = a.scale2[n];   // the up weight's scale rides in the spare register
+                return;
+            }
 #pragma unroll
             for (int i2 = 0; i2 < 2; ++i2) {
                 const int n = min(tile * tile_rows + wrow_off + g + i2 * 8, a.seg[0].N - 1);
@@ -946,6 +952,24 @@ __global__ void __launch_bounds__(THREADS) linear_stream_kernel(const __grid_con
         if (DUAL) {
             const int seg_n = a.seg[0].N, seg_ld = a.seg[0].ld_out, m_count = aM;
             uint16_t* const seg_out = a.seg[0].out;
+            if (m_count == 1) {
+                // single token: rows g, g + 8 of the warp's 16 gate / up rows sit in lanes 0, 4, .. 28;
+                // lane L < 16 takes row L and the 16 rows leave in one 32-byte store
+                const int src = (lane & 7) * 4, hi = (lane >> 3) & 1;
+                const float g0 = __shfl_sync(0xffffffffu, acc[0][0][0][0], src), g1 = __shfl_sync(0xffffffffu, acc[0][0][0][2], src);
+                const float u0 = __shfl_sync(0xffffffffu, acc[0][1][0][0], src), u1 = __shfl_sync(0xffffffffu, acc[0][1][0][2], src);
+                float gv = hi ? g1 : g0, uv = hi ? u1 : u0;
+                const int n = tile * tile_rows + wrow_off + lane;
+                if (lane < 16 && n < seg_n) {
+                    if (FMT == FMT_INT8) {
+                        gv *= __half2float(__ushort_as_half(sc1));
+                        uv *= __half2float(__ushort_as_half(res1));
+                    }
+                    const float r = (gv / (1.0f + expf(-gv))) * uv;
+                    seg_out[n] = __half_as_ushort(__float2half_rn(r));
+                }
+                continue;
+            }
 #pragma unroll
             for (int nt = 0; nt < NT; ++nt)
 #pragma unroll
