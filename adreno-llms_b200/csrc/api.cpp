@@ -317,10 +317,21 @@ static int run_linear(nn_context* c, int fmt, LinArgs a, int M_total, const char
     uint16_t* peer0[7];
     for (int p = 0; p < 7; ++p) peer0[p] = a.peer_out[p];
     const GatherSignal sig0 = a.sig;
-    for (int m0 = 0; m0 < M_total; m0 += 16) {
+    // Slices of at most 16 rows; when the activations of a slice do not fit in shared memory next
+    // to the weight ring (large K, int8 limb planes), the slice is halved until they do.
+    int slice = 16;
+    {
+        LinArgs probe = a;
+        while (slice > 1) {
+            probe.M = M_total < slice ? M_total : slice;
+            if (!stream_supported(fmt, probe.M, a.K, probe) || stream_plan(fmt, probe, c->sm_count, c->smem_limit).ok) break;
+            slice >>= 1;
+        }
+    }
+    for (int m0 = 0; m0 < M_total; m0 += slice) {
         a.sig = sig0;
-        if (m0 + 16 < M_total) a.sig.world = 0;  // the last slice sends the gather's signal
-        a.M = M_total - m0 < 16 ? M_total - m0 : 16;
+        if (m0 + slice < M_total) a.sig.world = 0;  // the last slice sends the gather's signal
+        a.M = M_total - m0 < slice ? M_total - m0 : slice;
         a.x = x0 + (size_t)m0 * a.K;
         for (int i = 0; i < a.nseg; ++i) a.seg[i].out = out0[i] + (size_t)m0 * a.seg[i].ld_out;
         for (int p = 0; p < a.npeer; ++p) a.peer_out[p] = peer0[p] + (size_t)m0 * a.seg[0].ld_out;

@@ -150,7 +150,7 @@ __device__ __forceinline__ void stage_x_int8(const uint16_t* __restrict__ x, int
         up = __int_as_float((127 + pw) << 23);
         if (tid == 0) rowscale[m] = bad ? __int_as_float(0x7FC00000) : __int_as_float((127 - pw) << 23);
     };
-    constexpr int REG_PIECES = 4;
+    constexpr int REG_PIECES = 4;   // rows of up to 4096 values stay in registers
     if (M == 1 && per_row <= REG_PIECES * nthreads) {
         // decode fast path: the row stays in registers between the max and the split
         uint4 v[REG_PIECES];
@@ -183,13 +183,27 @@ __device__ __forceinline__ void stage_x_int8(const uint16_t* __restrict__ x, int
         if ((tid & 31) == 0 && mx) atomicMax(&rowmax[m], mx);
     }
     asm volatile("bar.sync 1, %0;" ::"r"(nthreads) : "memory");
+    // Loads are issued in batches before the shared-memory stores that follow them: a store
+    // through a byte pointer may alias anything, so a load placed after one cannot be moved
+    // up by the compiler and every piece would pay its own round trip to L2.
+    constexpr int BATCH = 4;
     for (int m = 0; m < M; ++m) {
         bool bad;
         float up;
         row_params(m, bad, up);
-        for (int p = tid; p < per_row; p += nthreads)
-            quantise_piece(*reinterpret_cast<const uint4*>(x + (size_t)m * K + p * 8), bad, up, xs + (0 * M + m) * xstride,
-                           xs + (1 * M + m) * xstride, xs + (2 * M + m) * xstride, p);
+        for (int p0 = tid; p0 < per_row; p0 += BATCH * nthreads) {
+            uint4 v[BATCH];
+#pragma unroll
+            for (int j = 0; j < BATCH; ++j) {
+                const int p = p0 + j * nthreads;
+                v[j] = p < per_row ? *reinterpret_cast<const uint4*>(x + (size_t)m * K + p * 8) : make_uint4(0, 0, 0, 0);
+            }
+#pragma unroll
+            for (int j = 0; j < BATCH; ++j) {
+                const int p = p0 + j * nthreads;
+                if (p < per_row) quantise_piece(v[j], bad, up, xs + (0 * M + m) * xstride, xs + (1 * M + m) * xstride, xs + (2 * M + m) * xstride, p);
+            }
+        }
     }
 }
 
@@ -202,21 +216,44 @@ __device__ __forceinline__ void stage_x(const uint16_t* __restrict__ x, int M, i
                                         int nthreads) {
     if (FMT == FMT_FP16) {
         const int per_row = K / 8;  // 16-byte pieces
-        for (int i = tid; i < M * per_row; i += nthreads) {
-            const int m = i / per_row, p = i - m * per_row;
-            const uint4 v = *reinterpret_cast<const uint4*>(x + (size_t)m * K + p * 8);
-            *reinterpret_cast<uint4*>(xs + m * xstride + p * 16) = v;
+        constexpr int BATCH = 8;    // loads first, then the stores (see stage_x_int8)
+        for (int i0 = tid; i0 < M * per_row; i0 += BATCH * nthreads) {
+            uint4 v[BATCH];
+#pragma unroll
+            for (int j = 0; j < BATCH; ++j) {
+                const int i = i0 + j * nthreads;
+                v[j] = i < M * per_row ? *reinterpret_cast<const uint4*>(x + (size_t)i * 8) : make_uint4(0, 0, 0, 0);  // rows are contiguous
+            }
+#pragma unroll
+            for (int j = 0; j < BATCH; ++j) {
+                const int i = i0 + j * nthreads;
+                if (i < M * per_row) {
+                    const int m = i / per_row, p = i - m * per_row;
+                    *reinterpret_cast<uint4*>(xs + m * xstride + p * 16) = v[j];
+                }
+            }
         }
     } else {
         const int per_row = K / 32;
-        for (int i = tid; i < M * per_row; i += nthreads) {
+        // the four loads of the next block are issued before the stores of the current one
+        // (see stage_x_int8 for why the order has to be spelled out)
+        const int total = M * per_row;
+        uint4 cur[4], nxt[4];
+        if (tid < total) {
+#pragma unroll
+            for (int t = 0; t < 4; ++t) cur[t] = reinterpret_cast<const uint4*>(x + (size_t)tid * 32)[t];  // rows are contiguous
+        }
+        for (int i = tid; i < total; i += nthreads) {
             const int m = i / per_row, p = i - m * per_row;
-            const uint4* src = reinterpret_cast<const uint4*>(x + (size_t)m * K + p * 32);
+            if (i + nthreads < total) {
+#pragma unroll
+                for (int t = 0; t < 4; ++t) nxt[t] = reinterpret_cast<const uint4*>(x + (size_t)(i + nthreads) * 32)[t];
+            }
             uint32_t o[4][4];
             float bsum = 0.f;
 #pragma unroll
             for (int t = 0; t < 4; ++t) {
-                const uint4 v = src[t];  // k 8t .. 8t+7 as pairs (0,1)(2,3)(4,5)(6,7)
+                const uint4 v = cur[t];  // k 8t .. 8t+7 as pairs (0,1)(2,3)(4,5)(6,7)
                 const uint32_t vv[4] = {v.x, v.y, v.z, v.w};
 #pragma unroll
                 for (int q = 0; q < 4; ++q) {
@@ -241,6 +278,8 @@ __device__ __forceinline__ void stage_x(const uint16_t* __restrict__ x, int M, i
                 cq[1] = 0.f;
                 cq[3] = 0.f;
             }
+#pragma unroll
+            for (int t = 0; t < 4; ++t) cur[t] = nxt[t];
         }
     }
 }
@@ -1160,28 +1199,53 @@ typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t,
                                   CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
 EncodeTiledFn g_encode_tiled = nullptr;
 
-// 2-D byte view of a weight: [rows][rowbytes], box = 128 bytes x box_rows rows, 128-byte swizzle.
-bool make_weight_map(CUtensorMap* m, const void* W, int rows, int rowbytes, int box_rows) {
-    if (!g_encode_tiled) return false;
-    const cuuint64_t dims[2] = {(cuuint64_t)rowbytes, (cuuint64_t)rows};
-    const cuuint64_t strides[1] = {(cuuint64_t)rowbytes};
-    const cuuint32_t box[2] = {128u, (cuuint32_t)box_rows};
-    const cuuint32_t estr[2] = {1u, 1u};
-    return g_encode_tiled(m, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(W), dims, strides, box, estr,
-                          CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                          CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
-}
+// Encoding a tensor map costs the host about a microsecond, and a decode loop asks for the same
+// few hundred (weight, tile) views token after token: keep them in a small direct-mapped,
+// per-thread cache.  A map only describes (address, extents, box), so a hit is always valid.
+struct MapSlot {
+    const void* base;
+    int rows, rowbytes, box_bytes, box_rows, swizzled;
+    bool valid;
+    CUtensorMap map;
+};
+constexpr int MAP_SLOTS = 2048;
+thread_local MapSlot* t_map_cache = nullptr;
 
-// 2-D byte view of a Q4 scale tensor: [rows][rowbytes], dense box of box_bytes x box_rows.
-bool make_scale_map(CUtensorMap* m, const void* S, int rows, int rowbytes, int box_bytes, int box_rows) {
-    if (!g_encode_tiled || box_bytes % 16 || box_bytes > 256 || box_rows > 256) return false;
+bool cached_byte_map(CUtensorMap* m, const void* base, int rows, int rowbytes, int box_bytes, int box_rows, bool swizzled) {
+    if (!g_encode_tiled) return false;
+    if (!t_map_cache) t_map_cache = new MapSlot[MAP_SLOTS]();
+    uint64_t h = reinterpret_cast<uintptr_t>(base) >> 4;
+    h ^= (uint64_t)rows * 0x9E3779B97F4A7C15ull + (uint64_t)rowbytes * 0xC2B2AE3D27D4EB4Full + (uint64_t)(box_rows * 4 + box_bytes * 2 + (swizzled ? 1 : 0));
+    MapSlot& s = t_map_cache[(h ^ (h >> 17) ^ (h >> 31)) % MAP_SLOTS];
+    if (s.valid && s.base == base && s.rows == rows && s.rowbytes == rowbytes && s.box_bytes == box_bytes && s.box_rows == box_rows &&
+        s.swizzled == (swizzled ? 1 : 0)) {
+        *m = s.map;
+        return true;
+    }
     const cuuint64_t dims[2] = {(cuuint64_t)rowbytes, (cuuint64_t)rows};
     const cuuint64_t strides[1] = {(cuuint64_t)rowbytes};
     const cuuint32_t box[2] = {(cuuint32_t)box_bytes, (cuuint32_t)box_rows};
     const cuuint32_t estr[2] = {1u, 1u};
-    return g_encode_tiled(m, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(S), dims, strides, box, estr,
-                          CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
-                          CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+    if (g_encode_tiled(m, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                       swizzled ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE,
+                       swizzled ? CU_TENSOR_MAP_L2_PROMOTION_L2_256B : CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                       CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+        return false;
+    s.base = base; s.rows = rows; s.rowbytes = rowbytes; s.box_bytes = box_bytes; s.box_rows = box_rows; s.swizzled = swizzled ? 1 : 0;
+    s.map = *m;
+    s.valid = true;
+    return true;
+}
+
+// 2-D byte view of a weight: [rows][rowbytes], box = 128 bytes x box_rows rows, 128-byte swizzle.
+bool make_weight_map(CUtensorMap* m, const void* W, int rows, int rowbytes, int box_rows) {
+    return cached_byte_map(m, W, rows, rowbytes, 128, box_rows, true);
+}
+
+// 2-D byte view of a Q4 scale tensor: [rows][rowbytes], dense box of box_bytes x box_rows.
+bool make_scale_map(CUtensorMap* m, const void* S, int rows, int rowbytes, int box_bytes, int box_rows) {
+    if (box_bytes % 16 || box_bytes > 256 || box_rows > 256) return false;
+    return cached_byte_map(m, S, rows, rowbytes, box_bytes, box_rows, false);
 }
 
 template <int FMT, int NT, bool DUAL>

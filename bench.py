@@ -394,6 +394,9 @@ def main():
     ap.add_argument("--warmup", type=int, default=20)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--fmt", default="int8", choices=["int8", "fp16", "q4"])
+    ap.add_argument("--shape", default="smollm2", choices=["smollm2", "qwen", "lfm2"],
+                    help="model shape of the step (default: the configuration the metric is quoted on)")
+    ap.add_argument("--m", type=int, default=1, help="activation rows per projection (batched decode), 1..16")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--only", default=None, choices=["qkv", "o_add", "gate_up", "down_add", "lm_head"],
                     help="profiling aid: the step consists of this launch group only")
@@ -419,11 +422,13 @@ def main():
 
     ctx = pkg.Context(local_rank)
     sm_count, l2_bytes, _ = ctx.device_info()
-    shape, fmt = synth.SMOLLM2_135M, args.fmt
+    shape = {"smollm2": synth.SMOLLM2_135M, "qwen": synth.QWEN25_05B, "lfm2": synth.LFM25_350M}[args.shape]
+    fmt, MM = args.fmt, max(1, min(16, args.m))
+    default_workload = args.shape == "smollm2" and MM == 1
     if shape.vocab % world:
         raise SystemExit(f"vocab {shape.vocab} is not divisible by {world} ranks")
     vrows = shape.vocab // world
-    step_bytes_full = sum(synth.linear_bytes(fmt, n, k, 1) for kind, _, ws in synth.decode_step_ops(shape)
+    step_bytes_full = sum(synth.linear_bytes(fmt, n, k, MM) for kind, _, ws in synth.decode_step_ops(shape)
                           if args.only in (None, kind) for n, k in ws)
     n_sets = min(64, max(2, math.ceil(2.0 * l2_bytes / step_bytes_full) + 1))
     comm = None
@@ -436,7 +441,7 @@ def main():
         with StdoutToStderr():
             comm = pkg.Comm(ctx, bytes(idbuf.tolist()), rank, world)
             comm.symm_free(comm.symm_alloc(256))   # first collective on the communicator
-    step = dstep.DecodeStep(ctx, shape, fmt, M=1, n_sets=n_sets, vocab_rows=(rank * vrows, vrows), only=args.only, comm=comm)
+    step = dstep.DecodeStep(ctx, shape, fmt, M=MM, n_sets=n_sets, vocab_rows=(rank * vrows, vrows), only=args.only, comm=comm)
 
     def barrier():
         ctx.sync()
@@ -472,16 +477,16 @@ def main():
 
     # ---- e2e: host buffers in, logits out, every step ----
     e2e_steps = max(50, min(args.steps, 500))
-    hx = pkg.load().nn_host_alloc(shape.hidden * 2)
-    hl = pkg.load().nn_host_alloc(shape.vocab * 2)
+    hx = pkg.load().nn_host_alloc(MM * shape.hidden * 2)
+    hl = pkg.load().nn_host_alloc(MM * shape.vocab * 2)
     import ctypes
-    ctypes.memmove(hx, synth.activations(1, shape.hidden, np.random.default_rng(5)).ctypes.data, shape.hidden * 2)
+    ctypes.memmove(hx, synth.activations(MM, shape.hidden, np.random.default_rng(5)).ctypes.data, MM * shape.hidden * 2)
 
     def e2e_step(i):
-        pkg._check(ctx.L.nn_buf_write(ctx.h, step.x_h, 0, hx, shape.hidden * 2))
+        pkg._check(ctx.L.nn_buf_write(ctx.h, step.x_h, 0, hx, MM * shape.hidden * 2))
         enqueue_step(i)
         out_buf = step.gathered[i % n_sets] if comm else step.logits
-        pkg._check(ctx.L.nn_buf_read(ctx.h, hl, out_buf, 0, shape.vocab * 2))
+        pkg._check(ctx.L.nn_buf_read(ctx.h, hl, out_buf, 0, MM * shape.vocab * 2))
         ctx.sync()
 
     for i in range(5):
@@ -508,7 +513,7 @@ def main():
     for kind, layer, ws in step.ops:
         groups.setdefault(kind, []).append(layer)
     group_rows = []
-    sh, M = shape, 1
+    sh, M = shape, MM
     for kind, layers in groups.items():
         def run(i, kind=kind, layers=layers):
             s = step.sets[i % n_sets]
@@ -541,7 +546,7 @@ def main():
         nl = len(layers)
         per_launch_us = gms * 1e3 / (reps * nl)
         ws = next(w for k2, _, w in step.ops if k2 == kind)
-        b = sum(synth.linear_bytes(fmt, (step.vocab_n if kind == "lm_head" else n), k, 1) for n, k in ws)
+        b = sum(synth.linear_bytes(fmt, (step.vocab_n if kind == "lm_head" else n), k, MM) for n, k in ws)
         group_rows.append({"group": kind, "launches_per_step": nl, "us_per_launch": per_launch_us,
                            "bytes_per_launch": b, "gbps": b / (per_launch_us * 1e-6) / 1e9,
                            "share_of_step": per_launch_us * nl})
@@ -550,13 +555,13 @@ def main():
         g["share_of_step"] = g["share_of_step"] / tot
     dom = max(group_rows, key=lambda g: g["share_of_step"])
     big = max(group_rows, key=lambda g: g["bytes_per_launch"])
-    sharded = sharded_projections(pkg, ctx, synth, comm, rank, world, dist) if args.only is None else None
-    prefill = prefill_gemm(pkg, ctx, synth) if (args.only is None and world == 1) else None
+    sharded = sharded_projections(pkg, ctx, synth, comm, rank, world, dist) if (args.only is None and default_workload) else None
+    prefill = prefill_gemm(pkg, ctx, synth) if (args.only is None and world == 1 and default_workload) else None
     # the same step with the two layer norms of every layer fused into the projections that read
     # them (QKV and gate/up read the residual stream through an RMSNorm prologue): 60 norms more
     # work per step, no launch more
     norm_step_us = None
-    if args.only is None and world == 1:
+    if args.only is None and world == 1 and default_workload:
         nstep = dstep.DecodeStep(ctx, shape, fmt, M=1, n_sets=min(n_sets, 3), norm=True)
         nstep.record(with_argmax=True)
         for i in range(5):
@@ -567,7 +572,7 @@ def main():
     clocks = sampler.stop()
 
     cpu_base = None
-    if rank == 0 and world == 1 and not args.no_cpu_baseline:
+    if rank == 0 and world == 1 and not args.no_cpu_baseline and default_workload:
         r, cores, t_step, kind, sample = cpu_arm(pkg, fmt, 15.0)
         cpu_base = {"value": r, "unit": UNIT, "cores": cores, "kind": kind, "sample": f"{sample} ({t_step * 1e3:.1f} ms per step)"}
 
@@ -577,15 +582,15 @@ def main():
             "ms_per_step": ms_per_step, "decode_step_us": ms_per_step * 1e3, "higher_is_better": True,
             "scaling": "strong", "vs_baseline": None,
             "dtype": f"{fmt} weights, fp16 activations, fp32 accumulate", "data": "synthetic",
-            "config": {"workload": f"decode-step projection set, SmolLM2-135M shape, {fmt}, M=1 "
+            "config": {"workload": f"decode-step projection set, {shape.name} shape, {fmt}, M={MM} "
                                    f"({synth.decode_step_gemvs(shape)} GEMVs in {kernels_per_step} launches)",
                        "algorithmic_bytes_per_step": step_bytes_full,
                        "l2": f"{n_sets} resident weight copies rotated step to step "
                              f"({n_sets * step.weight_bytes / 1e6:.0f} MB > L2 {l2_bytes / 1e6:.0f} MB)",
                        "sharding": "none" if world == 1 else f"lm_head rows / {world} ranks, each rank's kernel stores into every rank's "
                                                                     "gather buffer over NVLink peer memory; layers replicated"},
-            "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": shape.hidden * 2,
-                    "d2h_bytes_per_step": shape.vocab * 2, "us_per_step": e2e_s / e2e_steps * 1e6, "steps": e2e_steps},
+            "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": MM * shape.hidden * 2,
+                    "d2h_bytes_per_step": MM * shape.vocab * 2, "us_per_step": e2e_s / e2e_steps * 1e6, "steps": e2e_steps},
             "gpu_launches": launches,
             "roofline": {"bound": "hbm", "kernel": f"linear_stream_kernel [{dom['group']}]", "achieved": dom["gbps"], "peak": peak,
                          "unit": "GB/s", "frac": dom["gbps"] / peak, "traffic": traffic_tbl.get(dom["group"]), "peak_source": peak_src,
