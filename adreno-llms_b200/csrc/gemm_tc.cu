@@ -384,7 +384,7 @@ __global__ void __launch_bounds__(WFMT == FMT_FP16 ? GEMM_THREADS : GEMM_THREADS
         for (int tile = blockIdx.x; tile < ntiles; tile += gridDim.x, ++tl) {
             const int wt = tile / g_ntok, tt = tile - wt * g_ntok;
             const int n0 = wt * BM, m0 = tt * g_bn, acc = tl & 1;
-            if (!failed && !mbar_wait_bounded(acc_full0 + acc * 8, (uint32_t)((tl >> 1) & 1))) {
+            if (!failed && !mbar_wait_bounded_warp(acc_full0 + acc * 8, (uint32_t)((tl >> 1) & 1))) {
                 failed = true;
                 if (lane == 0) *reinterpret_cast<volatile int*>(g_status) = 5;
             }
@@ -412,7 +412,7 @@ __global__ void __launch_bounds__(WFMT == FMT_FP16 ? GEMM_THREADS : GEMM_THREADS
                             mbar_arrive_expect_tx(res_bar, (uint32_t)(g_out_box * BM * 2));
                             tma_load_2d(out_stage, &g.tm_out, n0, m0 + h0, res_bar, l2_policy_evict_normal());
                         }
-                        if (!mbar_wait_bounded(res_bar, (uint32_t)(n_stores & 1))) {
+                        if (!mbar_wait_bounded_warp(res_bar, (uint32_t)(n_stores & 1))) {
                             failed = true;
                             if (lane == 0) *reinterpret_cast<volatile int*>(g_status) = 9;
                         }

@@ -48,6 +48,33 @@ __device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar, uint32_t parity,
     }
 }
 
+// Warp-wide form for long waits (a whole K loop): one lane polls, with a suspend-time hint so that
+// the hardware parks it between polls, and the result is shared by shuffle.  Thirty-two lanes
+// spinning on the same barrier would only take issue slots from the warps that do the work.
+__device__ __forceinline__ bool mbar_wait_bounded_warp(uint32_t bar, uint32_t parity, long long limit_cycles = 200000000ll) {
+    int ok = 1;
+    if ((threadIdx.x & 31) == 0) {
+        const long long t0 = clock64();
+        for (;;) {
+            uint32_t done;
+            asm volatile(
+                "{\n\t.reg .pred p;\n\t"
+                "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
+                "selp.u32 %0, 1, 0, p;\n\t}"
+                : "=r"(done)
+                : "r"(bar), "r"(parity), "r"(4000u)
+                : "memory");
+            if (done) break;
+            if (clock64() - t0 > limit_cycles) {
+                ok = 0;
+                break;
+            }
+        }
+    }
+    ok = __shfl_sync(0xffffffffu, ok, 0);
+    return ok != 0;
+}
+
 // ---- bulk async copy global -> shared (1-D, TMA unit) --------------------------
 // Both addresses 16-byte aligned, size a multiple of 16 bytes.
 __device__ __forceinline__ uint64_t l2_policy_evict_first() {
