@@ -172,7 +172,7 @@ __global__ void __launch_bounds__(WFMT == FMT_FP16 ? GEMM_THREADS : GEMM_THREADS
 
     if (tid == 0) {
         for (int s = 0; s < g_stages; ++s) {
-            mbar_init(full0 + s * 8, WFMT == FMT_FP16 ? 1 : 1 + DQ_WARPS);  // operands ready: TMA bytes (+ the expanding warps)
+            mbar_init(full0 + s * 8, WFMT == FMT_FP16 ? 1 : 1 + DQ_WARPS / 2);  // operands ready: TMA bytes (+ one group of expanding warps)
             mbar_init(empty0 + s * 8, 1);
         }
         for (int r = 0; r < g_raw_stages; ++r) {
@@ -273,59 +273,86 @@ __global__ void __launch_bounds__(WFMT == FMT_FP16 ? GEMM_THREADS : GEMM_THREADS
         // ---- expanding warps: packed stage -> fp16 rows in the operand's swizzled layout ----
         // Operand layout (K-major, 128-byte swizzle): row r of the stage at (r / 8) * 1024 + (r % 8) * 128,
         // its 16-byte piece c at ((c ^ (r % 8)) * 16).
-        const int dt = tid - (2 + EPI_WARPS) * 32;   // 0 .. DQ_WARPS * 32 - 1
-        constexpr int DQ_THREADS = DQ_WARPS * 32;
+        // The eight warps work as two groups of four: group 0 expands the even K blocks, group 1 the
+        // odd ones, so two K blocks are in conversion at any time and a group's round trip through the
+        // barriers is hidden behind the other group's.
+        constexpr int GRP_THREADS = DQ_WARPS * 32 / 2;
+        const int dq = tid - (2 + EPI_WARPS) * 32;   // 0 .. DQ_WARPS * 32 - 1
+        const int grp = dq / GRP_THREADS, dt = dq % GRP_THREADS;
         const int K32 = g.K / 32;
         const uint16_t* const q4s = g.q4_scale;
-        int it = 0, rit = 0;   // operand stages and packed spans consumed so far
-        bool ok = true;
-        constexpr int Q4_PASSES = BM * 2 / DQ_THREADS, I8_PASSES = BM * 4 / DQ_THREADS;
-        // Q4: a thread expands the same weight row and the same half (blk) of every stage, so its
-        // block scales are every other entry of the row's scale vector: one aligned 16-byte load
-        // brings the eight scales of four stages, fetched four stages ahead of their use
+        int it = 0, rit = 0;   // operand stages and packed spans passed so far
+        bool ok = true, span_waited = false;
+        constexpr int Q4_PASSES = BM * 2 / GRP_THREADS, I8_PASSES = BM * 4 / GRP_THREADS;
+        // Q4: a thread expands the same Q4_PASSES weight rows and the same half (blk) of every K block
+        // it handles, so its block scales are entries of those rows' scale vectors: one aligned
+        // 16-byte load per row brings the eight scales of four K blocks, fetched four blocks ahead
         // (rows whose scale vector is not a multiple of 16 bytes take two-byte loads).
-        static_assert(Q4_PASSES == 1 || WFMT != FMT_Q4, "one Q4 task per thread and stage");
-        const int q_row_in_tile = dt >> 1, q_blk = dt & 1;
+        const int q_blk = dt & 1;
         const bool q4_vec = (K32 % 8) == 0 && (reinterpret_cast<uintptr_t>(q4s) & 15) == 0;
-        uint4 sv_cur = make_uint4(0, 0, 0, 0), sv_next = make_uint4(0, 0, 0, 0);
-        auto load_group = [&](int tile, int grp) {   // scales 8 grp .. 8 grp + 7 of this thread's row
-            const int row = (tile / g_ntok) * BM + q_row_in_tile;
-            if (tile < ntiles && row < gN && grp * 8 < K32) return *reinterpret_cast<const uint4*>(q4s + (size_t)row * K32 + grp * 8);
+        uint4 sv_cur[Q4_PASSES], sv_next[Q4_PASSES];
+#pragma unroll
+        for (int ps = 0; ps < Q4_PASSES; ++ps) sv_cur[ps] = sv_next[ps] = make_uint4(0, 0, 0, 0);
+        auto load_group = [&](int tile, int grp8, int ps) {   // scales 8 grp8 .. 8 grp8 + 7 of row ((ps * GRP_THREADS + dt) >> 1)
+            const int row = (tile / g_ntok) * BM + ((ps * GRP_THREADS + dt) >> 1);
+            if (tile < ntiles && row < gN && grp8 * 8 < K32) return *reinterpret_cast<const uint4*>(q4s + (size_t)row * K32 + grp8 * 8);
             return make_uint4(0, 0, 0, 0);
         };
-        if (WFMT == FMT_Q4 && q4_vec) sv_next = load_group(blockIdx.x, 0);
+        if (WFMT == FMT_Q4 && q4_vec) {
+#pragma unroll
+            for (int ps = 0; ps < Q4_PASSES; ++ps) sv_next[ps] = load_group(blockIdx.x, 0, ps);
+        }
         for (int tile = blockIdx.x; tile < ntiles && ok; tile += gridDim.x) {
             for (int kb = 0; kb < nkb; ++kb, ++it) {
                 const int s = it % g_stages;
-                uint16_t sc[1] = {0};
-                if (WFMT == FMT_Q4) {
-                    if (q4_vec) {
-                        if ((kb & 3) == 0) {
-                            sv_cur = sv_next;
-                            sv_next = (kb + 4 < nkb) ? load_group(tile, (kb >> 2) + 1) : load_group(tile + (int)gridDim.x, 0);
-                        }
-                        const int e = (kb & 3) * 2 + q_blk;   // entry of the current group
-                        const uint32_t w32 = e < 2 ? sv_cur.x : e < 4 ? sv_cur.y : e < 6 ? sv_cur.z : sv_cur.w;
-                        sc[0] = (uint16_t)((e & 1) ? (w32 >> 16) : (w32 & 0xFFFFu));
-                    } else {
-                        const int row = (tile / g_ntok) * BM + q_row_in_tile, blk = kb * 2 + q_blk;
-                        if (row < gN && blk < K32) sc[0] = q4s[(size_t)row * K32 + blk];
+                const int r = rit % g_raw_stages, jspan = kb % RAW_SPAN;
+                const bool span_last = jspan == RAW_SPAN - 1 || kb == nkb - 1;
+                if (jspan == 0) span_waited = false;
+                if (WFMT == FMT_Q4 && q4_vec && (kb & 3) == 0) {
+#pragma unroll
+                    for (int ps = 0; ps < Q4_PASSES; ++ps) {
+                        sv_cur[ps] = sv_next[ps];
+                        sv_next[ps] = (kb + 4 < nkb) ? load_group(tile, (kb >> 2) + 1, ps) : load_group(tile + (int)gridDim.x, 0, ps);
                     }
                 }
-                const int r = rit % g_raw_stages, jspan = kb % RAW_SPAN;
-                // the packed span has landed (first K block of the span), and the MMAs that read this
-                // operand slot last are done
-                if ((jspan == 0 && !mbar_wait_bounded(raw_full0 + r * 8, (uint32_t)((rit / g_raw_stages) & 1))) ||
+                if ((kb & 1) != grp) {   // the other group's K block
+                    if (span_last) {
+                        __syncwarp();
+                        if (lane == 0) mbar_arrive(raw_empty0 + r * 8);
+                        ++rit;
+                    }
+                    continue;
+                }
+                uint16_t sc[Q4_PASSES];
+#pragma unroll
+                for (int ps = 0; ps < Q4_PASSES; ++ps) sc[ps] = 0;
+                if (WFMT == FMT_Q4) {
+#pragma unroll
+                    for (int ps = 0; ps < Q4_PASSES; ++ps) {
+                        if (q4_vec) {
+                            const int e = (kb & 3) * 2 + q_blk;   // entry of the current group of eight
+                            const uint32_t w32 = e < 2 ? sv_cur[ps].x : e < 4 ? sv_cur[ps].y : e < 6 ? sv_cur[ps].z : sv_cur[ps].w;
+                            sc[ps] = (uint16_t)((e & 1) ? (w32 >> 16) : (w32 & 0xFFFFu));
+                        } else {
+                            const int row = (tile / g_ntok) * BM + ((ps * GRP_THREADS + dt) >> 1), blk = kb * 2 + q_blk;
+                            if (row < gN && blk < K32) sc[ps] = q4s[(size_t)row * K32 + blk];
+                        }
+                    }
+                }
+                // the packed span has landed (this group's first K block of the span), and the MMAs that
+                // read this operand slot last are done
+                if ((!span_waited && !mbar_wait_bounded(raw_full0 + r * 8, (uint32_t)((rit / g_raw_stages) & 1))) ||
                     (it >= g_stages && !mbar_wait_bounded(empty0 + s * 8, (uint32_t)(((it / g_stages) - 1) & 1)))) {
                     if (lane == 0) *reinterpret_cast<volatile int*>(g_status) = 10;
                     ok = false;
                     break;
                 }
+                span_waited = true;
                 const uint32_t a_addr = ring + s * stage_bytes, raw = raw_ring + r * RAW_BYTES;
                 if (WFMT == FMT_INT8) {
 #pragma unroll
                     for (int ps = 0; ps < I8_PASSES; ++ps) {
-                        const int task = ps * DQ_THREADS + dt, row = task >> 2, ch = task & 3;  // 16 codes = 16 k
+                        const int task = ps * GRP_THREADS + dt, row = task >> 2, ch = task & 3;  // 16 codes = 16 k
                         uint32_t w0, w1, w2, w3;
                         asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(w0), "=r"(w1), "=r"(w2), "=r"(w3) : "r"(raw + (uint32_t)((row >> 3) * 1024 + (row & 7) * 128) + (((uint32_t)(jspan * 4 + ch) ^ (uint32_t)(row & 7)) << 4)));
                         uint32_t h[8];
@@ -341,7 +368,7 @@ __global__ void __launch_bounds__(WFMT == FMT_FP16 ? GEMM_THREADS : GEMM_THREADS
                 } else {
 #pragma unroll
                     for (int ps = 0; ps < Q4_PASSES; ++ps) {
-                        const int task = ps * DQ_THREADS + dt, row = task >> 1, blk = task & 1;  // 32 nibbles = one scale block
+                        const int task = ps * GRP_THREADS + dt, row = task >> 1, blk = task & 1;  // 32 nibbles = one scale block
                         uint32_t w[4];
                         asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(w[0]), "=r"(w[1]), "=r"(w[2]), "=r"(w[3]) : "r"(raw + (uint32_t)((row >> 3) * 1024 + (row & 7) * 128) + (((uint32_t)(jspan * 2 + blk) ^ (uint32_t)(row & 7)) << 4)));
                         const __half sh = __ushort_as_half(sc[ps]);
@@ -369,7 +396,7 @@ __global__ void __launch_bounds__(WFMT == FMT_FP16 ? GEMM_THREADS : GEMM_THREADS
                 fence_async_smem();   // the MMA reads the operand through the async proxy
                 __syncwarp();
                 if (lane == 0) mbar_arrive(full0 + s * 8);
-                if (jspan == RAW_SPAN - 1 || kb == nkb - 1) {   // last K block of the span: hand it back
+                if (span_last) {   // last K block of the span: hand it back
                     if (lane == 0) mbar_arrive(raw_empty0 + r * 8);
                     ++rit;
                 }
@@ -511,6 +538,7 @@ cudaError_t gemm_tc_configure() {
 
 bool gemm_tc_supported(int fmt, int M, int N, int K, const void* x, const void* W, const void* out) {
     if (M <= 16 || N < 1 || K < 64 || (K % 8) != 0) return false;
+    if (fmt != FMT_FP16 && K < 128) return false;   // the two expanding groups need two K blocks per tile
     if (fmt == FMT_INT8 && (K % 16) != 0) return false;   // packed rows keep a 16-byte pitch for the tensor copies
     if (fmt == FMT_Q4 && (K % 32) != 0) return false;
     auto al16 = [](const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; };
