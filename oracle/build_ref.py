@@ -1,6 +1,6 @@
 """Compiles the reference's own OpenCL kernel sources for the CPU (TEST INFRASTRUCTURE ONLY).
 
-    python oracle/build_ref.py            # needs the reference checkout (/root/reference or $NNOPT_REFERENCE)
+    python oracle/build_ref.py            # needs the reference checkout ($NNOPT_REFERENCE, or the default mount below)
 
 For each .cl file on the decode GEMV path, g++ reads from a pipe:
     oracle/cl_shim.h  +  #define USE_FP16  +  the .cl file exactly where it lies in the

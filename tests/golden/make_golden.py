@@ -1,7 +1,7 @@
 #!/usr/bin/env python3
 """Regenerates the committed fixtures in this folder from the reference's own code.
 
-Needs the reference checkout (default /root/reference, or $NNOPT_REFERENCE); the
+Needs the reference checkout ($NNOPT_REFERENCE, or the default mount named below); the
 tests themselves only read the committed outputs.  Run:  python tests/golden/make_golden.py
 
 What it produces
