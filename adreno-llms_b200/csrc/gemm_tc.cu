@@ -38,9 +38,13 @@ namespace {
 constexpr int BM = 128;       // weight rows per tile (UMMA M)
 constexpr int BK = 64;        // K elements per stage = one 128-byte swizzle span of fp16
 constexpr int EPI_WARPS = 4;
-constexpr int DQ_WARPS = 8;   // quantised weights only: warps that turn the raw stage into the fp16 operand
+// quantised weights only: warps that turn the packed stage into the fp16 operand, in groups of four
+// that take K blocks in turn (int8: two groups, Q4, whose expansion is heavier: four)
+__host__ __device__ constexpr int dq_warps(int wfmt) { return wfmt == FMT_Q4 ? 16 : wfmt == FMT_INT8 ? 8 : 0; }
 constexpr int GEMM_THREADS = (2 + EPI_WARPS) * 32;            // producer warp, MMA warp, four epilogue warps
-constexpr int GEMM_THREADS_Q = GEMM_THREADS + DQ_WARPS * 32 + 32;  // ... plus the expanding warps and the packed-weight producer
+__host__ __device__ constexpr int gemm_threads(int wfmt) {    // ... plus the expanding warps and the packed-weight producer
+    return wfmt == FMT_FP16 ? GEMM_THREADS : GEMM_THREADS + dq_warps(wfmt) * 32 + 32;
+}
 constexpr int A_BYTES = BM * BK * 2;  // 16 KB
 constexpr int OUT_ROWS = 128;         // tokens per output slab (staging buffer: OUT_ROWS x 128 fp16 = 32 KB)
 
@@ -139,8 +143,9 @@ __device__ __forceinline__ uint32_t instr_desc_f16(int bn) {
 // operand layout (int8 codes are exact in fp16 and the row scale is applied in the epilogue; a Q4
 // weight becomes fp16(code * block scale)), so a quantised weight is read from HBM once, packed.
 template <int WFMT>
-__global__ void __launch_bounds__(WFMT == FMT_FP16 ? GEMM_THREADS : GEMM_THREADS_Q) linear_gemm_tc_kernel(const __grid_constant__ GemmK g) {
+__global__ void __launch_bounds__(gemm_threads(WFMT)) linear_gemm_tc_kernel(const __grid_constant__ GemmK g) {
     extern __shared__ __align__(128) uint8_t smem[];
+    constexpr int DQ_WARPS = dq_warps(WFMT), NGRP = DQ_WARPS >= 4 ? DQ_WARPS / 4 : 1;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const uint32_t s_base = smem_u32(smem);
     // Scalars are read from the parameter block once: its address is taken (tensor maps), so a
@@ -172,7 +177,7 @@ __global__ void __launch_bounds__(WFMT == FMT_FP16 ? GEMM_THREADS : GEMM_THREADS
 
     if (tid == 0) {
         for (int s = 0; s < g_stages; ++s) {
-            mbar_init(full0 + s * 8, WFMT == FMT_FP16 ? 1 : 1 + DQ_WARPS / 2);  // operands ready: TMA bytes (+ one group of expanding warps)
+            mbar_init(full0 + s * 8, WFMT == FMT_FP16 ? 1 : 1 + 4);  // operands ready: TMA bytes (+ one group of four expanding warps)
             mbar_init(empty0 + s * 8, 1);
         }
         for (int r = 0; r < g_raw_stages; ++r) {
@@ -273,10 +278,10 @@ __global__ void __launch_bounds__(WFMT == FMT_FP16 ? GEMM_THREADS : GEMM_THREADS
         // ---- expanding warps: packed stage -> fp16 rows in the operand's swizzled layout ----
         // Operand layout (K-major, 128-byte swizzle): row r of the stage at (r / 8) * 1024 + (r % 8) * 128,
         // its 16-byte piece c at ((c ^ (r % 8)) * 16).
-        // The eight warps work as two groups of four: group 0 expands the even K blocks, group 1 the
-        // odd ones, so two K blocks are in conversion at any time and a group's round trip through the
-        // barriers is hidden behind the other group's.
-        constexpr int GRP_THREADS = DQ_WARPS * 32 / 2;
+        // The warps work as NGRP groups of four: group g expands the K blocks with kb % NGRP == g, so
+        // NGRP K blocks are in conversion at any time and a group's round trip through the barriers is
+        // hidden behind the other groups'.
+        constexpr int GRP_THREADS = 4 * 32;
         const int dq = tid - (2 + EPI_WARPS) * 32;   // 0 .. DQ_WARPS * 32 - 1
         const int grp = dq / GRP_THREADS, dt = dq % GRP_THREADS;
         const int K32 = g.K / 32;
@@ -315,7 +320,7 @@ __global__ void __launch_bounds__(WFMT == FMT_FP16 ? GEMM_THREADS : GEMM_THREADS
                         sv_next[ps] = (kb + 4 < nkb) ? load_group(tile, (kb >> 2) + 1, ps) : load_group(tile + (int)gridDim.x, 0, ps);
                     }
                 }
-                if ((kb & 1) != grp) {   // the other group's K block
+                if ((kb % NGRP) != grp) {   // another group's K block
                     if (span_last) {
                         __syncwarp();
                         if (lane == 0) mbar_arrive(raw_empty0 + r * 8);
@@ -538,7 +543,8 @@ cudaError_t gemm_tc_configure() {
 
 bool gemm_tc_supported(int fmt, int M, int N, int K, const void* x, const void* W, const void* out) {
     if (M <= 16 || N < 1 || K < 64 || (K % 8) != 0) return false;
-    if (fmt != FMT_FP16 && K < 128) return false;   // the two expanding groups need two K blocks per tile
+    if (fmt == FMT_INT8 && K < 128) return false;   // every expanding group needs a K block in every tile
+    if (fmt == FMT_Q4 && K < 256) return false;
     if (fmt == FMT_INT8 && (K % 16) != 0) return false;   // packed rows keep a 16-byte pitch for the tensor copies
     if (fmt == FMT_Q4 && (K % 32) != 0) return false;
     auto al16 = [](const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; };
@@ -599,8 +605,8 @@ cudaError_t launch_gemm_tc(int fmt, const void* W, const uint16_t* scale, const 
     unsigned grid = (unsigned)(((N + BM - 1) / BM) * g.ntok);
     if (grid > 148u) grid = 148u;  // persistent: one block per SM walks the tiles
     if (fmt == FMT_FP16) linear_gemm_tc_kernel<FMT_FP16><<<grid, GEMM_THREADS, smem, st>>>(g);
-    else if (fmt == FMT_INT8) linear_gemm_tc_kernel<FMT_INT8><<<grid, GEMM_THREADS_Q, smem, st>>>(g);
-    else linear_gemm_tc_kernel<FMT_Q4><<<grid, GEMM_THREADS_Q, smem, st>>>(g);
+    else if (fmt == FMT_INT8) linear_gemm_tc_kernel<FMT_INT8><<<grid, gemm_threads(FMT_INT8), smem, st>>>(g);
+    else linear_gemm_tc_kernel<FMT_Q4><<<grid, gemm_threads(FMT_Q4), smem, st>>>(g);
     return cudaGetLastError();
 }
 
