@@ -289,7 +289,10 @@ __device__ __forceinline__ void stage_x(const uint16_t* __restrict__ x, int M, i
 // the fused arg-max).  The plain instantiation carries none of that code: the per-layer operators
 // are launch-latency-bound, and every instruction-cache line their blocks have to fetch shows up
 // in the step time (the full variant is 0.5 us slower per small launch with nothing switched on).
-template <int FMT, int NT, bool DUAL, int VAR>
+// ONE: the launch has a single activation row (decode).  The row count then is a compile-time
+// constant and the multi-row staging loops and epilogues drop out of the instantiation, which the
+// launch-latency-bound decode step feels as instruction-cache footprint.
+template <int FMT, int NT, bool DUAL, int VAR, bool ONE>
 __global__ void __launch_bounds__(THREADS) linear_stream_kernel(const __grid_constant__ typename KArgsFor<FMT>::type ka) {
     constexpr bool EXT = VAR == 2;
     extern __shared__ __align__(128) uint8_t smem[];
@@ -298,7 +301,7 @@ __global__ void __launch_bounds__(THREADS) linear_stream_kernel(const __grid_con
     // Scalars used all over the kernel are read from the parameter block once.  The block's
     // address is taken (the tensor maps in it are handed to the TMA unit), so the compiler must
     // assume that any store may change it and would otherwise re-read a field after every store.
-    const int aM = a.M, aK = a.K, a_epi = a.epi, a_nseg = a.nseg;
+    const int aM = ONE ? 1 : a.M, aK = a.K, a_epi = a.epi, a_nseg = a.nseg;
     int* const a_status = a.status;
     const int seg1_tile0 = a.seg[1].tile0, seg2_tile0 = a.seg[2].tile0;
     const int stages = ka.stages, kcb = a.kcb;
@@ -1163,9 +1166,9 @@ int env_int(const char* name, int dflt) {
     return v && *v ? atoi(v) : dflt;
 }
 
-template <int FMT, int NT, bool DUAL, int VAR>
-cudaError_t launch_e(const typename KArgsFor<FMT>::type& ka, const StreamPlan& p, cudaStream_t st, bool pdl) {
-    auto kern = linear_stream_kernel<FMT, NT, DUAL, VAR>;
+template <int FMT, int NT, bool DUAL, int VAR, bool ONE>
+cudaError_t launch_o(const typename KArgsFor<FMT>::type& ka, const StreamPlan& p, cudaStream_t st, bool pdl) {
+    auto kern = linear_stream_kernel<FMT, NT, DUAL, VAR, ONE>;
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3((unsigned)p.grid);
     cfg.blockDim = dim3((unsigned)THREADS);
@@ -1177,6 +1180,12 @@ cudaError_t launch_e(const typename KArgsFor<FMT>::type& ka, const StreamPlan& p
     cfg.attrs = attr;
     cfg.numAttrs = 1;
     return cudaLaunchKernelEx(&cfg, kern, ka);
+}
+
+template <int FMT, int NT, bool DUAL, int VAR>
+cudaError_t launch_e(const typename KArgsFor<FMT>::type& ka, const StreamPlan& p, cudaStream_t st, bool pdl) {
+    if (NT == 1 && ka.a.M == 1) return launch_o<FMT, 1, DUAL, VAR, true>(ka, p, st, pdl);
+    return launch_o<FMT, NT, DUAL, VAR, false>(ka, p, st, pdl);
 }
 
 template <int FMT, int NT, bool DUAL>
@@ -1250,11 +1259,13 @@ bool make_scale_map(CUtensorMap* m, const void* S, int rows, int rowbytes, int b
 
 template <int FMT, int NT, bool DUAL>
 cudaError_t configure_one() {
-    cudaError_t e = cudaFuncSetAttribute(linear_stream_kernel<FMT, NT, DUAL, 0>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
-    if (e != cudaSuccess) return e;
-    e = cudaFuncSetAttribute(linear_stream_kernel<FMT, NT, DUAL, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
-    if (e != cudaSuccess) return e;
-    return cudaFuncSetAttribute(linear_stream_kernel<FMT, NT, DUAL, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+    cudaError_t e = cudaSuccess;
+#define SET_SMEM(V, O)                                                                                                                       \
+    if (e == cudaSuccess) e = cudaFuncSetAttribute(linear_stream_kernel<FMT, NT, DUAL, V, O>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+    SET_SMEM(0, false) SET_SMEM(1, false) SET_SMEM(2, false)
+    if (NT == 1) { SET_SMEM(0, true) SET_SMEM(1, true) SET_SMEM(2, true) }
+#undef SET_SMEM
+    return e;
 }
 
 int count_tiles(const LinArgs& a, int tile_rows) {
