@@ -86,6 +86,13 @@ extern "C" int nn_init(int device, nn_context** out) {
         delete c;
         return NN_FAIL(NN_ERR_CUDA, "nn_init: cudaMalloc failed");
     }
+    // normalised activations for the norm-then-project calls that cannot fuse the norm: sized for the
+    // decode shapes up front so that such calls also work inside a recording (it grows outside one)
+    c->norm_scratch_bytes = (size_t)1 << 20;
+    if (cudaMalloc(&c->norm_scratch, c->norm_scratch_bytes) != cudaSuccess) {
+        delete c;
+        return NN_FAIL(NN_ERR_CUDA, "nn_init: cudaMalloc failed");
+    }
     if ((e = stream_configure()) != cudaSuccess) {
         delete c;
         return NN_FAIL(NN_ERR_CUDA, "nn_init: kernel configuration failed: %s", cudaGetErrorString(e));
