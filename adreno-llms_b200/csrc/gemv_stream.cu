@@ -101,10 +101,25 @@ struct KArgs {
 struct KArgsQ4 : KArgs {
     alignas(64) CUtensorMap tm_s[4];  // Q4 scale views [N][K/16 bytes]: seg[0..2], and scale2
 };
+// The tensor maps travel in a kernel parameter of their own: their address is taken (the TMA unit
+// reads them in place), and everything that shares a parameter with them would be read through
+// generic loads; the scalars go by value in a second parameter and are read as constants.
+struct KMaps { alignas(64) CUtensorMap tm[4]; };
+struct KMapsQ4 { alignas(64) CUtensorMap tm[4]; alignas(64) CUtensorMap tm_s[4]; };
+template <int FMT> struct KMapsFor { typedef KMaps type; };
+template <> struct KMapsFor<FMT_Q4> { typedef KMapsQ4 type; };
+struct KScal {
+    LinArgs a;
+    int stages, rowbytes, nchunks, evict_first, scale_tma;
+#ifdef NNB_TRACE
+    unsigned long long* trace;
+    int trace_slot;
+#endif
+};
+__device__ __forceinline__ const CUtensorMap* scale_map(const KMaps&, int) { return nullptr; }
+__device__ __forceinline__ const CUtensorMap* scale_map(const KMapsQ4& km, int i) { return &km.tm_s[i]; }
 template <int FMT> struct KArgsFor { typedef KArgs type; };
 template <> struct KArgsFor<FMT_Q4> { typedef KArgsQ4 type; };
-__device__ __forceinline__ const CUtensorMap* scale_map(const KArgs&, int) { return nullptr; }
-__device__ __forceinline__ const CUtensorMap* scale_map(const KArgsQ4& ka, int i) { return &ka.tm_s[i]; }
 
 // int8 weights are multiplied on the integer tensor-core path, with no conversion of the
 // weights at all: each activation row is turned into 24-bit fixed point
@@ -293,7 +308,7 @@ __device__ __forceinline__ void stage_x(const uint16_t* __restrict__ x, int M, i
 // constant and the multi-row staging loops and epilogues drop out of the instantiation, which the
 // launch-latency-bound decode step feels as instruction-cache footprint.
 template <int FMT, int NT, bool DUAL, int VAR, bool ONE>
-__global__ void __launch_bounds__(THREADS) linear_stream_kernel(const __grid_constant__ typename KArgsFor<FMT>::type ka) {
+__global__ void __launch_bounds__(THREADS) linear_stream_kernel(const __grid_constant__ typename KMapsFor<FMT>::type km, const KScal ka) {
     constexpr bool EXT = VAR == 2;
     extern __shared__ __align__(128) uint8_t smem[];
     const LinArgs& a = ka.a;
@@ -392,19 +407,19 @@ __global__ void __launch_bounds__(THREADS) linear_stream_kernel(const __grid_con
                     if (stma) {
                         const uint32_t sdst = dst + geo.nbox * CTA_BOX;
                         if (DUAL) {
-                            tma_load_2d(sdst, scale_map(ka, 0), cg * bw, row0, bar, policy);
-                            tma_load_2d(sdst + (NCW * WARP_ROWS / 2) * bw, scale_map(ka, 3), cg * bw, row0, bar, policy);
+                            tma_load_2d(sdst, scale_map(km, 0), cg * bw, row0, bar, policy);
+                            tma_load_2d(sdst + (NCW * WARP_ROWS / 2) * bw, scale_map(km, 3), cg * bw, row0, bar, policy);
                         } else {
-                            tma_load_2d(sdst, scale_map(ka, sg), cg * bw, row0, bar, policy);
+                            tma_load_2d(sdst, scale_map(km, sg), cg * bw, row0, bar, policy);
                         }
                     }
                     for (int b = 0; b < nb; ++b) {
                         const int x = cg * kcb + b * 128;
                         if (DUAL) {
-                            tma_load_2d(dst + b * CTA_BOX, &ka.tm[0], x, row0, bar, policy);
-                            tma_load_2d(dst + b * CTA_BOX + CTA_BOX / 2, &ka.tm[3], x, row0, bar, policy);
+                            tma_load_2d(dst + b * CTA_BOX, &km.tm[0], x, row0, bar, policy);
+                            tma_load_2d(dst + b * CTA_BOX + CTA_BOX / 2, &km.tm[3], x, row0, bar, policy);
                         } else {
-                            tma_load_2d(dst + b * CTA_BOX, &ka.tm[sg], x, row0, bar, policy);
+                            tma_load_2d(dst + b * CTA_BOX, &km.tm[sg], x, row0, bar, policy);
                         }
                     }
                 } else {
@@ -423,20 +438,20 @@ __global__ void __launch_bounds__(THREADS) linear_stream_kernel(const __grid_con
                         if (stma) {
                             const uint32_t sdst = dst + geo.nbox * CTA_BOX;
                             if (DUAL) {
-                                tma_load_2d(sdst + w * (WARP_ROWS / 2) * bw, scale_map(ka, 0), c * bw, row0, bar, policy);
-                                tma_load_2d(sdst + (NCW * WARP_ROWS / 2 + w * (WARP_ROWS / 2)) * bw, scale_map(ka, 3), c * bw, row0, bar, policy);
+                                tma_load_2d(sdst + w * (WARP_ROWS / 2) * bw, scale_map(km, 0), c * bw, row0, bar, policy);
+                                tma_load_2d(sdst + (NCW * WARP_ROWS / 2 + w * (WARP_ROWS / 2)) * bw, scale_map(km, 3), c * bw, row0, bar, policy);
                             } else {
-                                tma_load_2d(sdst + w * WARP_ROWS * bw, scale_map(ka, sg), c * bw, row0, bar, policy);
+                                tma_load_2d(sdst + w * WARP_ROWS * bw, scale_map(km, sg), c * bw, row0, bar, policy);
                             }
                         }
                         const int nb = (min(kcb, rowbytes - c * kcb) + 127) >> 7;
                         for (int b = 0; b < nb; ++b) {
                             const int x = c * kcb + b * 128;
                             if (DUAL) {
-                                tma_load_2d(dst + b * CTA_BOX + w * (BOX_BYTES / 2), &ka.tm[0], x, row0, bar, policy);
-                                tma_load_2d(dst + b * CTA_BOX + CTA_BOX / 2 + w * (BOX_BYTES / 2), &ka.tm[3], x, row0, bar, policy);
+                                tma_load_2d(dst + b * CTA_BOX + w * (BOX_BYTES / 2), &km.tm[0], x, row0, bar, policy);
+                                tma_load_2d(dst + b * CTA_BOX + CTA_BOX / 2 + w * (BOX_BYTES / 2), &km.tm[3], x, row0, bar, policy);
                             } else {
-                                tma_load_2d(dst + b * CTA_BOX + w * BOX_BYTES, &ka.tm[sg], x, row0, bar, policy);
+                                tma_load_2d(dst + b * CTA_BOX + w * BOX_BYTES, &km.tm[sg], x, row0, bar, policy);
                             }
                         }
                     }
@@ -1161,6 +1176,13 @@ __global__ void __launch_bounds__(THREADS) linear_stream_kernel(const __grid_con
 #endif
 }
 
+inline void fill_maps(KMaps& km, const KArgs& ka) {
+    for (int i = 0; i < 4; ++i) km.tm[i] = ka.tm[i];
+}
+inline void fill_maps(KMapsQ4& km, const KArgsQ4& ka) {
+    for (int i = 0; i < 4; ++i) { km.tm[i] = ka.tm[i]; km.tm_s[i] = ka.tm_s[i]; }
+}
+
 int env_int(const char* name, int dflt) {
     const char* v = getenv(name);
     return v && *v ? atoi(v) : dflt;
@@ -1179,7 +1201,15 @@ cudaError_t launch_o(const typename KArgsFor<FMT>::type& ka, const StreamPlan& p
     attr[0].val.programmaticStreamSerializationAllowed = pdl ? 1 : 0;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
-    return cudaLaunchKernelEx(&cfg, kern, ka);
+    typename KMapsFor<FMT>::type km;
+    fill_maps(km, ka);
+    KScal ks;
+    ks.a = ka.a;
+    ks.stages = ka.stages; ks.rowbytes = ka.rowbytes; ks.nchunks = ka.nchunks; ks.evict_first = ka.evict_first; ks.scale_tma = ka.scale_tma;
+#ifdef NNB_TRACE
+    ks.trace = ka.trace; ks.trace_slot = ka.trace_slot;
+#endif
+    return cudaLaunchKernelEx(&cfg, kern, km, ks);
 }
 
 template <int FMT, int NT, bool DUAL, int VAR>
