@@ -86,6 +86,7 @@ def load():
         "nn_comm_all_gather": ([vp, vp, vp, sz], i), "nn_comm_free": ([vp], i),
         "nn_comm_symm_alloc": ([vp, sz, pvp], i), "nn_comm_symm_free": ([vp, vp], i),
         "nn_linear_gather": ([vp, i, i, i, vp, vp, vp], i),
+        "nn_linear_argmax_sharded": ([vp, i, i, vp, vp, vp, vp], i),
         "nn_comm_signal": ([vp], i), "nn_comm_wait": ([vp, ctypes.c_uint], i),
         "nn_device_count": ([], i),
     }
@@ -297,6 +298,9 @@ class Comm:
 
     def linear_gather(self, M, n_local, K, x, W, gathered):
         _check(self.ctx.L.nn_linear_gather(self.h, M, n_local, K, x, W, gathered))
+
+    def linear_argmax_sharded(self, n_local, K, x, W, logits_local, out_idx):
+        _check(self.ctx.L.nn_linear_argmax_sharded(self.h, n_local, K, x, W, logits_local, out_idx))
 
     def signal(self):
         _check(self.ctx.L.nn_comm_signal(self.h))

@@ -518,13 +518,18 @@ extern "C" int nn_dequant(nn_context* c, int N, int K, nn_buf W, nn_buf out) {
 }
 
 extern "C" int nn_linear_argmax(nn_context* c, int N, int K, nn_buf x, nn_buf W, nn_buf logits, nn_buf out_idx) {
-    int rc = check_common(c, 1, N, K, x, W, out_idx, "nn_linear_argmax");
+    return nnb::linear_argmax(c, N, K, x, W, logits, out_idx, 0, nullptr, "nn_linear_argmax");
+}
+
+int nnb::linear_argmax(nn_context* c, int N, int K, nn_buf x, nn_buf W, nn_buf logits, nn_buf out_idx, int row_base, const GatherSignal* sig,
+                       const char* who) {
+    int rc = check_common(c, 1, N, K, x, W, out_idx, who);
     if (rc) return rc;
     ResolvedW r;
     if (!resolve_weight(c, W, K, &r))
-        return NN_FAIL(NN_ERR_ARG, "nn_linear_argmax: W points into a registered quantised weight but K=%d or the row offset does not match", K);
+        return NN_FAIL(NN_ERR_ARG, "%s: W points into a registered quantised weight but K=%d or the row offset does not match", who, K);
     if (r.rows_avail >= 0 && N > r.rows_avail)
-        return NN_FAIL(NN_ERR_ARG, "nn_linear_argmax: N=%d exceeds the %d rows registered for this weight", N, r.rows_avail);
+        return NN_FAIL(NN_ERR_ARG, "%s: N=%d exceeds the %d rows registered for this weight", who, N, r.rows_avail);
     LinArgs a = {};
     a.nseg = 1;
     a.seg[0].W = (const uint8_t*)W;
@@ -543,17 +548,19 @@ extern "C" int nn_linear_argmax(nn_context* c, int N, int K, nn_buf x, nn_buf W,
     if (stream_supported(r.fmt, 1, K, a)) p = stream_plan(r.fmt, a, c->sm_count, c->smem_limit);
     if (!p.ok) {
         // shapes the streaming kernel does not take: projection, then the separate arg-max
-        if (!logits) return NN_FAIL(NN_ERR_UNSUPPORTED, "nn_linear_argmax: this shape (K=%d) needs a logits buffer", K);
-        rc = one_weight(c, 1, N, K, x, W, logits, EPI_STORE, "nn_linear_argmax");
+        if (sig) return NN_FAIL(NN_ERR_UNSUPPORTED, "%s: this shape (K=%d) is not taken by the streaming kernel", who, K);
+        if (!logits) return NN_FAIL(NN_ERR_UNSUPPORTED, "%s: this shape (K=%d) needs a logits buffer", who, K);
+        rc = one_weight(c, 1, N, K, x, W, logits, EPI_STORE, who);
         if (rc) return rc;
         return nn_argmax(c, N, logits, out_idx);
     }
     a.argmax_slot = c->argmax_slot + 1;
     a.argmax_done = reinterpret_cast<unsigned*>(c->argmax_slot + 2);
     a.argmax_out = (int*)out_idx;
-    a.argmax_base = 0;
+    a.argmax_base = row_base;
+    if (sig) a.sig = *sig;
     cudaError_t e = launch_stream(r.fmt, a, p, c->stream, c->use_pdl);
-    if (e != cudaSuccess) return NN_FAIL(NN_ERR_CUDA, "nn_linear_argmax: launch failed: %s (N=%d K=%d)", cudaGetErrorString(e), N, K);
+    if (e != cudaSuccess) return NN_FAIL(NN_ERR_CUDA, "%s: launch failed: %s (N=%d K=%d)", who, cudaGetErrorString(e), N, K);
     c->launches++;
     return NN_OK;
 }

@@ -73,7 +73,7 @@ struct nn_comm {
     int rank = 0, world = 1;
     std::vector<SymmAlloc> symm;
     unsigned* flags = nullptr;   // symmetric: word g is written by rank g's signal kernel
-    unsigned* epochs = nullptr;  // local: [0] signals sent, [1] waits done
+    unsigned* epochs = nullptr;  // local: [0] signals sent, [1] waits done, [2] blocks done, [3] picks sent, [4] picks waited
 };
 
 #define COMM_CUDA(call)                                                                                   \
@@ -242,6 +242,26 @@ extern "C" int nn_linear_gather(nn_comm* c, int M, int n_local, int K, nn_buf x,
     int rc = nnb::linear_to_peers(c->ctx, M, n_local, K, x, W, (char*)gathered + block * c->rank, peers, np, &sig, "nn_linear_gather");
     if (rc) return rc;
     COMM_CUDA(nnb::launch_comm_wait(c->flags, c->world, c->epochs + 1, 2000, c->ctx->status_dev, c->ctx->use_pdl, c->ctx->stream));
+    c->ctx->launches++;
+    return NN_OK;
+}
+
+extern "C" int nn_linear_argmax_sharded(nn_comm* c, int n_local, int K, nn_buf x, nn_buf W, nn_buf logits_local, nn_buf out_idx) {
+    const char* who = "nn_linear_argmax_sharded";
+    if (!c || !out_idx) return NN_FAIL(NN_ERR_ARG, "%s: null argument", who);
+    if (!c->flags) return NN_FAIL(NN_ERR_ARG, "%s: no symmetric buffer has been allocated on this communicator", who);
+    if (n_local <= 0 || (long long)n_local * c->world > 0x7fffffffLL) return NN_FAIL(NN_ERR_ARG, "%s: bad n_local=%d", who, n_local);
+    nnb::GatherSignal sig = {};
+    sig.world = c->world;
+    sig.rank = c->rank;
+    for (int g = 0; g < c->world; ++g) sig.flags[g] = (unsigned*)c->symm[0].base[g];
+    sig.epoch = c->epochs + 3;  // picks sent
+    sig.done = nullptr;         // no flag exchange: the key word is its own arrival mark
+    // the block that finishes the projection's arg-max leaves this rank's key with every rank;
+    // the pick kernel, already spinning by then, takes the best of the G keys
+    int rc = nnb::linear_argmax(c->ctx, n_local, K, x, W, logits_local, out_idx, c->rank * n_local, &sig, who);
+    if (rc) return rc;
+    COMM_CUDA(nnb::launch_comm_pick(c->flags, c->world, c->epochs + 4, 2000, c->ctx->status_dev, c->ctx->use_pdl, (int*)out_idx, c->ctx->stream));
     c->ctx->launches++;
     return NN_OK;
 }

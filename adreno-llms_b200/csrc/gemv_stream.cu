@@ -1152,13 +1152,20 @@ __global__ void __launch_bounds__(THREADS) linear_stream_kernel(const __grid_con
             if (prev == gridDim.x - 1u) {
                 __threadfence();
                 const unsigned long long k = *reinterpret_cast<volatile unsigned long long*>(a.argmax_slot);
-                *a.argmax_out = k ? (int)(0xFFFFFFFFu - (unsigned int)(k & 0xFFFFFFFFull)) : -1;
                 *reinterpret_cast<volatile unsigned long long*>(a.argmax_slot) = 0ull;
                 *reinterpret_cast<volatile unsigned*>(a.argmax_done) = 0u;
+                if (a.sig.world > 0) {
+                    // row-sharded pick: comm_pick_kernel chooses among the ranks' keys.  The words
+                    // above are clear before the key can release the next launch that uses them.
+                    __threadfence();
+                    argmax_share_key(a.sig, k);
+                } else {
+                    *a.argmax_out = k ? (int)(0xFFFFFFFFu - (unsigned int)(k & 0xFFFFFFFFull)) : -1;
+                }
             }
         }
     }
-    if (EXT && a.sig.world > 0) {
+    if (EXT && a.sig.world > 0 && !a.argmax_slot) {
         // row-sharded gather: all of this block's outputs are stored; count the block in
         asm volatile("bar.sync 1, %0;" ::"n"(NCW * 32) : "memory");
         if (tid == 0) gather_signal_block_done(a.sig);

@@ -47,6 +47,12 @@ struct GatherSignal;
 int linear_to_peers(nn_context* c, int M, int N, int K, void* x, void* W, void* out, uint16_t* const* peers, int npeer,
                     const GatherSignal* sig, const char* who);
 
+// nn_linear_argmax with the winning row reported as row_base + row; with `sig` the kernel leaves
+// its best key in every rank's key table and sends the completion signal instead of writing
+// out_idx (the wait kernel that follows picks among the ranks); api.cpp
+int linear_argmax(nn_context* c, int N, int K, void* x, void* W, void* logits, void* out_idx, int row_base, const GatherSignal* sig,
+                  const char* who);
+
 int fail(int code, const char* file, int line, const char* fmt, ...) __attribute__((format(printf, 4, 5)));
 
 }  // namespace nnb

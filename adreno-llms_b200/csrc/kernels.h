@@ -19,6 +19,11 @@ enum Epi : int {
 
 // Completion signal of a row-sharded gather, sent by the projection kernel itself: the last
 // block to finish publishes the next epoch number in word `rank` of every rank's flag array.
+// Byte offset, inside each rank's symmetric flag allocation, of the key tables of the row-sharded
+// greedy pick: two tables (parity of the pick number) of eight 64-bit words, word g written by
+// rank g: pick number (16 bits) | ordered fp16 value (16 bits) | ~row (32 bits).
+constexpr int KEY_TABLE_OFFSET = 64;
+
 struct GatherSignal {
     unsigned* flags[8];  // flags[g] = rank g's flag array (peer-mapped for g != rank)
     unsigned* epoch;     // local: signals sent so far
@@ -117,6 +122,10 @@ cudaError_t launch_comm_signal(const PeerFlags& pf, unsigned* epoch_sent, cudaSt
 // the kernel before it still runs (valid when that kernel sends this rank's own signal).
 cudaError_t launch_comm_wait(const unsigned* my_flags, int world, unsigned* epoch_waited, unsigned timeout_ms, int* status, bool overlap,
                              cudaStream_t st);
+// Row-sharded greedy pick: waits (bounded) for pick number *picks_waited + 1 of every rank in this
+// rank's key tables and writes the winning row (-1: every value was NaN, or the wait ran out).
+cudaError_t launch_comm_pick(const unsigned* my_flags, int world, unsigned* picks_waited, unsigned timeout_ms, int* status, bool overlap,
+                             int* out_row, cudaStream_t st);
 
 // misc.cu
 cudaError_t launch_dequant(int fmt, int N, int K, const void* W, const uint16_t* scale, float* out, cudaStream_t st);

@@ -223,6 +223,33 @@ __device__ __forceinline__ unsigned long long argmax_key_half(uint16_t h, int id
 // count with a device-scope fence; the block that completes the count publishes the epoch with
 // one system-scope release, which is cumulative over what the counts it observed had ordered.
 // System-scope fences cost microseconds each, so there is exactly one on this path.
+// Row-sharded greedy pick: this rank's best key (ordered fp32 bits of an fp16 value << 32 |
+// ~global row; 0 = no candidate) goes, re-packed as pick number (16 bits) | ordered fp16 value
+// (16) | ~row (32), into word `rank` of every rank's key table, which follows the flag words in
+// the same symmetric allocation.  The word carries its own arrival mark, so no fence or flag
+// accompanies it.  Two tables alternate with the pick number: a rank already one pick ahead
+// cannot overwrite a word that a slower rank has not read yet, and it cannot be two ahead because
+// its own next pick waits for every rank's word.  `s.epoch` counts this rank's picks here.
+// Called by one thread of the block that finishes the launch's arg-max.
+__device__ __forceinline__ void argmax_share_key(const nnb::GatherSignal& s, unsigned long long key) {
+    const unsigned e = *reinterpret_cast<volatile unsigned*>(s.epoch) + 1u;
+    *reinterpret_cast<volatile unsigned*>(s.epoch) = e;
+    unsigned long long payload = 0ull;
+    if (key) {
+        const unsigned ob = (unsigned)(key >> 32);
+        const unsigned fb = (ob & 0x80000000u) ? (ob & 0x7FFFFFFFu) : ~ob;  // back to the float's bits
+        const unsigned h = __half_as_ushort(__float2half_rn(__uint_as_float(fb)));  // exact: the value is an fp16
+        const unsigned oh = (h & 0x8000u) ? (~h & 0xFFFFu) : (h | 0x8000u);       // never 0 for a non-NaN
+        payload = ((unsigned long long)oh << 32) | (key & 0xFFFFFFFFull);
+    }
+    const unsigned long long word = ((unsigned long long)(e & 0xFFFFu) << 48) | payload;
+    for (int g = 0; g < s.world; ++g) {
+        unsigned long long* dst =
+            reinterpret_cast<unsigned long long*>(reinterpret_cast<char*>(s.flags[g]) + nnb::KEY_TABLE_OFFSET) + (e & 1u) * 8u + (unsigned)s.rank;
+        asm volatile("st.relaxed.sys.global.u64 [%0], %1;" ::"l"(dst), "l"(word) : "memory");
+    }
+}
+
 __device__ __forceinline__ void gather_signal_block_done(const nnb::GatherSignal& s) {
     __threadfence();
     const unsigned prev = atomicAdd(s.done, 1u);

@@ -19,12 +19,15 @@ from . import synth
 
 class DecodeStep:
     def __init__(self, ctx, shape: synth.ModelShape, fmt: str, M: int = 1, n_sets: int = 1, seed: int = 1235,
-                 vocab_rows=None, keep_host=False, only=None, comm=None, norm=False):
+                 vocab_rows=None, keep_host=False, only=None, comm=None, norm=False, gather_logits=False):
         self.ctx, self.shape, self.fmt, self.M = ctx, shape, fmt, M
         # with a communicator the lm_head rows are this rank's shard and the projection
         # stores into every rank's gather buffer (one buffer per weight set, so that
         # consecutive steps never share one)
+        # gather_logits=False: a single-token step with the greedy pick exchanges one (value, row)
+        # key per rank instead of the logits (each rank still stores its own shard of them)
         self.comm = comm
+        self.gather_logits = gather_logits
         self.gathered = [comm.symm_alloc(M * shape.vocab * 2) for _ in range(n_sets)] if comm else None
         self.vocab_lo, self.vocab_n = vocab_rows if vocab_rows else (0, shape.vocab)
         rng = np.random.default_rng(seed)
@@ -107,6 +110,8 @@ class DecodeStep:
                 c.fused_gate_up_silu(M, sh.ffn, sh.hidden, self.x_h, w[0], w[1], self.act)
             elif kind == "down_add":
                 c.linear_add(M, sh.hidden, sh.ffn, self.x_act, w[0], self.resid)
+            elif self.comm and with_argmax and M == 1 and not self.gather_logits:
+                self.comm.linear_argmax_sharded(self.vocab_n, sh.hidden, self.x_h, w[0], self.logits, self.token)
             elif self.comm:
                 self.comm.linear_gather(M, self.vocab_n, sh.hidden, self.x_h, w[0], self.gathered[set_index])
                 if with_argmax and M == 1:   # [G][1][V/G] is the full logits vector

@@ -23,8 +23,9 @@ achieved weight-stream rate: algorithmic bytes of the step / step time, in GB/s.
             at M = 512 / 2048 on the tensor-core path), each timed alone
 
 With --gpus N > 1 (launched under torchrun) the lm_head rows are sharded across the
-ranks and every rank's lm_head kernel stores its rows into every rank's gather buffer
-over NVLink peer memory; the per-layer projections stay replicated
+ranks; every rank keeps its rows of the logits and the greedy pick exchanges one 8-byte
+(value, row) key per rank over NVLink peer memory (the step with the logits gathered to
+every rank instead is timed beside it); the per-layer projections stay replicated
 (north star: only the large row-sharded projections are partitioned).
 --impl reference times the reference's own CPU implementation of the path
 (oracle/_ref when it was built, else the oracle port) on the host cores.
@@ -482,11 +483,21 @@ def main():
     import ctypes
     ctypes.memmove(hx, synth.activations(MM, shape.hidden, np.random.default_rng(5)).ctypes.data, MM * shape.hidden * 2)
 
+    # With several ranks and the greedy pick, the step's result on a rank is the token plus this
+    # rank's rows of the logits (the other rows stay with their ranks); otherwise the full logits.
+    keys_pick = bool(comm) and MM == 1 and args.only is None
+    hl_tok = pkg.load().nn_host_alloc(64)
+    d2h_bytes = (MM * step.vocab_n * 2 + 4) if keys_pick else MM * shape.vocab * 2
+
     def e2e_step(i):
         pkg._check(ctx.L.nn_buf_write(ctx.h, step.x_h, 0, hx, MM * shape.hidden * 2))
         enqueue_step(i)
-        out_buf = step.gathered[i % n_sets] if comm else step.logits
-        pkg._check(ctx.L.nn_buf_read(ctx.h, hl, out_buf, 0, MM * shape.vocab * 2))
+        if keys_pick:
+            pkg._check(ctx.L.nn_buf_read(ctx.h, hl, step.logits, 0, MM * step.vocab_n * 2))
+            pkg._check(ctx.L.nn_buf_read(ctx.h, hl_tok, step.token, 0, 4))
+        else:
+            out_buf = step.gathered[i % n_sets] if comm else step.logits
+            pkg._check(ctx.L.nn_buf_read(ctx.h, hl, out_buf, 0, MM * shape.vocab * 2))
         ctx.sync()
 
     for i in range(5):
@@ -502,6 +513,24 @@ def main():
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         e2e_s = float(t.item())
     e2e_value = step_bytes_full / (e2e_s / e2e_steps) / 1e9
+
+    # ---- several ranks: the same step with the logits gathered to every rank instead (each
+    #      rank's lm_head kernel stores its rows into all gather buffers, then one arg-max) ----
+    gathered_step_us = None
+    if keys_pick:
+        step.gather_logits = True
+        for pl in step.plans:
+            ctx.L.nn_plan_free(pl)
+        step.record(with_argmax=True)
+        for i in range(args.warmup):
+            enqueue_step(i)
+        barrier()
+        gms = time_group(ctx, enqueue_step, args.steps)
+        barrier()
+        import torch
+        t = torch.tensor([gms], dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        gathered_step_us = float(t.item()) / args.steps * 1e3
 
     # ---- roofline: each launch group of the step timed alone (same launches, rotating sets) ----
     peak, peak_src = measured_peaks()
@@ -527,6 +556,8 @@ def main():
                     ctx.fused_gate_up_silu(M, sh.ffn, sh.hidden, step.x_h, w[0], w[1], step.act)
                 elif kind == "down_add":
                     ctx.linear_add(M, sh.hidden, sh.ffn, step.x_act, w[0], step.resid)
+                elif keys_pick:
+                    comm.linear_argmax_sharded(step.vocab_n, sh.hidden, step.x_h, w[0], step.logits, step.token)
                 elif comm:
                     comm.linear_gather(M, step.vocab_n, sh.hidden, step.x_h, w[0], step.gathered[i % n_sets])
                 else:
@@ -587,10 +618,13 @@ def main():
                        "algorithmic_bytes_per_step": step_bytes_full,
                        "l2": f"{n_sets} resident weight copies rotated step to step "
                              f"({n_sets * step.weight_bytes / 1e6:.0f} MB > L2 {l2_bytes / 1e6:.0f} MB)",
-                       "sharding": "none" if world == 1 else f"lm_head rows / {world} ranks, each rank's kernel stores into every rank's "
-                                                                    "gather buffer over NVLink peer memory; layers replicated"},
+                       "sharding": "none" if world == 1 else
+                                   (f"lm_head rows / {world} ranks; every rank stores its rows of the logits locally and the greedy pick "
+                                    "exchanges one 8-byte (value, row) key per rank over NVLink peer memory; layers replicated" if keys_pick else
+                                    f"lm_head rows / {world} ranks, each rank's kernel stores into every rank's "
+                                    "gather buffer over NVLink peer memory; layers replicated")},
             "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": MM * shape.hidden * 2,
-                    "d2h_bytes_per_step": MM * shape.vocab * 2, "us_per_step": e2e_s / e2e_steps * 1e6, "steps": e2e_steps},
+                    "d2h_bytes_per_step": d2h_bytes, "us_per_step": e2e_s / e2e_steps * 1e6, "steps": e2e_steps},
             "gpu_launches": launches,
             "roofline": {"bound": "hbm", "kernel": f"linear_stream_kernel [{dom['group']}]", "achieved": dom["gbps"], "peak": peak,
                          "unit": "GB/s", "frac": dom["gbps"] / peak, "traffic": traffic_tbl.get(dom["group"]), "peak_source": peak_src,
@@ -602,6 +636,7 @@ def main():
             "sharded_projections": sharded,
             "prefill_gemm": prefill,
             "decode_step_with_fused_rmsnorm_us": norm_step_us,
+            "decode_step_with_gathered_logits_us": gathered_step_us,
             "clocks": clocks,
         }
         if cpu_base:

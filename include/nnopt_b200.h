@@ -233,10 +233,24 @@ int nn_comm_free(nn_comm* comm);
  *   nn_comm_wait        hold the stream until every rank's signal count has reached this
  *                       rank's wait count, at most timeout_ms (1..10000); when the wait runs
  *                       out the next nn_sync returns NN_ERR_TIMEOUT and the context stays usable.
+ *   nn_linear_argmax_sharded  greedy pick over a row-sharded lm_head (M = 1) without moving the
+ *                       logits: rank g holds rows [g*n_local, (g+1)*n_local) of the weight; each
+ *                       rank's projection kernel folds its rows into one (value, row) key and
+ *                       stores it, tagged with the pick's number, in a table on every rank (one
+ *                       8-byte peer store per rank, no fence: the word is its own arrival mark);
+ *                       a one-warp kernel then waits (bounded, 2 s) for the G words and takes the
+ *                       best.  Every rank's out_index (device int) receives the index
+ *                       nn_linear_argmax would give on the whole weight (lowest row on ties, -1
+ *                       when all values are NaN).  8 bytes per rank cross NVLink instead of 2*N.
+ *                       `logits_local_fp16` may be NULL; otherwise this rank's n_local logits are
+ *                       also stored there (ordinary device memory).  Every rank must make the
+ *                       same sequence of these calls.  Needs one prior nn_comm_symm_alloc on the
+ *                       communicator (which creates the flag and key words).
  * No counterpart in the reference. */
 int nn_comm_symm_alloc(nn_comm* comm, size_t bytes, nn_buf* out);
 int nn_comm_symm_free(nn_comm* comm, nn_buf buf);
 int nn_linear_gather(nn_comm* comm, int M, int n_local, int K, nn_buf x, nn_buf W, nn_buf gathered);
+int nn_linear_argmax_sharded(nn_comm* comm, int n_local, int K, nn_buf x, nn_buf W, nn_buf logits_local_fp16, nn_buf out_index_i32);
 int nn_comm_signal(nn_comm* comm);
 int nn_comm_wait(nn_comm* comm, unsigned timeout_ms);
 /* Number of CUDA devices visible to the process (0 when there is none). */

@@ -6,6 +6,10 @@ Every rank builds the same seeded weight, keeps its row block, and runs the proj
   * nn_linear_gather, whose kernel stores into every rank's gather buffer over peer memory.
 Both gathered results must be bit-identical, and, reassembled to [M, N], must match the CPU
 oracle on the unsharded weight within the path's tolerance.
+
+Then the row-sharded greedy pick (nn_linear_argmax_sharded, one key per rank instead of the
+logits): on every rank it must name the row that the arg-max over the gathered logits names,
+lowest row on ties, over repeated calls (the key tables alternate with the epoch).
 """
 import os
 import sys
@@ -23,6 +27,14 @@ CASES = [  # fmt, N, K, M
     ("fp16", 2048, 512, 64),    # tensor-core path
     ("int8", 3072, 896, 256),   # tensor-core path, quantised weight
     ("q4", 1024, 2048, 40),
+]
+
+
+PICK_CASES = [  # fmt, N, K
+    ("int8", 4096, 576),
+    ("q4", 2048, 1024),
+    ("fp16", 1536, 896),
+    ("int8", 49152, 576),   # the lm_head of the benchmarked shape
 ]
 
 
@@ -81,6 +93,39 @@ def main():
         qw.release()
         ctx.free(g1)
         ctx.free(dx)
+    for fmt, N, K in PICK_CASES:
+        W, s = make_weight(fmt, N, K, 9100 + N)
+        Wl, sl = sharding.shard_weight(fmt, W, s, world, rank)
+        lo, n = sharding.shard_rows(N, world, rank)
+        qw = pkg.QuantWeight(ctx, fmt, Wl, sl)
+        tok = ctx.alloc(4)
+        local = ctx.alloc(n * 2)
+        g1 = ctx.alloc(n * 2 * world)
+        for rep in range(5):
+            # rep 4: all-zero activations, every logit ties at 0 and row 0 (rank 0's first) must win
+            x = make_x(1, K, 9200 + K + rep) if rep < 4 else np.zeros((1, K), np.float16)
+            dx = ctx.upload(x.view(np.uint16))
+            ctx.linear(1, n, K, dx, qw.buf, g1 + rank * n * 2)
+            comm.all_gather(g1 + rank * n * 2, g1, n * 2)
+            bits = ctx.download(g1, (N,), np.uint16)
+            logits = bits.view(np.float16).astype(np.float32)
+            # first maximum in the kernel's total order (sign-magnitude bits made monotonic, so -0 < +0)
+            b32 = bits.astype(np.uint32)
+            want = int(np.argmax(np.where(b32 & 0x8000, 0xFFFF - b32, b32 | 0x8000)))
+            comm.linear_argmax_sharded(n, K, dx, qw.buf, local if rep & 1 else None, tok)
+            got = int(ctx.download(tok, (1,), np.int32)[0])
+            if got != want:
+                failures.append(f"pick {fmt} N={N} K={K} rep {rep}: row {got}, the gathered logits say {want}")
+            if rep & 1:
+                mine = ctx.download(local, (n,), np.uint16).view(np.float16).astype(np.float32)
+                if not np.array_equal(mine, logits[lo:lo + n]):
+                    failures.append(f"pick {fmt} N={N} K={K} rep {rep}: the locally stored logits differ from nn_linear's")
+            ctx.free(dx)
+        ctx.sync()
+        dist.barrier()
+        qw.release()
+        for b in (tok, local, g1):
+            ctx.free(b)
     ctx.sync()
     dist.barrier()
     comm.close()

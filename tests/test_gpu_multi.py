@@ -58,6 +58,35 @@ def test_single_rank_gather_is_linear(nnb, ctx, fmt, N, K, M):
         comm.close()
 
 
+@pytest.mark.parametrize("fmt,N,K", [("int8", 49152, 576), ("q4", 4096, 1024), ("fp16", 1536, 896)])
+def test_single_rank_sharded_pick_is_linear_argmax(nnb, ctx, fmt, N, K):
+    comm = nnb.Comm(ctx, None, 0, 1)
+    try:
+        g = comm.symm_alloc(256)   # creates the communicator's flag and key words
+        W, s = make_weight(fmt, N, K, 41)
+        qw = nnb.QuantWeight(ctx, fmt, W, s)
+        tok, tok2 = ctx.alloc(4), ctx.alloc(4)
+        logits = ctx.alloc(N * 2)
+        for rep in range(3):
+            x = make_x(1, K, 42 + rep)
+            dx = ctx.upload(x.view(np.uint16))
+            comm.linear_argmax_sharded(N, K, dx, qw.buf, logits if rep else None, tok)
+            ctx.linear_argmax(N, K, dx, qw.buf, None, tok2)
+            a, b = int(ctx.download(tok, (1,), np.int32)[0]), int(ctx.download(tok2, (1,), np.int32)[0])
+            assert a == b and 0 <= a < N
+            if rep:
+                lg = ctx.download(logits, (N,), np.uint16).view(np.float16).astype(np.float32)
+                assert int(np.argmax(lg)) == a
+            ctx.free(dx)
+        qw.release()
+        for b_ in (tok, tok2, logits):
+            ctx.free(b_)
+        comm.symm_free(g)
+    finally:
+        ctx.sync()
+        comm.close()
+
+
 def test_gather_rejects_foreign_buffer(nnb, ctx):
     comm = nnb.Comm(ctx, None, 0, 1)
     try:
