@@ -1465,7 +1465,8 @@ cudaError_t launch_stream(int fmt, const LinArgs& a, const StreamPlan& p, cudaSt
     ka.nchunks = (ka.rowbytes + p.kcb - 1) / p.kcb;
     size_t wbytes = 0;
     for (int i = 0; i < a.nseg; ++i) wbytes += (size_t)a.seg[i].N * ka.rowbytes;
-    ka.evict_first = wbytes > ((size_t)96 << 20) ? 1 : 0;
+    static const int evict_mb = env_int("NNB_EVICT_MB", 96);  // tuning: weights above this many MB are streamed evict-first
+    ka.evict_first = wbytes > ((size_t)evict_mb << 20) ? 1 : 0;
     const bool dual = a.epi == EPI_SWIGLU;
     const int nt = a.M > 8 ? 2 : 1;
     const int warp_rows = dual ? 16 : WARP_ROWS;
