@@ -285,13 +285,18 @@ __device__ __forceinline__ void stage_x(const uint16_t* __restrict__ x, int M, i
             for (int j = 0; j < 4; ++j)
                 *reinterpret_cast<uint4*>(xs + m * xstride + p * 64 + j * 16) = make_uint4(o[j][0], o[j][1], o[j][2], o[j][3]);
             // accumulator start of block p, token m: (c0, c1, c0, c1) per token pair
-            float* cq = ctab + ((size_t)p * ((M + 1) / 2) + (m >> 1)) * 4 + (m & 1);
             const float nc = -Q4_BIAS * bsum;
-            cq[0] = nc;
-            cq[2] = nc;
-            if (m == M - 1 && !(m & 1)) {  // odd token count: the pair's second column is unused
-                cq[1] = 0.f;
-                cq[3] = 0.f;
+            if (M == 1) {
+                // single token: one float per block, so that four blocks' values are one 16-byte read
+                ctab[p] = nc;
+            } else {
+                float* cq = ctab + ((size_t)p * ((M + 1) / 2) + (m >> 1)) * 4 + (m & 1);
+                cq[0] = nc;
+                cq[2] = nc;
+                if (m == M - 1 && !(m & 1)) {  // odd token count: the pair's second column is unused
+                    cq[1] = 0.f;
+                    cq[3] = 0.f;
+                }
             }
 #pragma unroll
             for (int t = 0; t < 4; ++t) cur[t] = nxt[t];
@@ -843,13 +848,15 @@ __global__ void __launch_bounds__(THREADS) linear_stream_kernel(const __grid_con
             const uint8_t* scb = smem + (sw - s_base) + geo.nbox * CTA_BOX;
             const uint8_t* sc_rb[2] = {scb + (srow0 + g) * sstr, scb + (srow1 + g) * sstr};
             const int g0 = (c * kcb) / 16;
-            auto step = [&](int s, float (&ac)[2][NT][4]) {
+            const float* ctab1 = reinterpret_cast<const float*>(smem + geo.off_ctab);  // single token: one float per block
+            auto step = [&](int s, float (&ac)[2][NT][4], const float (&s_lo2)[2], const float (&s_hi2)[2], float c_one) {
                 uint32_t b[NT][4];
                 float4 cq[NT];
 #pragma unroll
                 for (int nt = 0; nt < NT; ++nt) {
                     ldsm_x4(b_base[nt] + s * b_step[nt], b[nt][0], b[nt][1], b[nt][2], b[nt][3]);
-                    cq[nt] = *reinterpret_cast<const float4*>(ctab_lane[nt] + (size_t)s * ctab_step);
+                    if (ONE) cq[nt] = make_float4(c_one, 0.f, c_one, 0.f);  // only column 0 is read back
+                    else cq[nt] = *reinterpret_cast<const float4*>(ctab_lane[nt] + (size_t)s * ctab_step);
                 }
                 uint32_t w[4];
                 ldsm_x4(piece_addr(sw, aq_off, (uint32_t)(s - g0)), w[0], w[1], w[2], w[3]);
@@ -858,8 +865,7 @@ __global__ void __launch_bounds__(THREADS) linear_stream_kernel(const __grid_con
                     uint32_t p04, p15, p26, p37, q04, q15, q26, q37;
                     q4x8_to_half2x4_biased(w[rb * 2], p04, p15, p26, p37);
                     q4x8_to_half2x4_biased(w[rb * 2 + 1], q04, q15, q26, q37);
-                    const float s_lo = __half2float(__ushort_as_half(*reinterpret_cast<const uint16_t*>(sc_rb[rb] + (s - g0) * 2)));
-                    const float s_hi = __half2float(__ushort_as_half(*reinterpret_cast<const uint16_t*>(sc_rb[rb] + 8 * sstr + (s - g0) * 2)));
+                    const float s_lo = s_lo2[rb], s_hi = s_hi2[rb];
 #pragma unroll
                     for (int nt = 0; nt < NT; ++nt) {
                         float d[4];
@@ -875,14 +881,37 @@ __global__ void __launch_bounds__(THREADS) linear_stream_kernel(const __grid_con
             const int s1 = g0 + cb / 16;
             int s = g0;
             for (; s + 4 <= s1; s += 4) {
-                step(s, acc[0]);
-                step(s + 1, acc[1]);
-                step(s + 2, acc[0]);
-                step(s + 3, acc[1]);
+                // the scales of four consecutive blocks of a row are 8 contiguous, aligned bytes
+                uint2 sq[2][2];
+#pragma unroll
+                for (int rb = 0; rb < 2; ++rb) {
+                    sq[rb][0] = *reinterpret_cast<const uint2*>(sc_rb[rb] + (s - g0) * 2);
+                    sq[rb][1] = *reinterpret_cast<const uint2*>(sc_rb[rb] + 8 * sstr + (s - g0) * 2);
+                }
+                float4 c4 = make_float4(0.f, 0.f, 0.f, 0.f);
+                if (ONE) c4 = *reinterpret_cast<const float4*>(ctab1 + s);  // s is a multiple of 8 here
+#pragma unroll
+                for (int u = 0; u < 4; ++u) {
+                    float lo2[2], hi2[2];
+#pragma unroll
+                    for (int rb = 0; rb < 2; ++rb) {
+                        const uint32_t wl = u < 2 ? sq[rb][0].x : sq[rb][0].y, wh = u < 2 ? sq[rb][1].x : sq[rb][1].y;
+                        lo2[rb] = __half2float(__ushort_as_half((uint16_t)(u & 1 ? wl >> 16 : wl & 0xFFFFu)));
+                        hi2[rb] = __half2float(__ushort_as_half((uint16_t)(u & 1 ? wh >> 16 : wh & 0xFFFFu)));
+                    }
+                    step(s + u, acc[u & 1], lo2, hi2, u == 0 ? c4.x : u == 1 ? c4.y : u == 2 ? c4.z : c4.w);
+                }
             }
             for (; s < s1; ++s) {
-                if (s & 1) step(s, acc[1]);
-                else step(s, acc[0]);
+                float lo2[2], hi2[2];
+#pragma unroll
+                for (int rb = 0; rb < 2; ++rb) {
+                    lo2[rb] = __half2float(__ushort_as_half(*reinterpret_cast<const uint16_t*>(sc_rb[rb] + (s - g0) * 2)));
+                    hi2[rb] = __half2float(__ushort_as_half(*reinterpret_cast<const uint16_t*>(sc_rb[rb] + 8 * sstr + (s - g0) * 2)));
+                }
+                const float c1 = ONE ? ctab1[s] : 0.f;
+                if (s & 1) step(s, acc[1], lo2, hi2, c1);
+                else step(s, acc[0], lo2, hi2, c1);
             }
         }
         CYC_END(cyc_comp);
