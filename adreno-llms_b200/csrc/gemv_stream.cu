@@ -285,18 +285,13 @@ __device__ __forceinline__ void stage_x(const uint16_t* __restrict__ x, int M, i
             for (int j = 0; j < 4; ++j)
                 *reinterpret_cast<uint4*>(xs + m * xstride + p * 64 + j * 16) = make_uint4(o[j][0], o[j][1], o[j][2], o[j][3]);
             // accumulator start of block p, token m: (c0, c1, c0, c1) per token pair
+            float* cq = ctab + ((size_t)p * ((M + 1) / 2) + (m >> 1)) * 4 + (m & 1);
             const float nc = -Q4_BIAS * bsum;
-            if (M == 1) {
-                // single token: one float per block, so that four blocks' values are one 16-byte read
-                ctab[p] = nc;
-            } else {
-                float* cq = ctab + ((size_t)p * ((M + 1) / 2) + (m >> 1)) * 4 + (m & 1);
-                cq[0] = nc;
-                cq[2] = nc;
-                if (m == M - 1 && !(m & 1)) {  // odd token count: the pair's second column is unused
-                    cq[1] = 0.f;
-                    cq[3] = 0.f;
-                }
+            cq[0] = nc;
+            cq[2] = nc;
+            if (m == M - 1 && !(m & 1)) {  // odd token count: the pair's second column is unused
+                cq[1] = 0.f;
+                cq[3] = 0.f;
             }
 #pragma unroll
             for (int t = 0; t < 4; ++t) cur[t] = nxt[t];
@@ -848,18 +843,19 @@ __global__ void __launch_bounds__(THREADS) linear_stream_kernel(const __grid_con
             const uint8_t* scb = smem + (sw - s_base) + geo.nbox * CTA_BOX;
             const uint8_t* sc_rb[2] = {scb + (srow0 + g) * sstr, scb + (srow1 + g) * sstr};
             const int g0 = (c * kcb) / 16;
-            const float* ctab1 = reinterpret_cast<const float*>(smem + geo.off_ctab);  // single token: one float per block
-            auto step = [&](int s, float (&ac)[2][NT][4], const float (&s_lo2)[2], const float (&s_hi2)[2], float c_one) {
+            uint32_t w_xor[4];
+#pragma unroll
+            for (int u = 0; u < 4; ++u) w_xor[u] = (((uint32_t)u ^ (xr & 3u)) << 4);
+            auto step = [&](int s, float (&ac)[2][NT][4], const float (&s_lo2)[2], const float (&s_hi2)[2], uint32_t w_addr) {
                 uint32_t b[NT][4];
                 float4 cq[NT];
 #pragma unroll
                 for (int nt = 0; nt < NT; ++nt) {
                     ldsm_x4(b_base[nt] + s * b_step[nt], b[nt][0], b[nt][1], b[nt][2], b[nt][3]);
-                    if (ONE) cq[nt] = make_float4(c_one, 0.f, c_one, 0.f);  // only column 0 is read back
-                    else cq[nt] = *reinterpret_cast<const float4*>(ctab_lane[nt] + (size_t)s * ctab_step);
+                    cq[nt] = *reinterpret_cast<const float4*>(ctab_lane[nt] + (size_t)s * ctab_step);
                 }
                 uint32_t w[4];
-                ldsm_x4(piece_addr(sw, aq_off, (uint32_t)(s - g0)), w[0], w[1], w[2], w[3]);
+                ldsm_x4(w_addr, w[0], w[1], w[2], w[3]);
 #pragma unroll
                 for (int rb = 0; rb < 2; ++rb) {
                     uint32_t p04, p15, p26, p37, q04, q15, q26, q37;
@@ -888,8 +884,10 @@ __global__ void __launch_bounds__(THREADS) linear_stream_kernel(const __grid_con
                     sq[rb][0] = *reinterpret_cast<const uint2*>(sc_rb[rb] + (s - g0) * 2);
                     sq[rb][1] = *reinterpret_cast<const uint2*>(sc_rb[rb] + 8 * sstr + (s - g0) * 2);
                 }
-                float4 c4 = make_float4(0.f, 0.f, 0.f, 0.f);
-                if (ONE) c4 = *reinterpret_cast<const float4*>(ctab1 + s);  // s is a multiple of 8 here
+                // four consecutive 16-byte pieces of a 128-byte swizzled row: the group's part of the
+                // address once, the lane's xor pattern for piece u from a table
+                const uint32_t q0 = (uint32_t)(s - g0);
+                const uint32_t w_grp = sw + aq_off + (q0 >> 3) * CTA_BOX + (((q0 & 4u) ^ (xr & 4u)) << 4);
 #pragma unroll
                 for (int u = 0; u < 4; ++u) {
                     float lo2[2], hi2[2];
@@ -899,7 +897,7 @@ __global__ void __launch_bounds__(THREADS) linear_stream_kernel(const __grid_con
                         lo2[rb] = __half2float(__ushort_as_half((uint16_t)(u & 1 ? wl >> 16 : wl & 0xFFFFu)));
                         hi2[rb] = __half2float(__ushort_as_half((uint16_t)(u & 1 ? wh >> 16 : wh & 0xFFFFu)));
                     }
-                    step(s + u, acc[u & 1], lo2, hi2, u == 0 ? c4.x : u == 1 ? c4.y : u == 2 ? c4.z : c4.w);
+                    step(s + u, acc[u & 1], lo2, hi2, w_grp + w_xor[u]);
                 }
             }
             for (; s < s1; ++s) {
@@ -909,9 +907,9 @@ __global__ void __launch_bounds__(THREADS) linear_stream_kernel(const __grid_con
                     lo2[rb] = __half2float(__ushort_as_half(*reinterpret_cast<const uint16_t*>(sc_rb[rb] + (s - g0) * 2)));
                     hi2[rb] = __half2float(__ushort_as_half(*reinterpret_cast<const uint16_t*>(sc_rb[rb] + 8 * sstr + (s - g0) * 2)));
                 }
-                const float c1 = ONE ? ctab1[s] : 0.f;
-                if (s & 1) step(s, acc[1], lo2, hi2, c1);
-                else step(s, acc[0], lo2, hi2, c1);
+                const uint32_t wa = piece_addr(sw, aq_off, (uint32_t)(s - g0));
+                if (s & 1) step(s, acc[1], lo2, hi2, wa);
+                else step(s, acc[0], lo2, hi2, wa);
             }
         }
         CYC_END(cyc_comp);
