@@ -29,3 +29,40 @@ def gathered_to_row_major(gathered: np.ndarray, world: int, M: int, N: int) -> n
     """[G][M][N/G] (what the all-gather produces) -> [M][N] (what pytorch_linear writes)."""
     n = N // world
     return np.ascontiguousarray(gathered.reshape(world, M, n).transpose(1, 0, 2)).reshape(M, N)
+
+
+# --- row-sharded greedy pick: host mirror of the 64-bit word the ranks exchange ------------------
+# nn_linear_argmax_sharded leaves, on every rank, one word per rank:
+#   pick number (16 bits) | ordered fp16 value (16 bits) | ~row (32 bits)
+# "ordered" maps the sign-magnitude fp16 bits to an unsigned key that grows with the value
+# (negative values complemented, the others with the top bit set; -0 sorts below +0), so the
+# largest word is the largest value and, among equal values, the lowest row.  A payload of 0 means
+# the rank saw only NaNs.
+
+def ordered_half_bits(bits: np.ndarray) -> np.ndarray:
+    """fp16 bit patterns -> unsigned keys that sort like the values (NaNs are the caller's to drop)."""
+    b = np.asarray(bits).astype(np.uint32) & 0xFFFF
+    return np.where(b & 0x8000, 0xFFFF - b, b | 0x8000).astype(np.uint32)
+
+
+def pick_key(logits_fp16: np.ndarray, row_base: int, pick_number: int = 0) -> int:
+    """The word a rank contributes for its rows `row_base + i` (first maximum, NaNs never win)."""
+    bits = np.ascontiguousarray(logits_fp16, dtype=np.float16).view(np.uint16).reshape(-1)
+    valid = (bits & 0x7FFF) <= 0x7C00
+    tag = (pick_number & 0xFFFF) << 48
+    if not valid.any():
+        return tag
+    keys = np.where(valid, ordered_half_bits(bits), 0)
+    i = int(np.argmax(keys))                      # first of the largest keys = lowest row
+    return tag | (int(keys[i]) << 32) | (0xFFFFFFFF - (row_base + i))
+
+
+def pick_from_keys(words, pick_number: int = 0) -> int:
+    """Winning global row among the ranks' words of one pick (-1: every value was NaN)."""
+    best = 0
+    for w in words:
+        w = int(w)
+        if (w >> 48) != (pick_number & 0xFFFF):
+            raise ValueError(f"word {w:#018x} does not belong to pick {pick_number}")
+        best = max(best, w & 0xFFFFFFFFFFFF)
+    return -1 if best == 0 else 0xFFFFFFFF - (best & 0xFFFFFFFF)

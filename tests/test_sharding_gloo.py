@@ -1,6 +1,8 @@
 """World-size-2 CPU test of the row-sharding host logic (gloo): each rank computes its row
 block with the oracle, the blocks are all-gathered in rank order, and the reassembled
-[M, N] equals the unsharded result.  The GPU path uses the same arithmetic with NCCL."""
+[M, N] equals the unsharded result.  The GPU path uses the same arithmetic with NCCL.
+The row-sharded greedy pick is covered the same way: every rank packs the key word of its rows,
+the words are all-gathered, and every rank must name the first maximum of the unsharded logits."""
 import os
 import socket
 import sys
@@ -76,3 +78,61 @@ def test_shard_arithmetic(nnb):
     g = np.arange(2 * 3 * 4).reshape(2, 3, 4)
     rm = sharding.gathered_to_row_major(g, 2, 3, 8)
     assert rm.shape == (3, 8) and list(rm[1]) == [4, 5, 6, 7, 16, 17, 18, 19]
+
+
+def _pick_worker(rank, world, port, fmt, N, K, case, out_dir):
+    sys.path.insert(0, REPO)
+    sys.path.insert(0, os.path.join(REPO, "tests"))
+    from conftest import load_package
+    load_package()
+    import importlib
+    sharding = importlib.import_module("adreno_llms_b200.sharding")
+    from oracle import cpu
+    from helpers import make_weight, make_x
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    W, s = make_weight(fmt, N, K, 5151)
+    x = make_x(1, K, 5152) if case != "ties" else np.zeros((1, K), np.float16)
+    full = cpu.linear(fmt, x, W, s).reshape(-1)
+    if case == "nan":                                  # rank 1's rows are all NaN, rank 0 has one NaN
+        full = full.copy()
+        full[N // 2:] = np.float16(np.nan)
+        full[3] = np.float16(np.nan)
+    lo, n = sharding.shard_rows(N, world, rank)
+    word = sharding.pick_key(full[lo:lo + n], lo, pick_number=7)
+    send = torch.tensor([word - (1 << 64) if word >= (1 << 63) else word], dtype=torch.int64)
+    recv = [torch.empty_like(send) for _ in range(world)]
+    dist.all_gather(recv, send)
+    words = [int(r.item()) & 0xFFFFFFFFFFFFFFFF for r in recv]
+    got = sharding.pick_from_keys(words, pick_number=7)
+    f32 = full.astype(np.float32)
+    keys = np.where(np.isnan(f32), 0, sharding.ordered_half_bits(full.view(np.uint16)))
+    want = int(np.argmax(keys)) if keys.max() > 0 else -1
+    np.save(os.path.join(out_dir, f"pick{rank}.npy"), np.array([got, want]))
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("fmt,N,K,case", [("int8", 256, 128, "plain"), ("q4", 128, 256, "plain"), ("fp16", 96, 64, "ties"),
+                                         ("int8", 64, 128, "nan")])
+def test_row_sharded_pick_world2(tmp_path, fmt, N, K, case):
+    port = _free_port()
+    mp.spawn(_pick_worker, args=(2, port, fmt, N, K, case, str(tmp_path)), nprocs=2, join=True)
+    for r in range(2):
+        got, want = np.load(tmp_path / f"pick{r}.npy")
+        assert got == want and (case != "ties" or got == 0)
+
+
+def test_pick_key_order_and_nan(nnb):
+    import importlib
+    sharding = importlib.import_module("adreno_llms_b200.sharding")
+    vals = np.array([-np.inf, -3.5, -6e-8, -0.0, 0.0, 6e-8, 1.0, 65504.0, np.inf], np.float16)
+    k = sharding.ordered_half_bits(vals.view(np.uint16))
+    assert np.all(np.diff(k.astype(np.int64)) > 0) and k.min() > 0          # strictly increasing, never 0
+    assert sharding.pick_from_keys([sharding.pick_key(np.full(4, np.nan, np.float16), 0)]) == -1
+    a = sharding.pick_key(np.array([1, 5, 5, 2], np.float16), 100)           # first of the equal maxima
+    b = sharding.pick_key(np.array([5, 0, 0, 0], np.float16), 104)           # equal value on a later rank
+    assert sharding.pick_from_keys([a, b]) == 101 and sharding.pick_from_keys([b, a]) == 101
+    with pytest.raises(ValueError):
+        sharding.pick_from_keys([sharding.pick_key(np.ones(2, np.float16), 0, pick_number=3)], pick_number=4)
