@@ -17,17 +17,18 @@ enum Epi : int {
     EPI_SILU_GATE = 3,  // out = half(out * sigmoid(out) * acc)       (in place)
 };
 
-// Completion signal of a row-sharded gather, sent by the projection kernel itself: the last
-// block to finish publishes the next epoch number in word `rank` of every rank's flag array.
 // Byte offset, inside each rank's symmetric flag allocation, of the key tables of the row-sharded
 // greedy pick: two tables (parity of the pick number) of eight 64-bit words, word g written by
 // rank g: pick number (16 bits) | ordered fp16 value (16 bits) | ~row (32 bits).
 constexpr int KEY_TABLE_OFFSET = 64;
 
+// Completion signal of a row-sharded gather, sent by the projection kernel itself: the last
+// block to finish publishes the next epoch number in word `rank` of every rank's flag array.
 struct GatherSignal {
     unsigned* flags[8];  // flags[g] = rank g's flag array (peer-mapped for g != rank)
-    unsigned* epoch;     // local: signals sent so far
-    unsigned* done;      // local: blocks of the current launch that have finished (returns to 0)
+    unsigned* epoch;     // local: signals sent so far (with a fused arg-max: picks sent so far)
+    unsigned* done;      // local: blocks of the current launch that have finished (returns to 0);
+                         // unused with a fused arg-max, whose key word is its own arrival mark
     int world, rank;     // world == 0: no signal
 };
 
