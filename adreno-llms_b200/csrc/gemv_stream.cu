@@ -1378,7 +1378,9 @@ cudaError_t stream_configure() {
 bool stream_supported(int fmt, int M, int K, const LinArgs& a) {
     if (M < 1 || M > 16) return false;
     const int rb = fmt_row_bytes(fmt, K);
-    if (rb < 128 || (rb % 64) != 0) return false;
+    // fp16 / int8 consume a row in 64-byte steps; a Q4 step is one 16-byte block, and its scale
+    // rows are copied in 4-byte pieces (two blocks), so Q4 rows only have to be whole pairs of blocks
+    if (rb < 128 || (rb % (fmt == FMT_Q4 ? 32 : 64)) != 0) return false;
     auto al16 = [](const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; };
     for (int i = 0; i < a.nseg; ++i) {
         if (!al16(a.seg[i].W)) return false;
