@@ -73,6 +73,9 @@ def load():
         "nn_rmsnorm_gate_up_silu": ([vp, i, i, i, vp, vp, ctypes.c_float, vp, vp, vp], i),
         "nn_plan_begin": ([vp], i), "nn_plan_end": ([vp, pvp], i), "nn_plan_launch": ([vp, vp], i),
         "nn_plan_num_kernels": ([vp], i), "nn_plan_free": ([vp], i),
+        "nn_plan_num_recorded": ([vp], i), "nn_plan_num_resident_runs": ([vp], i),
+        "nn_plan_set_wait_limit": ([vp, ctypes.c_uint], i), "nn_plan_withhold_output": ([vp, i, i], i),
+        "nn_plan_analyze": ([i, vp, vp, vp, vp, vp, vp, i, vp, vp, vp, vp], i),
         "nn_weights_load": ([vp, cp, cp, pvp], i), "nn_weights_free": ([vp], i),
         "nn_weights_has_tensor": ([vp, cp], i), "nn_weights_get_buffer": ([vp, cp, i], vp),
         "nn_weights_get_dtype": ([vp, cp], cp), "nn_weights_get_shape": ([vp, cp, ctypes.POINTER(i), i], i),

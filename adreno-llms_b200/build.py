@@ -14,7 +14,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 LIB_DIR = os.path.join(HERE, "lib")
 LIB = os.path.join(LIB_DIR, "libnnopt_b200.so")
-SOURCES = ["api.cpp", "weights.cpp", "comm.cpp", "comm_kernels.cu", "gemv_stream.cu", "gemv_generic.cu", "misc.cu", "gemm_tc.cu", "noalloc.cu"]
+SOURCES = ["api.cpp", "weights.cpp", "comm.cpp", "comm_kernels.cu", "gemv_stream.cu", "decode_plan.cu", "plan.cpp", "gemv_generic.cu", "misc.cu", "gemm_tc.cu", "noalloc.cu"]
 ARCH = ["-gencode", "arch=compute_100a,code=sm_100a"]
 
 
@@ -44,8 +44,6 @@ def build(force=False, verbose=False):
         cmd = [_nvcc(), *ARCH, "-lineinfo", "-O3", "-std=c++17", "-Xcompiler", "-fPIC,-Wall", "-x", "cu", "-c", src, "-o", obj]
         if verbose:
             cmd += ["-Xptxas", "-v"]
-        if os.environ.get("NNB_BUILD_TRACE"):  # debug build with per-launch phase timestamps
-            cmd += ["-DNNB_TRACE"]
         if not force and os.path.exists(obj) and all(
                 os.path.getmtime(obj) > os.path.getmtime(os.path.join(CSRC, f)) for f in os.listdir(CSRC)
                 if f.endswith((".h", ".cuh")) or os.path.join(CSRC, f) == src):

@@ -14,6 +14,7 @@
 #include "../../include/nnopt_b200.h"
 #include "internal.h"
 #include "kernels.h"
+#include "plan.h"
 
 using namespace nnb;
 
@@ -164,6 +165,11 @@ extern "C" int nn_buf_free(nn_context* c, nn_buf b) {
     if (!b) return NN_OK;
     cudaSetDevice(c->device);
     CUDA_TRY(cudaStreamSynchronize(c->stream));
+    // a freed weight or scale buffer must not keep resolving: the address may be handed out again
+    for (auto it = c->registry.begin(); it != c->registry.end();) {
+        if (it->first == (uintptr_t)b || (const void*)it->second.scale == (const void*)b) it = c->registry.erase(it);
+        else ++it;
+    }
     CUDA_TRY(cudaFree(b));
     return NN_OK;
 }
@@ -277,17 +283,33 @@ static int run_gemm_tc(nn_context* c, int fmt, const LinArgs& a, int M, const ch
     return NN_OK;
 }
 
-// The nn_rmsnorm_* entry points are the plain ones with a norm to apply first; they leave it
-// here for run_linear to pick up (one host thread drives a context).
-static thread_local const uint16_t* t_norm_w = nullptr;
-static thread_local float t_norm_eps = 0.f;
+// While a step is being recorded, every launch of the streaming kernel is also noted with its
+// arguments and its graph node, so that nn_plan_end can hand runs of them to the resident kernel.
+static void note_recorded(nn_context* c, int fmt, const LinArgs& a, const StreamPlan& p) {
+    if (!c->capturing) return;
+    RecordedOp r;
+    r.fmt = fmt;
+    r.a = a;
+    r.p = p;
+    r.node = nullptr;
+    cudaStreamCaptureStatus st = cudaStreamCaptureStatusNone;
+    const cudaGraphNode_t* tail = nullptr;
+    size_t ntail = 0;
+    if (cudaStreamGetCaptureInfo(c->stream, &st, nullptr, nullptr, &tail, &ntail) == cudaSuccess && st == cudaStreamCaptureStatusActive && ntail == 1)
+        r.node = tail[0];
+    bool q4_ok = true;
+    if (fmt == FMT_Q4) {  // block scales must be reachable by tensor copies
+        q4_ok = a.K % 256 == 0;
+        for (int i = 0; i < a.nseg; ++i) q4_ok = q4_ok && (reinterpret_cast<uintptr_t>(a.seg[i].scale) & 15) == 0;
+        if (a.epi == EPI_SWIGLU) q4_ok = q4_ok && (reinterpret_cast<uintptr_t>(a.scale2) & 15) == 0;
+    }
+    r.eligible = r.node && a.M == 1 && !p.streamk && a.npeer == 0 && a.sig.world == 0 && q4_ok;
+    c->rec.push_back(r);
+}
 
 static int run_linear(nn_context* c, int fmt, LinArgs a, int M_total, const char* who) {
     a.sk_scratch = c->sk_scratch;
     a.sk_flags = c->sk_flags;
-    a.norm_w = t_norm_w;
-    a.norm_eps = t_norm_eps;
-    t_norm_w = nullptr;
     if (a.norm_w) {
         // the prologue is fused into the streaming kernel; every other route normalises into
         // context scratch first
@@ -347,6 +369,7 @@ static int run_linear(nn_context* c, int fmt, LinArgs a, int M_total, const char
         if (stream_supported(fmt, a.M, a.K, a)) p = stream_plan(fmt, a, c->sm_count, c->smem_limit);
         if (p.ok) {
             e = launch_stream(fmt, a, p, c->stream, c->use_pdl);
+            if (e == cudaSuccess && M_total == 1) note_recorded(c, fmt, a, p);
         } else {
             if (a.npeer > 0)
                 return NN_FAIL(NN_ERR_UNSUPPORTED, "%s: this shape takes the any-shape kernel, which does not write to peer ranks (K=%d)", who, a.K);
@@ -365,8 +388,9 @@ static int check_common(nn_context* c, int M, int N, int K, const void* x, const
     return NN_OK;
 }
 
+// `gamma` (with `eps`): RMSNorm of the activations before the projection, or null.
 static int one_weight(nn_context* c, int M, int N, int K, nn_buf x, nn_buf W, nn_buf out, int epi, const char* who,
-                      uint16_t* const* peers = nullptr, int npeer = 0, const GatherSignal* sig = nullptr) {
+                      uint16_t* const* peers = nullptr, int npeer = 0, const GatherSignal* sig = nullptr, nn_buf gamma = nullptr, float eps = 0.f) {
     int rc = check_common(c, M, N, K, x, W, out, who);
     if (rc) return rc;
     if (M == 0) return NN_OK;
@@ -386,6 +410,8 @@ static int one_weight(nn_context* c, int M, int N, int K, nn_buf x, nn_buf W, nn
     a.K = K;
     a.epi = epi;
     a.status = c->status_dev;
+    a.norm_w = (const uint16_t*)gamma;
+    a.norm_eps = eps;
     if (npeer < 0 || npeer > 7) return NN_FAIL(NN_ERR_ARG, "%s: %d peers", who, npeer);
     a.npeer = npeer;
     for (int p = 0; p < npeer; ++p) a.peer_out[p] = peers[p];
@@ -408,8 +434,7 @@ extern "C" int nn_linear_silu_gate_fused(nn_context* c, int M, int N, int K, nn_
     return one_weight(c, M, N, K, x, W3, g, EPI_SILU_GATE, "nn_linear_silu_gate_fused");
 }
 
-extern "C" int nn_fused_gate_up_silu(nn_context* c, int M, int N, int K, nn_buf x, nn_buf Wg, nn_buf Wu, nn_buf out) {
-    const char* who = "nn_fused_gate_up_silu";
+static int gate_up_silu(nn_context* c, int M, int N, int K, nn_buf x, nn_buf Wg, nn_buf Wu, nn_buf out, nn_buf gamma, float eps, const char* who) {
     int rc = check_common(c, M, N, K, x, Wg, out, who);
     if (rc) return rc;
     if (!Wu) return NN_FAIL(NN_ERR_ARG, "%s: null Wu", who);
@@ -433,12 +458,17 @@ extern "C" int nn_fused_gate_up_silu(nn_context* c, int M, int N, int K, nn_buf 
     a.K = K;
     a.epi = EPI_SWIGLU;
     a.status = c->status_dev;
+    a.norm_w = (const uint16_t*)gamma;
+    a.norm_eps = eps;
     return run_linear(c, rg.fmt, a, M, who);
 }
 
-extern "C" int nn_linear_qkv(nn_context* c, int M, int K, nn_buf x, nn_buf Wq, int Nq, nn_buf Wk, int Nk, nn_buf Wv, int Nv,
-                             nn_buf q, nn_buf k, nn_buf v) {
-    const char* who = "nn_linear_qkv";
+extern "C" int nn_fused_gate_up_silu(nn_context* c, int M, int N, int K, nn_buf x, nn_buf Wg, nn_buf Wu, nn_buf out) {
+    return gate_up_silu(c, M, N, K, x, Wg, Wu, out, nullptr, 0.f, "nn_fused_gate_up_silu");
+}
+
+static int linear_qkv(nn_context* c, int M, int K, nn_buf x, nn_buf Wq, int Nq, nn_buf Wk, int Nk, nn_buf Wv, int Nv, nn_buf q, nn_buf k, nn_buf v,
+                      nn_buf gamma, float eps, const char* who) {
     if (!c) return NN_FAIL(NN_ERR_ARG, "%s: null context", who);
     if (!x || !Wq || !Wk || !Wv || !q || !k || !v) return NN_FAIL(NN_ERR_ARG, "%s: null buffer", who);
     if (M < 0 || K <= 0 || Nq <= 0 || Nk <= 0 || Nv <= 0) return NN_FAIL(NN_ERR_ARG, "%s: bad shape", who);
@@ -465,7 +495,14 @@ extern "C" int nn_linear_qkv(nn_context* c, int M, int K, nn_buf x, nn_buf Wq, i
     a.K = K;
     a.epi = EPI_STORE;
     a.status = c->status_dev;
+    a.norm_w = (const uint16_t*)gamma;
+    a.norm_eps = eps;
     return run_linear(c, fmt, a, M, who);
+}
+
+extern "C" int nn_linear_qkv(nn_context* c, int M, int K, nn_buf x, nn_buf Wq, int Nq, nn_buf Wk, int Nk, nn_buf Wv, int Nv,
+                             nn_buf q, nn_buf k, nn_buf v) {
+    return linear_qkv(c, M, K, x, Wq, Nq, Wk, Nk, Wv, Nv, q, k, v, nullptr, 0.f, "nn_linear_qkv");
 }
 
 extern "C" int nn_rmsnorm(nn_context* c, int rows, int cols, nn_buf x, nn_buf weight, float eps, nn_buf out) {
@@ -477,33 +514,20 @@ extern "C" int nn_rmsnorm(nn_context* c, int rows, int cols, nn_buf x, nn_buf we
     return NN_OK;
 }
 
-static int with_norm(nn_buf gamma, float eps, const char* who) {
-    if (!gamma) return NN_FAIL(NN_ERR_ARG, "%s: null norm weight", who);
-    t_norm_w = (const uint16_t*)gamma;
-    t_norm_eps = eps;
-    return NN_OK;
-}
-
 extern "C" int nn_rmsnorm_linear(nn_context* c, int M, int N, int K, nn_buf x, nn_buf gamma, float eps, nn_buf W, nn_buf out) {
-    int rc = with_norm(gamma, eps, "nn_rmsnorm_linear");
-    if (rc == NN_OK) rc = one_weight(c, M, N, K, x, W, out, EPI_STORE, "nn_rmsnorm_linear");
-    t_norm_w = nullptr;
-    return rc;
+    if (!gamma) return NN_FAIL(NN_ERR_ARG, "nn_rmsnorm_linear: null norm weight");
+    return one_weight(c, M, N, K, x, W, out, EPI_STORE, "nn_rmsnorm_linear", nullptr, 0, nullptr, gamma, eps);
 }
 
 extern "C" int nn_rmsnorm_linear_qkv(nn_context* c, int M, int K, nn_buf x, nn_buf gamma, float eps, nn_buf Wq, int Nq, nn_buf Wk, int Nk,
                                      nn_buf Wv, int Nv, nn_buf q, nn_buf k, nn_buf v) {
-    int rc = with_norm(gamma, eps, "nn_rmsnorm_linear_qkv");
-    if (rc == NN_OK) rc = nn_linear_qkv(c, M, K, x, Wq, Nq, Wk, Nk, Wv, Nv, q, k, v);
-    t_norm_w = nullptr;
-    return rc;
+    if (!gamma) return NN_FAIL(NN_ERR_ARG, "nn_rmsnorm_linear_qkv: null norm weight");
+    return linear_qkv(c, M, K, x, Wq, Nq, Wk, Nk, Wv, Nv, q, k, v, gamma, eps, "nn_rmsnorm_linear_qkv");
 }
 
 extern "C" int nn_rmsnorm_gate_up_silu(nn_context* c, int M, int N, int K, nn_buf x, nn_buf gamma, float eps, nn_buf Wg, nn_buf Wu, nn_buf out) {
-    int rc = with_norm(gamma, eps, "nn_rmsnorm_gate_up_silu");
-    if (rc == NN_OK) rc = nn_fused_gate_up_silu(c, M, N, K, x, Wg, Wu, out);
-    t_norm_w = nullptr;
-    return rc;
+    if (!gamma) return NN_FAIL(NN_ERR_ARG, "nn_rmsnorm_gate_up_silu: null norm weight");
+    return gate_up_silu(c, M, N, K, x, Wg, Wu, out, gamma, eps, "nn_rmsnorm_gate_up_silu");
 }
 
 extern "C" int nn_dequant(nn_context* c, int N, int K, nn_buf W, nn_buf out) {
@@ -561,6 +585,7 @@ int nnb::linear_argmax(nn_context* c, int N, int K, nn_buf x, nn_buf W, nn_buf l
     if (sig) a.sig = *sig;
     cudaError_t e = launch_stream(r.fmt, a, p, c->stream, c->use_pdl);
     if (e != cudaSuccess) return NN_FAIL(NN_ERR_CUDA, "%s: launch failed: %s (N=%d K=%d)", who, cudaGetErrorString(e), N, K);
+    note_recorded(c, r.fmt, a, p);
     c->launches++;
     return NN_OK;
 }
@@ -574,12 +599,20 @@ extern "C" int nn_argmax(nn_context* c, int n, nn_buf logits, nn_buf out_idx) {
 }
 
 // ---------------------------------------------------------------------------------
-// recorded decode step (CUDA graph of the captured launches, PDL edges kept)
+// recorded decode step.  The operator calls between nn_plan_begin and nn_plan_end are captured
+// into a CUDA graph (programmatic-launch edges kept).  Runs of consecutive single-token
+// streaming operators inside it are then replaced by one launch each of the resident kernel
+// (decode_plan.cu); whatever else was recorded on the stream in between (other library
+// kernels, the caller's own kernels and copies) stays where it is, as the node it was.
 // ---------------------------------------------------------------------------------
 struct nn_plan {
+    int device = 0;
     cudaGraph_t graph = nullptr;
     cudaGraphExec_t exec = nullptr;
-    int kernels = 0;
+    int kernels = 0;      // launches per replay
+    int recorded = 0;     // launches that were recorded
+    std::vector<PlanRun> runs;
+    std::vector<cudaGraphNode_t> run_nodes;  // the graph node of each run
 };
 
 extern "C" int nn_plan_begin(nn_context* c) {
@@ -587,8 +620,130 @@ extern "C" int nn_plan_begin(nn_context* c) {
     if (c->capturing) return NN_FAIL(NN_ERR_ARG, "nn_plan_begin: already recording");
     CUDA_TRY(cudaStreamBeginCapture(c->stream, cudaStreamCaptureModeThreadLocal));
     c->capturing = true;
+    c->rec.clear();
     c->launches_at_capture = c->launches;
     return NN_OK;
+}
+
+static HazardOp hazard_view(const RecordedOp& r) {
+    HazardOp h;
+    const LinArgs& a = r.a;
+    h.x = (uintptr_t)a.x;
+    h.x_bytes = (size_t)a.K * 2;
+    for (int k = 0; k < a.nseg; ++k)
+        if (a.seg[k].out) {
+            h.out[h.nout] = (uintptr_t)a.seg[k].out;
+            h.out_bytes[h.nout] = (size_t)a.seg[k].N * 2;
+            h.nout++;
+        }
+    h.inplace = a.epi == EPI_RESIDUAL || a.epi == EPI_SILU_GATE;
+    if (a.argmax_slot) {
+        h.has_argmax = true;
+        h.out[h.nout] = (uintptr_t)a.argmax_out;
+        h.out_bytes[h.nout] = 4;
+        h.nout++;
+    }
+    return h;
+}
+
+static void set_run_node_params(cudaGraphNode_t node, PlanRun& run, cudaError_t* err) {
+    const void* fn = nullptr;
+    decode_plan_func(&fn);
+    cudaKernelNodeParams kp = {};
+    kp.func = const_cast<void*>(fn);
+    kp.gridDim = dim3((unsigned)run.grid);
+    kp.blockDim = dim3((unsigned)DECODE_PLAN_THREADS);
+    kp.sharedMemBytes = (unsigned)run.smem;
+    void* args[1] = {&run.params};
+    kp.kernelParams = args;
+    kp.extra = nullptr;
+    *err = cudaGraphKernelNodeSetParams(node, &kp);
+}
+
+// Replace runs of recorded streaming operators by resident launches, on a clone of the captured
+// graph; any failure leaves the captured graph as it was.  Returns the graph to instantiate.
+static cudaGraph_t consolidate_runs(nn_context* c, nn_plan* p, cudaGraph_t g) {
+    const std::vector<RecordedOp>& rec = c->rec;
+    if (rec.size() < 2 || getenv("NNB_PLAN_SEPARATE")) return g;
+    // the capture of one stream is a chain: successor of every node
+    size_t ne = 0;
+    if (cudaGraphGetEdges_v2(g, nullptr, nullptr, nullptr, &ne) != cudaSuccess) return g;
+    std::vector<cudaGraphNode_t> from(ne), to(ne);
+    std::vector<cudaGraphEdgeData> ed(ne);
+    if (ne && cudaGraphGetEdges_v2(g, from.data(), to.data(), ed.data(), &ne) != cudaSuccess) return g;
+    std::map<cudaGraphNode_t, cudaGraphNode_t> succ;
+    std::map<cudaGraphNode_t, int> npred;
+    for (size_t i = 0; i < ne; ++i) {
+        if (succ.count(from[i])) return g;  // a fork: not a simple chain
+        succ[from[i]] = to[i];
+        if (++npred[to[i]] > 1) return g;   // a join
+    }
+    std::vector<HazardOp> hz(rec.size());
+    for (size_t i = 0; i < rec.size(); ++i) hz[i] = hazard_view(rec[i]);
+    cudaGraph_t g2 = nullptr;
+    if (cudaGraphClone(&g2, g) != cudaSuccess) return g;
+    auto give_up = [&]() {
+        for (PlanRun& r : p->runs) free_run(&r);
+        p->runs.clear();
+        p->run_nodes.clear();
+        cudaGraphDestroy(g2);
+        return g;
+    };
+    cudaSetDevice(c->device);
+    int removed = 0;
+    size_t i = 0;
+    while (i < rec.size()) {
+        if (!rec[i].eligible) { ++i; continue; }
+        // operators that follow one another directly in the graph
+        size_t j = i + 1;
+        while (j < rec.size() && rec[j].eligible && succ.count(rec[j - 1].node) && succ[rec[j - 1].node] == rec[j].node) ++j;
+        // [i, j) is a candidate; the data hazards may cut it shorter
+        std::vector<HazardOp> cand(hz.begin() + i, hz.begin() + j);
+        std::vector<OpDeps> deps;
+        const int len = analyze_run(cand, 0, &deps);
+        if (len < 2) { ++i; continue; }
+        PlanRun run;
+        const char* why = "";
+        cudaError_t e = build_run(rec, deps, (int)i, len, c->sm_count, c->smem_limit, c->status_dev, &run, &why);
+        if (e != cudaSuccess) {
+            free_run(&run);
+            cudaGetLastError();
+            i += len;  // these operators stay separate launches
+            continue;
+        }
+        p->runs.push_back(run);
+        PlanRun& kept = p->runs.back();
+        // the run's first node becomes the resident launch; the others leave the graph
+        cudaGraphNode_t head = nullptr;
+        if (cudaGraphNodeFindInClone(&head, rec[i].node, g2) != cudaSuccess) return give_up();
+        set_run_node_params(head, kept, &e);
+        if (e != cudaSuccess) return give_up();
+        cudaGraphNode_t after = nullptr;
+        const cudaGraphNode_t last = rec[i + len - 1].node;
+        if (succ.count(last) && cudaGraphNodeFindInClone(&after, succ[last], g2) != cudaSuccess) return give_up();
+        for (int k = 1; k < len; ++k) {
+            cudaGraphNode_t n2 = nullptr;
+            if (cudaGraphNodeFindInClone(&n2, rec[i + k].node, g2) != cudaSuccess || cudaGraphDestroyNode(n2) != cudaSuccess) return give_up();
+        }
+        if (after && cudaGraphAddDependencies(g2, &head, &after, 1) != cudaSuccess) return give_up();
+        p->run_nodes.push_back(head);
+        removed += len - 1;
+        i += len;
+    }
+    if (p->runs.empty()) {
+        cudaGraphDestroy(g2);
+        return g;
+    }
+    // run.params was copied into the node when it was set; p->runs keeps the device tables alive
+    cudaGraphExec_t probe = nullptr;
+    if (cudaGraphInstantiate(&probe, g2, 0) != cudaSuccess) {
+        cudaGetLastError();
+        return give_up();
+    }
+    p->exec = probe;
+    p->kernels -= removed;
+    cudaGraphDestroy(g);
+    return g2;
 }
 
 extern "C" int nn_plan_end(nn_context* c, nn_plan** out) {
@@ -596,19 +751,25 @@ extern "C" int nn_plan_end(nn_context* c, nn_plan** out) {
     if (!c->capturing) return NN_FAIL(NN_ERR_ARG, "nn_plan_end: not recording");
     c->capturing = false;
     nn_plan* p = new nn_plan();
+    p->device = c->device;
     cudaError_t e = cudaStreamEndCapture(c->stream, &p->graph);
     if (e != cudaSuccess || !p->graph) {
         delete p;
+        c->rec.clear();
         return NN_FAIL(NN_ERR_CUDA, "nn_plan_end: capture failed: %s", cudaGetErrorString(e));
     }
-    e = cudaGraphInstantiate(&p->exec, p->graph, 0);
-    if (e != cudaSuccess) {
-        cudaGraphDestroy(p->graph);
-        delete p;
-        return NN_FAIL(NN_ERR_CUDA, "nn_plan_end: instantiate failed: %s", cudaGetErrorString(e));
-    }
-    p->kernels = (int)(c->launches - c->launches_at_capture);
+    p->recorded = p->kernels = (int)(c->launches - c->launches_at_capture);
     c->launches = c->launches_at_capture;  // recorded, not run
+    p->graph = consolidate_runs(c, p, p->graph);
+    c->rec.clear();
+    if (!p->exec) {
+        e = cudaGraphInstantiate(&p->exec, p->graph, 0);
+        if (e != cudaSuccess) {
+            cudaGraphDestroy(p->graph);
+            delete p;
+            return NN_FAIL(NN_ERR_CUDA, "nn_plan_end: instantiate failed: %s", cudaGetErrorString(e));
+        }
+    }
     *out = p;
     return NN_OK;
 }
@@ -621,11 +782,83 @@ extern "C" int nn_plan_launch(nn_context* c, nn_plan* p) {
 }
 
 extern "C" int nn_plan_num_kernels(const nn_plan* p) { return p ? p->kernels : 0; }
+extern "C" int nn_plan_num_recorded(const nn_plan* p) { return p ? p->recorded : 0; }
+extern "C" int nn_plan_num_resident_runs(const nn_plan* p) { return p ? (int)p->runs.size() : 0; }
+
+extern "C" int nn_plan_set_wait_limit(nn_plan* p, unsigned timeout_ms) {
+    if (!p || !p->exec) return NN_FAIL(NN_ERR_ARG, "nn_plan_set_wait_limit: null plan");
+    if (timeout_ms < 1 || timeout_ms > 10000) return NN_FAIL(NN_ERR_ARG, "nn_plan_set_wait_limit: %u ms is outside [1, 10000]", timeout_ms);
+    for (size_t i = 0; i < p->runs.size(); ++i) {
+        p->runs[i].params.wait_cycles = (long long)timeout_ms * 2000000ll;  // at most 2 GHz
+        cudaError_t e;
+        set_run_node_params(p->run_nodes[i], p->runs[i], &e);
+        if (e != cudaSuccess) return NN_FAIL(NN_ERR_CUDA, "nn_plan_set_wait_limit: %s", cudaGetErrorString(e));
+    }
+    if (!p->runs.empty()) {
+        cudaGraphExec_t ex = nullptr;
+        CUDA_TRY(cudaGraphInstantiate(&ex, p->graph, 0));
+        cudaGraphExecDestroy(p->exec);
+        p->exec = ex;
+    }
+    return NN_OK;
+}
+
+extern "C" int nn_plan_withhold_output(nn_plan* p, int run_index, int op_index) {
+    if (!p || !p->exec) return NN_FAIL(NN_ERR_ARG, "nn_plan_withhold_output: null plan");
+    if (run_index < 0 || run_index >= (int)p->runs.size()) return NN_FAIL(NN_ERR_ARG, "nn_plan_withhold_output: the plan has %zu resident runs", p->runs.size());
+    PlanRun& r = p->runs[run_index];
+    if (op_index < -1 || op_index >= r.count) return NN_FAIL(NN_ERR_ARG, "nn_plan_withhold_output: run %d has %d operators", run_index, r.count);
+    r.params.drop_publish_op = op_index;
+    cudaError_t e;
+    set_run_node_params(p->run_nodes[run_index], r, &e);
+    if (e != cudaSuccess) return NN_FAIL(NN_ERR_CUDA, "nn_plan_withhold_output: %s", cudaGetErrorString(e));
+    cudaGraphExec_t ex = nullptr;
+    CUDA_TRY(cudaGraphInstantiate(&ex, p->graph, 0));
+    cudaGraphExecDestroy(p->exec);
+    p->exec = ex;
+    return NN_OK;
+}
+
+extern "C" int nn_plan_analyze(int nops, const uint64_t* x_addr, const uint64_t* x_bytes, const uint64_t* out_addr, const uint64_t* out_bytes,
+                               const int* nout, const int* flags, int first, int* x_dep, int* res_dep, int* store_mask, int* publish_mask) {
+    if (nops < 0 || first < 0 || first > nops || (nops && (!x_addr || !x_bytes || !out_addr || !out_bytes || !nout || !flags)))
+        return NN_FAIL(NN_ERR_ARG, "nn_plan_analyze: bad argument");
+    std::vector<HazardOp> ops((size_t)nops);
+    for (int i = 0; i < nops; ++i) {
+        if (nout[i] < 0 || nout[i] > 4) return NN_FAIL(NN_ERR_ARG, "nn_plan_analyze: operator %d has %d outputs", i, nout[i]);
+        ops[i].x = (uintptr_t)x_addr[i];
+        ops[i].x_bytes = (size_t)x_bytes[i];
+        ops[i].nout = nout[i];
+        for (int k = 0; k < nout[i]; ++k) {
+            ops[i].out[k] = (uintptr_t)out_addr[4 * i + k];
+            ops[i].out_bytes[k] = (size_t)out_bytes[4 * i + k];
+        }
+        ops[i].inplace = (flags[i] & 1) != 0;
+        ops[i].has_argmax = (flags[i] & 2) != 0;
+    }
+    std::vector<OpDeps> deps;
+    const int len = analyze_run(ops, first, &deps);
+    for (int i = 0; i < len; ++i) {
+        if (x_dep) x_dep[i] = deps[i].x_dep;
+        if (res_dep) res_dep[i] = deps[i].res_dep;
+        int sm = 0, pm = 0;
+        const int nweights = ops[first + i].nout - (ops[first + i].has_argmax ? 1 : 0);
+        for (int k = 0; k < 3 && k < nweights; ++k) {
+            if (deps[i].store[k]) sm |= 1 << k;
+            if (deps[i].publish[k]) pm |= 1 << k;
+        }
+        if (store_mask) store_mask[i] = sm;
+        if (publish_mask) publish_mask[i] = pm;
+    }
+    return len;
+}
 
 extern "C" int nn_plan_free(nn_plan* p) {
     if (!p) return NN_OK;
+    cudaSetDevice(p->device);
     if (p->exec) cudaGraphExecDestroy(p->exec);
     if (p->graph) cudaGraphDestroy(p->graph);
+    for (PlanRun& r : p->runs) free_run(&r);
     delete p;
     return NN_OK;
 }

@@ -603,7 +603,8 @@ cudaError_t launch_gemm_tc(int fmt, const void* W, const uint16_t* scale, const 
         return cudaErrorInvalidValue;
     const size_t smem = 2048 + (size_t)stages * stage_bytes + (size_t)raw_stages * raw_bytes + out_bytes;
     unsigned grid = (unsigned)(((N + BM - 1) / BM) * g.ntok);
-    if (grid > 148u) grid = 148u;  // persistent: one block per SM walks the tiles
+    const unsigned sms = (unsigned)current_sm_count();
+    if (grid > sms) grid = sms;  // persistent: one block per SM walks the tiles
     if (fmt == FMT_FP16) linear_gemm_tc_kernel<FMT_FP16><<<grid, GEMM_THREADS, smem, st>>>(g);
     else if (fmt == FMT_INT8) linear_gemm_tc_kernel<FMT_INT8><<<grid, gemm_threads(FMT_INT8), smem, st>>>(g);
     else linear_gemm_tc_kernel<FMT_Q4><<<grid, gemm_threads(FMT_Q4), smem, st>>>(g);

@@ -97,7 +97,8 @@ cudaError_t launch_generic(int fmt, const LinArgs& a, cudaStream_t st) {
     if (rows == 0 || a.M == 0) return cudaSuccess;
     const int threads = 256, wpb = threads / 32;
     int grid = (rows + wpb - 1) / wpb;
-    if (grid > 148 * 8) grid = 148 * 8;
+    const int cap = current_sm_count() * 8;
+    if (grid > cap) grid = cap;
     if (fmt == FMT_FP16) linear_generic_kernel<FMT_FP16><<<grid, threads, 0, st>>>(a, rows);
     else if (fmt == FMT_INT8) linear_generic_kernel<FMT_INT8><<<grid, threads, 0, st>>>(a, rows);
     else linear_generic_kernel<FMT_Q4><<<grid, threads, 0, st>>>(a, rows);

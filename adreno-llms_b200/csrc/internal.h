@@ -4,6 +4,9 @@
 #include <stdint.h>
 
 #include <map>
+#include <vector>
+
+#include "plan.h"
 
 struct QuantEntry {
     int fmt;
@@ -29,6 +32,7 @@ struct nn_context {
     size_t flush_bytes = 0;
     bool use_pdl = true;
     bool capturing = false;
+    std::vector<nnb::RecordedOp> rec;  // streamed single-token operators of the recording in progress
     long long launches = 0, launches_at_capture = 0;
 };
 

@@ -91,7 +91,7 @@ struct StreamPlan {  // launch geometry chosen on the host
 };
 
 // gemv_stream.cu
-constexpr int SK_MAX_BLOCKS = 148 * 4;                      // grid limit of a balanced launch
+constexpr int SK_MAX_BLOCKS = 1024;                         // grid limit of a balanced launch (sizes its scratch)
 constexpr size_t SK_SCRATCH_BYTES = (size_t)SK_MAX_BLOCKS * 128 * 16 * sizeof(float);
 bool stream_supported(int fmt, int M, int K, const LinArgs& a);
 StreamPlan stream_plan(int fmt, const LinArgs& a, int sm_count, size_t smem_limit);
@@ -129,6 +129,8 @@ cudaError_t launch_comm_pick(const unsigned* my_flags, int world, unsigned* pick
                              int* out_row, cudaStream_t st);
 
 // misc.cu
+// Multiprocessors of the current device (cached per device; allocates nothing).
+int current_sm_count();
 cudaError_t launch_dequant(int fmt, int N, int K, const void* W, const uint16_t* scale, float* out, cudaStream_t st);
 cudaError_t launch_argmax_half(const uint16_t* v, int n, int* out_idx, unsigned long long* slot, cudaStream_t st);
 cudaError_t launch_fill_u64(unsigned long long* p, unsigned long long v, cudaStream_t st);

@@ -107,12 +107,25 @@ __global__ void l2_flush_kernel(uint4* buf, size_t n16) {
 
 }  // namespace
 
+int current_sm_count() {
+    static int cached[64] = {};
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 132;
+    if (!cached[dev]) {
+        int n = 0;
+        if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) return 132;
+        cached[dev] = n;
+    }
+    return cached[dev];
+}
+
 cudaError_t launch_dequant(int fmt, int N, int K, const void* W, const uint16_t* scale, float* out, cudaStream_t st) {
     const size_t total = (size_t)N * K;
     if (total == 0) return cudaSuccess;
     const int threads = 256;
     size_t blocks = (total + threads - 1) / threads;
-    if (blocks > 148 * 16) blocks = 148 * 16;
+    const size_t cap = (size_t)current_sm_count() * 16;
+    if (blocks > cap) blocks = cap;
     const uint8_t* w = static_cast<const uint8_t*>(W);
     if (fmt == FMT_FP16) dequant_kernel<FMT_FP16><<<(unsigned)blocks, threads, 0, st>>>(w, scale, out, N, K);
     else if (fmt == FMT_INT8) dequant_kernel<FMT_INT8><<<(unsigned)blocks, threads, 0, st>>>(w, scale, out, N, K);
@@ -135,7 +148,8 @@ cudaError_t launch_argmax_half(const uint16_t* v, int n, int* out_idx, unsigned 
     if (e != cudaSuccess) return e;
     if (n > 0) {
         int blocks = (n + 1023) / 1024;
-        if (blocks > 148 * 4) blocks = 148 * 4;
+        const int cap = current_sm_count() * 4;
+        if (blocks > cap) blocks = cap;
         argmax_half_kernel<<<blocks, 256, 0, st>>>(v, n, slot);
         if ((e = cudaGetLastError()) != cudaSuccess) return e;
     }
@@ -151,7 +165,7 @@ cudaError_t launch_rmsnorm(const uint16_t* x, const uint16_t* w, uint16_t* out, 
 cudaError_t launch_l2_flush(void* buf, size_t bytes, cudaStream_t st) {
     const size_t n16 = bytes / 16;
     if (!n16) return cudaSuccess;
-    l2_flush_kernel<<<148 * 8, 256, 0, st>>>(static_cast<uint4*>(buf), n16);
+    l2_flush_kernel<<<(unsigned)current_sm_count() * 8u, 256, 0, st>>>(static_cast<uint4*>(buf), n16);
     return cudaGetLastError();
 }
 

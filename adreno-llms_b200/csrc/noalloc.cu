@@ -23,6 +23,7 @@
 
 #include "../../include/nnopt_b200.h"
 #include "internal.h"
+#include "kernels.h"
 
 namespace {
 
@@ -97,7 +98,8 @@ extern "C" int nn_argmax_static(void* cuda_stream, int n, nn_buf logits_fp16, nn
     static_clear_kernel<<<1, 1, 0, st>>>(slot);
     if (n > 0) {
         int blocks = (n + 1023) / 1024;
-        if (blocks > 148 * 4) blocks = 148 * 4;
+        const int cap = nnb::current_sm_count() * 4;
+        if (blocks > cap) blocks = cap;
         static_argmax_kernel<<<blocks, 256, 0, st>>>(static_cast<const uint16_t*>(logits_fp16), n, slot);
     }
     static_finish_kernel<<<1, 1, 0, st>>>(slot, static_cast<int*>(out_index_i32));

@@ -4,9 +4,17 @@ Mirrors the call points of the reference's decode loop
 (src/models/smollm2-135m-instruct/src/model.cpp:88-239): per layer a fused QKV
 launch, o_proj + residual, fused gate/up/SiLU, down + residual, then the lm_head
 GEMV and the arg-max.  The operators between the projections (norms, RoPE,
-attention) are not on this path; each projection reads a fixed N(0,1) activation
-buffer, and stream order carries the step's launch-to-launch dependencies the way
-the reference's in-order queue does.
+attention) are not on this path.  Two wirings:
+
+  fixed inputs   each projection reads a fixed N(0,1) activation buffer, as in a host
+                 program whose own kernels sit between the projections; only the in-place
+                 residual adds depend on one another.
+  chained        the data flows as in the model: QKV and gate/up read the residual stream
+                 (through the fused layer norms when norm=True), o_proj reads q (attention
+                 itself is not on the path, so q stands in for its output), down reads the
+                 SwiGLU output, lm_head reads the final residual stream.  Every projection
+                 then waits for the one before it, which is what a decode step's latency is
+                 made of.
 
 Several copies ("sets") of the weights can be resident so that consecutive steps
 stream from HBM rather than L2.
@@ -19,7 +27,7 @@ from . import synth
 
 class DecodeStep:
     def __init__(self, ctx, shape: synth.ModelShape, fmt: str, M: int = 1, n_sets: int = 1, seed: int = 1235,
-                 vocab_rows=None, keep_host=False, only=None, comm=None, norm=False, gather_logits=False):
+                 vocab_rows=None, keep_host=False, only=None, comm=None, norm=False, gather_logits=False, chained=False):
         self.ctx, self.shape, self.fmt, self.M = ctx, shape, fmt, M
         # with a communicator the lm_head rows are this rank's shard and the projection
         # stores into every rank's gather buffer (one buffer per weight set, so that
@@ -40,6 +48,7 @@ class DecodeStep:
         # them: QKV and gate/up take the residual stream itself through an RMSNorm prologue
         # (input_layernorm / post_attention_layernorm of the decoder layer)
         self.norm = norm
+        self.chained = chained
         self.eps = 1e-5
         if norm:
             g = (1.0 + 0.1 * rng.standard_normal(H)).astype(np.float32).astype(np.float16)
@@ -95,6 +104,11 @@ class DecodeStep:
     def enqueue(self, set_index=0, with_argmax=True):
         """Issue the step's launches on the context's stream (or into a recording)."""
         c, s, M, sh = self.ctx, self.sets[set_index], self.M, self.shape
+        ch = self.chained
+        x_qkv = self.resid if (ch or self.norm) else self.x_h
+        x_o = self.q if ch else self.x_attn
+        x_down = self.act if ch else self.x_act
+        x_head = self.resid if ch else self.x_h
         for kind, layer, ws in self.ops:
             w = [s[f"{kind}.{layer}.{j}"].buf for j in range(len(ws))]
             if kind == "qkv" and self.norm:
@@ -103,24 +117,24 @@ class DecodeStep:
             elif kind == "gate_up" and self.norm:
                 c.rmsnorm_gate_up_silu(M, sh.ffn, sh.hidden, self.resid, self.gamma, self.eps, w[0], w[1], self.act)
             elif kind == "qkv":
-                c.linear_qkv(M, sh.hidden, self.x_h, w[0], sh.q_dim, w[1], sh.kv_dim, w[2], sh.kv_dim, self.q, self.k, self.v)
+                c.linear_qkv(M, sh.hidden, x_qkv, w[0], sh.q_dim, w[1], sh.kv_dim, w[2], sh.kv_dim, self.q, self.k, self.v)
             elif kind == "o_add":
-                c.linear_add(M, sh.hidden, sh.q_dim, self.x_attn, w[0], self.resid)
+                c.linear_add(M, sh.hidden, sh.q_dim, x_o, w[0], self.resid)
             elif kind == "gate_up":
-                c.fused_gate_up_silu(M, sh.ffn, sh.hidden, self.x_h, w[0], w[1], self.act)
+                c.fused_gate_up_silu(M, sh.ffn, sh.hidden, x_qkv, w[0], w[1], self.act)
             elif kind == "down_add":
-                c.linear_add(M, sh.hidden, sh.ffn, self.x_act, w[0], self.resid)
+                c.linear_add(M, sh.hidden, sh.ffn, x_down, w[0], self.resid)
             elif self.comm and with_argmax and M == 1 and not self.gather_logits:
-                self.comm.linear_argmax_sharded(self.vocab_n, sh.hidden, self.x_h, w[0], self.logits, self.token)
+                self.comm.linear_argmax_sharded(self.vocab_n, sh.hidden, x_head, w[0], self.logits, self.token)
             elif self.comm:
-                self.comm.linear_gather(M, self.vocab_n, sh.hidden, self.x_h, w[0], self.gathered[set_index])
+                self.comm.linear_gather(M, self.vocab_n, sh.hidden, x_head, w[0], self.gathered[set_index])
                 if with_argmax and M == 1:   # [G][1][V/G] is the full logits vector
                     c.argmax(sh.vocab, self.gathered[set_index], self.token)
             elif with_argmax and M == 1:
                 # lm_head and the greedy pick in one launch (the logits are still stored)
-                c.linear_argmax(self.vocab_n, sh.hidden, self.x_h, w[0], self.logits, self.token)
+                c.linear_argmax(self.vocab_n, sh.hidden, x_head, w[0], self.logits, self.token)
             else:
-                c.linear(M, self.vocab_n, sh.hidden, self.x_h, w[0], self.logits)
+                c.linear(M, self.vocab_n, sh.hidden, x_head, w[0], self.logits)
 
     def record(self, with_argmax=True):
         """Record one plan per weight set (the reference's recorded-queue replay)."""
@@ -132,6 +146,9 @@ class DecodeStep:
             self.kernels_per_step = self.ctx.L.nn_plan_num_kernels(self.plans[i])
             assert self.ctx.launch_count() == before
         return self.kernels_per_step
+
+    def resident_runs(self, set_index=0):
+        return self.ctx.L.nn_plan_num_resident_runs(self.plans[set_index])
 
     def launch(self, set_index=0):
         self.ctx.plan_launch(self.plans[set_index])

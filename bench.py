@@ -5,16 +5,23 @@
 
 A step is one pass over every projection of a SmolLM2-135M-shaped decode step
 (30 x {QKV, o_proj+residual, gate/up/SiLU, down+residual} + tied lm_head; 211 GEMVs
-issued as 121 fused launches, the last of which also takes the greedy token) at M = 1 on
-seeded synthetic weights.  The metric is the
-achieved weight-stream rate: algorithmic bytes of the step / step time, in GB/s.
+recorded as 121 fused operators, the last of which also takes the greedy token) at M = 1 on
+seeded synthetic weights, with the data flowing as in the model: QKV and gate/up read the
+residual stream through the layer norms (fused into them), o_proj reads q (attention itself
+is not on the path), down reads the SwiGLU output, lm_head reads the final residual stream.
+Every projection waits for the one before it, as in a real token.  The recorded step is
+replayed as ONE resident launch.  The metric is the achieved weight-stream rate:
+algorithmic bytes of the step / step time, in GB/s.
 
   value     steps replayed from a recorded plan, operands resident in HBM, timed with
             CUDA events on the launching stream; consecutive steps use different
             resident weight copies so that every step streams from HBM, not L2
   e2e       the same step driven from HOST buffers through the C ABI: pinned-host
-            hidden vector -> device, step, logits -> pinned host, every step
-  roofline  the launch group that takes most of the step, replayed alone the same way
+            hidden vector -> device, step, logits and token -> pinned host, every step
+  roofline  the resident launch (the whole step is one kernel), against the HBM copy rate
+  roofline_targets   the large single operators the north star names, each timed alone
+  parity_checked     the replay's logits and token are compared inside the run with the same
+            operators launched one by one (and, with several ranks, across the ranks)
   cpu_baseline  the reference's own .cl kernels compiled for the CPU (oracle/_ref; the oracle
             port when that build is absent), all host cores, on a bounded sample of the step
 
@@ -28,7 +35,8 @@ ranks; every rank keeps its rows of the logits and the greedy pick exchanges one
 every rank instead is timed beside it); the per-layer projections stay replicated
 (north star: only the large row-sharded projections are partitioned).
 --impl reference times the reference's own CPU implementation of the path
-(oracle/_ref when it was built, else the oracle port) on the host cores.
+(oracle/_ref when it was built, else the oracle port) on the host cores: whole steps, every
+launch of the step executed.
 """
 import argparse
 import importlib.util
@@ -171,47 +179,23 @@ class ClockSampler:
 # ------------------------------------------------------------------------------------
 # CPU arm: the oracle (checker code) used ONLY here as the timed CPU baseline
 # ------------------------------------------------------------------------------------
-def cpu_step_rate(pkg, fmt, budget_s=12.0):
-    """GB/s of the CPU restatement on the step's projections, all host cores.
-    The sample is every distinct projection shape of the step once (weights of one
-    layer + the lm_head), scaled by how often each occurs in the step."""
-    sys.path.insert(0, REPO)
-    from oracle import cpu as ocpu  # noqa: E402  (CPU-baseline leg only)
-    synth = importlib.import_module("adreno_llms_b200.synth")
-    shape = synth.SMOLLM2_135M
-    cores = os.cpu_count() or 1
-    rng = np.random.default_rng(99)
-    groups = {}
-    for kind, _, ws in synth.decode_step_ops(shape):
-        for n, k in ws:
-            groups[(n, k)] = groups.get((n, k), 0) + 1
-    total_t, total_b = 0.0, 0
-    t_begin = time.perf_counter()
-    for (n, k), count in groups.items():
-        W, s = synth.weight(fmt, n, k, rng)
-        x = synth.activations(1, k, rng)
-        ocpu.linear_acc(fmt, x, W, s, ocpu.ORDER_KERNEL, cores)  # warm
-        reps, t = 0, 0.0
-        while reps < 3 and (time.perf_counter() - t_begin) < budget_s:
-            t0 = time.perf_counter()
-            ocpu.linear_acc(fmt, x, W, s, ocpu.ORDER_KERNEL, cores)
-            t += time.perf_counter() - t0
-            reps += 1
-        reps = max(reps, 1)
-        total_t += (t / reps if t else 0.0) * count
-        total_b += synth.linear_bytes(fmt, n, k, 1) * count
-    return total_b / total_t / 1e9, cores, total_t
-
-
 def ref_build_present():
     return os.path.exists(os.path.join(REPO, "oracle", "_ref", "libsmollm2_block_fused_int8.so"))
 
 
-def cpu_reference_rate(fmt, budget_s=25.0):
-    """GB/s of the reference's OWN kernels (its .cl sources compiled for the CPU,
-    oracle/_ref) on the step's launches, all host cores.  Sample: the launches of one
-    transformer layer (three QKV GEMVs, o_proj+residual, gate/up/SiLU, down+residual) and a
-    4096-row slice of the lm_head, each timed and scaled by how often it occurs in the step."""
+def workload_text(shape, fmt, M):
+    """config.workload: the same string in both arms."""
+    synth = importlib.import_module("adreno_llms_b200.synth")
+    return (f"decode-step projection set, {shape.name} shape, {fmt}, M={M} ({synth.decode_step_gemvs(shape)} GEMVs, "
+            f"data flowing as in the model: layer norms fused into QKV and gate/up, o_proj reads q)")
+
+
+def cpu_reference_steps(fmt, steps, budget_s=60.0):
+    """Whole steps on the reference's OWN kernels (its .cl sources compiled for the CPU, oracle/_ref),
+    all host cores: every launch of the step is executed, in order (per layer the three QKV GEMVs,
+    o_proj+residual, gate/up/SiLU, down+residual; then the whole lm_head).  Timing does not depend on
+    the values, so the thirty layers run on one layer's synthetic weights.  Returns
+    (GB/s, cores, seconds per step, steps timed)."""
     sys.path.insert(0, REPO)
     from oracle import ref_cl  # noqa: E402  (CPU-baseline leg only)
     synth = importlib.import_module("adreno_llms_b200.synth")
@@ -220,72 +204,111 @@ def cpu_reference_rate(fmt, budget_s=25.0):
     rng = np.random.default_rng(98)
     H, F = sh.hidden, sh.ffn
     x_h, x_f, r = synth.activations(1, H, rng), synth.activations(1, F, rng), synth.activations(1, H, rng)
-    head_rows = 4096
 
     def w(n, k):
         return synth.weight(fmt, n, k, rng)
 
+    Wq, Wk, Wv, Wo, Wg, Wu, Wd, Wl = w(sh.q_dim, H), w(sh.kv_dim, H), w(sh.kv_dim, H), w(H, sh.q_dim), w(F, H), w(F, H), w(H, F), w(sh.vocab, H)
     if fmt == "int8":
         lib = "smollm2_block_fused_int8"
-        launches = [
-            (lambda W=w(sh.q_dim, H): ref_cl.gemv_scaled(lib, "gemv_m1_k576_no4_img_int8", 4, x_h, W[0], W[1], cores), sh.layers, (sh.q_dim, H)),
-            (lambda W=w(sh.kv_dim, H): ref_cl.gemv_scaled(lib, "gemv_m1_k576_no4_img_int8", 4, x_h, W[0], W[1], cores), 2 * sh.layers, (sh.kv_dim, H)),
-            (lambda W=w(H, sh.q_dim): ref_cl.residual_scaled(lib, "fused_oproj_residual_m1_no4_img_int8", x_h, W[0], W[1], r, cores), sh.layers, (H, sh.q_dim)),
-            (lambda Wg=w(F, H), Wu=w(F, H): ref_cl.swiglu_int8(x_h, Wg[0], Wg[1], Wu[0], Wu[1], cores), sh.layers, (2 * F, H)),
-            (lambda W=w(H, F): ref_cl.residual_scaled(lib, "fused_down_residual_m1_no4_img_int8", x_f, W[0], W[1], r, cores), sh.layers, (H, F)),
-            (lambda W=w(head_rows, H): ref_cl.gemv_scaled(lib, "gemv_m1_k576_no4_img_int8", 4, x_h, W[0], W[1], cores), sh.vocab / head_rows, (head_rows, H)),
-        ]
+
+        def gemv(W):
+            return ref_cl.gemv_scaled(lib, "gemv_m1_k576_no4_img_int8", 4, x_h, W[0], W[1], cores)
+
+        def layer():
+            gemv(Wq), gemv(Wk), gemv(Wv)
+            ref_cl.residual_scaled(lib, "fused_oproj_residual_m1_no4_img_int8", x_h, Wo[0], Wo[1], r, cores)
+            ref_cl.swiglu_int8(x_h, Wg[0], Wg[1], Wu[0], Wu[1], cores)
+            ref_cl.residual_scaled(lib, "fused_down_residual_m1_no4_img_int8", x_f, Wd[0], Wd[1], r, cores)
     else:
         lib = "smollm2_block_fused"
-        launches = [
-            (lambda W=w(sh.q_dim, H): ref_cl.gemv_fp16_img(lib, "gemv_m1_k576_no4_img", 4, x_h, W[0], cores), sh.layers, (sh.q_dim, H)),
-            (lambda W=w(sh.kv_dim, H): ref_cl.gemv_fp16_img(lib, "gemv_m1_k576_no4_img", 4, x_h, W[0], cores), 2 * sh.layers, (sh.kv_dim, H)),
-            (lambda W=w(H, sh.q_dim): ref_cl.residual_fp16_img(lib, "fused_oproj_residual_m1_no4_img", x_h, W[0], r, cores), sh.layers, (H, sh.q_dim)),
-            (lambda Wg=w(F, H), Wu=w(F, H): ref_cl.swiglu_fp16(x_h, Wg[0], Wu[0], cores), sh.layers, (2 * F, H)),
-            (lambda W=w(H, F): ref_cl.residual_fp16_img(lib, "fused_down_residual_m1_no4_img", x_f, W[0], r, cores), sh.layers, (H, F)),
-            (lambda W=w(head_rows, H): ref_cl.gemv_fp16_img(lib, "gemv_m1_k576_no4_img", 4, x_h, W[0], cores), sh.vocab / head_rows, (head_rows, H)),
-        ]
-    t_step, t_begin = 0.0, time.perf_counter()
-    for fn, count, _ in launches:
-        fn()  # warm
-        reps, t = 0, 0.0
-        while reps < 3 and (reps == 0 or time.perf_counter() - t_begin < budget_s):
-            t0 = time.perf_counter()
-            fn()
-            t += time.perf_counter() - t0
-            reps += 1
-        t_step += t / reps * count
-    return synth.decode_step_bytes(sh, fmt, 1) / t_step / 1e9, cores, t_step
+
+        def gemv(W):
+            return ref_cl.gemv_fp16_img(lib, "gemv_m1_k576_no4_img", 4, x_h, W[0], cores)
+
+        def layer():
+            gemv(Wq), gemv(Wk), gemv(Wv)
+            ref_cl.residual_fp16_img(lib, "fused_oproj_residual_m1_no4_img", x_h, Wo[0], r, cores)
+            ref_cl.swiglu_fp16(x_h, Wg[0], Wu[0], cores)
+            ref_cl.residual_fp16_img(lib, "fused_down_residual_m1_no4_img", x_f, Wd[0], r, cores)
+
+    def one_step():
+        for _ in range(sh.layers):
+            layer()
+        gemv(Wl)
+
+    layer()  # warm (page in the libraries, start the worker threads)
+    times, t_begin = [], time.perf_counter()
+    while len(times) < steps and (not times or time.perf_counter() - t_begin < budget_s):
+        t0 = time.perf_counter()
+        one_step()
+        times.append(time.perf_counter() - t0)
+    t_step = statistics.median(times)
+    return synth.decode_step_bytes(sh, fmt, 1) / t_step / 1e9, cores, t_step, len(times)
 
 
-def cpu_arm(pkg, fmt, budget_s):
-    """(rate GB/s, cores, seconds per step, kind, sample text)."""
+def cpu_port_steps(fmt, steps, budget_s=30.0):
+    """Whole steps on the CPU restatement (oracle/oracle.c, -O3 -march=native, rows split over all
+    host cores); same launch list and weight reuse as cpu_reference_steps."""
+    sys.path.insert(0, REPO)
+    from oracle import cpu as ocpu  # noqa: E402  (CPU-baseline leg only)
+    synth = importlib.import_module("adreno_llms_b200.synth")
+    sh = synth.SMOLLM2_135M
+    cores = os.cpu_count() or 1
+    rng = np.random.default_rng(99)
+    H, F = sh.hidden, sh.ffn
+    x_h, x_f = synth.activations(1, H, rng), synth.activations(1, F, rng)
+    ws = {(n, k): synth.weight(fmt, n, k, rng) for _, _, lst in synth.decode_step_ops(sh) for n, k in lst}
+
+    def one_step():
+        for kind, _, lst in synth.decode_step_ops(sh):
+            for n, k in lst:
+                W, s = ws[(n, k)]
+                ocpu.linear_acc(fmt, x_f if k == F else x_h, W, s, ocpu.ORDER_KERNEL, cores)
+
+    ocpu.linear_acc(fmt, x_h, *ws[(sh.kv_dim, H)], ocpu.ORDER_KERNEL, cores)  # warm
+    times, t_begin = [], time.perf_counter()
+    while len(times) < steps and (not times or time.perf_counter() - t_begin < budget_s):
+        t0 = time.perf_counter()
+        one_step()
+        times.append(time.perf_counter() - t0)
+    t_step = statistics.median(times)
+    return synth.decode_step_bytes(sh, fmt, 1) / t_step / 1e9, cores, t_step, len(times)
+
+
+def cpu_arm(fmt, steps):
+    """The CPU baseline as a dict: the reference's own kernels when they were built (kind
+    "reference"), else the restatement (kind "port"); the other kind is reported beside it."""
+    out = {}
     if ref_build_present() and fmt in ("int8", "fp16"):
-        r, cores, t = cpu_reference_rate(fmt, budget_s)
-        return r, cores, t, "reference", ("the reference's .cl kernels compiled for the CPU: the launches of one layer and a "
-                                          "4096-row lm_head slice, each timed up to 3x on all cores and scaled by its count in the step")
-    r, cores, t = cpu_step_rate(pkg, fmt, budget_s)
-    return r, cores, t, "port", "each distinct projection shape of the step timed up to 3x on all cores, scaled by its count in the step"
+        r, cores, t, n = cpu_reference_steps(fmt, steps)
+        out = {"value": r, "unit": UNIT, "cores": cores, "kind": "reference", "seconds_per_step": t, "steps_timed": n, "extrapolated": False,
+               "sample": f"{n} whole step(s): every launch of the step executed on the reference's .cl kernels compiled for the CPU "
+                         f"(64 work-items of a group run as fibers), all {cores} cores; thirty layers on one layer's synthetic weights"}
+    pr, pcores, pt, pn = cpu_port_steps(fmt, steps)
+    port = {"value": pr, "unit": UNIT, "cores": pcores, "kind": "port", "seconds_per_step": pt, "steps_timed": pn, "extrapolated": False,
+            "sample": f"{pn} whole step(s) on the C restatement of the kernels (-O3 -march=native), rows split over {pcores} cores"}
+    if not out:
+        return port
+    out["port"] = port
+    return out
 
 
 def run_reference_arm(args, pkg, rank):
     if rank != 0:
         return
     fmt = args.fmt
-    rates = [cpu_arm(pkg, fmt, 20.0) for _ in range(max(1, min(args.steps, 3)))]
-    r = statistics.median([a[0] for a in rates])
-    t_step = statistics.median([a[2] for a in rates])
-    _, cores, _, kind, sample = rates[0]
     synth = importlib.import_module("adreno_llms_b200.synth")
+    base = cpu_arm(fmt, max(1, min(args.steps, 3)))
     line = {
-        "impl": "reference", "metric": METRIC, "value": r, "unit": UNIT, "n_gpus": args.gpus,
-        "steps": args.steps, "warmup": args.warmup, "ms_per_step": t_step * 1e3, "higher_is_better": True,
+        "impl": "reference", "metric": METRIC, "value": base["value"], "unit": UNIT, "n_gpus": args.gpus,
+        "steps": base["steps_timed"], "steps_requested": args.steps, "warmup": 1, "ms_per_step": base["seconds_per_step"] * 1e3,
+        "extrapolated": False, "higher_is_better": True,
         "scaling": "strong", "vs_baseline": None, "dtype": f"{fmt} weights, fp16 activations, fp32 accumulate",
         "data": "synthetic",
-        "config": {"workload": f"decode-step projection set, SmolLM2-135M shape, {fmt}, M=1 "
-                               f"({synth.decode_step_gemvs(synth.SMOLLM2_135M)} GEMVs)"},
-        "cpu_baseline": {"value": r, "unit": UNIT, "cores": cores, "kind": kind, "sample": sample},
-        "e2e": {"value": r, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "config": {"workload": workload_text(synth.SMOLLM2_135M, fmt, 1)},
+        "cpu_baseline": base,
+        "e2e": {"value": base["value"], "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
     }
     print(json.dumps(line), flush=True)
 

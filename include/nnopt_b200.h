@@ -165,14 +165,44 @@ int nn_linear_argmax(nn_context* ctx, int N, int K, nn_buf x, nn_buf W, nn_buf l
 int nn_argmax_static(void* cuda_stream, int n, nn_buf logits_fp16, nn_buf out_index_i32);
 
 /* ---- recorded decode step: the reference's recordable-queue replay
- *      (src/models/smollm2-135m-instruct/src/model.cpp:104-195,312-344).
- *      Between nn_plan_begin and nn_plan_end the operator calls above are captured
- *      instead of run; nn_plan_launch replays them in order on the stream. -------- */
+ *      (src/models/smollm2-135m-instruct/src/model.cpp:104-195,312-344;
+ *      src/models/lfm2-5-350m/src/model.cpp:188-228,376-458).
+ *      Between nn_plan_begin and nn_plan_end the operator calls above (and anything else the
+ *      caller enqueues on nn_stream) are captured instead of run; nn_plan_launch replays them
+ *      in order on the stream, with the same results as the calls made one by one.
+ *      Runs of consecutive single-token (M = 1) operators are replayed as ONE resident launch
+ *      each: its blocks walk the run's operators, stream every operator's weights ahead of time
+ *      and hand activations from operator to operator through device memory, so the replay
+ *      pays no per-operator launch.  An operator joins a run when each buffer it reads is
+ *      either untouched by the run so far or exactly one earlier operator's output (the whole
+ *      buffer); other operators, M > 1 calls, row-sharded calls and the caller's own kernels
+ *      stay separate launches between the runs.  A plan is replayed on its context's stream
+ *      only, one replay at a time. ------------------------------------------------------- */
 int nn_plan_begin(nn_context* ctx);
 int nn_plan_end(nn_context* ctx, nn_plan** out_plan);
 int nn_plan_launch(nn_context* ctx, nn_plan* plan);
-int nn_plan_num_kernels(const nn_plan* plan);
+int nn_plan_num_kernels(const nn_plan* plan);       /* launches per replay */
+int nn_plan_num_recorded(const nn_plan* plan);      /* launches that were recorded */
+int nn_plan_num_resident_runs(const nn_plan* plan); /* resident launches among them */
 int nn_plan_free(nn_plan* plan);
+/* Limit of every device-side wait inside the plan's resident launches (default about 200 ms,
+ * 1..10000).  When a wait runs out the launch ends early, the next nn_sync returns
+ * NN_ERR_TIMEOUT and the context stays usable.  No counterpart in the reference. */
+int nn_plan_set_wait_limit(nn_plan* plan, unsigned timeout_ms);
+/* Fault injection on the host side, for tests of that time-out: operator `op_index` of
+ * resident run `run_index` computes but never hands its outputs to the operators that wait
+ * for them (-1 restores normal behaviour).  No counterpart in the reference. */
+int nn_plan_withhold_output(nn_plan* plan, int run_index, int op_index);
+/* The grouping rule of nn_plan_end on address ranges alone (needs no GPU): operator i reads
+ * x_addr[i] .. + x_bytes[i], writes its nout[i] <= 4 outputs out_addr[4*i + k] .. + out_bytes[4*i + k];
+ * flags[i] bit 0: in-place epilogue (reads output 0 before writing it), bit 1: the last output is
+ * the 4-byte index of a fused greedy pick.  Returns how many operators from `first` on may share a
+ * resident launch and, for each of them, the operator (relative to `first`, -1 = not in the run)
+ * that produces its x and its in-place values, a bit mask of outputs it still stores to memory
+ * (an output overwritten later in the run is not stored) and of outputs it hands to later
+ * operators.  No counterpart in the reference. */
+int nn_plan_analyze(int nops, const uint64_t* x_addr, const uint64_t* x_bytes, const uint64_t* out_addr, const uint64_t* out_bytes,
+                    const int* nout, const int* flags, int first, int* x_dep, int* res_dep, int* store_mask, int* publish_mask);
 
 /* ---- class Weights, src/models/lfm2-5-350m/src/weights.h:13-51 (weights.cpp:169-297):
  *      mmap model.{fp16,int8,q4}.bin, parse meta.json, upload a tensor on first use. - */

@@ -66,7 +66,8 @@ def test_recorded_step_equals_eager(nnb, ctx):
         eager_logits, eager_tok = step.read_logits(), step.read_token()
         step.reset_residual()
         n = step.record()
-        assert n == 4 * shape.layers + 1          # lm_head and the greedy pick are one launch
+        assert ctx.L.nn_plan_num_recorded(step.plans[0]) == 4 * shape.layers + 1   # lm_head and the greedy pick are one launch
+        assert n == 1 and step.resident_runs() == 1   # ... and the whole step replays as one resident launch
         before = ctx.launch_count()
         step.launch(0)
         ctx.sync()
@@ -97,8 +98,8 @@ def test_step_with_fused_rmsnorm_follows_the_oracle_chain(nnb, ctx, fmt):
     dstep = importlib.import_module("adreno_llms_b200.decode_step")
     shape = synth.ModelShape("tiny-norm", 1024, 2, 1024, 512, 4608, 2048)
     step = dstep.DecodeStep(ctx, shape, fmt, M=1, n_sets=1, keep_host=True, norm=True)
-    n = step.record()
-    assert n == 4 * shape.layers + 1          # the norms add no launch
+    step.record()
+    assert ctx.L.nn_plan_num_recorded(step.plans[0]) == 4 * shape.layers + 1          # the norms add no launch
     step.launch(0)
     ctx.sync()
     h = step.host
