@@ -188,8 +188,18 @@ cudaError_t build_run(const std::vector<RecordedOp>& rec, const std::vector<OpDe
         s.nbox = stage_nbox(r.p.kcb);
         size_t wbytes = 0;
         for (int k = 0; k < a.nseg; ++k) wbytes += (size_t)a.seg[k].N * rowbytes;
-        s.evict_first = wbytes > ((size_t)96 << 20) ? 1 : 0;
-        s.scale_tma = r.fmt == FMT_Q4 ? 1 : 0;
+        s.flags = (wbytes > ((size_t)96 << 20) ? PLAN_EVICT_FIRST : 0) | (r.fmt == FMT_Q4 ? PLAN_SCALE_TMA : 0);
+        if (r.fmt == FMT_INT8) {
+            // the row scales are static data like the weights: the producer brings them along
+            bool aligned = true;
+            for (int k = 0; k < a.nseg; ++k) aligned = aligned && (reinterpret_cast<uintptr_t>(a.seg[k].scale) & 15) == 0;
+            if (dual) aligned = aligned && (reinterpret_cast<uintptr_t>(a.scale2) & 15) == 0;
+            if (aligned) {
+                s.flags |= PLAN_ROW_SCALES;
+                s.scale_off = s.item_bytes;
+                s.item_bytes += PLAN_ROW_SCALE_BYTES;
+            }
+        }
         int t0 = 0;
         for (int k = 0; k < a.nseg; ++k) {
             PlanSeg& sg = s.seg[k];
@@ -253,7 +263,8 @@ cudaError_t build_run(const std::vector<RecordedOp>& rec, const std::vector<OpDe
     P.off_xs = P.off_xraw + up128(k_ll * 2);
     P.off_ctab = P.off_xs + x_bytes;
     P.off_norm = P.off_ctab + up128(ctab_bytes);
-    P.off_red = P.off_norm + up128(k_norm * 2);
+    P.off_gamma = P.off_norm + up128(k_norm * 2);
+    P.off_red = P.off_gamma + up128(k_norm * 2);
     P.off_ring = (P.off_red + red_bytes_of(1) + 1023) / 1024 * 1024;
     const long long room = (long long)smem_limit - P.off_ring - 1024;  // 1 KB of slack to align the ring
     P.ring_bytes = room > 0 ? (int)(room / 1024 * 1024) : 0;

@@ -42,7 +42,8 @@ struct PlanOpScalars {
     int fmt, epi, dual, ksplit;
     int kcb, nchunks, groups, rowbytes;
     int K, nseg, ntiles, tile_start;     // tile_start: tiles of the run before this operator, modulo the grid
-    int item_bytes, nbox, evict_first, scale_tma;
+    int item_bytes, nbox, flags;         // flags: PLAN_EVICT_FIRST | PLAN_SCALE_TMA | PLAN_ROW_SCALES
+    int scale_off;                       // int8 row scales ride in the last item of each tile, at this offset inside it
     int x_epoch, res_epoch, epoch, nblocks;  // epochs are 1 + index of the producing operator; nblocks = blocks that hold tiles of this one
 };
 static_assert(sizeof(PlanOpScalars) == 256, "descriptor scalars are copied in sixteen 16-byte pieces");
@@ -53,6 +54,15 @@ struct alignas(128) PlanOp {
     PlanOpScalars s;
 };
 
+enum : int {
+    PLAN_EVICT_FIRST = 1,  // weights larger than L2 are streamed with an evict-first policy
+    PLAN_SCALE_TMA = 2,    // Q4: block scales arrive by tensor copies
+    PLAN_ROW_SCALES = 4,   // int8: the tile's row scales arrive with its last item (bulk copy), when the tile's rows allow it
+};
+constexpr int PLAN_ROW_SCALE_BYTES = 1024;  // room for them at the end of an item: first weight at +0, second at +512
+// Bulk copies move multiples of 16 bytes: a tile's row scales travel with it when its valid rows are a multiple of 8.
+__host__ __device__ inline bool plan_rows_bulk_ok(int rows_valid) { return rows_valid > 0 && (rows_valid & 7) == 0; }
+
 constexpr int PLAN_SLOTS = 16;        // ring items in flight per block
 constexpr int PLAN_MAX_OPS = 1024;    // operators per run (their tile table sits in shared memory)
 // head of the kernel's shared memory: 64 bytes of zeros, full[] and empty[] barriers, the producer's
@@ -60,8 +70,9 @@ constexpr int PLAN_MAX_OPS = 1024;    // operators per run (their tile table sit
 constexpr int PLAN_HDR_BARS = 64;
 constexpr int PLAN_HDR_SLOTS = PLAN_HDR_BARS + 2 * PLAN_SLOTS * 8;
 constexpr int PLAN_HDR_ISSUED = PLAN_HDR_SLOTS + 2 * PLAN_SLOTS * 4;
-constexpr int PLAN_HDR_BYTES = 512;
-static_assert(PLAN_HDR_ISSUED + 4 <= PLAN_HDR_BYTES, "header layout");
+constexpr int PLAN_HDR_STATE = PLAN_HDR_ISSUED + 16;  // the consumers' state between operators (64 bytes)
+constexpr int PLAN_HDR_BYTES = 640;
+static_assert(PLAN_HDR_STATE + 64 <= PLAN_HDR_BYTES, "header layout");
 
 struct PlanParams {
     const PlanOp* ops;
@@ -71,13 +82,13 @@ struct PlanParams {
     int* status;            // mapped host word: non-zero when a bounded wait ran out
     long long wait_cycles;  // limit of every wait
     int drop_publish_op;    // fault injection for tests: this operator never publishes its outputs (-1: none)
-    int off_tiles, off_desc, off_xraw, off_xs, off_ctab, off_norm, off_red, off_ring, ring_bytes;
+    int off_tiles, off_desc, off_xraw, off_xs, off_ctab, off_norm, off_gamma, off_red, off_ring, ring_bytes;
 };
 
 // decode_plan.cu
 cudaError_t decode_plan_configure();
 cudaError_t decode_plan_func(const void** func);   // the kernel's address, for a graph kernel node
-constexpr int DECODE_PLAN_THREADS = (4 + 1) * 32;
+constexpr int DECODE_PLAN_THREADS = (8 + 1) * 32;  // eight consumer warps and the producer warp
 
 // ---- host side (plan.cpp) ---------------------------------------------------------------------
 // What the recorder keeps of one streamed single-token operator.

@@ -44,6 +44,8 @@ __host__ __device__ inline int x_bytes_of(int fmt, int M, int K) {
 __host__ __device__ inline int ctab_bytes_of(int fmt, int M, int K) { return fmt == FMT_Q4 ? (K / 32) * ((M + 1) / 2) * 16 : 0; }
 // two reduction buffers for the consumers that split K of one tile
 __host__ __device__ inline int red_bytes_of(int nt) { return 2 * NCW * 32 * 2 * nt * 4 * 4; }
+// K parts of a tile whose K is split, one token (see "Accumulator sets" below)
+constexpr int KPARTS = 4 * NCW;
 
 // int8 weights are multiplied on the integer tensor-core path, with no conversion of the
 // weights at all: each activation row is turned into 24-bit fixed point
@@ -224,6 +226,65 @@ __device__ __forceinline__ void stage_x(const uint16_t* __restrict__ x, int M, i
     }
 }
 
+// RMSNorm of a single row whose norm weight is already in registers (piece j of thread tid is the
+// 16-byte piece tid + j * NCW * 32 of the weight): sum of squares, then xn[k] = half((x[k] *
+// rsqrt(mean x^2 + eps)) * g[k]).  Rows of up to RMSNORM_REG * NCW * 32 * 8 values.  The weight does
+// not depend on the activations, so a caller that waits for x loads it while it waits.
+constexpr int RMSNORM_REG = 4;
+__device__ __forceinline__ void rmsnorm_load_weight(const uint16_t* __restrict__ gw, int aK, int tid, uint4 (&gv4)[RMSNORM_REG]) {
+    const int per_row = aK / 8;
+#pragma unroll
+    for (int j = 0; j < RMSNORM_REG; ++j) {
+        const int p = tid + j * NCW * 32;
+        gv4[j] = p < per_row ? *reinterpret_cast<const uint4*>(gw + p * 8) : make_uint4(0, 0, 0, 0);
+    }
+}
+__device__ __forceinline__ void rmsnorm_one_row(const uint16_t* __restrict__ x, const uint4 (&gv4)[RMSNORM_REG], float n_eps, int aK, uint16_t* xn,
+                                                float* red, int tid, int lane, int warp) {
+    const int per_row = aK / 8;
+    constexpr int NREG = RMSNORM_REG;
+    uint4 xv4[NREG];
+    float ss = 0.f;
+#pragma unroll
+    for (int j = 0; j < NREG; ++j) {
+        const int p = tid + j * NCW * 32;
+        xv4[j] = p < per_row ? *reinterpret_cast<const uint4*>(x + p * 8) : make_uint4(0, 0, 0, 0);
+    }
+#pragma unroll
+    for (int j = 0; j < NREG; ++j) {
+        const uint32_t wv[4] = {xv4[j].x, xv4[j].y, xv4[j].z, xv4[j].w};
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+            const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&wv[q]));
+            ss += f.x * f.x;
+            ss += f.y * f.y;
+        }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+    if (lane == 0) red[warp * 16] = ss;
+    asm volatile("bar.sync 1, %0;" ::"n"(NCW * 32) : "memory");
+    float tot = 0.f;
+#pragma unroll
+    for (int w2 = 0; w2 < NCW; ++w2) tot += red[w2 * 16];
+    const float inv = 1.0f / sqrtf(tot / (float)aK + n_eps);
+#pragma unroll
+    for (int j = 0; j < NREG; ++j) {
+        const int p = tid + j * NCW * 32;
+        if (p >= per_row) continue;
+        const uint32_t xv[4] = {xv4[j].x, xv4[j].y, xv4[j].z, xv4[j].w}, gv[4] = {gv4[j].x, gv4[j].y, gv4[j].z, gv4[j].w};
+        uint32_t o4[4];
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+            const float2 fx = __half22float2(*reinterpret_cast<const __half2*>(&xv[q]));
+            const float2 fg = __half22float2(*reinterpret_cast<const __half2*>(&gv[q]));
+            const __half2 h = __floats2half2_rn((fx.x * inv) * fg.x, (fx.y * inv) * fg.y);
+            o4[q] = *reinterpret_cast<const uint32_t*>(&h);
+        }
+        *reinterpret_cast<uint4*>(xn + p * 8) = make_uint4(o4[0], o4[1], o4[2], o4[3]);
+    }
+}
+
 // RMSNorm prologue (src/models/smollm2-135m-instruct/kernels/rmsnorm.cl:27-104 fused into the
 // projection that reads its output): sum of squares per row, then the normalised fp16 rows
 // xn[m][k] = half((x[m][k] * rsqrt(mean_k x[m]^2 + eps)) * gw[k]) go to shared memory.  Called by
@@ -231,50 +292,11 @@ __device__ __forceinline__ void stage_x(const uint16_t* __restrict__ x, int M, i
 __device__ __forceinline__ void rmsnorm_rows(const uint16_t* __restrict__ x, const uint16_t* __restrict__ gw, float n_eps, int aM, int aK,
                                              uint16_t* xn, float* red, int tid, int lane, int warp) {
     const int per_row = aK / 8;
-    constexpr int NREG = 4;
-    if (aM == 1 && per_row <= NREG * NCW * 32) {
+    if (aM == 1 && per_row <= RMSNORM_REG * NCW * 32) {
         // decode fast path: the row and the norm weight are read once and stay in registers
-        uint4 xv4[NREG], gv4[NREG];
-        float ss = 0.f;
-#pragma unroll
-        for (int j = 0; j < NREG; ++j) {
-            const int p = tid + j * NCW * 32;
-            xv4[j] = p < per_row ? *reinterpret_cast<const uint4*>(x + p * 8) : make_uint4(0, 0, 0, 0);
-            gv4[j] = p < per_row ? *reinterpret_cast<const uint4*>(gw + p * 8) : make_uint4(0, 0, 0, 0);
-        }
-#pragma unroll
-        for (int j = 0; j < NREG; ++j) {
-            const uint32_t wv[4] = {xv4[j].x, xv4[j].y, xv4[j].z, xv4[j].w};
-#pragma unroll
-            for (int q = 0; q < 4; ++q) {
-                const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&wv[q]));
-                ss += f.x * f.x;
-                ss += f.y * f.y;
-            }
-        }
-#pragma unroll
-        for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
-        if (lane == 0) red[warp * 16] = ss;
-        asm volatile("bar.sync 1, %0;" ::"n"(NCW * 32) : "memory");
-        float tot = 0.f;
-#pragma unroll
-        for (int w2 = 0; w2 < NCW; ++w2) tot += red[w2 * 16];
-        const float inv = 1.0f / sqrtf(tot / (float)aK + n_eps);
-#pragma unroll
-        for (int j = 0; j < NREG; ++j) {
-            const int p = tid + j * NCW * 32;
-            if (p >= per_row) continue;
-            const uint32_t xv[4] = {xv4[j].x, xv4[j].y, xv4[j].z, xv4[j].w}, gv[4] = {gv4[j].x, gv4[j].y, gv4[j].z, gv4[j].w};
-            uint32_t o4[4];
-#pragma unroll
-            for (int q = 0; q < 4; ++q) {
-                const float2 fx = __half22float2(*reinterpret_cast<const __half2*>(&xv[q]));
-                const float2 fg = __half22float2(*reinterpret_cast<const __half2*>(&gv[q]));
-                const __half2 h = __floats2half2_rn((fx.x * inv) * fg.x, (fx.y * inv) * fg.y);
-                o4[q] = *reinterpret_cast<const uint32_t*>(&h);
-            }
-            *reinterpret_cast<uint4*>(xn + p * 8) = make_uint4(o4[0], o4[1], o4[2], o4[3]);
-        }
+        uint4 gv4[RMSNORM_REG];
+        rmsnorm_load_weight(gw, aK, tid, gv4);
+        rmsnorm_one_row(x, gv4, n_eps, aK, xn, red, tid, lane, warp);
     } else {
         for (int m = 0; m < aM; ++m) {
             float ss = 0.f;
@@ -361,38 +383,59 @@ __device__ __forceinline__ void lane_geo_init(LaneGeo<NT>& L, bool two_weights, 
     }
 }
 
-// fp16: K chunk c (kcb bytes of every row, cb of them valid) of the stage at `sw`.
-// One step = 64 bytes of each row = 32 k = two MMAs per row block; steps alternate between the
-// two accumulator sets.
+// Accumulator sets.  A consumer keeps SETS independent fp32 accumulators and deals the units of a K
+// chunk (fp16 / int8-direct: 64-byte steps; Q4: 32-weight blocks) out to them in turn, unit u of the
+// chunk to set u mod SETS, so that consecutive MMAs do not wait for one another.  Rows streamed whole
+// by one warp use two sets and add them at the end.  Tiles whose K is split over the four consumers
+// (few-row operators, one token) use four: that makes sixteen K parts per tile, part 4 * (chunk mod 4)
+// + (unit mod 4), each summed in unit order and added in part order at the end.  The resident kernel
+// gives every part a warp of its own (step_fp16 / step_int8_direct / block_q4 below) and adds the
+// parts in the same order, hence the same bits.
+
+// fp16: one step = 64 bytes of each row = 32 k = two MMAs per row block.  `s` counts steps from the
+// start of the row (it addresses the activations), `s_in_chunk` from the start of the chunk.
 template <int NT>
-__device__ __forceinline__ void chunk_fp16(const LaneGeo<NT>& L, uint32_t sw, int c, int kcb, int cb, float (&acc)[2][2][NT][4]) {
-    auto step = [&](int s, float (&ac)[2][NT][4]) {
-        uint32_t b[NT][4];
+__device__ __forceinline__ void step_fp16(const LaneGeo<NT>& L, uint32_t sw, int s, int s_in_chunk, float (&ac)[2][NT][4]) {
+    uint32_t b[NT][4];
 #pragma unroll
-        for (int nt = 0; nt < NT; ++nt) ldsm_x4(L.b_base[nt] + s * L.b_step[nt], b[nt][0], b[nt][1], b[nt][2], b[nt][3]);
-        uint32_t av[2][2][4];
-        const uint32_t q = (uint32_t)(s - (c * kcb) / 64) * 4 + L.a_q_lane;
+    for (int nt = 0; nt < NT; ++nt) ldsm_x4(L.b_base[nt] + s * L.b_step[nt], b[nt][0], b[nt][1], b[nt][2], b[nt][3]);
+    uint32_t av[2][2][4];
+    const uint32_t q = (uint32_t)s_in_chunk * 4 + L.a_q_lane;
 #pragma unroll
-        for (int rb = 0; rb < 2; ++rb) {
-            const uint32_t off = (rb ? L.rb_base1 : L.rb_base0) + L.a_row_off;
-            ldsm_x4(L.piece_addr(sw, off, q), av[rb][0][0], av[rb][0][1], av[rb][0][2], av[rb][0][3]);
-            ldsm_x4(L.piece_addr(sw, off, q + 2), av[rb][1][0], av[rb][1][1], av[rb][1][2], av[rb][1][3]);
+    for (int rb = 0; rb < 2; ++rb) {
+        const uint32_t off = (rb ? L.rb_base1 : L.rb_base0) + L.a_row_off;
+        ldsm_x4(L.piece_addr(sw, off, q), av[rb][0][0], av[rb][0][1], av[rb][0][2], av[rb][0][3]);
+        ldsm_x4(L.piece_addr(sw, off, q + 2), av[rb][1][0], av[rb][1][1], av[rb][1][2], av[rb][1][3]);
+    }
+#pragma unroll
+    for (int h = 0; h < 2; ++h)
+#pragma unroll
+        for (int rb = 0; rb < 2; ++rb)
+#pragma unroll
+            for (int nt = 0; nt < NT; ++nt)
+                mma_16816(ac[rb][nt], av[rb][h][0], av[rb][h][1], av[rb][h][2], av[rb][h][3], b[nt][2 * h], b[nt][2 * h + 1]);
+}
+// K chunk c (kcb bytes of every row, cb of them valid) of the stage at `sw`.
+template <int NT, int SETS>
+__device__ __forceinline__ void chunk_fp16(const LaneGeo<NT>& L, uint32_t sw, int c, int kcb, int cb, float (&acc)[SETS][2][NT][4]) {
+    const int s0 = (c * kcb) / 64, ns = cb / 64;
+    if (SETS == 2) {
+        int u = 0;
+        for (; u + 2 <= ns; u += 2) {
+            step_fp16<NT>(L, sw, s0 + u, u, acc[0]);
+            step_fp16<NT>(L, sw, s0 + u + 1, u + 1, acc[1]);
+        }
+        if (u < ns) step_fp16<NT>(L, sw, s0 + u, u, acc[0]);
+    } else {
+        int u = 0;
+        for (; u + 4 <= ns; u += 4) {
+#pragma unroll
+            for (int i = 0; i < 4; ++i) step_fp16<NT>(L, sw, s0 + u + i, u + i, acc[i % SETS]);
         }
 #pragma unroll
-        for (int h = 0; h < 2; ++h)
-#pragma unroll
-            for (int rb = 0; rb < 2; ++rb)
-#pragma unroll
-                for (int nt = 0; nt < NT; ++nt)
-                    mma_16816(ac[rb][nt], av[rb][h][0], av[rb][h][1], av[rb][h][2], av[rb][h][3], b[nt][2 * h], b[nt][2 * h + 1]);
-    };
-    const int s0 = (c * kcb) / 64, s1 = s0 + cb / 64;
-    int s = s0;
-    for (; s + 2 <= s1; s += 2) {
-        step(s, acc[0]);
-        step(s + 1, acc[1]);
+        for (int i = 0; i < 3; ++i)
+            if (u + i < ns) step_fp16<NT>(L, sw, s0 + u + i, u + i, acc[i % SETS]);
     }
-    if (s < s1) step(s, acc[0]);
 }
 
 // int8: one step = 64 bytes of each row = 64 k = two integer MMAs (k32) per row block and
@@ -425,6 +468,67 @@ __device__ __forceinline__ void chunk_int8(const LaneGeo<NT>& L, uint32_t sw, in
     }
 }
 
+// int8 for operators with few rows (the consumers split K of one tile): such operators are bound by
+// latency, not by the weight stream, and turning the activations into fixed-point limb planes costs
+// more than the whole dot product.  Here the weights are converted to exact fp16 integers in registers
+// and multiplied with the fp16 activations as they are (fp32 accumulation of exact products).
+// One ldmatrix.x4 yields 16 rows x 32 k: lane (g, t) holds k 4t .. 4t+3 of rows g and g + 8 of two
+// 16-byte pieces.  The two k16 MMAs per load take those four k as the fragment's (2t, 2t+1) and
+// (2t+8, 2t+9) columns, so the B operand of lane (g, t) is simply x[token g][k0 + 4t .. 4t+3]: one
+// 8-byte shared-memory load from the token's plain fp16 row, no permuted copy.
+// xrow[nt] = shared-memory address of this lane's token row (a row of zeros, with xstep 0, for absent
+// tokens).  One step = 64 bytes of each row = two such loads per row block = four MMAs per row block;
+// `k` = first k of the step counted from the start of the row, `s_in_chunk` = step inside the chunk.
+template <int NT>
+__device__ __forceinline__ void step_int8_direct(const LaneGeo<NT>& L, uint32_t sw, int k, int s_in_chunk, const uint32_t (&xrow)[NT],
+                                                 const uint32_t (&xstep)[NT], float (&ac)[2][NT][4]) {
+    const int t = (int)(threadIdx.x & 3);
+    uint32_t w[2][2][4];  // [32-byte half][row block]
+    uint32_t b[2][NT][4];
+    // all loads first: a warp may be alone on its scheduler, and nothing else would cover their latency
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+        const uint32_t q = (uint32_t)(s_in_chunk * 2 + h) * 2 + L.a_q_lane;
+#pragma unroll
+        for (int rb = 0; rb < 2; ++rb)
+            ldsm_x4(L.piece_addr(sw, (rb ? L.rb_base1 : L.rb_base0) + L.a_row_off, q), w[h][rb][0], w[h][rb][1], w[h][rb][2], w[h][rb][3]);
+#pragma unroll
+        for (int nt = 0; nt < NT; ++nt) {
+            const uint32_t xa = xrow[nt] + (uint32_t)((k + h * 32 + 4 * t) * 2) * xstep[nt];
+            asm volatile("ld.shared.v2.b32 {%0, %1}, [%2];" : "=r"(b[h][nt][0]), "=r"(b[h][nt][1]) : "r"(xa));
+            asm volatile("ld.shared.v2.b32 {%0, %1}, [%2];" : "=r"(b[h][nt][2]), "=r"(b[h][nt][3]) : "r"(xa + 32u * xstep[nt]));
+        }
+    }
+#pragma unroll
+    for (int h = 0; h < 2; ++h)
+#pragma unroll
+        for (int rb = 0; rb < 2; ++rb) {
+            uint32_t a0, a2, a1, a3, c0, c2, c1, c3;
+            int8x4_to_half2x2(w[h][rb][0], a0, a2);  // rows g:     piece q
+            int8x4_to_half2x2(w[h][rb][1], a1, a3);  // rows g + 8: piece q
+            int8x4_to_half2x2(w[h][rb][2], c0, c2);  // rows g:     piece q + 1
+            int8x4_to_half2x2(w[h][rb][3], c1, c3);  // rows g + 8: piece q + 1
+#pragma unroll
+            for (int nt = 0; nt < NT; ++nt) {
+                mma_16816(ac[rb][nt], a0, a1, a2, a3, b[h][nt][0], b[h][nt][1]);
+                mma_16816(ac[rb][nt], c0, c1, c2, c3, b[h][nt][2], b[h][nt][3]);
+            }
+        }
+}
+template <int NT, int SETS>
+__device__ __forceinline__ void chunk_int8_direct(const LaneGeo<NT>& L, uint32_t sw, int c, int kcb, int cb, const uint32_t (&xrow)[NT],
+                                                  const uint32_t (&xstep)[NT], float (&acc)[SETS][2][NT][4]) {
+    const int k0 = c * kcb, ns = cb / 64;  // int8: one byte per k
+    int u = 0;
+    for (; u + SETS <= ns; u += SETS) {
+#pragma unroll
+        for (int i = 0; i < SETS; ++i) step_int8_direct<NT>(L, sw, k0 + (u + i) * 64, u + i, xrow, xstep, acc[i]);
+    }
+#pragma unroll
+    for (int i = 0; i < SETS - 1; ++i)
+        if (u + i < ns) step_int8_direct<NT>(L, sw, k0 + (u + i) * 64, u + i, xrow, xstep, acc[i]);
+}
+
 // int8: recombine the limb sums, (hi * 2^16 + mid * 2^8 + lo) * 2^-p, in fp32, into acc
 template <int NT>
 __device__ __forceinline__ void int8_recombine(const int (&iacc)[3][2][NT][4], float (&acc)[2][NT][4], const float* rowscale, int aM, int t) {
@@ -442,43 +546,60 @@ __device__ __forceinline__ void int8_recombine(const int (&iacc)[3][2][NT][4], f
 
 // Q4: one step = 16 bytes of each row = one 32-weight block = two MMAs per row block on the
 // biased codes (64 + nibble), started from -72 * sum(x) of the block so that the result is
-// sum((nibble - 8) x), then folded in with the block's scale.  `sc_rb[rb]` = the stage's scale
-// row of this lane's row g of row block rb (rows g + 8 are 8 * sstr bytes further).
+// sum((nibble - 8) x), then folded in with the block's scale.  `s` = block counted from the start of
+// the row, w_addr = address of this lane's part of the block's 16-byte piece, s_lo2 / s_hi2 = the
+// block's scales of rows g and g + 8 of the two row blocks.
 template <int NT>
-__device__ __forceinline__ void chunk_q4(const LaneGeo<NT>& L, uint32_t sw, int c, int kcb, int cb, float (&acc)[2][2][NT][4],
+__device__ __forceinline__ void block_q4(const LaneGeo<NT>& L, int s, float (&ac)[2][NT][4], const float (&s_lo2)[2], const float (&s_hi2)[2],
+                                         uint32_t w_addr) {
+    uint32_t b[NT][4];
+    float4 cq[NT];
+#pragma unroll
+    for (int nt = 0; nt < NT; ++nt) {
+        ldsm_x4(L.b_base[nt] + s * L.b_step[nt], b[nt][0], b[nt][1], b[nt][2], b[nt][3]);
+        cq[nt] = *reinterpret_cast<const float4*>(L.ctab_lane[nt] + (size_t)s * L.ctab_step);
+    }
+    uint32_t w[4];
+    ldsm_x4(w_addr, w[0], w[1], w[2], w[3]);
+#pragma unroll
+    for (int rb = 0; rb < 2; ++rb) {
+        uint32_t p04, p15, p26, p37, q04, q15, q26, q37;
+        q4x8_to_half2x4_biased(w[rb * 2], p04, p15, p26, p37);
+        q4x8_to_half2x4_biased(w[rb * 2 + 1], q04, q15, q26, q37);
+        const float s_lo = s_lo2[rb], s_hi = s_hi2[rb];
+#pragma unroll
+        for (int nt = 0; nt < NT; ++nt) {
+            float d[4];
+            mma_16816_c(d, p04, q04, p15, q15, b[nt][0], b[nt][1], cq[nt]);  // starts at -72 * sum(x)
+            mma_16816(d, p26, q26, p37, q37, b[nt][2], b[nt][3]);
+            ac[rb][nt][0] = fmaf(d[0], s_lo, ac[rb][nt][0]);
+            ac[rb][nt][1] = fmaf(d[1], s_lo, ac[rb][nt][1]);
+            ac[rb][nt][2] = fmaf(d[2], s_hi, ac[rb][nt][2]);
+            ac[rb][nt][3] = fmaf(d[3], s_hi, ac[rb][nt][3]);
+        }
+    }
+}
+// One block on its own: block `u` of chunk c (the resident kernel's warps take every fourth block).
+// `sc_rb[rb]` = the stage's scale row of this lane's row g of row block rb (rows g + 8 are 8 * sstr
+// bytes further).
+template <int NT>
+__device__ __forceinline__ void block_q4_at(const LaneGeo<NT>& L, uint32_t sw, int c, int kcb, int u, float (&ac)[2][NT][4],
+                                            const uint8_t* const (&sc_rb)[2], int sstr) {
+    float lo2[2], hi2[2];
+#pragma unroll
+    for (int rb = 0; rb < 2; ++rb) {
+        lo2[rb] = __half2float(__ushort_as_half(*reinterpret_cast<const uint16_t*>(sc_rb[rb] + u * 2)));
+        hi2[rb] = __half2float(__ushort_as_half(*reinterpret_cast<const uint16_t*>(sc_rb[rb] + 8 * sstr + u * 2)));
+    }
+    block_q4<NT>(L, (c * kcb) / 16 + u, ac, lo2, hi2, L.piece_addr(sw, L.aq_off, (uint32_t)u));
+}
+template <int NT, int SETS>
+__device__ __forceinline__ void chunk_q4(const LaneGeo<NT>& L, uint32_t sw, int c, int kcb, int cb, float (&acc)[SETS][2][NT][4],
                                          const uint8_t* const (&sc_rb)[2], int sstr) {
     const int g0 = (c * kcb) / 16;
     uint32_t w_xor[4];
 #pragma unroll
     for (int u = 0; u < 4; ++u) w_xor[u] = (((uint32_t)u ^ (L.xr & 3u)) << 4);
-    auto step = [&](int s, float (&ac)[2][NT][4], const float (&s_lo2)[2], const float (&s_hi2)[2], uint32_t w_addr) {
-        uint32_t b[NT][4];
-        float4 cq[NT];
-#pragma unroll
-        for (int nt = 0; nt < NT; ++nt) {
-            ldsm_x4(L.b_base[nt] + s * L.b_step[nt], b[nt][0], b[nt][1], b[nt][2], b[nt][3]);
-            cq[nt] = *reinterpret_cast<const float4*>(L.ctab_lane[nt] + (size_t)s * L.ctab_step);
-        }
-        uint32_t w[4];
-        ldsm_x4(w_addr, w[0], w[1], w[2], w[3]);
-#pragma unroll
-        for (int rb = 0; rb < 2; ++rb) {
-            uint32_t p04, p15, p26, p37, q04, q15, q26, q37;
-            q4x8_to_half2x4_biased(w[rb * 2], p04, p15, p26, p37);
-            q4x8_to_half2x4_biased(w[rb * 2 + 1], q04, q15, q26, q37);
-            const float s_lo = s_lo2[rb], s_hi = s_hi2[rb];
-#pragma unroll
-            for (int nt = 0; nt < NT; ++nt) {
-                float d[4];
-                mma_16816_c(d, p04, q04, p15, q15, b[nt][0], b[nt][1], cq[nt]);  // starts at -72 * sum(x)
-                mma_16816(d, p26, q26, p37, q37, b[nt][2], b[nt][3]);
-                ac[rb][nt][0] = fmaf(d[0], s_lo, ac[rb][nt][0]);
-                ac[rb][nt][1] = fmaf(d[1], s_lo, ac[rb][nt][1]);
-                ac[rb][nt][2] = fmaf(d[2], s_hi, ac[rb][nt][2]);
-                ac[rb][nt][3] = fmaf(d[3], s_hi, ac[rb][nt][3]);
-            }
-        }
-    };
     const int s1 = g0 + cb / 16;
     int s = g0;
     for (; s + 4 <= s1; s += 4) {
@@ -502,19 +623,20 @@ __device__ __forceinline__ void chunk_q4(const LaneGeo<NT>& L, uint32_t sw, int 
                 lo2[rb] = __half2float(__ushort_as_half((uint16_t)(u & 1 ? wl >> 16 : wl & 0xFFFFu)));
                 hi2[rb] = __half2float(__ushort_as_half((uint16_t)(u & 1 ? wh >> 16 : wh & 0xFFFFu)));
             }
-            step(s + u, acc[u & 1], lo2, hi2, w_grp + w_xor[u]);
+            block_q4<NT>(L, s + u, acc[u % SETS], lo2, hi2, w_grp + w_xor[u]);
         }
     }
     for (; s < s1; ++s) {
-        float lo2[2], hi2[2];
-#pragma unroll
-        for (int rb = 0; rb < 2; ++rb) {
-            lo2[rb] = __half2float(__ushort_as_half(*reinterpret_cast<const uint16_t*>(sc_rb[rb] + (s - g0) * 2)));
-            hi2[rb] = __half2float(__ushort_as_half(*reinterpret_cast<const uint16_t*>(sc_rb[rb] + 8 * sstr + (s - g0) * 2)));
+        const int u = s - g0;
+        if (SETS == 2) {
+            if (u & 1) block_q4_at<NT>(L, sw, c, kcb, u, acc[1], sc_rb, sstr);
+            else block_q4_at<NT>(L, sw, c, kcb, u, acc[0], sc_rb, sstr);
+        } else {
+            if ((u & 3) == 0) block_q4_at<NT>(L, sw, c, kcb, u, acc[0], sc_rb, sstr);
+            else if ((u & 3) == 1) block_q4_at<NT>(L, sw, c, kcb, u, acc[1 % SETS], sc_rb, sstr);
+            else if ((u & 3) == 2) block_q4_at<NT>(L, sw, c, kcb, u, acc[2 % SETS], sc_rb, sstr);
+            else block_q4_at<NT>(L, sw, c, kcb, u, acc[3 % SETS], sc_rb, sstr);
         }
-        const uint32_t wa = L.piece_addr(sw, L.aq_off, (uint32_t)(s - g0));
-        if (s & 1) step(s, acc[1], lo2, hi2, wa);
-        else step(s, acc[0], lo2, hi2, wa);
     }
 }
 

@@ -46,22 +46,23 @@ SHAPES = {
 }
 
 
-@pytest.mark.parametrize("fmt", ["int8", "fp16", "q4"])
-@pytest.mark.parametrize("wiring", ["fixed", "fixed+norm", "chained+norm"])
-@pytest.mark.parametrize("shape_name", ["smollm2", "lfm2", "qwen"])
+CASES = [("lfm2", f, w) for f in ("int8", "fp16", "q4") for w in ("fixed", "fixed+norm", "chained+norm")] + \
+        [(s, f, w) for s in ("smollm2", "qwen") for f in ("int8", "fp16") for w in ("fixed", "chained+norm")]
+
+
+@pytest.mark.parametrize("shape_name,fmt,wiring", CASES)
 def test_resident_replay_equals_separate_launches(nnb, ctx, fmt, wiring, shape_name):
     synth, dstep = _mods()
     H, Q, KV, F, V = SHAPES[shape_name]
-    if fmt == "q4" and H % 256:
-        pytest.skip("Q4 block scales travel by tensor copies only when K is a multiple of 256")
     layers = 3
     shape = synth.ModelShape(shape_name, H, layers, Q, KV, F, V)
-    step = dstep.DecodeStep(ctx, shape, fmt, M=1, n_sets=1, keep_host=True, norm="norm" in wiring, chained="chained" in wiring)
+    step = dstep.DecodeStep(ctx, shape, fmt, M=1, n_sets=1, norm="norm" in wiring, chained="chained" in wiring)
     _poison(ctx, step)
     step.enqueue(0)
     ctx.sync()
     eager = _snapshot(ctx, step)
-    assert eager["token"] == cpu.argmax_half(eager["logits"].view(np.float16))
+    lg = eager["logits"].view(np.float16).astype(np.float32).reshape(-1)
+    assert np.isfinite(lg).all() and eager["token"] == int(np.argmax(lg))
     step.record()
     plan = step.plans[0]
     assert ctx.L.nn_plan_num_recorded(plan) == 4 * layers + 1
@@ -77,6 +78,9 @@ def test_resident_replay_equals_separate_launches(nnb, ctx, fmt, wiring, shape_n
         got = _snapshot(ctx, step)
         for key in eager:
             assert np.array_equal(got[key], eager[key]), f"{key} differs from the separate launches (replay {rep})"
+    for st in step.sets:
+        for w in st.values():
+            w.release()
 
 
 @pytest.mark.parametrize("fmt", ["int8", "fp16", "q4"])
