@@ -82,7 +82,7 @@ __device__ __forceinline__ int ring_place(int& head, int bytes, int ring_bytes) 
     return off;
 }
 
-constexpr int PCW = KPARTS / 2;           // consumer warps of the resident kernel: two K parts of a split tile each
+constexpr int PCW = KPARTS;               // consumer warps of the resident kernel: one per K part of a split tile
 constexpr int PTHREADS = PCW * 32;        // consumer threads
 constexpr int PLAN_BLOCK = PTHREADS + 32; // + the producer warp
 static_assert(PLAN_BLOCK == DECODE_PLAN_THREADS, "block size");
@@ -238,10 +238,9 @@ __device__ __forceinline__ uint16_t poll_row(const PlanParams& P, CState& S, con
 }
 
 // One operator on the consumer warps.  D lives in shared memory.
-// WIDE: the operator's tiles split K (few rows): sixteen K parts per tile, one per consumer warp
-// (stream_core.cuh: "Accumulator sets"), int8 on plain fp16 activations.  Otherwise the first NCW
-// warps each stream whole rows of a tile, exactly as the separate launch does, and the others only
-// keep step with the ring.
+// WIDE: the operator's tiles split K (few rows): eight K parts per tile, one per consumer warp
+// (stream_core.cuh: "K parts").  Otherwise the first NCW warps each stream whole rows of a tile,
+// exactly as the separate launch does, and the others only keep step with the ring.
 // (The two-weight epilogue is a run-time property: the operators of a layer then share one copy of
 // the code, which matters because each runs only once per layer and instruction fetch is not free.)
 template <int FMT, bool WIDE>
@@ -268,9 +267,8 @@ __device__ __noinline__ void run_op(const PlanParams& P, const PlanOpScalars& D,
     uint8_t* xs = smem + P.off_xs;
     float* red = reinterpret_cast<float*>(smem + P.off_red);
 
-    // WIDE: warp = 2 * quarter + half: chunk `quarter` of every item, units sub, sub + 4, ... and
-    // sub + 1, sub + 5, ... of the chunk (K parts 4 * quarter + sub and + 1), sub = 2 * half
-    const int quarter = WIDE ? warp >> 1 : warp, sub = (warp & 1) * 2;
+    // WIDE: warp = 2 * quarter + set: chunk `quarter` of every item, units set, set + 2, ... of the chunk
+    const int quarter = WIDE ? warp >> 1 : warp, set = warp & 1;
     const bool worker = WIDE || warp < NCW;           // has arithmetic to do
     const int wrow_off = WIDE ? 0 : warp * warp_rows;
     const bool writer = WIDE ? warp == 0 : warp < NCW;  // finishes rows
@@ -296,9 +294,9 @@ __device__ __noinline__ void run_op(const PlanParams& P, const PlanOpScalars& D,
     if (tile_first < ntiles) fetch_res(tile_first);
 
     // ... what a tile needs besides its weights and the activations
-    constexpr int SETS = 2;  // WIDE: one per K part of this warp
-    constexpr bool IMMA = FMT == FMT_INT8 && !WIDE;
-    float acc[2][2][1][4];
+    constexpr int SETS = WIDE ? 1 : 2;
+    constexpr bool IMMA = FMT == FMT_INT8;
+    float acc[2][2][1][4];  // WIDE uses set 0 only
     int iacc[IMMA ? 3 : 1][2][1][4];
     unsigned long long am_best = 0ull;
     uint16_t sc1 = 0, res1 = 0;
@@ -360,11 +358,10 @@ __device__ __noinline__ void run_op(const PlanParams& P, const PlanOpScalars& D,
     if (tile_first < ntiles) claim_item(off_first, slot_first);
 
     // ---------------- activations: fetch (poll the producer's words), normalise, stage ----------------
-    // fp16 weights, and int8 weights of few-row operators (stream_core.cuh: step_int8_direct), multiply
-    // the activations as a plain fp16 row: when the row is in shared memory already (fetched from another
-    // operator, or normalised) it is used where it lies and nothing is staged.
-    constexpr bool plain = FMT == FMT_FP16 || (FMT == FMT_INT8 && WIDE);
-    constexpr int mode = FMT * 2 + ((FMT == FMT_INT8 && WIDE) ? 1 : 0);
+    // fp16 weights multiply the activations as a plain fp16 row: when the row is in shared memory already
+    // (fetched from another operator, or normalised) it is used where it lies and nothing is staged.
+    constexpr bool plain = FMT == FMT_FP16;
+    constexpr int mode = FMT;
     const void* src_id = D.x_ll ? (const void*)D.x_ll : (const void*)D.x;
     const unsigned x_epoch = D.x_ll ? S.ebase + (unsigned)D.x_epoch : 0u;
     const bool reuse = S.st_src == src_id && S.st_epoch == x_epoch && S.st_fmt == mode && S.st_norm == (const void*)D.norm_w;
@@ -374,7 +371,6 @@ __device__ __noinline__ void run_op(const PlanParams& P, const PlanOpScalars& D,
     LaneGeo<1> lg;
     lane_geo_init<FMT, 1>(lg, DUAL, quarter, lane, 1, x_addr, xstride, s_base, smem + P.off_ctab);
     const float* rowscale = reinterpret_cast<const float*>(xs + 3 * xstride + 64);
-    const uint32_t xrow[1] = {g == 0 ? x_addr : s_base}, xstep[1] = {g == 0 ? 1u : 0u};  // int8 direct: token 0 is column g == 0
     if (!reuse) {
         const uint16_t* x_src = D.x;
         // ... and the norm weight, which goes to shared memory
@@ -440,19 +436,14 @@ __device__ __noinline__ void run_op(const PlanParams& P, const PlanOpScalars& D,
             if constexpr (FMT == FMT_FP16) {
                 if constexpr (WIDE) {
                     const int s0 = (c * kcb) / 64;
-                    for (int u = sub; u < cb / 64; u += 4) {
-                        step_fp16<1>(lg, sw, s0 + u, u, acc[0]);
-                        if (u + 1 < cb / 64) step_fp16<1>(lg, sw, s0 + u + 1, u + 1, acc[1]);
-                    }
+                    for (int u = set; u < cb / 64; u += 2) step_fp16<1>(lg, sw, s0 + u, u, acc[0]);
                 } else {
-                    chunk_fp16<1, 2>(lg, sw, c, kcb, cb, acc);
+                    chunk_fp16<1>(lg, sw, c, kcb, cb, acc);
                 }
             } else if constexpr (FMT == FMT_INT8) {
                 if constexpr (WIDE) {
-                    for (int u = sub; u < cb / 64; u += 4) {
-                        step_int8_direct<1>(lg, sw, c * kcb + u * 64, u, xrow, xstep, acc[0]);
-                        if (u + 1 < cb / 64) step_int8_direct<1>(lg, sw, c * kcb + (u + 1) * 64, u + 1, xrow, xstep, acc[1]);
-                    }
+                    const int s0 = (c * kcb) / 64;
+                    for (int u = set; u < cb / 64; u += 2) step_int8<1>(lg, sw, s0 + u, u, iacc);
                 } else {
                     chunk_int8<1>(lg, sw, c, kcb, cb, iacc);
                 }
@@ -465,12 +456,9 @@ __device__ __noinline__ void run_op(const PlanParams& P, const PlanOpScalars& D,
                 const uint8_t* scb = smem + ring_off + off + nbox * CTA_BOX;
                 const uint8_t* const sc_rb[2] = {scb + (srow0 + g) * sstr, scb + (srow1 + g) * sstr};
                 if constexpr (WIDE) {
-                    for (int u = sub; u < cb / 16; u += 4) {
-                        block_q4_at<1>(lg, sw, c, kcb, u, acc[0], sc_rb, sstr);
-                        if (u + 1 < cb / 16) block_q4_at<1>(lg, sw, c, kcb, u + 1, acc[1], sc_rb, sstr);
-                    }
+                    for (int u = set; u < cb / 16; u += 2) block_q4_at<1>(lg, sw, c, kcb, u, acc[0], sc_rb, sstr);
                 } else {
-                    chunk_q4<1, 2>(lg, sw, c, kcb, cb, acc, sc_rb, sstr);
+                    chunk_q4<1>(lg, sw, c, kcb, cb, acc, sc_rb, sstr);
                 }
             }
             __syncwarp();
@@ -482,27 +470,55 @@ __device__ __noinline__ void run_op(const PlanParams& P, const PlanOpScalars& D,
         //      row block.  Row L of the tile is finished by lane L of the warp that holds its sum. ----
         float v0, v1 = 0.f;  // v1: the second weight's sum (two-weight epilogue)
         if constexpr (WIDE) {
-            // the sixteen K parts meet in shared memory and are added in part order
-            float* buf = red + (S.ti & 1) * (KPARTS * 32);
-            if (t == 0) {
-#pragma unroll
-                for (int i = 0; i < 2; ++i) {
-                    float* mine = buf + (warp * 2 + i) * 32 + g;
-                    mine[0] = acc[i][0][0][0];
-                    mine[8] = acc[i][0][0][2];
-                    mine[16] = acc[i][1][0][0];
-                    mine[24] = acc[i][1][0][2];
-                }
-            }
-            consumers_sync();
+            // The eight K parts meet in shared memory.  Per consumer of the separate launch (quarter) the
+            // two sets are added first, then the quarters in order; int8 parts are exact integer limb
+            // sums, added as integers and turned into a float once per quarter, as that consumer does.
             const int r0 = DUAL ? (lane & 15) : lane;
-            v0 = buf[r0];
+            if constexpr (IMMA) {
+                int* ibuf = reinterpret_cast<int*>(red) + (S.ti & 1) * (KPARTS * 3 * 32);
+                if (t == 0) {
 #pragma unroll
-            for (int p = 1; p < KPARTS; ++p) v0 += buf[p * 32 + r0];
-            if (DUAL) {
-                v1 = buf[16 + r0];
+                    for (int l = 0; l < 3; ++l) {
+                        int* mine = ibuf + (warp * 3 + l) * 32 + g;
+                        mine[0] = iacc[l][0][0][0];
+                        mine[8] = iacc[l][0][0][2];
+                        mine[16] = iacc[l][1][0][0];
+                        mine[24] = iacc[l][1][0][2];
+                    }
+                }
+                consumers_sync();
+                auto quarter_sum = [&](int q, int r) {
+                    const int* a = ibuf + (2 * q) * 3 * 32 + r;
+                    const int* b2 = a + 3 * 32;
+                    const float f = fmaf((float)(a[0] + b2[0]), 65536.f, fmaf((float)(a[32] + b2[32]), 256.f, (float)(a[64] + b2[64])));
+                    return f * rowscale[0] + 0.f;  // (+ 0: the consumer adds its empty second set)
+                };
+                v0 = quarter_sum(0, r0);
 #pragma unroll
-                for (int p = 1; p < KPARTS; ++p) v1 += buf[p * 32 + 16 + r0];
+                for (int q = 1; q < NCW; ++q) v0 += quarter_sum(q, r0);
+                if (DUAL) {
+                    v1 = quarter_sum(0, 16 + r0);
+#pragma unroll
+                    for (int q = 1; q < NCW; ++q) v1 += quarter_sum(q, 16 + r0);
+                }
+            } else {
+                float* buf = red + (S.ti & 1) * (KPARTS * 32);
+                if (t == 0) {
+                    float* mine = buf + warp * 32 + g;
+                    mine[0] = acc[0][0][0][0];
+                    mine[8] = acc[0][0][0][2];
+                    mine[16] = acc[0][1][0][0];
+                    mine[24] = acc[0][1][0][2];
+                }
+                consumers_sync();
+                v0 = buf[r0] + buf[32 + r0];
+#pragma unroll
+                for (int q = 1; q < NCW; ++q) v0 += buf[(2 * q) * 32 + r0] + buf[(2 * q + 1) * 32 + r0];
+                if (DUAL) {
+                    v1 = buf[16 + r0] + buf[32 + 16 + r0];
+#pragma unroll
+                    for (int q = 1; q < NCW; ++q) v1 += buf[(2 * q) * 32 + 16 + r0] + buf[(2 * q + 1) * 32 + 16 + r0];
+                }
             }
         } else {
             if constexpr (IMMA) int8_recombine<1>(iacc, acc[0], rowscale, 1, t);

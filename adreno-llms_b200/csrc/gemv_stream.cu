@@ -274,27 +274,12 @@ __global__ void __launch_bounds__(THREADS) linear_stream_kernel(const __grid_con
     LaneGeo<NT> lg;
     lane_geo_init<FMT, NT>(lg, DUAL, warp, lane, aM, smem_u32(xs), geo.xstride, zero_addr, smem + geo.off_ctab);
     const float* rowscale = reinterpret_cast<const float*>(xs + 3 * aM * geo.xstride + 64);
-    // int8 operators with few rows take the activations as plain fp16 rows (stream_core.cuh: chunk_int8_direct)
-    const bool int8_direct = FMT == FMT_INT8 && ksplit;
-    const int xstride_d = aK * 2 + 16;
-    uint32_t xrow[NT], xstep[NT];
-#pragma unroll
-    for (int nt = 0; nt < NT; ++nt) {
-        const int tok = g + nt * 8;
-        xrow[nt] = tok < aM ? smem_u32(xs) + (uint32_t)(tok * xstride_d) : zero_addr;
-        xstep[nt] = tok < aM ? 1u : 0u;
-    }
 
     // rows of this warp inside its tile, and which warp writes results
     const int wrow_off = ksplit ? 0 : warp * warp_rows;
     const bool writer = !ksplit || warp == 0;
 
-    // [accumulator set][row block][n tile][frag]; a single token whose tile splits K over the
-    // consumers uses four sets = sixteen K parts per tile (stream_core.cuh: "Accumulator sets")
-    constexpr int SETS = ONE ? 4 : 2;
-    float acc[SETS][2][NT][4];
-    float (&acc2)[2][2][NT][4] = reinterpret_cast<float (&)[2][2][NT][4]>(acc);
-    const bool wide = ONE && ksplit && !sk;
+    float acc[2][2][NT][4];      // [accumulator set][row block][n tile][frag]
     int iacc[FMT == FMT_INT8 ? 3 : 1][2][NT][4];  // int8: exact integer sums per activation limb
     // Prefetched epilogue operands stay as raw fp16 bits until they are used, so that the
     // loads' latency is not waited for where they are issued.
@@ -408,8 +393,7 @@ __global__ void __launch_bounds__(THREADS) linear_stream_kernel(const __grid_con
         rmsnorm_rows(a.x, a.norm_w, a.norm_eps, aM, aK, xn, red, tid, lane, warp);
         x_src = xn;
     }
-    if (int8_direct) stage_x<FMT_FP16>(x_src, aM, aK, xs, xstride_d, nullptr, tid, NCW * 32);
-    else if (FMT == FMT_INT8) stage_x_int8(x_src, aM, aK, xs, geo.xstride, tid, NCW * 32);
+    if (FMT == FMT_INT8) stage_x_int8(x_src, aM, aK, xs, geo.xstride, tid, NCW * 32);
     else stage_x<FMT>(x_src, aM, aK, xs, geo.xstride, reinterpret_cast<float*>(smem + geo.off_ctab), tid, NCW * 32);
     asm volatile("bar.sync 1, %0;" ::"n"(NCW * 32) : "memory");
 
@@ -424,7 +408,7 @@ __global__ void __launch_bounds__(THREADS) linear_stream_kernel(const __grid_con
         if (cg == 0 || it == 0) {
             seg_has_head = (cg == 0);
 #pragma unroll
-            for (int u = 0; u < SETS; ++u)
+            for (int u = 0; u < 2; ++u)
 #pragma unroll
                 for (int rb = 0; rb < 2; ++rb)
 #pragma unroll
@@ -460,12 +444,9 @@ __global__ void __launch_bounds__(THREADS) linear_stream_kernel(const __grid_con
         const int cb = (failed || !active) ? 0 : min(kcb, rowbytes - c * kcb);
 
         if constexpr (FMT == FMT_FP16) {
-            if (ONE && wide) chunk_fp16<NT, SETS>(lg, sw, c, kcb, cb, acc);
-            else chunk_fp16<NT, 2>(lg, sw, c, kcb, cb, acc2);
+            chunk_fp16<NT>(lg, sw, c, kcb, cb, acc);
         } else if constexpr (FMT == FMT_INT8) {
-            if (ONE && wide) chunk_int8_direct<NT, SETS>(lg, sw, c, kcb, cb, xrow, xstep, acc);
-            else if (int8_direct) chunk_int8_direct<NT, 2>(lg, sw, c, kcb, cb, xrow, xstep, acc2);
-            else chunk_int8<NT>(lg, sw, c, kcb, cb, iacc);
+            chunk_int8<NT>(lg, sw, c, kcb, cb, iacc);
         } else {
             // scale rows of this warp's two row blocks inside the stage's scale region: the
             // cp.async path keeps each warp's 32 rows together; tensor copies land whole boxes,
@@ -475,8 +456,7 @@ __global__ void __launch_bounds__(THREADS) linear_stream_kernel(const __grid_con
             const int srow1 = (ka.scale_tma && DUAL) ? NCW * WARP_ROWS / 2 + warp * (WARP_ROWS / 2) : warp * WARP_ROWS + 16;
             const uint8_t* scb = smem + (sw - s_base) + geo.nbox * CTA_BOX;
             const uint8_t* const sc_rb[2] = {scb + (srow0 + g) * sstr, scb + (srow1 + g) * sstr};
-            if (ONE && wide) chunk_q4<NT, SETS>(lg, sw, c, kcb, cb, acc, sc_rb, sstr);
-            else chunk_q4<NT, 2>(lg, sw, c, kcb, cb, acc2, sc_rb, sstr);
+            chunk_q4<NT>(lg, sw, c, kcb, cb, acc, sc_rb, sstr);
         }
 
         // hand the stage back to the producer
@@ -489,47 +469,16 @@ __global__ void __launch_bounds__(THREADS) linear_stream_kernel(const __grid_con
         if (!seg_end) continue;
         ++ti;
 
-        if constexpr (FMT == FMT_INT8) {
-            if (!int8_direct) int8_recombine<NT>(iacc, acc[0], rowscale, aM, t);
-        }
+        if constexpr (FMT == FMT_INT8) int8_recombine<NT>(iacc, acc[0], rowscale, aM, t);
         // ---- tile finished: fold the two accumulator sets, combine the K parts (fixed
         //      order), then the epilogue ----
-        float wide_v0 = 0.f, wide_v1 = 0.f;  // wide: this lane's row (and the second weight's) summed over the sixteen parts
-        if (ONE && wide) {
-            // the token's results sit in the lanes with t == 0: rows g and g + 8 of each row block;
-            // warp w holds parts 4w .. 4w+3
-            float* buf = red + (ti & 1) * (KPARTS * 32);
-            if (t == 0) {
-#pragma unroll
-                for (int u = 0; u < SETS; ++u) {
-                    float* mine = buf + (warp * 4 + u) * 32 + g;
-                    mine[0] = acc[u][0][0][0];
-                    mine[8] = acc[u][0][0][2];
-                    mine[16] = acc[u][1][0][0];
-                    mine[24] = acc[u][1][0][2];
-                }
-            }
-            asm volatile("bar.sync 1, %0;" ::"n"(NCW * 32) : "memory");
-            if (warp == 0) {
-                const int r0 = DUAL ? (lane & 15) : lane;
-                wide_v0 = buf[r0];
-#pragma unroll
-                for (int p = 1; p < KPARTS; ++p) wide_v0 += buf[p * 32 + r0];
-                if (DUAL) {
-                    wide_v1 = buf[16 + r0];
-#pragma unroll
-                    for (int p = 1; p < KPARTS; ++p) wide_v1 += buf[p * 32 + 16 + r0];
-                }
-            }
-        } else {
 #pragma unroll
         for (int rb = 0; rb < 2; ++rb)
 #pragma unroll
             for (int nt = 0; nt < NT; ++nt)
 #pragma unroll
                 for (int i = 0; i < 4; ++i) acc[0][rb][nt][i] += acc[1][rb][nt][i];
-        }
-        if (ksplit && !(ONE && wide)) {
+        if (ksplit) {
             // partial sums meet in shared memory; the buffer alternates between tiles so one
             // barrier per tile is enough
             float* buf = red + (ti & 1) * (NCW * 32 * 2 * NT * 4);
@@ -619,7 +568,6 @@ __global__ void __launch_bounds__(THREADS) linear_stream_kernel(const __grid_con
                 const float g0 = __shfl_sync(0xffffffffu, acc[0][0][0][0], src), g1 = __shfl_sync(0xffffffffu, acc[0][0][0][2], src);
                 const float u0 = __shfl_sync(0xffffffffu, acc[0][1][0][0], src), u1 = __shfl_sync(0xffffffffu, acc[0][1][0][2], src);
                 float gv = hi ? g1 : g0, uv = hi ? u1 : u0;
-                if (ONE && wide) { gv = wide_v0; uv = wide_v1; }
                 const int n = tile * tile_rows + wrow_off + lane;
                 if (lane < 16 && n < seg_n) {
                     if (FMT == FMT_INT8) {
@@ -670,7 +618,6 @@ __global__ void __launch_bounds__(THREADS) linear_stream_kernel(const __grid_con
                 const float v00 = __shfl_sync(0xffffffffu, acc[0][0][0][0], src), v01 = __shfl_sync(0xffffffffu, acc[0][0][0][2], src);
                 const float v10 = __shfl_sync(0xffffffffu, acc[0][1][0][0], src), v11 = __shfl_sync(0xffffffffu, acc[0][1][0][2], src);
                 float v = sel == 0 ? v00 : sel == 1 ? v01 : sel == 2 ? v10 : v11;
-                if (ONE && wide) v = wide_v0;
                 const int n = row0 + lane;
                 if (n < seg_n) {
                     if (FMT == FMT_INT8) v *= __half2float(__ushort_as_half(sc1));

@@ -88,7 +88,7 @@ struct PlanParams {
 // decode_plan.cu
 cudaError_t decode_plan_configure();
 cudaError_t decode_plan_func(const void** func);   // the kernel's address, for a graph kernel node
-constexpr int DECODE_PLAN_THREADS = (8 + 1) * 32;  // eight consumer warps and the producer warp
+constexpr int DECODE_PLAN_THREADS = (8 + 1) * 32;  // eight consumer warps (one per K part of a split tile) and the producer warp
 
 // ---- host side (plan.cpp) ---------------------------------------------------------------------
 // What the recorder keeps of one streamed single-token operator.

@@ -44,8 +44,8 @@ __host__ __device__ inline int x_bytes_of(int fmt, int M, int K) {
 __host__ __device__ inline int ctab_bytes_of(int fmt, int M, int K) { return fmt == FMT_Q4 ? (K / 32) * ((M + 1) / 2) * 16 : 0; }
 // two reduction buffers for the consumers that split K of one tile
 __host__ __device__ inline int red_bytes_of(int nt) { return 2 * NCW * 32 * 2 * nt * 4 * 4; }
-// K parts of a tile whose K is split, one token (see "Accumulator sets" below)
-constexpr int KPARTS = 4 * NCW;
+// K parts of a tile whose K is split over the consumers (see "K parts" below)
+constexpr int KPARTS = 2 * NCW;
 
 // int8 weights are multiplied on the integer tensor-core path, with no conversion of the
 // weights at all: each activation row is turned into 24-bit fixed point
@@ -383,14 +383,15 @@ __device__ __forceinline__ void lane_geo_init(LaneGeo<NT>& L, bool two_weights, 
     }
 }
 
-// Accumulator sets.  A consumer keeps SETS independent fp32 accumulators and deals the units of a K
-// chunk (fp16 / int8-direct: 64-byte steps; Q4: 32-weight blocks) out to them in turn, unit u of the
-// chunk to set u mod SETS, so that consecutive MMAs do not wait for one another.  Rows streamed whole
-// by one warp use two sets and add them at the end.  Tiles whose K is split over the four consumers
-// (few-row operators, one token) use four: that makes sixteen K parts per tile, part 4 * (chunk mod 4)
-// + (unit mod 4), each summed in unit order and added in part order at the end.  The resident kernel
-// gives every part a warp of its own (step_fp16 / step_int8_direct / block_q4 below) and adds the
-// parts in the same order, hence the same bits.
+// K parts.  A consumer keeps two independent fp32 accumulators and deals the units of a K chunk
+// (fp16: 64-byte steps; Q4: 32-weight blocks) out to them in turn, unit u of the chunk to set u mod 2,
+// so that consecutive MMAs do not wait for one another; at the end of a tile it adds set 1 to set 0.
+// A tile whose K is split over the four consumers (few-row operators) therefore is the sum of eight
+// K parts, part 2 * (chunk mod 4) + (unit mod 2): each consumer's two sets added first, then the four
+// consumers' sums in consumer order.  The resident kernel (decode_plan.cu) gives every part a warp of
+// its own, built from the same unit functions below (step_fp16 / step_int8 / block_q4_at), and adds
+// the parts in the same order, hence the same bits.  int8 sums are exact integers until the tile's
+// end, so how a consumer's steps are dealt out does not matter there.
 
 // fp16: one step = 64 bytes of each row = 32 k = two MMAs per row block.  `s` counts steps from the
 // start of the row (it addresses the activations), `s_in_chunk` from the start of the chunk.
@@ -416,117 +417,48 @@ __device__ __forceinline__ void step_fp16(const LaneGeo<NT>& L, uint32_t sw, int
                 mma_16816(ac[rb][nt], av[rb][h][0], av[rb][h][1], av[rb][h][2], av[rb][h][3], b[nt][2 * h], b[nt][2 * h + 1]);
 }
 // K chunk c (kcb bytes of every row, cb of them valid) of the stage at `sw`.
-template <int NT, int SETS>
-__device__ __forceinline__ void chunk_fp16(const LaneGeo<NT>& L, uint32_t sw, int c, int kcb, int cb, float (&acc)[SETS][2][NT][4]) {
+template <int NT>
+__device__ __forceinline__ void chunk_fp16(const LaneGeo<NT>& L, uint32_t sw, int c, int kcb, int cb, float (&acc)[2][2][NT][4]) {
     const int s0 = (c * kcb) / 64, ns = cb / 64;
-    if (SETS == 2) {
-        int u = 0;
-        for (; u + 2 <= ns; u += 2) {
-            step_fp16<NT>(L, sw, s0 + u, u, acc[0]);
-            step_fp16<NT>(L, sw, s0 + u + 1, u + 1, acc[1]);
-        }
-        if (u < ns) step_fp16<NT>(L, sw, s0 + u, u, acc[0]);
-    } else {
-        int u = 0;
-        for (; u + 4 <= ns; u += 4) {
-#pragma unroll
-            for (int i = 0; i < 4; ++i) step_fp16<NT>(L, sw, s0 + u + i, u + i, acc[i % SETS]);
-        }
-#pragma unroll
-        for (int i = 0; i < 3; ++i)
-            if (u + i < ns) step_fp16<NT>(L, sw, s0 + u + i, u + i, acc[i % SETS]);
+    int u = 0;
+    for (; u + 2 <= ns; u += 2) {
+        step_fp16<NT>(L, sw, s0 + u, u, acc[0]);
+        step_fp16<NT>(L, sw, s0 + u + 1, u + 1, acc[1]);
     }
+    if (u < ns) step_fp16<NT>(L, sw, s0 + u, u, acc[0]);
 }
 
 // int8: one step = 64 bytes of each row = 64 k = two integer MMAs (k32) per row block and
-// activation limb; the weights go from ldmatrix straight into the MMA.
+// activation limb; the weights go from ldmatrix straight into the MMA.  `s` counts steps from the
+// start of the row (it addresses the activations), `s_in_chunk` from the start of the chunk.
+template <int NT>
+__device__ __forceinline__ void step_int8(const LaneGeo<NT>& L, uint32_t sw, int s, int s_in_chunk, int (&iacc)[3][2][NT][4]) {
+    uint32_t b[3][NT][4];
+#pragma unroll
+    for (int l = 0; l < 3; ++l)
+#pragma unroll
+        for (int nt = 0; nt < NT; ++nt)
+            ldsm_x4(L.b_base[nt] + l * L.b_plane[nt] + s * L.b_step[nt], b[l][nt][0], b[l][nt][1], b[l][nt][2], b[l][nt][3]);
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+        const uint32_t q = (uint32_t)s_in_chunk * 4 + 2 * h + L.a_q_lane;
+#pragma unroll
+        for (int rb = 0; rb < 2; ++rb) {
+            uint32_t w0, w1, w2, w3;
+            ldsm_x4(L.piece_addr(sw, (rb ? L.rb_base1 : L.rb_base0) + L.a_row_off, q), w0, w1, w2, w3);
+#pragma unroll
+            for (int nt = 0; nt < NT; ++nt) {
+                imma_16832<true>(iacc[0][rb][nt], w0, w1, w2, w3, b[0][nt][2 * h], b[0][nt][2 * h + 1]);
+                imma_16832<false>(iacc[1][rb][nt], w0, w1, w2, w3, b[1][nt][2 * h], b[1][nt][2 * h + 1]);
+                imma_16832<false>(iacc[2][rb][nt], w0, w1, w2, w3, b[2][nt][2 * h], b[2][nt][2 * h + 1]);
+            }
+        }
+    }
+}
 template <int NT>
 __device__ __forceinline__ void chunk_int8(const LaneGeo<NT>& L, uint32_t sw, int c, int kcb, int cb, int (&iacc)[3][2][NT][4]) {
     const int s0 = (c * kcb) / 64;
-    for (int s = 0; s < cb / 64; ++s) {
-        uint32_t b[3][NT][4];
-#pragma unroll
-        for (int l = 0; l < 3; ++l)
-#pragma unroll
-            for (int nt = 0; nt < NT; ++nt)
-                ldsm_x4(L.b_base[nt] + l * L.b_plane[nt] + (s0 + s) * L.b_step[nt], b[l][nt][0], b[l][nt][1], b[l][nt][2], b[l][nt][3]);
-#pragma unroll
-        for (int h = 0; h < 2; ++h) {
-            const uint32_t q = (uint32_t)s * 4 + 2 * h + L.a_q_lane;
-#pragma unroll
-            for (int rb = 0; rb < 2; ++rb) {
-                uint32_t w0, w1, w2, w3;
-                ldsm_x4(L.piece_addr(sw, (rb ? L.rb_base1 : L.rb_base0) + L.a_row_off, q), w0, w1, w2, w3);
-#pragma unroll
-                for (int nt = 0; nt < NT; ++nt) {
-                    imma_16832<true>(iacc[0][rb][nt], w0, w1, w2, w3, b[0][nt][2 * h], b[0][nt][2 * h + 1]);
-                    imma_16832<false>(iacc[1][rb][nt], w0, w1, w2, w3, b[1][nt][2 * h], b[1][nt][2 * h + 1]);
-                    imma_16832<false>(iacc[2][rb][nt], w0, w1, w2, w3, b[2][nt][2 * h], b[2][nt][2 * h + 1]);
-                }
-            }
-        }
-    }
-}
-
-// int8 for operators with few rows (the consumers split K of one tile): such operators are bound by
-// latency, not by the weight stream, and turning the activations into fixed-point limb planes costs
-// more than the whole dot product.  Here the weights are converted to exact fp16 integers in registers
-// and multiplied with the fp16 activations as they are (fp32 accumulation of exact products).
-// One ldmatrix.x4 yields 16 rows x 32 k: lane (g, t) holds k 4t .. 4t+3 of rows g and g + 8 of two
-// 16-byte pieces.  The two k16 MMAs per load take those four k as the fragment's (2t, 2t+1) and
-// (2t+8, 2t+9) columns, so the B operand of lane (g, t) is simply x[token g][k0 + 4t .. 4t+3]: one
-// 8-byte shared-memory load from the token's plain fp16 row, no permuted copy.
-// xrow[nt] = shared-memory address of this lane's token row (a row of zeros, with xstep 0, for absent
-// tokens).  One step = 64 bytes of each row = two such loads per row block = four MMAs per row block;
-// `k` = first k of the step counted from the start of the row, `s_in_chunk` = step inside the chunk.
-template <int NT>
-__device__ __forceinline__ void step_int8_direct(const LaneGeo<NT>& L, uint32_t sw, int k, int s_in_chunk, const uint32_t (&xrow)[NT],
-                                                 const uint32_t (&xstep)[NT], float (&ac)[2][NT][4]) {
-    const int t = (int)(threadIdx.x & 3);
-    uint32_t w[2][2][4];  // [32-byte half][row block]
-    uint32_t b[2][NT][4];
-    // all loads first: a warp may be alone on its scheduler, and nothing else would cover their latency
-#pragma unroll
-    for (int h = 0; h < 2; ++h) {
-        const uint32_t q = (uint32_t)(s_in_chunk * 2 + h) * 2 + L.a_q_lane;
-#pragma unroll
-        for (int rb = 0; rb < 2; ++rb)
-            ldsm_x4(L.piece_addr(sw, (rb ? L.rb_base1 : L.rb_base0) + L.a_row_off, q), w[h][rb][0], w[h][rb][1], w[h][rb][2], w[h][rb][3]);
-#pragma unroll
-        for (int nt = 0; nt < NT; ++nt) {
-            const uint32_t xa = xrow[nt] + (uint32_t)((k + h * 32 + 4 * t) * 2) * xstep[nt];
-            asm volatile("ld.shared.v2.b32 {%0, %1}, [%2];" : "=r"(b[h][nt][0]), "=r"(b[h][nt][1]) : "r"(xa));
-            asm volatile("ld.shared.v2.b32 {%0, %1}, [%2];" : "=r"(b[h][nt][2]), "=r"(b[h][nt][3]) : "r"(xa + 32u * xstep[nt]));
-        }
-    }
-#pragma unroll
-    for (int h = 0; h < 2; ++h)
-#pragma unroll
-        for (int rb = 0; rb < 2; ++rb) {
-            uint32_t a0, a2, a1, a3, c0, c2, c1, c3;
-            int8x4_to_half2x2(w[h][rb][0], a0, a2);  // rows g:     piece q
-            int8x4_to_half2x2(w[h][rb][1], a1, a3);  // rows g + 8: piece q
-            int8x4_to_half2x2(w[h][rb][2], c0, c2);  // rows g:     piece q + 1
-            int8x4_to_half2x2(w[h][rb][3], c1, c3);  // rows g + 8: piece q + 1
-#pragma unroll
-            for (int nt = 0; nt < NT; ++nt) {
-                mma_16816(ac[rb][nt], a0, a1, a2, a3, b[h][nt][0], b[h][nt][1]);
-                mma_16816(ac[rb][nt], c0, c1, c2, c3, b[h][nt][2], b[h][nt][3]);
-            }
-        }
-}
-template <int NT, int SETS>
-__device__ __forceinline__ void chunk_int8_direct(const LaneGeo<NT>& L, uint32_t sw, int c, int kcb, int cb, const uint32_t (&xrow)[NT],
-                                                  const uint32_t (&xstep)[NT], float (&acc)[SETS][2][NT][4]) {
-    const int k0 = c * kcb, ns = cb / 64;  // int8: one byte per k
-    int u = 0;
-    for (; u + SETS <= ns; u += SETS) {
-#pragma unroll
-        for (int i = 0; i < SETS; ++i) step_int8_direct<NT>(L, sw, k0 + (u + i) * 64, u + i, xrow, xstep, acc[i]);
-    }
-#pragma unroll
-    for (int i = 0; i < SETS - 1; ++i)
-        if (u + i < ns) step_int8_direct<NT>(L, sw, k0 + (u + i) * 64, u + i, xrow, xstep, acc[i]);
+    for (int s = 0; s < cb / 64; ++s) step_int8<NT>(L, sw, s0 + s, s, iacc);
 }
 
 // int8: recombine the limb sums, (hi * 2^16 + mid * 2^8 + lo) * 2^-p, in fp32, into acc
@@ -593,8 +525,8 @@ __device__ __forceinline__ void block_q4_at(const LaneGeo<NT>& L, uint32_t sw, i
     }
     block_q4<NT>(L, (c * kcb) / 16 + u, ac, lo2, hi2, L.piece_addr(sw, L.aq_off, (uint32_t)u));
 }
-template <int NT, int SETS>
-__device__ __forceinline__ void chunk_q4(const LaneGeo<NT>& L, uint32_t sw, int c, int kcb, int cb, float (&acc)[SETS][2][NT][4],
+template <int NT>
+__device__ __forceinline__ void chunk_q4(const LaneGeo<NT>& L, uint32_t sw, int c, int kcb, int cb, float (&acc)[2][2][NT][4],
                                          const uint8_t* const (&sc_rb)[2], int sstr) {
     const int g0 = (c * kcb) / 16;
     uint32_t w_xor[4];
@@ -623,20 +555,13 @@ __device__ __forceinline__ void chunk_q4(const LaneGeo<NT>& L, uint32_t sw, int 
                 lo2[rb] = __half2float(__ushort_as_half((uint16_t)(u & 1 ? wl >> 16 : wl & 0xFFFFu)));
                 hi2[rb] = __half2float(__ushort_as_half((uint16_t)(u & 1 ? wh >> 16 : wh & 0xFFFFu)));
             }
-            block_q4<NT>(L, s + u, acc[u % SETS], lo2, hi2, w_grp + w_xor[u]);
+            block_q4<NT>(L, s + u, acc[u & 1], lo2, hi2, w_grp + w_xor[u]);
         }
     }
     for (; s < s1; ++s) {
         const int u = s - g0;
-        if (SETS == 2) {
-            if (u & 1) block_q4_at<NT>(L, sw, c, kcb, u, acc[1], sc_rb, sstr);
-            else block_q4_at<NT>(L, sw, c, kcb, u, acc[0], sc_rb, sstr);
-        } else {
-            if ((u & 3) == 0) block_q4_at<NT>(L, sw, c, kcb, u, acc[0], sc_rb, sstr);
-            else if ((u & 3) == 1) block_q4_at<NT>(L, sw, c, kcb, u, acc[1 % SETS], sc_rb, sstr);
-            else if ((u & 3) == 2) block_q4_at<NT>(L, sw, c, kcb, u, acc[2 % SETS], sc_rb, sstr);
-            else block_q4_at<NT>(L, sw, c, kcb, u, acc[3 % SETS], sc_rb, sstr);
-        }
+        if (u & 1) block_q4_at<NT>(L, sw, c, kcb, u, acc[1], sc_rb, sstr);
+        else block_q4_at<NT>(L, sw, c, kcb, u, acc[0], sc_rb, sstr);
     }
 }
 
