@@ -64,6 +64,11 @@ def load():
         "nn_linear_silu_gate_fused": ([vp, i, i, i, vp, vp, vp], i),
         "nn_fused_gate_up_silu": ([vp, i, i, i, vp, vp, vp, vp], i),
         "nn_linear_qkv": ([vp, i, i, vp, vp, i, vp, i, vp, i, vp, vp, vp], i),
+        "nn_linear_qkv_bias": ([vp, i, i, vp, vp, i, vp, i, vp, i, vp, vp, vp, vp, vp, vp], i),
+        "nn_bias_add": ([vp, i, i, vp, vp], i),
+        "nn_bandwidth_probe": ([vp, sz, i, ctypes.POINTER(ctypes.c_double), ctypes.POINTER(ctypes.c_double)], i),
+        "nn_profile_enabled": ([vp], i), "nn_profile_report": ([vp, cp, sz, i], i),
+        "nn_profile_aggregate": ([i, ctypes.POINTER(cp), ctypes.POINTER(ctypes.c_double), cp, sz], i),
         "nn_dequant": ([vp, i, i, vp, vp], i), "nn_argmax": ([vp, i, vp, vp], i),
         "nn_argmax_static": ([vp, i, vp, vp], i),
         "nn_linear_argmax": ([vp, i, i, vp, vp, vp, vp], i),
@@ -91,6 +96,7 @@ def load():
         "nn_linear_gather": ([vp, i, i, i, vp, vp, vp], i),
         "nn_linear_argmax_sharded": ([vp, i, i, vp, vp, vp, vp], i),
         "nn_comm_signal": ([vp], i), "nn_comm_wait": ([vp, ctypes.c_uint], i),
+        "nn_comm_pick_unsent": ([vp, ctypes.c_uint, vp], i),
         "nn_device_count": ([], i),
     }
     for name, (args, res) in sig.items():
@@ -188,6 +194,29 @@ class Context:
 
     def linear_qkv(self, M, K, x, Wq, Nq, Wk, Nk, Wv, Nv, q, k, v):
         _check(self.L.nn_linear_qkv(self.h, M, K, x, Wq, Nq, Wk, Nk, Wv, Nv, q, k, v))
+
+    def linear_qkv_bias(self, M, K, x, Wq, Nq, Wk, Nk, Wv, Nv, bq, bk, bv, q, k, v):
+        _check(self.L.nn_linear_qkv_bias(self.h, M, K, x, Wq, Nq, Wk, Nk, Wv, Nv, bq, bk, bv, q, k, v))
+
+    def bias_add(self, rows, cols, out, bias):
+        _check(self.L.nn_bias_add(self.h, rows, cols, out, bias))
+
+    def bandwidth_probe(self, nbytes=0, trials=5):
+        """Best-of-trials read bandwidth in GB/s: (plain 16-byte loads, TMA bulk copies)."""
+        a, b = ctypes.c_double(), ctypes.c_double()
+        _check(self.L.nn_bandwidth_probe(self.h, nbytes, trials, ctypes.byref(a), ctypes.byref(b)))
+        return a.value, b.value
+
+    def profile_enabled(self):
+        return bool(self.L.nn_profile_enabled(self.h))
+
+    def profile_report(self, reset=False):
+        """The per-launch profile so far as the table nn_shutdown prints."""
+        buf = ctypes.create_string_buffer(1 << 16)
+        n = self.L.nn_profile_report(self.h, buf, len(buf), 1 if reset else 0)
+        if n < 0:
+            _check(n)
+        return buf.value.decode()
 
     def dequant(self, N, K, W, out):
         _check(self.L.nn_dequant(self.h, N, K, W, out))
@@ -304,6 +333,9 @@ class Comm:
 
     def linear_argmax_sharded(self, n_local, K, x, W, logits_local, out_idx):
         _check(self.ctx.L.nn_linear_argmax_sharded(self.h, n_local, K, x, W, logits_local, out_idx))
+
+    def pick_unsent(self, timeout_ms, out_idx):
+        _check(self.ctx.L.nn_comm_pick_unsent(self.h, timeout_ms, out_idx))
 
     def signal(self):
         _check(self.ctx.L.nn_comm_signal(self.h))

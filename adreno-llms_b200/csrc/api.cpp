@@ -6,6 +6,7 @@
 #include <cstdarg>
 #include <cstdio>
 #include <cstdlib>
+#include <algorithm>
 #include <cstring>
 #include <map>
 #include <string>
@@ -41,6 +42,112 @@ extern "C" const char* nn_version(void) { return "nnopt_b200 0.1 (sm_100a)"; }
         cudaError_t e_ = (call);                                                              \
         if (e_ != cudaSuccess) return NN_FAIL(NN_ERR_CUDA, "%s: %s", #call, cudaGetErrorString(e_)); \
     } while (0)
+
+// ---------------------------------------------------------------------------------
+// per-launch profile (NNOPT_KERNEL_PROFILE=1 or NNOPT_PROFILE=1)
+// ---------------------------------------------------------------------------------
+namespace {
+
+const char* fmt_name(int fmt) { return fmt == FMT_FP16 ? "fp16" : fmt == FMT_INT8 ? "int8" : "q4"; }
+
+// Labels in the reference's form, e.g. gemv_m1_K1024_N4608_int8 (utils.cpp:519 of the lfm2 port),
+// with the fused form appended.
+std::string op_label(int M, int N, int K, int fmt, const char* form) {
+    char b[96];
+    if (M == 1) snprintf(b, sizeof(b), "gemv_m1_K%d_N%d_%s%s", K, N, fmt_name(fmt), form);
+    else snprintf(b, sizeof(b), "gemm_M%d_K%d_N%d_%s%s", M, K, N, fmt_name(fmt), form);
+    return b;
+}
+
+struct ProfScope {  // event pair around whatever the scope enqueues
+    nn_context* c;
+    size_t slot = (size_t)-1;
+    ProfScope(nn_context* ctx, const std::string& label) : c(ctx) {
+        if (!c || !c->profiling || c->capturing) return;
+        ProfPending p;
+        p.label = label;
+        if (cudaEventCreate(&p.start) != cudaSuccess) return;
+        if (cudaEventCreate(&p.stop) != cudaSuccess) { cudaEventDestroy(p.start); return; }
+        cudaEventRecord(p.start, c->stream);
+        c->prof_pending.push_back(p);
+        slot = c->prof_pending.size() - 1;
+    }
+    ~ProfScope() {
+        if (slot != (size_t)-1) cudaEventRecord(c->prof_pending[slot].stop, c->stream);
+    }
+};
+
+void prof_add(std::map<std::string, ProfAgg>& agg, const std::string& label, double us) {
+    ProfAgg& a = agg[label];
+    a.count++;
+    a.total_us += us;
+    if (us > a.max_us) a.max_us = us;
+}
+
+void prof_collect(nn_context* c) {
+    if (c->prof_pending.empty()) return;
+    cudaStreamSynchronize(c->stream);
+    for (ProfPending& p : c->prof_pending) {
+        float ms = 0.f;
+        if (cudaEventElapsedTime(&ms, p.start, p.stop) == cudaSuccess) prof_add(c->prof, p.label, (double)ms * 1e3);
+        cudaEventDestroy(p.start);
+        cudaEventDestroy(p.stop);
+    }
+    c->prof_pending.clear();
+}
+
+// The table of the reference's dump, largest total first.
+std::string prof_format(const std::map<std::string, ProfAgg>& agg) {
+    std::vector<std::pair<std::string, ProfAgg>> rows(agg.begin(), agg.end());
+    std::sort(rows.begin(), rows.end(), [](const std::pair<std::string, ProfAgg>& a, const std::pair<std::string, ProfAgg>& b) {
+        return a.second.total_us != b.second.total_us ? a.second.total_us > b.second.total_us : a.first < b.first;
+    });
+    double grand = 0;
+    for (const auto& r : rows) grand += r.second.total_us;
+    char line[256];
+    std::string out = "=== KERNEL PROFILE (env NNOPT_KERNEL_PROFILE=1) ===\n";
+    snprintf(line, sizeof(line), "%-40s %12s %8s %12s %8s %8s\n", "label", "total_ms", "%total", "calls", "avg_us", "max_us");
+    out += line;
+    for (const auto& r : rows) {
+        const ProfAgg& a = r.second;
+        snprintf(line, sizeof(line), "%-40s %12.3f %7.2f%% %12llu %8.2f %8.2f\n", r.first.c_str(), a.total_us / 1e3,
+                 grand > 0 ? 100.0 * a.total_us / grand : 0.0, a.count, a.count ? a.total_us / (double)a.count : 0.0, a.max_us);
+        out += line;
+    }
+    snprintf(line, sizeof(line), "=== TOTAL GPU kernel time: %.3f ms ===\n", grand / 1e3);
+    out += line;
+    return out;
+}
+
+}  // namespace
+
+extern "C" int nn_profile_enabled(const nn_context* c) { return c && c->profiling ? 1 : 0; }
+
+extern "C" int nn_profile_report(nn_context* c, char* buf, size_t cap, int reset) {
+    if (!c) return NN_FAIL(NN_ERR_ARG, "nn_profile_report: null context");
+    prof_collect(c);
+    const std::string s = prof_format(c->prof);
+    if (buf && cap) {
+        const size_t n = s.size() < cap - 1 ? s.size() : cap - 1;
+        memcpy(buf, s.data(), n);
+        buf[n] = 0;
+    }
+    if (reset) c->prof.clear();
+    return (int)s.size();
+}
+
+extern "C" int nn_profile_aggregate(int n, const char* const* labels, const double* us, char* buf, size_t cap) {
+    if (n < 0 || (n && (!labels || !us))) return NN_FAIL(NN_ERR_ARG, "nn_profile_aggregate: bad argument");
+    std::map<std::string, ProfAgg> agg;
+    for (int i = 0; i < n; ++i) prof_add(agg, labels[i] ? labels[i] : "", us[i]);
+    const std::string s = prof_format(agg);
+    if (buf && cap) {
+        const size_t m = s.size() < cap - 1 ? s.size() : cap - 1;
+        memcpy(buf, s.data(), m);
+        buf[m] = 0;
+    }
+    return (int)s.size();
+}
 
 // ---------------------------------------------------------------------------------
 // context
@@ -100,6 +207,9 @@ extern "C" int nn_init(int device, nn_context** out) {
     }
     const char* pdl = getenv("NNB_PDL");
     c->use_pdl = !(pdl && pdl[0] == '0');
+    const char* kp = getenv("NNOPT_KERNEL_PROFILE");
+    const char* pp = getenv("NNOPT_PROFILE");
+    c->profiling = (kp && kp[0] == '1') || (pp && pp[0] == '1');
     *out = c;
     return NN_OK;
 }
@@ -108,6 +218,10 @@ extern "C" int nn_shutdown(nn_context* c) {
     if (!c) return NN_OK;
     cudaSetDevice(c->device);
     cudaStreamSynchronize(c->stream);
+    if (c->profiling) {  // the reference dumps its per-kernel table when the program ends
+        prof_collect(c);
+        if (!c->prof.empty()) fprintf(stderr, "\n%s\n", prof_format(c->prof).c_str());
+    }
     if (c->flush_buf) cudaFree(c->flush_buf);
     if (c->argmax_slot) cudaFree(c->argmax_slot);
     if (c->norm_scratch) cudaFree(c->norm_scratch);
@@ -412,6 +526,7 @@ static int one_weight(nn_context* c, int M, int N, int K, nn_buf x, nn_buf W, nn
     a.status = c->status_dev;
     a.norm_w = (const uint16_t*)gamma;
     a.norm_eps = eps;
+    ProfScope prof(c, op_label(M, N, K, r.fmt, epi == EPI_RESIDUAL ? "_add" : epi == EPI_SILU_GATE ? "_silu_gate" : gamma ? "_rmsnorm" : ""));
     if (npeer < 0 || npeer > 7) return NN_FAIL(NN_ERR_ARG, "%s: %d peers", who, npeer);
     a.npeer = npeer;
     for (int p = 0; p < npeer; ++p) a.peer_out[p] = peers[p];
@@ -460,6 +575,7 @@ static int gate_up_silu(nn_context* c, int M, int N, int K, nn_buf x, nn_buf Wg,
     a.status = c->status_dev;
     a.norm_w = (const uint16_t*)gamma;
     a.norm_eps = eps;
+    ProfScope prof(c, op_label(M, N, K, rg.fmt, gamma ? "_rmsnorm_swiglu" : "_swiglu"));
     return run_linear(c, rg.fmt, a, M, who);
 }
 
@@ -497,6 +613,7 @@ static int linear_qkv(nn_context* c, int M, int K, nn_buf x, nn_buf Wq, int Nq, 
     a.status = c->status_dev;
     a.norm_w = (const uint16_t*)gamma;
     a.norm_eps = eps;
+    ProfScope prof(c, op_label(M, Nq + Nk + Nv, K, fmt, gamma ? "_rmsnorm_qkv" : "_qkv"));
     return run_linear(c, fmt, a, M, who);
 }
 
@@ -505,10 +622,44 @@ extern "C" int nn_linear_qkv(nn_context* c, int M, int K, nn_buf x, nn_buf Wq, i
     return linear_qkv(c, M, K, x, Wq, Nq, Wk, Nk, Wv, Nv, q, k, v, nullptr, 0.f, "nn_linear_qkv");
 }
 
+extern "C" int nn_bias_add(nn_context* c, int rows, int cols, nn_buf out, nn_buf bias) {
+    if (!c || !out || !bias) return NN_FAIL(NN_ERR_ARG, "nn_bias_add: null argument");
+    if (rows < 0 || cols <= 0) return NN_FAIL(NN_ERR_ARG, "nn_bias_add: bad shape rows=%d cols=%d", rows, cols);
+    if (rows == 0) return NN_OK;
+    BiasArgs a = {};
+    a.out[0] = (uint16_t*)out;
+    a.bias[0] = (const uint16_t*)bias;
+    a.cols[0] = cols;
+    a.rows = rows;
+    a.nseg = 1;
+    ProfScope prof(c, "bias_add_rows" + std::to_string(rows) + "_cols" + std::to_string(cols));
+    CUDA_TRY(launch_bias_add(a, c->stream));
+    c->launches++;
+    return NN_OK;
+}
+
+extern "C" int nn_linear_qkv_bias(nn_context* c, int M, int K, nn_buf x, nn_buf Wq, int Nq, nn_buf Wk, int Nk, nn_buf Wv, int Nv,
+                                  nn_buf bq, nn_buf bk, nn_buf bv, nn_buf q, nn_buf k, nn_buf v) {
+    if (!bq || !bk || !bv) return NN_FAIL(NN_ERR_ARG, "nn_linear_qkv_bias: null bias");
+    int rc = linear_qkv(c, M, K, x, Wq, Nq, Wk, Nk, Wv, Nv, q, k, v, nullptr, 0.f, "nn_linear_qkv_bias");
+    if (rc || M == 0) return rc;
+    BiasArgs a = {};
+    a.out[0] = (uint16_t*)q; a.out[1] = (uint16_t*)k; a.out[2] = (uint16_t*)v;
+    a.bias[0] = (const uint16_t*)bq; a.bias[1] = (const uint16_t*)bk; a.bias[2] = (const uint16_t*)bv;
+    a.cols[0] = Nq; a.cols[1] = Nk; a.cols[2] = Nv;
+    a.rows = M;
+    a.nseg = 3;
+    ProfScope prof(c, "bias_add_qkv_rows" + std::to_string(M));
+    CUDA_TRY(launch_bias_add(a, c->stream));
+    c->launches++;
+    return NN_OK;
+}
+
 extern "C" int nn_rmsnorm(nn_context* c, int rows, int cols, nn_buf x, nn_buf weight, float eps, nn_buf out) {
     if (!c || !x || !weight || !out) return NN_FAIL(NN_ERR_ARG, "nn_rmsnorm: null argument");
     if (rows < 0 || cols <= 0) return NN_FAIL(NN_ERR_ARG, "nn_rmsnorm: bad shape rows=%d cols=%d", rows, cols);
     if (rows == 0) return NN_OK;
+    ProfScope prof(c, "rmsnorm_rows" + std::to_string(rows) + "_cols" + std::to_string(cols));
     CUDA_TRY(launch_rmsnorm((const uint16_t*)x, (const uint16_t*)weight, (uint16_t*)out, rows, cols, eps, c->stream));
     c->launches++;
     return NN_OK;
@@ -578,6 +729,7 @@ int nnb::linear_argmax(nn_context* c, int N, int K, nn_buf x, nn_buf W, nn_buf l
         if (rc) return rc;
         return nn_argmax(c, N, logits, out_idx);
     }
+    ProfScope prof(c, op_label(1, N, K, r.fmt, "_argmax"));
     a.argmax_slot = c->argmax_slot + 1;
     a.argmax_done = reinterpret_cast<unsigned*>(c->argmax_slot + 2);
     a.argmax_out = (int*)out_idx;
@@ -593,6 +745,7 @@ int nnb::linear_argmax(nn_context* c, int N, int K, nn_buf x, nn_buf W, nn_buf l
 extern "C" int nn_argmax(nn_context* c, int n, nn_buf logits, nn_buf out_idx) {
     if (!c || !logits || !out_idx) return NN_FAIL(NN_ERR_ARG, "nn_argmax: null argument");
     if (n < 0) return NN_FAIL(NN_ERR_ARG, "nn_argmax: n=%d", n);
+    ProfScope prof(c, "argmax_n" + std::to_string(n));
     CUDA_TRY(launch_argmax_half((const uint16_t*)logits, n, (int*)out_idx, c->argmax_slot, c->stream));
     c->launches += n > 0 ? 3 : 2;
     return NN_OK;
@@ -776,6 +929,7 @@ extern "C" int nn_plan_end(nn_context* c, nn_plan** out) {
 
 extern "C" int nn_plan_launch(nn_context* c, nn_plan* p) {
     if (!c || !p || !p->exec) return NN_FAIL(NN_ERR_ARG, "nn_plan_launch: null argument");
+    ProfScope prof(c, "plan_replay_" + std::to_string(p->recorded) + "ops_" + std::to_string(p->kernels) + "launches");
     CUDA_TRY(cudaGraphLaunch(p->exec, c->stream));
     c->launches += p->kernels;
     return NN_OK;
@@ -886,6 +1040,59 @@ extern "C" int nn_event_elapsed_ms(void* a, void* b, float* ms) {
 }
 extern "C" int nn_event_destroy(void* ev) {
     if (ev) CUDA_TRY(cudaEventDestroy((cudaEvent_t)ev));
+    return NN_OK;
+}
+
+extern "C" int nn_bandwidth_probe(nn_context* c, size_t bytes, int trials, double* out_loads_gbs, double* out_tma_gbs) {
+    if (!c) return NN_FAIL(NN_ERR_ARG, "nn_bandwidth_probe: null context");
+    if (c->capturing) return NN_FAIL(NN_ERR_UNSUPPORTED, "nn_bandwidth_probe: not inside a recording");
+    if (bytes == 0) bytes = c->l2_bytes * 8 > ((size_t)1 << 30) ? c->l2_bytes * 8 : ((size_t)1 << 30);
+    bytes &= ~(size_t)16383;
+    if (bytes < ((size_t)1 << 20) || trials < 1 || trials > 100)
+        return NN_FAIL(NN_ERR_ARG, "nn_bandwidth_probe: bytes=%zu (at least 1 MiB) trials=%d (1..100)", bytes, trials);
+    cudaSetDevice(c->device);
+    uint8_t* src = nullptr;
+    float* sink = nullptr;
+    cudaEvent_t e0 = nullptr, e1 = nullptr;
+    int rc = NN_OK;
+    double best[2] = {0, 0};
+    auto fail = [&](cudaError_t e, const char* what) { rc = NN_FAIL(NN_ERR_CUDA, "nn_bandwidth_probe: %s: %s", what, cudaGetErrorString(e)); };
+    cudaError_t e = cudaMalloc((void**)&src, bytes);
+    if (e != cudaSuccess) { fail(e, "cudaMalloc"); return rc; }
+    if ((e = cudaMalloc((void**)&sink, 2048)) != cudaSuccess) fail(e, "cudaMalloc");
+    if (!rc && (e = cudaMemsetAsync(src, 0x3c, bytes, c->stream)) != cudaSuccess) fail(e, "cudaMemsetAsync");
+    if (!rc && (e = cudaMemsetAsync(sink, 0, 2048, c->stream)) != cudaSuccess) fail(e, "cudaMemsetAsync");
+    if (!rc && ((e = cudaEventCreate(&e0)) != cudaSuccess || (e = cudaEventCreate(&e1)) != cudaSuccess)) fail(e, "cudaEventCreate");
+    unsigned* status = reinterpret_cast<unsigned*>(sink + 256);
+    for (int path = 0; path < 2 && !rc; ++path) {
+        for (int t = 0; t < trials && !rc; ++t) {
+            for (int rep = 0; rep < 2 && !rc; ++rep) {  // one untimed, one timed: the buffer is larger than L2, nothing of it stays
+                if (rep) cudaEventRecord(e0, c->stream);
+                e = path == 0 ? launch_probe_loads(src, bytes, sink, c->stream) : launch_probe_tma(src, bytes, status, c->stream);
+                if (e != cudaSuccess) fail(e, "launch");
+                c->launches++;
+            }
+            if (rc) break;
+            cudaEventRecord(e1, c->stream);
+            if ((e = cudaEventSynchronize(e1)) != cudaSuccess) { fail(e, "cudaEventSynchronize"); break; }
+            float ms = 0.f;
+            cudaEventElapsedTime(&ms, e0, e1);
+            const double gbs = ms > 0 ? (double)bytes / (ms * 1e-3) / 1e9 : 0.0;
+            if (gbs > best[path]) best[path] = gbs;
+        }
+    }
+    if (!rc) {
+        unsigned st = 0;
+        if ((e = cudaMemcpy(&st, status, sizeof(st), cudaMemcpyDeviceToHost)) != cudaSuccess) fail(e, "cudaMemcpy");
+        else if (st) rc = NN_FAIL(NN_ERR_TIMEOUT, "nn_bandwidth_probe: a bulk copy did not land within the wait limit");
+    }
+    if (e0) cudaEventDestroy(e0);
+    if (e1) cudaEventDestroy(e1);
+    cudaFree(sink);
+    cudaFree(src);
+    if (rc) return rc;
+    if (out_loads_gbs) *out_loads_gbs = best[0];
+    if (out_tma_gbs) *out_tma_gbs = best[1];
     return NN_OK;
 }
 

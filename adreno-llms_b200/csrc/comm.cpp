@@ -39,10 +39,16 @@ NcclApi g_nccl;
 bool load_nccl() {
     if (g_nccl.tried) return g_nccl.handle != nullptr;
     g_nccl.tried = true;
-    const char* names[4] = {getenv("NNB_NCCL_LIB"), "libnccl.so.2", "libnccl.so", nullptr};
+    // NNB_NCCL_LIB, when set, names the only library tried: a wrong path is an error, never a
+    // silent switch to whatever libnccl the loader finds
+    const char* forced = getenv("NNB_NCCL_LIB");
     void* h = nullptr;
-    for (int i = 0; i < 3 && !h; ++i)
-        if (names[i] && names[i][0]) h = dlopen(names[i], RTLD_NOW | RTLD_GLOBAL);
+    if (forced && forced[0]) {
+        h = dlopen(forced, RTLD_NOW | RTLD_GLOBAL);
+    } else {
+        const char* names[2] = {"libnccl.so.2", "libnccl.so"};
+        for (int i = 0; i < 2 && !h; ++i) h = dlopen(names[i], RTLD_NOW | RTLD_GLOBAL);
+    }
     if (!h) return false;
     g_nccl.get_unique_id = (fn_get_unique_id)dlsym(h, "ncclGetUniqueId");
     g_nccl.comm_init_rank = (fn_comm_init_rank)dlsym(h, "ncclCommInitRank");
@@ -86,57 +92,91 @@ namespace {
 
 // Allocates `bytes` on this rank, exchanges CUDA IPC handles through the communicator and maps the
 // other ranks' allocations.  Collective: every rank calls it with the same size, in the same order.
+// The allocation is rounded up to whole 2 MiB pages: an exported IPC handle opens the allocation's whole
+// page range on the peers, and nothing else of this process may live there.
 int symm_alloc(nn_comm* c, size_t bytes, SymmAlloc* out) {
     SymmAlloc sa;
     sa.bytes = bytes;
     cudaSetDevice(c->ctx->device);
+    const size_t page = (size_t)2 << 20;
+    const size_t padded = (bytes + page - 1) / page * page;
     void* local = nullptr;
-    COMM_CUDA(cudaMalloc(&local, bytes));
-    COMM_CUDA(cudaMemsetAsync(local, 0, bytes, c->ctx->stream));
-    sa.base[c->rank] = local;
+    void* dev = nullptr;  // staging for the handle exchange
+    auto fail = [&](int rc) {
+        for (int g = 0; g < c->world; ++g)
+            if (g != c->rank && sa.base[g]) cudaIpcCloseMemHandle(sa.base[g]);
+        if (dev) cudaFree(dev);
+        if (local) cudaFree(local);
+        return rc;
+    };
+#define SYMM_CUDA(call)                                                                                         \
+    do {                                                                                                        \
+        cudaError_t e_ = (call);                                                                                \
+        if (e_ != cudaSuccess) return fail(NN_FAIL(NN_ERR_CUDA, "%s: %s", #call, cudaGetErrorString(e_)));      \
+    } while (0)
+    SYMM_CUDA(cudaMalloc(&local, padded));
+    SYMM_CUDA(cudaMemsetAsync(local, 0, padded, c->ctx->stream));
     if (c->world > 1) {
         cudaIpcMemHandle_t mine;
-        COMM_CUDA(cudaIpcGetMemHandle(&mine, local));
+        SYMM_CUDA(cudaIpcGetMemHandle(&mine, local));
         const size_t hb = sizeof(cudaIpcMemHandle_t);
         std::vector<cudaIpcMemHandle_t> all((size_t)c->world);
-        void* dev = nullptr;
-        COMM_CUDA(cudaMalloc(&dev, hb * c->world));
-        COMM_CUDA(cudaMemcpyAsync((char*)dev + hb * c->rank, &mine, hb, cudaMemcpyHostToDevice, c->ctx->stream));
+        SYMM_CUDA(cudaMalloc(&dev, hb * c->world));
+        SYMM_CUDA(cudaMemcpyAsync((char*)dev + hb * c->rank, &mine, hb, cudaMemcpyHostToDevice, c->ctx->stream));
         const int rc = g_nccl.all_gather((char*)dev + hb * c->rank, dev, hb, /*ncclInt8*/ 0, c->comm, c->ctx->stream);
-        if (rc != 0) return NN_FAIL(NN_ERR_COMM, "ncclAllGather (handle exchange): %s", nccl_err(rc));
-        COMM_CUDA(cudaMemcpyAsync(all.data(), dev, hb * c->world, cudaMemcpyDeviceToHost, c->ctx->stream));
-        COMM_CUDA(cudaStreamSynchronize(c->ctx->stream));
-        COMM_CUDA(cudaFree(dev));
+        if (rc != 0) return fail(NN_FAIL(NN_ERR_COMM, "ncclAllGather (handle exchange): %s", nccl_err(rc)));
+        SYMM_CUDA(cudaMemcpyAsync(all.data(), dev, hb * c->world, cudaMemcpyDeviceToHost, c->ctx->stream));
+        SYMM_CUDA(cudaStreamSynchronize(c->ctx->stream));
+        cudaFree(dev);
+        dev = nullptr;
         for (int g = 0; g < c->world; ++g) {
             if (g == c->rank) continue;
             void* p = nullptr;
             cudaError_t e = cudaIpcOpenMemHandle(&p, all[(size_t)g], cudaIpcMemLazyEnablePeerAccess);
             if (e != cudaSuccess)
-                return NN_FAIL(NN_ERR_COMM, "rank %d cannot map rank %d's buffer (cudaIpcOpenMemHandle: %s); peer access is required",
-                               c->rank, g, cudaGetErrorString(e));
+                return fail(NN_FAIL(NN_ERR_COMM, "rank %d cannot map rank %d's buffer (cudaIpcOpenMemHandle: %s); peer access is required",
+                                    c->rank, g, cudaGetErrorString(e)));
             sa.base[g] = p;
         }
     } else {
-        COMM_CUDA(cudaStreamSynchronize(c->ctx->stream));
+        SYMM_CUDA(cudaStreamSynchronize(c->ctx->stream));
     }
+#undef SYMM_CUDA
+    sa.base[c->rank] = local;
     *out = sa;
     return NN_OK;
 }
 
-void symm_release(nn_comm* c, SymmAlloc& sa) {
+// Releasing is collective and has two phases with a barrier between them: first every rank closes
+// its mappings of the others' buffers, then, once all ranks have done so, each frees its own (freeing
+// memory that a peer still has open through an IPC handle is undefined).
+void symm_close_peers(nn_comm* c, SymmAlloc& sa) {
     for (int g = 0; g < c->world; ++g) {
-        if (!sa.base[g]) continue;
-        if (g == c->rank) cudaFree(sa.base[g]);
-        else cudaIpcCloseMemHandle(sa.base[g]);
+        if (g == c->rank || !sa.base[g]) continue;
+        cudaIpcCloseMemHandle(sa.base[g]);
         sa.base[g] = nullptr;
     }
+}
+void ranks_barrier(nn_comm* c) {
+    if (c->world <= 1 || !c->comm || !c->epochs) return;
+    // one byte per rank through the communicator, then a host wait: every rank has reached this point
+    char* scratch = reinterpret_cast<char*>(c->epochs) + 32;
+    if (g_nccl.all_gather(scratch + c->rank, scratch, 1, /*ncclInt8*/ 0, c->comm, c->ctx->stream) == 0) cudaStreamSynchronize(c->ctx->stream);
+}
+void symm_free_local(nn_comm* c, SymmAlloc& sa) {
+    if (sa.base[c->rank]) cudaFree(sa.base[c->rank]);
+    sa.base[c->rank] = nullptr;
 }
 
 }  // namespace
 
 extern "C" int nn_comm_unique_id(void* out) {
     if (!out) return NN_FAIL(NN_ERR_ARG, "nn_comm_unique_id: null argument");
-    if (!load_nccl()) return NN_FAIL(NN_ERR_COMM, "NCCL could not be loaded (set NNB_NCCL_LIB to libnccl.so.2): %s", dlerror());
+    if (!load_nccl()) {
+        const char* why = dlerror();
+        return NN_FAIL(NN_ERR_COMM, "NCCL could not be loaded (NNB_NCCL_LIB names the library to use, default libnccl.so.2): %s",
+                       why ? why : "see the first failure");
+    }
     NcclId id;
     const int rc = g_nccl.get_unique_id(&id);
     if (rc != 0) return NN_FAIL(NN_ERR_COMM, "ncclGetUniqueId: %s", nccl_err(rc));
@@ -154,7 +194,7 @@ extern "C" int nn_comm_init(nn_context* ctx, const void* id_bytes, int rank, int
     c->world = world;
     if (world > 1) {
         if (!id_bytes) { delete c; return NN_FAIL(NN_ERR_ARG, "nn_comm_init: null unique id"); }
-        if (!load_nccl()) { delete c; return NN_FAIL(NN_ERR_COMM, "NCCL could not be loaded (set NNB_NCCL_LIB to libnccl.so.2)"); }
+        if (!load_nccl()) { delete c; return NN_FAIL(NN_ERR_COMM, "NCCL could not be loaded (NNB_NCCL_LIB names the library to use, default libnccl.so.2)"); }
         NcclId id;
         memcpy(id.bytes, id_bytes, sizeof(id.bytes));
         cudaSetDevice(ctx->device);
@@ -191,7 +231,11 @@ extern "C" int nn_comm_symm_free(nn_comm* c, nn_buf buf) {
     if (!c || !buf) return NN_OK;
     for (size_t i = 0; i < c->symm.size(); ++i)
         if (c->symm[i].base[c->rank] == buf && buf != (void*)c->flags) {
-            symm_release(c, c->symm[i]);
+            cudaSetDevice(c->ctx->device);
+            cudaStreamSynchronize(c->ctx->stream);
+            symm_close_peers(c, c->symm[i]);
+            ranks_barrier(c);
+            symm_free_local(c, c->symm[i]);
             c->symm.erase(c->symm.begin() + (long)i);
             return NN_OK;
         }
@@ -266,6 +310,17 @@ extern "C" int nn_linear_argmax_sharded(nn_comm* c, int n_local, int K, nn_buf x
     return NN_OK;
 }
 
+extern "C" int nn_comm_pick_unsent(nn_comm* c, unsigned timeout_ms, nn_buf out_idx) {
+    if (!c || !out_idx) return NN_FAIL(NN_ERR_ARG, "nn_comm_pick_unsent: null argument");
+    if (!c->flags) return NN_FAIL(NN_ERR_ARG, "nn_comm_pick_unsent: no symmetric buffer has been allocated on this communicator");
+    if (timeout_ms == 0 || timeout_ms > 10000) return NN_FAIL(NN_ERR_ARG, "nn_comm_pick_unsent: timeout %u ms outside 1..10000", timeout_ms);
+    // one pick round counted on both sides (sent and waited) in which no key is stored anywhere
+    COMM_CUDA(nnb::launch_comm_count(c->epochs + 3, c->ctx->stream));
+    COMM_CUDA(nnb::launch_comm_pick(c->flags, c->world, c->epochs + 4, timeout_ms, c->ctx->status_dev, false, (int*)out_idx, c->ctx->stream));
+    c->ctx->launches += 2;
+    return NN_OK;
+}
+
 extern "C" int nn_comm_all_gather(nn_comm* c, nn_buf send, nn_buf recv, size_t bytes) {
     if (!c || !send || !recv) return NN_FAIL(NN_ERR_ARG, "nn_comm_all_gather: null argument");
     if (c->world == 1) {
@@ -284,7 +339,9 @@ extern "C" int nn_comm_free(nn_comm* c) {
     if (!c) return NN_OK;
     cudaSetDevice(c->ctx->device);
     cudaStreamSynchronize(c->ctx->stream);
-    for (SymmAlloc& sa : c->symm) symm_release(c, sa);
+    for (SymmAlloc& sa : c->symm) symm_close_peers(c, sa);
+    ranks_barrier(c);
+    for (SymmAlloc& sa : c->symm) symm_free_local(c, sa);
     if (c->epochs) cudaFree(c->epochs);
     if (c->comm && g_nccl.comm_destroy) g_nccl.comm_destroy(c->comm);
     delete c;

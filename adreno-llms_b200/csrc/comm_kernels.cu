@@ -106,7 +106,14 @@ __global__ void comm_pick_kernel(const unsigned long long* tables, int world, un
     if (threadIdx.x == 0) *out_row = (all_in && w) ? (int)(0xFFFFFFFFu - (unsigned)(w & 0xFFFFFFFFull)) : -1;
 }
 
+__global__ void comm_count_kernel(unsigned* counter) { *counter += 1u; }
+
 }  // namespace
+
+cudaError_t launch_comm_count(unsigned* counter, cudaStream_t st) {
+    comm_count_kernel<<<1, 1, 0, st>>>(counter);
+    return cudaGetLastError();
+}
 
 cudaError_t launch_comm_pick(const unsigned* my_flags, int world, unsigned* picks_waited, unsigned timeout_ms, int* status, bool overlap,
                              int* out_row, cudaStream_t st) {

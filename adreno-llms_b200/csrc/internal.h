@@ -4,6 +4,7 @@
 #include <stdint.h>
 
 #include <map>
+#include <string>
 #include <vector>
 
 #include "plan.h"
@@ -13,6 +14,18 @@ struct QuantEntry {
     const uint16_t* scale;
     int N, K;
     size_t rowbytes;
+};
+
+// Per-launch profile behind the reference's switches NNOPT_KERNEL_PROFILE / NNOPT_PROFILE
+// (src/models/lfm2-5-350m/src/kernel_profiler.cpp:18-62, src/models/smollm2-135m-instruct/src/prof.cpp:36-131):
+// a CUDA event pair around every call, aggregated by label at nn_shutdown or nn_profile_report.
+struct ProfPending {
+    std::string label;
+    cudaEvent_t start, stop;
+};
+struct ProfAgg {
+    unsigned long long count = 0;
+    double total_us = 0, max_us = 0;
 };
 
 struct nn_context {
@@ -33,6 +46,9 @@ struct nn_context {
     bool use_pdl = true;
     bool capturing = false;
     std::vector<nnb::RecordedOp> rec;  // streamed single-token operators of the recording in progress
+    bool profiling = false;
+    std::vector<ProfPending> prof_pending;
+    std::map<std::string, ProfAgg> prof;
     long long launches = 0, launches_at_capture = 0;
 };
 

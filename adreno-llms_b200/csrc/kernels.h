@@ -125,6 +125,7 @@ cudaError_t launch_comm_wait(const unsigned* my_flags, int world, unsigned* epoc
                              cudaStream_t st);
 // Row-sharded greedy pick: waits (bounded) for pick number *picks_waited + 1 of every rank in this
 // rank's key tables and writes the winning row (-1: every value was NaN, or the wait ran out).
+cudaError_t launch_comm_count(unsigned* counter, cudaStream_t st);
 cudaError_t launch_comm_pick(const unsigned* my_flags, int world, unsigned* picks_waited, unsigned timeout_ms, int* status, bool overlap,
                              int* out_row, cudaStream_t st);
 
@@ -136,6 +137,16 @@ cudaError_t launch_argmax_half(const uint16_t* v, int n, int* out_idx, unsigned 
 cudaError_t launch_fill_u64(unsigned long long* p, unsigned long long v, cudaStream_t st);
 cudaError_t launch_argmax_finish(const unsigned long long* slot, int* out_idx, cudaStream_t st);
 cudaError_t launch_l2_flush(void* buf, size_t bytes, cudaStream_t st);
+// read-bandwidth probes over `bytes` (a multiple of 16 KiB) at src; sink: 256 floats; status: one word, set on a timed-out wait
+cudaError_t launch_probe_loads(const void* src, size_t bytes, float* sink, cudaStream_t st);
+cudaError_t launch_probe_tma(const void* src, size_t bytes, unsigned* status, cudaStream_t st);
+struct BiasArgs {  // up to three [rows, cols] fp16 outputs with a bias row each
+    uint16_t* out[3];
+    const uint16_t* bias[3];
+    int cols[3];
+    int rows, nseg;
+};
+cudaError_t launch_bias_add(const BiasArgs& a, cudaStream_t st);
 cudaError_t launch_rmsnorm(const uint16_t* x, const uint16_t* w, uint16_t* out, int rows, int cols, float eps, cudaStream_t st);
 
 }  // namespace nnb

@@ -4,6 +4,7 @@
 #include <float.h>
 
 #include "kernels.h"
+#include "ptx.cuh"
 
 namespace nnb {
 namespace {
@@ -97,6 +98,77 @@ __global__ void rmsnorm_kernel(const uint16_t* __restrict__ x, const uint16_t* _
     for (int c = threadIdx.x; c < cols; c += blockDim.x) orow[c] = __half_as_ushort(__float2half_rn((h2f(xr[c]) * inv) * h2f(w[c])));
 }
 
+// out[r][c] = half(float(out[r][c]) + float(bias[c])) for up to three (out, bias) pairs of one launch:
+// bias_add_rowmajor, src/models/qwen2-5-0-5b/kernels/bias_add.cl:18-40 (the projection's result is
+// rounded to fp16 first, then the bias is added in fp32 and the sum rounded again, as there).
+__global__ void bias_add_kernel(BiasArgs a) {
+    const int seg = blockIdx.y;
+    uint16_t* out = a.out[seg];
+    const uint16_t* bias = a.bias[seg];
+    const int cols = a.cols[seg];
+    const long long total = (long long)a.rows * cols;
+    for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
+        const int c = (int)(i % cols);
+        out[i] = __half_as_ushort(__float2half_rn(h2f(out[i]) + h2f(bias[c])));
+    }
+}
+
+// Read-bandwidth probes: what the weight streams of this library can reach at best on this GPU
+// (the role of gemv_stream_buf / gemv_stream_img, src/models/lfm2-5-350m/kernels/gemv_m1.cl:537-589,
+// driven by run_bw_probe, src/models/lfm2-5-350m/src/main.cpp:29-139).  The two read paths of this
+// hardware stand where the reference has buffer and image reads: 16-byte loads by every thread, and
+// bulk copies into shared memory by the TMA unit (the path the streaming kernels use).
+__global__ void __launch_bounds__(256) probe_loads_kernel(const uint4* __restrict__ src, size_t n16, float* __restrict__ sink) {
+    const size_t stride = (size_t)gridDim.x * blockDim.x;
+    size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x;
+    unsigned int acc = 0u;
+    constexpr int U = 8;  // independent loads in flight per thread
+    for (; i + (U - 1) * stride < n16; i += U * stride) {
+        uint4 v[U];
+#pragma unroll
+        for (int u = 0; u < U; ++u)
+            asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0, %1, %2, %3}, [%4];"
+                         : "=r"(v[u].x), "=r"(v[u].y), "=r"(v[u].z), "=r"(v[u].w)
+                         : "l"(src + i + u * stride));
+#pragma unroll
+        for (int u = 0; u < U; ++u) acc += v[u].x ^ v[u].y ^ v[u].z ^ v[u].w;
+    }
+    for (; i < n16; i += stride) {
+        const uint4 v = src[i];
+        acc += v.x ^ v.y ^ v.z ^ v.w;
+    }
+    if (acc == 0x9E3779B9u) sink[threadIdx.x] = 1.f;  // keeps the loads alive; practically never taken
+}
+
+constexpr int PROBE_CHUNK = 16384;
+constexpr int PROBE_STAGES = 8;
+
+__global__ void __launch_bounds__(32) probe_tma_kernel(const uint8_t* __restrict__ src, size_t nchunks, unsigned* __restrict__ status) {
+    extern __shared__ __align__(128) uint8_t probe_smem[];
+    __shared__ __align__(8) uint64_t bars[PROBE_STAGES];
+    if (threadIdx.x != 0) return;
+    for (int s = 0; s < PROBE_STAGES; ++s) mbar_init(smem_u32(&bars[s]), 1);
+    mbar_init_fence();
+    const uint64_t pol = l2_policy_evict_first();
+    size_t issued = 0, waited = 0;   // per stage ring: copy number i lands in stage i % PROBE_STAGES
+    bool ok = true;
+    for (size_t c = blockIdx.x; c < nchunks && ok; c += gridDim.x) {
+        if (issued >= PROBE_STAGES) {  // the copy that used this stage before must have landed
+            ok = mbar_wait_bounded(smem_u32(&bars[waited % PROBE_STAGES]), (uint32_t)((waited / PROBE_STAGES) & 1));
+            if (!ok) break;
+            ++waited;
+        }
+        const int s = (int)(issued % PROBE_STAGES);
+        mbar_arrive_expect_tx(smem_u32(&bars[s]), PROBE_CHUNK);
+        bulk_g2s(smem_u32(probe_smem + (size_t)s * PROBE_CHUNK), src + c * (size_t)PROBE_CHUNK, PROBE_CHUNK, smem_u32(&bars[s]), pol);
+        ++issued;
+    }
+    // every copy in flight lands before the block gives its shared memory back (bounded as well)
+    for (; waited < issued; ++waited)
+        if (!mbar_wait_bounded(smem_u32(&bars[waited % PROBE_STAGES]), (uint32_t)((waited / PROBE_STAGES) & 1))) ok = false;
+    if (!ok) atomicExch(status, 1u);
+}
+
 __global__ void l2_flush_kernel(uint4* buf, size_t n16) {
     for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < n16; i += (size_t)gridDim.x * blockDim.x) {
         uint4 v = buf[i];
@@ -159,6 +231,35 @@ cudaError_t launch_argmax_half(const uint16_t* v, int n, int* out_idx, unsigned 
 cudaError_t launch_rmsnorm(const uint16_t* x, const uint16_t* w, uint16_t* out, int rows, int cols, float eps, cudaStream_t st) {
     if (rows <= 0 || cols <= 0) return cudaSuccess;
     rmsnorm_kernel<<<(unsigned)rows, 256, 0, st>>>(x, w, out, cols, eps);
+    return cudaGetLastError();
+}
+
+cudaError_t launch_bias_add(const BiasArgs& a, cudaStream_t st) {
+    if (a.rows <= 0 || a.nseg <= 0) return cudaSuccess;
+    int maxc = 0;
+    for (int i = 0; i < a.nseg; ++i) maxc = a.cols[i] > maxc ? a.cols[i] : maxc;
+    long long blocks = ((long long)a.rows * maxc + 255) / 256;
+    const long long cap = (long long)current_sm_count() * 8;
+    if (blocks > cap) blocks = cap;
+    if (blocks < 1) blocks = 1;
+    bias_add_kernel<<<dim3((unsigned)blocks, (unsigned)a.nseg), 256, 0, st>>>(a);
+    return cudaGetLastError();
+}
+
+cudaError_t launch_probe_loads(const void* src, size_t bytes, float* sink, cudaStream_t st) {
+    probe_loads_kernel<<<current_sm_count() * 8, 256, 0, st>>>(static_cast<const uint4*>(src), bytes / 16, sink);
+    return cudaGetLastError();
+}
+
+cudaError_t launch_probe_tma(const void* src, size_t bytes, unsigned* status, cudaStream_t st) {
+    static bool configured = false;
+    const int smem = PROBE_CHUNK * PROBE_STAGES;
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(probe_tma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+        if (e != cudaSuccess) return e;
+        configured = true;
+    }
+    probe_tma_kernel<<<current_sm_count(), 32, smem, st>>>(static_cast<const uint8_t*>(src), bytes / PROBE_CHUNK, status);
     return cudaGetLastError();
 }
 

@@ -66,3 +66,50 @@ def pick_from_keys(words, pick_number: int = 0) -> int:
             raise ValueError(f"word {w:#018x} does not belong to pick {pick_number}")
         best = max(best, w & 0xFFFFFFFFFFFF)
     return -1 if best == 0 else 0xFFFFFFFF - (best & 0xFFFFFFFF)
+
+
+class PeerLost(RuntimeError):
+    """A rank of the sharded step left or stopped reporting; nothing must be launched that waits for it."""
+
+
+class RollCall:
+    """Host-side roll call between decode steps of a row-sharded model.
+
+    The sharded lm_head stores into its peers' memory and waits (bounded) for their flags, so a
+    rank may only launch a step when every peer is going to run it too.  Each rank reports the
+    step it is about to launch into a key-value store (torch.distributed.TCPStore or anything
+    with set / get / check) and reads its peers' reports before launching: a peer that announced
+    its departure, or that has not reported within the timeout, raises PeerLost on the host,
+    before any kernel is in flight.  A rank leaves only between steps (`leave`)."""
+
+    def __init__(self, store, rank: int, world: int, timeout_s: float = 5.0, poll_s: float = 0.005):
+        self.store, self.rank, self.world = store, rank, world
+        self.timeout_s, self.poll_s = timeout_s, poll_s
+
+    def _key(self, rank):
+        return f"rollcall/{rank}"
+
+    def report(self, step: int):
+        self.store.set(self._key(self.rank), str(int(step)))
+
+    def leave(self):
+        self.store.set(self._key(self.rank), "left")
+
+    def check(self, step: int):
+        """Returns once every peer has reported `step` or a later one; raises PeerLost otherwise."""
+        import time
+        deadline = time.monotonic() + self.timeout_s
+        for peer in range(self.world):
+            if peer == self.rank:
+                continue
+            while True:
+                seen = None
+                if self.store.check([self._key(peer)]):
+                    seen = self.store.get(self._key(peer)).decode()
+                    if seen == "left":
+                        raise PeerLost(f"rank {peer} left before step {step}")
+                    if int(seen) >= step:
+                        break
+                if time.monotonic() > deadline:
+                    raise PeerLost(f"rank {peer} has not reported step {step} within {self.timeout_s} s (last report: {seen})")
+                time.sleep(self.poll_s)

@@ -390,7 +390,24 @@ def sharded_projections(pkg, ctx, synth, comm, rank, world, dist, reps=12):
                 comm.symm_free(b)
         else:
             t_fused = t_lin + t_ag
-        t = [t_lin / reps * 1e3, t_ag / reps * 1e3, t_fused / reps * 1e3]
+        # the whole operator on one GPU, timed the same way, for the efficiency figure t1 / (G * tG)
+        t_one = t_lin
+        if world > 1:
+            repn = (N + W.shape[0] - 1) // W.shape[0]
+            Wf = np.tile(W, (repn, 1))[:N]
+            sf = np.tile(sc, (repn, 1) if sc.ndim == 2 else repn)[:N]
+            qf = pkg.QuantWeight(ctx, fmt, Wf, sf)
+            t_one = 0.0
+            for i in range(reps + 2):
+                ctx.l2_flush()
+                ctx.record(ev[0])
+                ctx.linear(M, N, K, x, qf.buf, gathered)
+                ctx.record(ev[1])
+                ctx.sync()
+                if i >= 2:
+                    t_one += ctx.elapsed_ms(ev[0], ev[1])
+            qf.release()
+        t = [t_lin / reps * 1e3, t_ag / reps * 1e3, t_fused / reps * 1e3, t_one / reps * 1e3]
         if dist:
             import torch
             tt = torch.tensor(t, dtype=torch.float64)
@@ -399,6 +416,8 @@ def sharded_projections(pkg, ctx, synth, comm, rank, world, dist, reps=12):
         b = synth.linear_bytes(fmt, N, K, M)
         rows.append({"fmt": fmt, "N": N, "K": K, "M": M, "rows_per_rank": n, "linear_us": t[0], "nccl_all_gather_us": t[1],
                      "fused_gather_us": t[2],   # projection with peer stores + flag exchange, one call
+                     "single_gpu_us": t[3],     # the unsharded operator on one GPU of this run
+                     "efficiency_per_operator": t[3] / (world * t[2]) if t[2] > 0 else None,
                      "gbps_aggregate": b / (t[2] * 1e-6) / 1e9,
                      "tflops_aggregate": 2.0 * M * N * K / (t[2] * 1e-6) / 1e12})
         for e in ev:
@@ -701,6 +720,11 @@ def main():
     targets = roofline_targets(pkg, ctx, synth, l2_bytes) if (extras and world == 1) else None
     sharded = sharded_projections(pkg, ctx, synth, comm, rank, world, dist) if extras else None
     prefill = prefill_gemm(pkg, ctx, synth) if (extras and world == 1) else None
+    probe = None
+    if extras and world == 1:
+        # the library's own read ceiling on this GPU (the reference's STREAM probe): both read paths, best of 5
+        loads_gbs, tma_gbs = ctx.bandwidth_probe(0, 5)
+        probe = {"bytes": max(1 << 30, 8 * l2_bytes), "loads_gbs": loads_gbs, "tma_bulk_gbs": tma_gbs, "trials": 5}
 
     cpu_base = None
     if rank == 0 and world == 1 and not args.no_cpu_baseline and default_workload:
@@ -737,6 +761,7 @@ def main():
             "chained_step": chained,
             "sharded_projections": sharded,
             "prefill_gemm": prefill,
+            "read_bandwidth_probe": probe,
             "decode_step_with_gathered_logits_us": gathered_step_us,
             "clocks": clocks,
         }

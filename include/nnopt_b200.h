@@ -116,6 +116,14 @@ int nn_fused_gate_up_silu(nn_context* ctx, int M, int N, int K, nn_buf x, nn_buf
 int nn_linear_qkv(nn_context* ctx, int M, int K, nn_buf x, nn_buf Wq, int Nq, nn_buf Wk, int Nk, nn_buf Wv, int Nv,
                   nn_buf q, nn_buf k, nn_buf v);
 
+/* The same with Qwen's q/k/v bias added afterwards, and the bias add on its own:
+ * bias_add_rowmajor, src/models/qwen2-5-0-5b/kernels/bias_add.cl:18-40 (host:
+ * src/layers/attention.cpp:413-469): out[r,c] = half(float(out[r,c]) + float(bias[c])), applied to
+ * the fp16 result of the projection, as the reference does (one launch for the three outputs). */
+int nn_linear_qkv_bias(nn_context* ctx, int M, int K, nn_buf x, nn_buf Wq, int Nq, nn_buf Wk, int Nk, nn_buf Wv, int Nv,
+                       nn_buf bias_q, nn_buf bias_k, nn_buf bias_v, nn_buf q, nn_buf k, nn_buf v);
+int nn_bias_add(nn_context* ctx, int rows, int cols, nn_buf out_inout, nn_buf bias_fp16);
+
 /* RMSNorm on fp16 storage: out[r,c] = half( (x[r,c] * rsqrt(mean_c x[r,c]^2 + eps)) * weight[c] )
  * (rmsnorm_forward, src/models/smollm2-135m-instruct/kernels/rmsnorm.cl:27-104; host
  * src/layers/layer_norm.cpp:76-126).  The three nn_rmsnorm_* forms below are nn_linear,
@@ -229,6 +237,26 @@ int nn_event_create(void** out_event);
 int nn_event_record(nn_context* ctx, void* event);
 int nn_event_elapsed_ms(void* start, void* stop, float* out_ms); /* waits for stop */
 int nn_event_destroy(void* event);
+/* NNOPT_KERNEL_PROFILE=1 (or NNOPT_PROFILE=1) in the environment at nn_init switches the per-launch
+ * profile on, the reference's switches of the same names (src/models/lfm2-5-350m/src/
+ * kernel_profiler.cpp:18-62, src/models/smollm2-135m-instruct/src/prof.cpp:36-131): every call is
+ * bracketed by a CUDA event pair under a label of the reference's form (gemv_m1_K1024_N4608_int8, with
+ * the fused form appended; a plan replay is one entry), and nn_shutdown prints the table (label,
+ * total ms, share, calls, average and maximum us; largest first) to stderr, as the reference does at
+ * exit.  nn_profile_report formats the table so far into buf (returns its length; reset != 0 clears
+ * the sums).  nn_profile_aggregate is the same aggregation and table on given (label, us) samples: it
+ * needs no GPU. */
+int nn_profile_enabled(const nn_context* ctx);
+int nn_profile_report(nn_context* ctx, char* buf, size_t cap, int reset);
+int nn_profile_aggregate(int n, const char* const* labels, const double* us, char* buf, size_t cap);
+/* Read-bandwidth probe, the library's own measured ceiling for its weight streams: run_bw_probe,
+ * src/models/lfm2-5-350m/src/main.cpp:29-139 with gemv_stream_buf / gemv_stream_img
+ * (kernels/gemv_m1.cl:537-589).  Reads `bytes` (0: the larger of 1 GiB and eight times L2) of a
+ * scratch buffer it allocates and frees, once untimed and once timed per trial, and reports the best
+ * trial in GB/s (1e9 bytes) for the two read paths of this GPU: 16-byte loads by every thread, and
+ * bulk copies into shared memory by the TMA unit, the path the streaming kernels use (where the
+ * reference has buffer and image reads).  Either output may be NULL.  Synchronises the stream. */
+int nn_bandwidth_probe(nn_context* ctx, size_t bytes, int trials, double* out_loads_gbs, double* out_tma_gbs);
 /* Evict L2 between timed runs by rewriting a library-owned buffer larger than L2. */
 int nn_l2_flush(nn_context* ctx);
 /* Kernels launched by this context so far (for launch accounting). */
@@ -276,11 +304,17 @@ int nn_comm_free(nn_comm* comm);
  *                       also stored there (ordinary device memory).  Every rank must make the
  *                       same sequence of these calls.  Needs one prior nn_comm_symm_alloc on the
  *                       communicator (which creates the flag and key words).
+ *   nn_comm_pick_unsent fault injection on the host: one pick round, counted like any other, in
+ *                       which no rank stores its key.  The waiting kernel must give up after
+ *                       timeout_ms (1..10000), write -1 to out_index, and the next nn_sync must
+ *                       return NN_ERR_TIMEOUT with the context and the communicator usable.
+ *                       Every rank makes the call (or none).
  * No counterpart in the reference. */
 int nn_comm_symm_alloc(nn_comm* comm, size_t bytes, nn_buf* out);
 int nn_comm_symm_free(nn_comm* comm, nn_buf buf);
 int nn_linear_gather(nn_comm* comm, int M, int n_local, int K, nn_buf x, nn_buf W, nn_buf gathered);
 int nn_linear_argmax_sharded(nn_comm* comm, int n_local, int K, nn_buf x, nn_buf W, nn_buf logits_local_fp16, nn_buf out_index_i32);
+int nn_comm_pick_unsent(nn_comm* comm, unsigned timeout_ms, nn_buf out_index_i32);
 int nn_comm_signal(nn_comm* comm);
 int nn_comm_wait(nn_comm* comm, unsigned timeout_ms);
 /* Number of CUDA devices visible to the process (0 when there is none). */

@@ -1,4 +1,4 @@
-"""Time one projection on one GPU:  python adreno-llms_b200/opbench.py --fmt q4 --n 28672 --k 8192 --m 1
+"""Time one projection on one GPU:  python opbench.py --fmt q4 --n 28672 --k 8192 --m 1
 
 Prints one JSON line: microseconds per launch (CUDA events around `reps` back-to-back launches
 that rotate through enough weight copies to exceed L2), algorithmic GB/s and TFLOP/s.  Weights are
@@ -15,13 +15,14 @@ import sys
 import numpy as np
 
 HERE = os.path.dirname(os.path.abspath(__file__))
+PKG = os.path.join(HERE, "adreno-llms_b200")
 
 
 def load_pkg():
     name = "adreno_llms_b200"
     if name in sys.modules:
         return sys.modules[name]
-    spec = importlib.util.spec_from_file_location(name, os.path.join(HERE, "__init__.py"), submodule_search_locations=[HERE])
+    spec = importlib.util.spec_from_file_location(name, os.path.join(PKG, "__init__.py"), submodule_search_locations=[PKG])
     mod = importlib.util.module_from_spec(spec)
     sys.modules[name] = mod
     spec.loader.exec_module(mod)

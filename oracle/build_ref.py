@@ -1,6 +1,6 @@
 """Compiles the reference's own OpenCL kernel sources for the CPU (TEST INFRASTRUCTURE ONLY).
 
-    python oracle/build_ref.py            # needs the reference checkout ($NNOPT_REFERENCE, or the default mount below)
+    python oracle/build_ref.py            # needs the reference checkout ($NNOPT_REFERENCE, or a directory "reference" beside this repository)
 
 For each .cl file on the decode GEMV path, g++ reads from a pipe:
     oracle/cl_shim.h  +  #define USE_FP16  +  the .cl file exactly where it lies in the
@@ -21,7 +21,8 @@ import sys
 
 HERE = os.path.dirname(os.path.abspath(__file__))
 OUT = os.path.join(HERE, "_ref")
-REF = os.environ.get("NNOPT_REFERENCE", "/root/reference")
+# the reference project's checkout: $NNOPT_REFERENCE, else a directory named "reference" beside this repository
+REF = os.environ.get("NNOPT_REFERENCE") or os.path.join(os.path.dirname(os.path.dirname(HERE)), "reference")
 
 # (library tag, path inside the reference project)
 CL_FILES = [

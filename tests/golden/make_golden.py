@@ -1,7 +1,7 @@
 #!/usr/bin/env python3
 """Regenerates the committed fixtures in this folder from the reference's own code.
 
-Needs the reference checkout ($NNOPT_REFERENCE, or the default mount named below); the
+Needs the reference checkout ($NNOPT_REFERENCE, or a directory "reference" beside this repository); the
 tests themselves only read the committed outputs.  Run:  python tests/golden/make_golden.py
 
 What it produces
@@ -30,7 +30,8 @@ import numpy as np
 
 HERE = os.path.dirname(os.path.abspath(__file__))
 REPO = os.path.dirname(os.path.dirname(HERE))
-REF = os.environ.get("NNOPT_REFERENCE", "/root/reference")
+# the reference project's checkout: $NNOPT_REFERENCE, else a directory named "reference" beside this repository
+REF = os.environ.get("NNOPT_REFERENCE") or os.path.join(os.path.dirname(REPO), "reference")
 sys.path.insert(0, REPO)
 
 

@@ -99,3 +99,53 @@ def test_bundle_loader_errors(nnb, built_lib, tmp_path):
     assert L.nn_weights_load(None, str(binp).encode(), str(flat).encode(), ctypes.byref(w)) == 0
     assert L.nn_weights_num_keys(w) == 1 and L.nn_weights_get_num_elements(w, b"a.weight") == 16
     L.nn_weights_free(w)
+
+
+def test_profile_aggregation_table(nnb, built_lib):
+    """The per-launch profile's aggregation and table (the reference's exit-time table:
+    src/models/lfm2-5-350m/src/kernel_profiler.cpp:18-62): totals per label, largest first,
+    share of the whole, calls, average and maximum."""
+    L = built_lib
+    samples = [("gemv_m1_K1024_N4608_int8", 10.0), ("gemv_m1_K1024_N1024_int8_add", 4.0), ("gemv_m1_K1024_N4608_int8", 30.0),
+               ("plan_replay", 100.0), ("gemv_m1_K1024_N1024_int8_add", 6.0), ("gemv_m1_K1024_N4608_int8", 20.0)]
+    labels = (ctypes.c_char_p * len(samples))(*[s[0].encode() for s in samples])
+    us = (ctypes.c_double * len(samples))(*[s[1] for s in samples])
+    buf = ctypes.create_string_buffer(4096)
+    n = L.nn_profile_aggregate(len(samples), labels, us, buf, len(buf))
+    text = buf.value.decode()
+    assert n == len(text)
+    rows = [ln.split() for ln in text.splitlines() if ln and (ln.startswith("gemv") or ln.startswith("plan"))]
+    assert [r[0] for r in rows] == ["plan_replay", "gemv_m1_K1024_N4608_int8", "gemv_m1_K1024_N1024_int8_add"]
+    by = {r[0]: [float(v.rstrip("%")) for v in r[1:]] for r in rows}
+    total_ms, share, calls, avg_us, max_us = by["gemv_m1_K1024_N4608_int8"]
+    assert abs(total_ms - 0.060) < 1e-6 and calls == 3 and abs(avg_us - 20.0) < 1e-6 and abs(max_us - 30.0) < 1e-6
+    assert abs(share - 100.0 * 60.0 / 170.0) < 0.06
+    assert abs(by["plan_replay"][1] - 100.0 * 100.0 / 170.0) < 0.06
+    # a short buffer is cut, never overrun; the length returned is the full table's
+    small = ctypes.create_string_buffer(16)
+    assert L.nn_profile_aggregate(len(samples), labels, us, small, len(small)) == n
+    assert len(small.value) == 15
+    assert L.nn_profile_aggregate(2, None, None, buf, len(buf)) == nnb.NN_ERR_ARG
+    assert L.nn_profile_enabled(None) == 0
+
+
+def test_named_nccl_library_is_the_only_one_tried(nnb, built_lib):
+    """NNB_NCCL_LIB names the library to load: a wrong path is NN_ERR_COMM, not a silent
+    switch to the libnccl the loader would find (checked in a child process: the library
+    is loaded once per process)."""
+    import subprocess
+    import sys
+    code = (
+        "import ctypes, sys\n"
+        f"L = ctypes.CDLL({nnb.LIB_PATH!r})\n"
+        "L.nn_last_error.restype = ctypes.c_char_p\n"
+        "buf = ctypes.create_string_buffer(128)\n"
+        "rc = L.nn_comm_unique_id(buf)\n"
+        "print(rc, L.nn_last_error().decode())\n"
+    )
+    env = dict(os.environ, NNB_NCCL_LIB="/nonexistent/libnccl.so.2")
+    out = subprocess.run([sys.executable, "-c", code], env=env, capture_output=True, text=True, timeout=120)
+    assert out.returncode == 0, out.stderr
+    rc, msg = out.stdout.strip().split(" ", 1)
+    assert int(rc) == nnb.NN_ERR_COMM
+    assert "NNB_NCCL_LIB" in msg and "/nonexistent/libnccl.so.2" in msg

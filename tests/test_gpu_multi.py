@@ -131,3 +131,63 @@ def test_wait_that_nothing_signals_times_out_and_context_survives(nnb, ctx):
             ctx.free(b)
     finally:
         comm.close()
+
+
+def test_pick_whose_keys_never_arrive_times_out_and_the_next_pick_works(nnb, ctx):
+    """The row-sharded greedy pick waits for one key word per rank.  Fault injected on the host: a
+    pick round in which nothing stores a key.  The waiting kernel must give up after its limit
+    with -1, nn_sync must report NN_ERR_TIMEOUT, and the next regular pick on the same
+    communicator must give the single-device answer."""
+    comm = nnb.Comm(ctx, None, 0, 1)
+    try:
+        comm.symm_alloc(256)
+        N, K = 4096, 576
+        W, s = make_weight("int8", N, K, 901)
+        qw = nnb.QuantWeight(ctx, "int8", W, s)
+        x = make_x(1, K, 902)
+        dx, logits, idx = ctx.upload(x.view(np.uint16)), ctx.alloc(N * 2), ctx.upload(np.full(1, 77, np.int32))
+        comm.linear_argmax_sharded(N, K, dx, qw.buf, logits, idx)       # a regular pick first
+        ctx.sync()
+        want = int(ctx.download(idx, (1,), np.int32)[0])
+        assert want == cpu.argmax_half(ctx.download(logits, (N,), np.uint16).view(np.float16))
+        comm.pick_unsent(50, idx)
+        with pytest.raises(nnb.NNError) as ei:
+            ctx.sync()
+        assert ei.value.code == nnb.NN_ERR_TIMEOUT
+        assert int(ctx.download(idx, (1,), np.int32)[0]) == -1
+        for _ in range(3):                                            # odd and even table slots
+            ctx.upload(np.full(1, 77, np.int32), idx)
+            comm.linear_argmax_sharded(N, K, dx, qw.buf, logits, idx)
+            ctx.sync()
+            assert int(ctx.download(idx, (1,), np.int32)[0]) == want
+        assert ctx.L.nn_comm_pick_unsent(comm.h, 0, idx) == nnb.NN_ERR_ARG
+        qw.release()
+        for b in (dx, logits, idx):
+            ctx.free(b)
+    finally:
+        ctx.sync()
+        comm.close()
+
+
+def test_nccl_that_cannot_be_loaded_is_a_comm_error(nnb, built_lib):
+    """nn_comm_init for more than one rank with NNB_NCCL_LIB pointing nowhere: NN_ERR_COMM and no
+    communicator, in a child process (the library is looked up once per process)."""
+    code = (
+        "import ctypes, sys\n"
+        f"L = ctypes.CDLL({nnb.LIB_PATH!r})\n"
+        "L.nn_last_error.restype = ctypes.c_char_p\n"
+        "h = ctypes.c_void_p()\n"
+        "assert L.nn_init(0, ctypes.byref(h)) == 0\n"
+        "comm = ctypes.c_void_p()\n"
+        "rc = L.nn_comm_init(h, ctypes.create_string_buffer(128), 0, 2, ctypes.byref(comm))\n"
+        "print(rc, bool(comm.value), L.nn_last_error().decode())\n"
+        "one = ctypes.c_void_p()\n"
+        "print(L.nn_comm_init(h, None, 0, 1, ctypes.byref(one)), bool(one.value))\n"
+    )
+    env = dict(os.environ, NNB_NCCL_LIB="/nonexistent/libnccl.so.2")
+    out = subprocess.run([sys.executable, "-c", code], env=env, capture_output=True, text=True, timeout=300)
+    assert out.returncode == 0, out.stderr
+    first, second = out.stdout.strip().splitlines()
+    rc, made, msg = first.split(" ", 2)
+    assert int(rc) == nnb.NN_ERR_COMM and made == "False" and "NNB_NCCL_LIB" in msg
+    assert second == "0 True"          # a single rank needs no NCCL at all

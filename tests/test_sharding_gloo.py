@@ -136,3 +136,66 @@ def test_pick_key_order_and_nan(nnb):
     assert sharding.pick_from_keys([a, b]) == 101 and sharding.pick_from_keys([b, a]) == 101
     with pytest.raises(ValueError):
         sharding.pick_from_keys([sharding.pick_key(np.ones(2, np.float16), 0, pick_number=3)], pick_number=4)
+
+
+def _leaving_worker(rank, world, port, store_port, how, out_dir):
+    """Two steps; rank 1 goes away between them (announced, or silently).  Rank 0 must learn of it
+    on the host before its next launch, and a collective it starts anyway must end with an error."""
+    import datetime
+    import time
+    sys.path.insert(0, REPO)
+    sys.path.insert(0, os.path.join(REPO, "tests"))
+    from conftest import load_package
+    load_package()
+    import importlib
+    sharding = importlib.import_module("adreno_llms_b200.sharding")
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world, timeout=datetime.timedelta(seconds=5))
+    store = dist.TCPStore("127.0.0.1", store_port, world, is_master=(rank == 0), timeout=datetime.timedelta(seconds=20))
+    roll = sharding.RollCall(store, rank, world, timeout_s=1.0)
+    # step 0: everybody is there
+    roll.report(0)
+    roll.check(0)
+    t = torch.tensor([rank + 1])
+    out = [torch.empty_like(t) for _ in range(world)]
+    dist.all_gather(out, t)
+    assert [int(o) for o in out] == [1, 2]
+    if rank == 1:
+        if how == "announced":
+            roll.leave()
+        # between steps, nothing in flight: this rank is gone (its process ends)
+        if how == "announced":
+            dist.destroy_process_group()
+        return
+    # rank 0, step 1
+    roll.report(1)
+    t0 = time.monotonic()
+    try:
+        roll.check(1)
+        learned = "nothing"
+    except sharding.PeerLost as e:
+        learned = str(e)
+    waited = time.monotonic() - t0
+    # had it launched anyway: the collective ends with an error within the group's timeout, not a hang
+    t1 = time.monotonic()
+    try:
+        dist.all_gather(out, t)
+        collective = "completed"
+    except Exception as e:                      # gloo reports a closed connection or a timeout
+        collective = type(e).__name__
+    took = time.monotonic() - t1
+    with open(os.path.join(out_dir, "rank0.txt"), "w") as f:
+        f.write(f"{learned}\n{waited:.3f}\n{collective}\n{took:.3f}\n")
+
+
+@pytest.mark.parametrize("how", ["announced", "silent"])
+def test_rank_leaving_between_steps_is_seen_on_the_host(tmp_path, how):
+    port, store_port = _free_port(), _free_port()
+    mp.spawn(_leaving_worker, args=(2, port, store_port, how, str(tmp_path)), nprocs=2, join=True)
+    learned, waited, collective, took = open(tmp_path / "rank0.txt").read().splitlines()
+    if how == "announced":
+        assert "rank 1 left before step 1" in learned and float(waited) < 1.0
+    else:
+        assert "has not reported step 1" in learned and 0.9 <= float(waited) < 5.0
+    assert collective != "completed" and float(took) < 30.0
