@@ -645,10 +645,10 @@ def main():
         if keys_pick:
             # across the ranks: the exchanged pick must be the arg-max of all ranks' logits, on every rank
             import torch
-            mine = torch.from_numpy(want[0].view(np.int16).reshape(-1).copy())
+            mine = torch.from_numpy(want[0].view(np.uint16).reshape(-1).astype(np.int32))   # gloo carries no 16-bit integers
             allv = [torch.zeros_like(mine) for _ in range(world)]
             dist.all_gather(allv, mine)
-            full = torch.cat(allv).numpy().view(np.float16).astype(np.float32)
+            full = torch.cat(allv).numpy().astype(np.uint16).view(np.float16).astype(np.float32)
             best = int(np.flatnonzero(full == full.max())[0])
             toks = [torch.zeros(1, dtype=torch.int64) for _ in range(world)]
             dist.all_gather(toks, torch.tensor([want[1]], dtype=torch.int64))
