@@ -389,7 +389,6 @@ static int run_gemm_tc(nn_context* c, int fmt, const LinArgs& a, int M, const ch
     if (a.nseg != 1 || !(a.epi == EPI_STORE || a.epi == EPI_RESIDUAL)) return NN_OK;
     const LinSeg& sg = a.seg[0];
     if (!gemm_tc_supported(fmt, M, sg.N, a.K, a.x, sg.W, sg.out)) return NN_OK;
-    if (getenv("NNB_NO_TC")) return NN_OK;
     cudaError_t e = launch_gemm_tc(fmt, sg.W, sg.scale, a.x, sg.out, M, sg.N, a.K, sg.ld_out, a.epi, a.status, a.peer_out, a.npeer, &a.sig, c->stream);
     if (e != cudaSuccess) return NN_FAIL(NN_ERR_CUDA, "%s: tensor-core launch failed: %s (M=%d N=%d K=%d)", who, cudaGetErrorString(e), M, sg.N, a.K);
     c->launches++;

@@ -389,7 +389,7 @@ def sharded_projections(pkg, ctx, synth, comm, rank, world, dist, reps=12):
             for b in sym:
                 comm.symm_free(b)
         else:
-            t_fused = t_lin + t_ag
+            t_fused, t_ag = t_lin, 0.0   # one rank: nothing to gather
         # the whole operator on one GPU, timed the same way, for the efficiency figure t1 / (G * tG)
         t_one = t_lin
         if world > 1:
