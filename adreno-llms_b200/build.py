@@ -14,7 +14,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 LIB_DIR = os.path.join(HERE, "lib")
 LIB = os.path.join(LIB_DIR, "libnnopt_b200.so")
-SOURCES = ["api.cpp", "weights.cpp", "comm.cpp", "comm_kernels.cu", "gemv_stream.cu", "decode_plan.cu", "plan.cpp", "gemv_generic.cu", "misc.cu", "gemm_tc.cu", "noalloc.cu"]
+SOURCES = ["api.cpp", "weights.cpp", "comm.cpp", "comm_kernels.cu", "gemv_stream.cu", "stage_image.cu", "decode_plan.cu", "plan.cpp", "gemv_generic.cu", "misc.cu", "gemm_tc.cu", "noalloc.cu"]
 ARCH = ["-gencode", "arch=compute_100a,code=sm_100a"]
 
 

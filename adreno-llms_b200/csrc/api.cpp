@@ -196,6 +196,12 @@ extern "C" int nn_init(int device, nn_context** out) {
     }
     // normalised activations for the norm-then-project calls that cannot fuse the norm: sized for the
     // decode shapes up front so that such calls also work inside a recording (it grows outside one)
+    // the staged activations of a batched call never exceed the shared memory of one block
+    c->stage_img_bytes = (size_t)256 << 10;
+    if (cudaMalloc(&c->stage_img, c->stage_img_bytes) != cudaSuccess || cudaMemset(c->stage_img, 0, c->stage_img_bytes) != cudaSuccess) {
+        delete c;
+        return NN_FAIL(NN_ERR_CUDA, "nn_init: cudaMalloc failed");
+    }
     c->norm_scratch_bytes = (size_t)1 << 20;
     if (cudaMalloc(&c->norm_scratch, c->norm_scratch_bytes) != cudaSuccess) {
         delete c;
@@ -225,6 +231,7 @@ extern "C" int nn_shutdown(nn_context* c) {
     if (c->flush_buf) cudaFree(c->flush_buf);
     if (c->argmax_slot) cudaFree(c->argmax_slot);
     if (c->norm_scratch) cudaFree(c->norm_scratch);
+    if (c->stage_img) cudaFree(c->stage_img);
     if (c->sk_scratch) cudaFree(c->sk_scratch);
     if (c->sk_flags) cudaFree(c->sk_flags);
     if (c->status_host) cudaFreeHost(c->status_host);
@@ -428,7 +435,10 @@ static int run_linear(nn_context* c, int fmt, LinArgs a, int M_total, const char
         // context scratch first
         LinArgs probe = a;
         probe.M = M_total;
-        bool fused = M_total <= 16 && stream_supported(fmt, M_total, a.K, probe);
+        // a batched call (2..16 rows) normalises in the launch that stages its activations, so the
+        // projection itself needs no room for the normalised rows
+        if (M_total >= 2) probe.norm_w = nullptr;
+        bool fused = M_total <= 16 && stream_supported(fmt, M_total, a.K, probe) && (M_total == 1 || (size_t)a.K * 2 <= ((size_t)48 << 10));
         if (fused) fused = stream_plan(fmt, probe, c->sm_count, c->smem_limit).ok;
         if (!fused) {
             const size_t need = (size_t)M_total * a.K * 2;
@@ -464,6 +474,7 @@ static int run_linear(nn_context* c, int fmt, LinArgs a, int M_total, const char
     int slice = 16;
     {
         LinArgs probe = a;
+        if (M_total >= 2) probe.norm_w = nullptr;
         while (slice > 1) {
             probe.M = M_total < slice ? M_total : slice;
             if (!stream_supported(fmt, probe.M, a.K, probe) || stream_plan(fmt, probe, c->sm_count, c->smem_limit).ok) break;
@@ -479,9 +490,27 @@ static int run_linear(nn_context* c, int fmt, LinArgs a, int M_total, const char
         for (int p = 0; p < a.npeer; ++p) a.peer_out[p] = peer0[p] + (size_t)m0 * a.seg[0].ld_out;
         cudaError_t e;
         StreamPlan p = {};
-        if (stream_supported(fmt, a.M, a.K, a)) p = stream_plan(fmt, a, c->sm_count, c->smem_limit);
+        LinArgs b = a;
+        // Measured on whole batched steps: int8 and fp16 always gain from the staging launch; Q4 rows are cheap to
+        // stage in place, so it pays only from about 12K activation values (or when there is a norm to apply)
+        const bool stage_pays = fmt != FMT_Q4 || (long long)a.M * a.K >= 12288 || a.norm_w != nullptr;
+        if (a.M >= 2 && stage_pays && stream_supported(fmt, a.M, a.K, a) && stage_image_bytes(fmt, a.M, a.K) <= c->stage_img_bytes) {
+            // batched: the activations (normalised when asked) are staged once, by a launch of their own
+            b.norm_w = nullptr;
+            b.staged = (const uint8_t*)c->stage_img;
+            b.staged_bytes = (unsigned)stage_image_bytes(fmt, a.M, a.K);
+            p = stream_plan(fmt, b, c->sm_count, c->smem_limit);
+            if (p.ok) {
+                e = launch_stage_image(fmt, a.x, a.M, a.K, a.norm_w, a.norm_eps, (uint8_t*)c->stage_img, c->stream, c->use_pdl);
+                if (e != cudaSuccess) return NN_FAIL(NN_ERR_CUDA, "%s: staging launch failed: %s (M=%d K=%d)", who, cudaGetErrorString(e), a.M, a.K);
+                c->launches++;
+            } else {
+                b = a;
+            }
+        }
+        if (!p.ok && stream_supported(fmt, a.M, a.K, a)) p = stream_plan(fmt, a, c->sm_count, c->smem_limit);
         if (p.ok) {
-            e = launch_stream(fmt, a, p, c->stream, c->use_pdl);
+            e = launch_stream(fmt, b, p, c->stream, c->use_pdl);
             if (e == cudaSuccess && M_total == 1) note_recorded(c, fmt, a, p);
         } else {
             if (a.npeer > 0)

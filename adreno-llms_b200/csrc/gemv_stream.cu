@@ -143,11 +143,13 @@ __global__ void __launch_bounds__(THREADS) linear_stream_kernel(const __grid_con
 
     if (tid < 16) reinterpret_cast<uint32_t*>(smem)[tid] = 0u;
     if (FMT == FMT_INT8 && tid >= 32 && tid < 48) reinterpret_cast<uint32_t*>(xs + 3 * aM * geo.xstride)[tid - 32] = 0u;  // per-row max words
+    const uint32_t xbar = s_base + geo.off_x - 8;  // batched calls: the staged activations have landed
     if (tid == 0) {
         for (int s = 0; s < stages; ++s) {
             mbar_init(full0 + s * 8, (FMT == FMT_Q4 && !ka.scale_tma) ? 1u + NCW * 32u : 1u);
             mbar_init(empty0 + s * 8, (uint32_t)NCW);
         }
+        if (!ONE) mbar_init(xbar, 1u);
         mbar_init_fence();
     }
     __syncthreads();
@@ -386,6 +388,15 @@ __global__ void __launch_bounds__(THREADS) linear_stream_kernel(const __grid_con
     pdl_wait_prior_grid();
     if (n_items > 0 && writer) prefetch_residual(tile_first);
     const uint16_t* x_src = a.x;
+    if (!ONE && a.staged != nullptr) {
+        // the launch before this one (stage_image_kernel) wrote the staged form of all M rows in this
+        // kernel's shared-memory layout: one bulk copy instead of M rows converted by every block
+        if (tid == 0) {
+            mbar_arrive_expect_tx(xbar, a.staged_bytes);
+            bulk_g2s(smem_u32(xs), a.staged, a.staged_bytes, xbar, l2_policy_evict_normal());
+        }
+        if (!mbar_wait_bounded(xbar, 0u)) *reinterpret_cast<volatile int*>(a_status) = 5;
+    } else {
     if (a_norm) {
         // RMSNorm prologue: the normalised fp16 rows go to shared memory and the staging below
         // reads them from there
@@ -395,6 +406,7 @@ __global__ void __launch_bounds__(THREADS) linear_stream_kernel(const __grid_con
     }
     if (FMT == FMT_INT8) stage_x_int8(x_src, aM, aK, xs, geo.xstride, tid, NCW * 32);
     else stage_x<FMT>(x_src, aM, aK, xs, geo.xstride, reinterpret_cast<float*>(smem + geo.off_ctab), tid, NCW * 32);
+    }
     asm volatile("bar.sync 1, %0;" ::"n"(NCW * 32) : "memory");
 
 
@@ -620,9 +632,9 @@ __global__ void __launch_bounds__(THREADS) linear_stream_kernel(const __grid_con
                 float v = sel == 0 ? v00 : sel == 1 ? v01 : sel == 2 ? v10 : v11;
                 const int n = row0 + lane;
                 if (n < seg_n) {
-                    if (FMT == FMT_INT8) v *= __half2float(__ushort_as_half(sc1));
+                    if (FMT == FMT_INT8) v = __fmul_rn(v, __half2float(__ushort_as_half(sc1)));  // roundings as in finish_row
                     if (epi == EPI_RESIDUAL) {
-                        v = __half2float(__ushort_as_half(res1)) + v;
+                        v = __fadd_rn(__half2float(__ushort_as_half(res1)), v);
                     } else if (epi == EPI_SILU_GATE) {
                         const float gt = __half2float(__ushort_as_half(res1));
                         v = gt * (1.0f / (1.0f + expf(-gt))) * v;
@@ -654,9 +666,9 @@ __global__ void __launch_bounds__(THREADS) linear_stream_kernel(const __grid_con
                             const int m = nt * 8 + 2 * t + j;
                             if (m >= m_count) continue;
                             float v = acc[0][rb][nt][i2 * 2 + j];
-                            if (FMT == FMT_INT8) v *= __half2float(__ushort_as_half(sc_reg[rb][i2]));
+                            if (FMT == FMT_INT8) v = __fmul_rn(v, __half2float(__ushort_as_half(sc_reg[rb][i2])));  // roundings as in finish_row
                             if (epi == EPI_RESIDUAL) {
-                                v = __half2float(__ushort_as_half((uint16_t)res_reg[rb][i2][nt][j])) + v;
+                                v = __fadd_rn(__half2float(__ushort_as_half((uint16_t)res_reg[rb][i2][nt][j])), v);
                             } else if (epi == EPI_SILU_GATE) {
                                 const float gt = __half2float(__ushort_as_half((uint16_t)res_reg[rb][i2][nt][j]));
                                 v = gt * (1.0f / (1.0f + expf(-gt))) * v;
@@ -924,7 +936,16 @@ StreamPlan stream_plan(int fmt, const LinArgs& a, int sm_count, size_t smem_limi
     const int nt = M > 8 ? 2 : 1;
     const int rb_cols = ((rb + 127) / 128) * 128;
     const int warp_rows = dual ? 16 : WARP_ROWS;
-    const int kw = count_tiles(a, NCW * warp_rows) < 2 * sm_count && rb_cols >= 256 ? NCW : 1;
+    int kw = count_tiles(a, NCW * warp_rows) < 2 * sm_count && rb_cols >= 256 ? NCW : 1;
+    if (kw != 1 && fmt == FMT_Q4 && a.sk_scratch && a.sk_flags) {
+        // Between one and two 128-row tiles per SM with long rows (28672 x 8192: 224 tiles of 16 chunks): whole-row
+        // tiles dealt out evenly as pipeline items (the balanced launch below) beat the K split, which pays a
+        // four-way reduction and an epilogue per 32 rows (measured 33.8 against 37.6 us); with fewer than eight
+        // items per block the balanced launch does not apply and the K split stays (24576 x 4096: 16.6 against 19.6 us)
+        const int t128 = count_tiles(a, NCW * warp_rows);
+        const long long items = (long long)t128 * ((rb + 255) / 256);
+        if (t128 > sm_count && items >= (long long)8 * 2 * sm_count) kw = 1;
+    }
     int kcb = 256;
     if (kw != 1) {
         kcb = (((rb + NCW - 1) / NCW + 127) / 128) * 128;  // one chunk per consumer when the row is short

@@ -37,6 +37,8 @@ struct nn_context {
     int* status_host = nullptr;                // mapped pinned word written by kernels
     int* status_dev = nullptr;
     unsigned long long* argmax_slot = nullptr;
+    void* stage_img = nullptr;      // staged activations of a batched call, written once per launch (stage_image.cu)
+    size_t stage_img_bytes = 0;
     void* norm_scratch = nullptr;   // normalised activations when the fused prologue does not apply
     size_t norm_scratch_bytes = 0;
     float* sk_scratch = nullptr;   // partial sums of blocks that share a tile (balanced K-streaming)

@@ -73,6 +73,10 @@ struct LinArgs {
     // x_used[m][k] = half((x[m][k] * rsqrt(mean_k x[m]^2 + eps)) * norm_w[k])
     const uint16_t* norm_w;  // fp16 [K], null = no norm
     float norm_eps;
+    // batched calls (M >= 2): the staged form of the activations, written once per launch by
+    // stage_image_kernel in the kernel's own shared-memory layout; every block copies it in
+    const uint8_t* staged;
+    unsigned staged_bytes;
     float* sk_scratch;    // [blocks][consumer threads][2 * NT * 4] partial sums
     unsigned* sk_flags;   // [blocks] "partial written", consumed and cleared by the tile's owner
     int streamk;
@@ -137,6 +141,10 @@ cudaError_t launch_argmax_half(const uint16_t* v, int n, int* out_idx, unsigned 
 cudaError_t launch_fill_u64(unsigned long long* p, unsigned long long v, cudaStream_t st);
 cudaError_t launch_argmax_finish(const unsigned long long* slot, int* out_idx, cudaStream_t st);
 cudaError_t launch_l2_flush(void* buf, size_t bytes, cudaStream_t st);
+// the staged activations of a batched call (layout of the streaming kernel's shared memory), with the optional RMSNorm
+size_t stage_image_bytes(int fmt, int M, int K);
+cudaError_t launch_stage_image(int fmt, const uint16_t* x, int M, int K, const uint16_t* norm_w, float eps, uint8_t* img, cudaStream_t st,
+                               bool pdl);
 // read-bandwidth probes over `bytes` (a multiple of 16 KiB) at src; sink: 256 floats; status: one word, set on a timed-out wait
 cudaError_t launch_probe_loads(const void* src, size_t bytes, float* sink, cudaStream_t st);
 cudaError_t launch_probe_tma(const void* src, size_t bytes, unsigned* status, cudaStream_t st);

@@ -569,9 +569,11 @@ __device__ __forceinline__ void chunk_q4(const LaneGeo<NT>& L, uint32_t sw, int 
 // `prev` = the fp16 bits the in-place epilogues update (residual value, or the gate).
 template <int FMT>
 __device__ __forceinline__ uint16_t finish_row(float v, uint16_t scale_bits, int epi, uint16_t prev) {
-    if (FMT == FMT_INT8) v *= __half2float(__ushort_as_half(scale_bits));
+    // explicit roundings (no fused multiply-add across the two steps): every kernel that finishes a row
+    // (single-token, batched, resident) must give the same bits
+    if (FMT == FMT_INT8) v = __fmul_rn(v, __half2float(__ushort_as_half(scale_bits)));
     if (epi == EPI_RESIDUAL) {
-        v = __half2float(__ushort_as_half(prev)) + v;
+        v = __fadd_rn(__half2float(__ushort_as_half(prev)), v);
     } else if (epi == EPI_SILU_GATE) {
         const float gt = __half2float(__ushort_as_half(prev));
         v = gt * (1.0f / (1.0f + expf(-gt))) * v;

@@ -322,3 +322,41 @@ def test_linear_argmax_matches_linear_then_argmax(nnb, ctx, fmt, N, K):
     qw.release()
     for b_ in (logits, logits2, idx, idx2):
         ctx.free(b_)
+
+
+@pytest.mark.parametrize("fmt", FMTS)
+@pytest.mark.parametrize("N,K", [(1056, 1024), (576, 1536), (4864, 896)])
+def test_batch_rows_are_bitwise_the_single_token_results(nnb, ctx, fmt, N, K):
+    """Up to 16 rows share one pass over the weights; the activations of such a call are staged
+    once by a launch of their own.  Row m of the batch must carry exactly the bits of the
+    single-token call on row m (the reference's quantised M > 1 IS a loop of M = 1 calls,
+    src/models/lfm2-5-350m/src/model.cpp:243-251), for every M and for the fused forms."""
+    W, s = make_weight(fmt, N, K, 155)
+    qw = nnb.QuantWeight(ctx, fmt, W, s)
+    x = make_x(16, K, 156)
+    x[3] *= np.float16(37.0)                  # rows of different magnitude: the int8 rescale is per row
+    x[7] *= np.float16(0.01)
+    xb = ctx.upload(x.view(np.uint16))
+    ob = ctx.alloc(16 * N * 2)
+    singles = []
+    for m in range(16):
+        ctx.linear(1, N, K, xb + m * K * 2, qw.buf, ob)
+        singles.append(ctx.download(ob, (N,), np.uint16).copy())
+    singles = np.stack(singles)
+    for M in (2, 3, 8, 9, 13, 16):
+        ctx.upload(np.full((M, N), 0x7E00, np.uint16), ob)
+        ctx.linear(M, N, K, xb, qw.buf, ob)
+        got = ctx.download(ob, (M, N), np.uint16)
+        assert np.array_equal(got, singles[:M]), f"{fmt} {N}x{K} M={M}: a batch row differs from its single-token result"
+    # in-place residual, batched against single
+    r = make_x(16, N, 157)
+    rb = ctx.upload(r.view(np.uint16))
+    for m in range(16):
+        ctx.linear_add(1, N, K, xb + m * K * 2, qw.buf, rb + m * N * 2)
+    want = ctx.download(rb, (16, N), np.uint16).copy()
+    ctx.upload(r.view(np.uint16), rb)
+    ctx.linear_add(16, N, K, xb, qw.buf, rb)
+    assert np.array_equal(ctx.download(rb, (16, N), np.uint16), want)
+    qw.release()
+    for b in (xb, ob, rb):
+        ctx.free(b)

@@ -46,8 +46,10 @@ def test_rmsnorm_linear_fused_prologue(nnb, ctx, fmt, M, N, K):
     got = ctx.download(out, (M, N), np.uint16).view(np.float16)
     want = cpu.linear(fmt, cpu.rmsnorm(x, g, eps), W, s)
     check_close(got, want, what=f"rmsnorm->linear {fmt} M={M} K={K}")
-    if M <= 16 and K % 128 == 0:
+    if M == 1 and K % 128 == 0:
         assert launches == 1            # the norm is the projection kernel's prologue
+    elif M <= 16 and K % 128 == 0:
+        assert launches == 2            # batched: the norm runs once, in the launch that stages the activations
     qw.release()
     for b in (dx, dg, out):
         ctx.free(b)
