@@ -201,13 +201,13 @@ __global__ void __launch_bounds__(gemm_threads(WFMT)) linear_gemm_tc_kernel(cons
         // ---- TMA producer: one lane walks (tile, K block) and keeps the ring full ----
         if (lane == 0) {
             const uint64_t policy = l2_policy_evict_normal();
-            int it = 0;
+            int it = 0, s = 0;
+            uint32_t ph = 0;   // parity of the ring pass (it / g_stages) & 1, kept without divisions
             bool ok = true;
             for (int tile = blockIdx.x; tile < ntiles && ok; tile += gridDim.x) {
                 const int wt = tile / g_ntok, tt = tile - wt * g_ntok;
-                for (int kb = 0; kb < nkb; ++kb, ++it) {
-                    const int s = it % g_stages;
-                    if (it >= g_stages && !mbar_wait_bounded(empty0 + s * 8, (uint32_t)(((it / g_stages) - 1) & 1))) {
+                for (int kb = 0; kb < nkb; ++kb, ++it, s = (s + 1 == g_stages ? 0 : s + 1), ph ^= (s == 0 ? 1u : 0u)) {
+                    if (it >= g_stages && !mbar_wait_bounded(empty0 + s * 8, ph ^ 1u)) {
                         *reinterpret_cast<volatile int*>(g_status) = 3;
                         ok = false;
                         break;
@@ -227,7 +227,8 @@ __global__ void __launch_bounds__(gemm_threads(WFMT)) linear_gemm_tc_kernel(cons
         // ---- MMA issuer: one lane; accumulators alternate between two tensor-memory halves ----
         if (lane == 0) {
             const uint32_t idesc = instr_desc_f16(g_bn);
-            int it = 0, tl = 0;
+            int it = 0, tl = 0, s = 0;
+            uint32_t ph = 0;
             bool ok = true;
             for (int tile = blockIdx.x; tile < ntiles && ok; tile += gridDim.x, ++tl) {
                 const int acc = tl & 1;
@@ -237,9 +238,8 @@ __global__ void __launch_bounds__(gemm_threads(WFMT)) linear_gemm_tc_kernel(cons
                 }
                 tc_fence_after();
                 const uint32_t tmem_d = tmem_base + (uint32_t)(acc * g_cols);
-                for (int kb = 0; kb < nkb; ++kb, ++it) {
-                    const int s = it % g_stages;
-                    if (!mbar_wait_bounded(full0 + s * 8, (uint32_t)((it / g_stages) & 1))) {
+                for (int kb = 0; kb < nkb; ++kb, ++it, s = (s + 1 == g_stages ? 0 : s + 1), ph ^= (s == 0 ? 1u : 0u)) {
+                    if (!mbar_wait_bounded(full0 + s * 8, ph)) {
                         *reinterpret_cast<volatile int*>(g_status) = 4;
                         ok = false;
                         break;
@@ -286,8 +286,8 @@ __global__ void __launch_bounds__(gemm_threads(WFMT)) linear_gemm_tc_kernel(cons
         const int grp = dq / GRP_THREADS, dt = dq % GRP_THREADS;
         const int K32 = g.K / 32;
         const uint16_t* const q4s = g.q4_scale;
-        int it = 0, rit = 0;   // operand stages and packed spans passed so far
-        bool ok = true, span_waited = false;
+        int it = 0, rit = -1;   // operand stages and packed spans passed so far
+        bool ok = true;
         constexpr int Q4_PASSES = BM * 2 / GRP_THREADS, I8_PASSES = BM * 4 / GRP_THREADS;
         // Q4: a thread expands the same Q4_PASSES weight rows and the same half (blk) of every K block
         // it handles, so its block scales are entries of those rows' scale vectors: one aligned
@@ -307,26 +307,61 @@ __global__ void __launch_bounds__(gemm_threads(WFMT)) linear_gemm_tc_kernel(cons
 #pragma unroll
             for (int ps = 0; ps < Q4_PASSES; ++ps) sv_next[ps] = load_group(blockIdx.x, 0, ps);
         }
-        for (int tile = blockIdx.x; tile < ntiles && ok; tile += gridDim.x) {
-            for (int kb = 0; kb < nkb; ++kb, ++it) {
-                const int s = it % g_stages;
-                const int r = rit % g_raw_stages, jspan = kb % RAW_SPAN;
-                const bool span_last = jspan == RAW_SPAN - 1 || kb == nkb - 1;
-                if (jspan == 0) span_waited = false;
-                if (WFMT == FMT_Q4 && q4_vec && (kb & 3) == 0) {
+        // A group expands the K block of every packed span whose place in the span is the group's number
+        // (spans hold as many K blocks as there are groups), so a warp steps through spans, not K blocks:
+        // the bookkeeping of the blocks it does not expand would otherwise cost more than the expansion.
+        static_assert(WFMT == FMT_FP16 || RAW_SPAN == NGRP, "one K block of every span per group");
+        // a thread expands the same rows and the same place of every span: its offsets inside a packed span and
+        // inside an operand slot never change
+        constexpr int NPASS = WFMT == FMT_INT8 ? I8_PASSES : Q4_PASSES;
+        uint32_t src_off[NPASS], dst_off[NPASS][4];
+#pragma unroll
+        for (int ps = 0; ps < NPASS; ++ps) {
+            const int task = ps * GRP_THREADS + dt;
+            if (WFMT == FMT_INT8) {
+                const int row = task >> 2, ch = task & 3;   // 16 codes = 16 k
+                const uint32_t rbase = (uint32_t)((row >> 3) * 1024 + (row & 7) * 128), x7 = (uint32_t)(row & 7);
+                src_off[ps] = rbase + (((uint32_t)(grp * 4 + ch) ^ x7) << 4);
+                dst_off[ps][0] = rbase + (((uint32_t)(2 * ch) ^ x7) << 4);
+                dst_off[ps][1] = rbase + (((uint32_t)(2 * ch + 1) ^ x7) << 4);
+                dst_off[ps][2] = dst_off[ps][3] = 0;
+            } else {
+                const int row = task >> 1, blk = task & 1;  // 32 nibbles = one scale block
+                const uint32_t rbase = (uint32_t)((row >> 3) * 1024 + (row & 7) * 128), x7 = (uint32_t)(row & 7);
+                src_off[ps] = rbase + (((uint32_t)(grp * 2 + blk) ^ x7) << 4);
+#pragma unroll
+                for (int j = 0; j < 4; ++j) dst_off[ps][j] = rbase + (((uint32_t)(4 * blk + j) ^ x7) << 4);
+            }
+        }
+        const int spans = (nkb + RAW_SPAN - 1) / RAW_SPAN;
+        // ring positions and pass parities are stepped, not divided out: four divisions per K block and warp were a
+        // visible share of the loop
+        int tl = 0, it_prev = 0, s = 0, r = -1;
+        uint32_t ph = 0, rph = 1;   // (it / g_stages) & 1 and (rit / g_raw_stages) & 1
+        for (int tile = blockIdx.x; tile < ntiles && ok; tile += gridDim.x, ++tl) {
+            for (int sp = 0; sp < spans; ++sp) {
+                ++rit;
+                if (++r == g_raw_stages) r = 0;
+                if (r == 0) rph ^= 1u;
+                const int kb = sp * RAW_SPAN + grp;
+                if (WFMT == FMT_Q4 && q4_vec) {
 #pragma unroll
                     for (int ps = 0; ps < Q4_PASSES; ++ps) {
                         sv_cur[ps] = sv_next[ps];
-                        sv_next[ps] = (kb + 4 < nkb) ? load_group(tile, (kb >> 2) + 1, ps) : load_group(tile + (int)gridDim.x, 0, ps);
+                        sv_next[ps] = (sp + 1 < spans) ? load_group(tile, sp + 1, ps) : load_group(tile + (int)gridDim.x, 0, ps);
                     }
                 }
-                if ((kb % NGRP) != grp) {   // another group's K block
-                    if (span_last) {
-                        __syncwarp();
-                        if (lane == 0) mbar_arrive(raw_empty0 + r * 8);
-                        ++rit;
-                    }
+                if (kb >= nkb) {   // a short last span: nothing of it for this group
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(raw_empty0 + r * 8);
                     continue;
+                }
+                it = tl * nkb + kb;
+                s += it - it_prev;
+                it_prev = it;
+                while (s >= g_stages) {
+                    s -= g_stages;
+                    ph ^= 1u;
                 }
                 uint16_t sc[Q4_PASSES];
 #pragma unroll
@@ -346,44 +381,43 @@ __global__ void __launch_bounds__(gemm_threads(WFMT)) linear_gemm_tc_kernel(cons
                 }
                 // the packed span has landed (this group's first K block of the span), and the MMAs that
                 // read this operand slot last are done
-                if ((!span_waited && !mbar_wait_bounded(raw_full0 + r * 8, (uint32_t)((rit / g_raw_stages) & 1))) ||
-                    (it >= g_stages && !mbar_wait_bounded(empty0 + s * 8, (uint32_t)(((it / g_stages) - 1) & 1)))) {
+                if (!mbar_wait_bounded(raw_full0 + r * 8, rph) || (it >= g_stages && !mbar_wait_bounded(empty0 + s * 8, ph ^ 1u))) {
                     if (lane == 0) *reinterpret_cast<volatile int*>(g_status) = 10;
                     ok = false;
                     break;
                 }
-                span_waited = true;
                 const uint32_t a_addr = ring + s * stage_bytes, raw = raw_ring + r * RAW_BYTES;
+                // all of the thread's packed pieces are read before the first conversion: the loads are
+                // volatile (ordered among themselves and with the stores), so a load placed after a store
+                // would wait for it and every pass would pay the shared-memory latency again
                 if (WFMT == FMT_INT8) {
+                    uint32_t w[I8_PASSES][4];
+#pragma unroll
+                    for (int ps = 0; ps < I8_PASSES; ++ps)
+                        asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(w[ps][0]), "=r"(w[ps][1]), "=r"(w[ps][2]), "=r"(w[ps][3]) : "r"(raw + src_off[ps]));
 #pragma unroll
                     for (int ps = 0; ps < I8_PASSES; ++ps) {
-                        const int task = ps * GRP_THREADS + dt, row = task >> 2, ch = task & 3;  // 16 codes = 16 k
-                        uint32_t w0, w1, w2, w3;
-                        asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(w0), "=r"(w1), "=r"(w2), "=r"(w3) : "r"(raw + (uint32_t)((row >> 3) * 1024 + (row & 7) * 128) + (((uint32_t)(jspan * 4 + ch) ^ (uint32_t)(row & 7)) << 4)));
                         uint32_t h[8];
-                        int8x4_to_half2x2(w0, h[0], h[1]);
-                        int8x4_to_half2x2(w1, h[2], h[3]);
-                        int8x4_to_half2x2(w2, h[4], h[5]);
-                        int8x4_to_half2x2(w3, h[6], h[7]);
-                        const uint32_t rbase = a_addr + (uint32_t)((row >> 3) * 1024 + (row & 7) * 128);
-                        const uint32_t x7 = (uint32_t)(row & 7);
-                        asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(rbase + (((uint32_t)(2 * ch) ^ x7) << 4)), "r"(h[0]), "r"(h[1]), "r"(h[2]), "r"(h[3]) : "memory");
-                        asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(rbase + (((uint32_t)(2 * ch + 1) ^ x7) << 4)), "r"(h[4]), "r"(h[5]), "r"(h[6]), "r"(h[7]) : "memory");
+                        int8x4_to_half2x2(w[ps][0], h[0], h[1]);
+                        int8x4_to_half2x2(w[ps][1], h[2], h[3]);
+                        int8x4_to_half2x2(w[ps][2], h[4], h[5]);
+                        int8x4_to_half2x2(w[ps][3], h[6], h[7]);
+                        asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(a_addr + dst_off[ps][0]), "r"(h[0]), "r"(h[1]), "r"(h[2]), "r"(h[3]) : "memory");
+                        asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(a_addr + dst_off[ps][1]), "r"(h[4]), "r"(h[5]), "r"(h[6]), "r"(h[7]) : "memory");
                     }
                 } else {
+                    uint32_t w[Q4_PASSES][4];
+#pragma unroll
+                    for (int ps = 0; ps < Q4_PASSES; ++ps)
+                        asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(w[ps][0]), "=r"(w[ps][1]), "=r"(w[ps][2]), "=r"(w[ps][3]) : "r"(raw + src_off[ps]));
 #pragma unroll
                     for (int ps = 0; ps < Q4_PASSES; ++ps) {
-                        const int task = ps * GRP_THREADS + dt, row = task >> 1, blk = task & 1;  // 32 nibbles = one scale block
-                        uint32_t w[4];
-                        asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(w[0]), "=r"(w[1]), "=r"(w[2]), "=r"(w[3]) : "r"(raw + (uint32_t)((row >> 3) * 1024 + (row & 7) * 128) + (((uint32_t)(jspan * 2 + blk) ^ (uint32_t)(row & 7)) << 4)));
                         const __half sh = __ushort_as_half(sc[ps]);
                         const __half2 s2 = __halves2half2(sh, sh);
-                        const uint32_t rbase = a_addr + (uint32_t)((row >> 3) * 1024 + (row & 7) * 128);
-                        const uint32_t x7 = (uint32_t)(row & 7);
 #pragma unroll
                         for (int j = 0; j < 4; ++j) {
                             uint32_t p04, p15, p26, p37;
-                            q4x8_to_half2x4(w[j], p04, p15, p26, p37);   // (n0,n4) (n1,n5) (n2,n6) (n3,n7), exact codes
+                            q4x8_to_half2x4(w[ps][j], p04, p15, p26, p37);   // (n0,n4) (n1,n5) (n2,n6) (n3,n7), exact codes
                             uint32_t o[4];
                             asm("prmt.b32 %0, %1, %2, 0x5410;" : "=r"(o[0]) : "r"(p04), "r"(p15));  // (n0, n1)
                             asm("prmt.b32 %0, %1, %2, 0x5410;" : "=r"(o[1]) : "r"(p26), "r"(p37));  // (n2, n3)
@@ -394,16 +428,15 @@ __global__ void __launch_bounds__(gemm_threads(WFMT)) linear_gemm_tc_kernel(cons
                                 const __half2 v = __hmul2(*reinterpret_cast<const __half2*>(&o[e]), s2);  // fp16(code * scale)
                                 o[e] = *reinterpret_cast<const uint32_t*>(&v);
                             }
-                            asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(rbase + (((uint32_t)(4 * blk + j) ^ x7) << 4)), "r"(o[0]), "r"(o[1]), "r"(o[2]), "r"(o[3]) : "memory");
+                            asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(a_addr + dst_off[ps][j]), "r"(o[0]), "r"(o[1]), "r"(o[2]), "r"(o[3]) : "memory");
                         }
                     }
                 }
                 fence_async_smem();   // the MMA reads the operand through the async proxy
                 __syncwarp();
-                if (lane == 0) mbar_arrive(full0 + s * 8);
-                if (span_last) {   // last K block of the span: hand it back
-                    if (lane == 0) mbar_arrive(raw_empty0 + r * 8);
-                    ++rit;
+                if (lane == 0) {
+                    mbar_arrive(full0 + s * 8);
+                    mbar_arrive(raw_empty0 + r * 8);   // this warp is done with the span
                 }
             }
         }
@@ -561,32 +594,43 @@ cudaError_t launch_gemm_tc(int fmt, const void* W, const uint16_t* scale, const 
     if (npeer < 0 || npeer > 7) return cudaErrorInvalidValue;
     g.npeer = npeer;
     for (int p = 0; p < 7; ++p) g.peer_out[p] = p < npeer ? peer_out[p] : nullptr;
-    const int bn_max = 256;
-    int bn = M >= bn_max ? bn_max : ((M + 15) / 16) * 16;
-    g.bn = bn;
-    g.ntok = (M + bn - 1) / bn;
-    g.tmem_cols = 32;
-    while (g.tmem_cols < bn) g.tmem_cols *= 2;
-    const int b_bytes = ((bn * BK * 2 + 1023) / 1024) * 1024;
-    const int raw_bytes = fmt == FMT_FP16 ? 0 : BM * 128;  // packed spans: 128 bytes of each of the tile's rows
-    const int stage_bytes = A_BYTES + b_bytes;
     // The epilogue goes through a staging tile in shared memory and one tensor store per tile
     // when the output rows keep 16-byte pitch and alignment (lane-by-lane stores otherwise).
     bool aligned = (ld_out % 8) == 0 && (reinterpret_cast<uintptr_t>(out) & 15) == 0;
     for (int p = 0; p < npeer; ++p) aligned = aligned && (reinterpret_cast<uintptr_t>(peer_out[p]) & 15) == 0;
     g.tma_store = aligned ? 1 : 0;
-    const int out_rows = bn < OUT_ROWS ? ((bn + 31) / 32) * 32 : OUT_ROWS;  // the epilogue reads 32 columns at a time
-    const int out_bytes = g.tma_store ? out_rows * BM * 2 : 0;
-    // packed weights get a ring of their own, deep enough to cover the HBM latency
-    int raw_stages = 0;
-    if (raw_bytes) {
-        raw_stages = 4;
-        while (raw_stages > 2 && (227 * 1024 - 2048 - out_bytes - raw_stages * raw_bytes) / stage_bytes < 3) --raw_stages;
+    const int raw_bytes = fmt == FMT_FP16 ? 0 : BM * 128;  // packed spans: 128 bytes of each of the tile's rows
+    // The groups of expanding warps fill consecutive operand slots at the same time, each waiting for "the MMAs that
+    // read my slot one ring pass ago".  That wait is by phase parity, and it is only meaningful when the pass before
+    // that one is certainly over, which the group knows from its own previous K block as long as the ring has at
+    // least as many slots as there are groups (MMAs complete in order).  A ring shorter than the group count could let
+    // a group pass a stale phase and overwrite a slot in use, so the token tile is narrowed until the ring is deep enough.
+    const int min_stages = dq_warps(fmt) >= 4 ? dq_warps(fmt) / 4 : 2;
+    const int bn_max = 256;
+    int bn = M >= bn_max ? bn_max : ((M + 15) / 16) * 16;
+    int b_bytes = 0, stage_bytes = 0, out_bytes = 0, raw_stages = 0, stages = 0;
+    for (;;) {
+        b_bytes = ((bn * BK * 2 + 1023) / 1024) * 1024;
+        stage_bytes = A_BYTES + b_bytes;
+        const int out_rows = bn < OUT_ROWS ? ((bn + 31) / 32) * 32 : OUT_ROWS;  // the epilogue reads 32 columns at a time
+        out_bytes = g.tma_store ? out_rows * BM * 2 : 0;
+        // packed weights get a ring of their own, deep enough to cover the HBM latency
+        raw_stages = 0;
+        if (raw_bytes) {
+            raw_stages = 4;
+            while (raw_stages > 2 && (227 * 1024 - 2048 - out_bytes - raw_stages * raw_bytes) / stage_bytes < (min_stages > 3 ? min_stages : 3)) --raw_stages;
+        }
+        stages = (227 * 1024 - 2048 - out_bytes - raw_stages * raw_bytes) / stage_bytes;
+        if (stages > 6) stages = 6;
+        if (stages >= (min_stages > 2 ? min_stages : 2) || bn <= 32) break;
+        bn = (bn / 2 + 15) / 16 * 16;
     }
+    if (stages < (min_stages > 2 ? min_stages : 2)) return cudaErrorInvalidValue;
+    g.bn = bn;
+    g.ntok = (M + bn - 1) / bn;
+    g.tmem_cols = 32;
+    while (g.tmem_cols < bn) g.tmem_cols *= 2;
     g.raw_stages = raw_stages;
-    int stages = (227 * 1024 - 2048 - out_bytes - raw_stages * raw_bytes) / stage_bytes;
-    if (stages > 6) stages = 6;
-    if (stages < 2) return cudaErrorInvalidValue;
     g.stages = stages;
     g.out = out;
     g.row_scale = row_scale;

@@ -263,7 +263,7 @@ def test_argmax_agreement(nnb, ctx):
 
 @pytest.mark.parametrize("fmt,N,K,M", [("fp16", 896, 896, 64), ("fp16", 4864, 896, 512), ("fp16", 1000, 1024, 100), ("fp16", 256, 4864, 17),
                                        ("fp16", 640, 200, 48), ("int8", 1152, 896, 256), ("int8", 900, 576, 33), ("q4", 1024, 1024, 128),
-                                       ("q4", 4608, 1024, 64), ("fp16", 2048, 896, 2048)])
+                                       ("q4", 4608, 1024, 64), ("fp16", 2048, 896, 2048), ("q4", 640, 2048, 300), ("int8", 512, 1024, 300), ("q4", 1152, 8192, 257)])
 def test_tensor_core_path_large_m(nnb, ctx, fmt, N, K, M):
     """M > 16 (batched decode beyond 16 rows, prefill): the tcgen05 GEMM.  The reference is
     M independent M = 1 results; compared here against an fp64 product of the dequantised
