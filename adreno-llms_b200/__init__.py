@@ -97,6 +97,7 @@ def load():
         "nn_linear_argmax_sharded": ([vp, i, i, vp, vp, vp, vp], i),
         "nn_comm_signal": ([vp], i), "nn_comm_wait": ([vp, ctypes.c_uint], i),
         "nn_comm_pick_unsent": ([vp, ctypes.c_uint, vp], i),
+        "nn_linear_argmax_sharded_rows": ([vp, i, i, i, vp, vp, vp, vp], i),
         "nn_device_count": ([], i),
     }
     for name, (args, res) in sig.items():
@@ -333,6 +334,9 @@ class Comm:
 
     def linear_argmax_sharded(self, n_local, K, x, W, logits_local, out_idx):
         _check(self.ctx.L.nn_linear_argmax_sharded(self.h, n_local, K, x, W, logits_local, out_idx))
+
+    def linear_argmax_sharded_rows(self, M, n_local, K, x, W, logits_local, out_idx):
+        _check(self.ctx.L.nn_linear_argmax_sharded_rows(self.h, M, n_local, K, x, W, logits_local, out_idx))
 
     def pick_unsent(self, timeout_ms, out_idx):
         _check(self.ctx.L.nn_comm_pick_unsent(self.h, timeout_ms, out_idx))

@@ -79,7 +79,9 @@ struct nn_comm {
     int rank = 0, world = 1;
     std::vector<SymmAlloc> symm;
     unsigned* flags = nullptr;   // symmetric: word g is written by rank g's signal kernel
-    unsigned* epochs = nullptr;  // local: [0] signals sent, [1] waits done, [2] blocks done, [3] picks sent, [4] picks waited
+    unsigned* epochs = nullptr;  // local: [0] signals sent, [1] waits done, [2] blocks done, [3] picks sent, [4] picks waited,
+                                 // [5] batched picks done
+    int row_keys = -1;           // index in symm of the batched pick's key tables, allocated on first use
 };
 
 #define COMM_CUDA(call)                                                                                   \
@@ -307,6 +309,33 @@ extern "C" int nn_linear_argmax_sharded(nn_comm* c, int n_local, int K, nn_buf x
     if (rc) return rc;
     COMM_CUDA(nnb::launch_comm_pick(c->flags, c->world, c->epochs + 4, 2000, c->ctx->status_dev, c->ctx->use_pdl, (int*)out_idx, c->ctx->stream));
     c->ctx->launches++;
+    return NN_OK;
+}
+
+extern "C" int nn_linear_argmax_sharded_rows(nn_comm* c, int M, int n_local, int K, nn_buf x, nn_buf W, nn_buf logits_local, nn_buf out_idx) {
+    const char* who = "nn_linear_argmax_sharded_rows";
+    if (!c || !out_idx || !logits_local) return NN_FAIL(NN_ERR_ARG, "%s: null argument (the local logits are needed: the pick reads them)", who);
+    if (!c->flags) return NN_FAIL(NN_ERR_ARG, "%s: no symmetric buffer has been allocated on this communicator", who);
+    if (M < 1 || M > nnb::ROW_KEYS_MAX) return NN_FAIL(NN_ERR_ARG, "%s: M=%d outside 1..%d", who, M, nnb::ROW_KEYS_MAX);
+    if (n_local <= 0 || (long long)n_local * c->world > 0x7fffffffLL) return NN_FAIL(NN_ERR_ARG, "%s: bad n_local=%d", who, n_local);
+    if (c->row_keys < 0) {   // first use: the key tables (collective, like every symmetric allocation)
+        if (c->ctx->capturing) return NN_FAIL(NN_ERR_UNSUPPORTED, "%s: make the first call outside a recording (it allocates the key tables)", who);
+        SymmAlloc kt;
+        int rc = symm_alloc(c, nnb::ROW_KEYS_BYTES, &kt);
+        if (rc) return rc;
+        c->symm.push_back(kt);
+        c->row_keys = (int)c->symm.size() - 1;
+    }
+    // the projection of this rank's rows, into ordinary local memory
+    int rc = nnb::linear_to_peers(c->ctx, M, n_local, K, x, W, logits_local, nullptr, 0, nullptr, who);
+    if (rc) return rc;
+    nnb::RowKeyTables kt = {};
+    kt.world = c->world;
+    kt.rank = c->rank;
+    for (int g = 0; g < c->world; ++g) kt.table[g] = (unsigned long long*)c->symm[c->row_keys].base[g];
+    COMM_CUDA(nnb::launch_rows_keys((const uint16_t*)logits_local, M, n_local, c->rank * n_local, kt, c->epochs + 5, c->ctx->stream));
+    COMM_CUDA(nnb::launch_rows_pick(kt.table[c->rank], c->world, M, c->epochs + 5, 2000, c->ctx->status_dev, (int*)out_idx, c->ctx->stream));
+    c->ctx->launches += 2;
     return NN_OK;
 }
 

@@ -108,10 +108,115 @@ __global__ void comm_pick_kernel(const unsigned long long* tables, int world, un
 
 __global__ void comm_count_kernel(unsigned* counter) { *counter += 1u; }
 
+// One block per activation row m: the best (value, row) of this rank's n_local logits of that row, as the same tagged
+// 64-bit word the single-token pick uses (pick number | ordered fp16 value | ~row), stored into slot [pick & 1][rank][m]
+// of every rank's table.  The word is its own arrival mark.  The pick's number is one more than the counter, which the
+// pick kernel (the next launch on the stream) advances when it is done.
+__device__ __forceinline__ unsigned long long row_key(unsigned h, int col) {
+    if ((h & 0x7FFFu) > 0x7C00u) return 0ull;  // NaNs never win
+    const unsigned oh = (h & 0x8000u) ? (~h & 0xFFFFu) : (h | 0x8000u);  // order-preserving, never 0
+    return ((unsigned long long)oh << 32) | (unsigned long long)(0xFFFFFFFFu - (unsigned)col);
+}
+
+__global__ void __launch_bounds__(256) rows_keys_kernel(const uint16_t* __restrict__ logits, int n_local, int row_base, RowKeyTables kt,
+                                                       const unsigned* __restrict__ picks_done) {
+    const int m = blockIdx.x;
+    const uint16_t* row = logits + (size_t)m * n_local;
+    unsigned long long best = 0ull;
+    // 16-byte pieces where the row allows it (eight logits per load), single values at the ragged ends
+    const int head = (int)((16u - (unsigned)(reinterpret_cast<uintptr_t>(row) & 15u)) & 15u) / 2;
+    const int h0 = head < n_local ? head : n_local;
+    const int pieces = (n_local - h0) / 8;
+    for (int i = threadIdx.x; i < h0; i += blockDim.x) {
+        const unsigned long long k = row_key(row[i], row_base + i);
+        best = k > best ? k : best;
+    }
+    const uint4* v4 = reinterpret_cast<const uint4*>(row + h0);
+    for (int p = threadIdx.x; p < pieces; p += blockDim.x) {
+        const uint4 v = v4[p];
+        const unsigned w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            const unsigned h = (j & 1) ? (w[j >> 1] >> 16) : (w[j >> 1] & 0xFFFFu);
+            const unsigned long long k = row_key(h, row_base + h0 + p * 8 + j);
+            best = k > best ? k : best;
+        }
+    }
+    for (int i = h0 + pieces * 8 + threadIdx.x; i < n_local; i += blockDim.x) {
+        const unsigned long long k = row_key(row[i], row_base + i);
+        best = k > best ? k : best;
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        const unsigned long long other = __shfl_xor_sync(0xffffffffu, best, o);
+        best = other > best ? other : best;
+    }
+    __shared__ unsigned long long sm[8];
+    if ((threadIdx.x & 31) == 0) sm[threadIdx.x >> 5] = best;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        for (int w = 1; w < (int)(blockDim.x >> 5); ++w) best = sm[w] > best ? sm[w] : best;
+        const unsigned e = *picks_done + 1u;
+        // the tag is never 0, so a slot that no pick has written yet (the tables start zeroed; M may grow from call to
+        // call) cannot pass for an arrived word
+        const unsigned long long word = ((unsigned long long)(e % 65535u + 1u) << 48) | best;
+        for (int g = 0; g < kt.world; ++g) {
+            unsigned long long* dst = kt.table[g] + ((size_t)(e & 1u) * 8u + (unsigned)kt.rank) * ROW_KEYS_MAX + m;
+            asm volatile("st.relaxed.sys.global.u64 [%0], %1;" ::"l"(dst), "l"(word) : "memory");
+        }
+    }
+}
+
+// One block; thread m waits (bounded) for the G words of row m that carry this pick's number and takes the largest:
+// largest value, lowest row on ties, as on one device; -1 when every value of the row is NaN or a word did not arrive.
+// The last thing the block does is to advance the pick counter.
+__global__ void __launch_bounds__(1024) rows_pick_kernel(const unsigned long long* __restrict__ my_table, int world, int M, unsigned* picks_done,
+                                                        unsigned timeout_ms, int* status, int* __restrict__ out_rows) {
+    const int m = threadIdx.x;
+    const unsigned e = *picks_done + 1u;
+    if (m < M) {
+        const unsigned long long t0 = global_ns();
+        const unsigned long long limit = (unsigned long long)timeout_ms * 1000000ull;
+        unsigned long long best = 0ull;
+        bool arrived = true;
+        for (int g = 0; g < world && arrived; ++g) {
+            const unsigned long long* src = my_table + ((size_t)(e & 1u) * 8u + (unsigned)g) * ROW_KEYS_MAX + m;
+            unsigned long long w;
+            for (;;) {
+                asm volatile("ld.relaxed.sys.global.u64 %0, [%1];" : "=l"(w) : "l"(src) : "memory");
+                if ((unsigned)(w >> 48) == e % 65535u + 1u) break;
+                if (global_ns() - t0 > limit) {
+                    *reinterpret_cast<volatile int*>(status) = 7;
+                    arrived = false;
+                    break;
+                }
+                __nanosleep(32);
+            }
+            w &= 0x0000FFFFFFFFFFFFull;
+            best = w > best ? w : best;
+        }
+        out_rows[m] = (arrived && best) ? (int)(0xFFFFFFFFu - (unsigned)(best & 0xFFFFFFFFull)) : -1;
+    }
+    __syncthreads();   // every thread has read the counter
+    if (threadIdx.x == 0) *picks_done = e;
+}
+
 }  // namespace
 
 cudaError_t launch_comm_count(unsigned* counter, cudaStream_t st) {
     comm_count_kernel<<<1, 1, 0, st>>>(counter);
+    return cudaGetLastError();
+}
+
+cudaError_t launch_rows_keys(const uint16_t* logits, int M, int n_local, int row_base, const RowKeyTables& kt, const unsigned* picks_done,
+                             cudaStream_t st) {
+    rows_keys_kernel<<<M, 256, 0, st>>>(logits, n_local, row_base, kt, picks_done);
+    return cudaGetLastError();
+}
+
+cudaError_t launch_rows_pick(const unsigned long long* my_table, int world, int M, unsigned* picks_done, unsigned timeout_ms, int* status,
+                             int* out_rows, cudaStream_t st) {
+    rows_pick_kernel<<<1, 1024, 0, st>>>(my_table, world, M, picks_done, timeout_ms, status, out_rows);
     return cudaGetLastError();
 }
 

@@ -130,6 +130,14 @@ cudaError_t launch_comm_wait(const unsigned* my_flags, int world, unsigned* epoc
 // Row-sharded greedy pick: waits (bounded) for pick number *picks_waited + 1 of every rank in this
 // rank's key tables and writes the winning row (-1: every value was NaN, or the wait ran out).
 cudaError_t launch_comm_count(unsigned* counter, cudaStream_t st);
+// Row-sharded greedy pick of M rows at once.  Key tables: [2][8 ranks][ROW_KEYS_MAX] 64-bit words on every rank.
+constexpr int ROW_KEYS_MAX = 1024;
+constexpr size_t ROW_KEYS_BYTES = (size_t)2 * 8 * ROW_KEYS_MAX * 8;
+struct RowKeyTables { unsigned long long* table[8]; int world, rank; };
+cudaError_t launch_rows_keys(const uint16_t* logits, int M, int n_local, int row_base, const RowKeyTables& kt, const unsigned* picks_done,
+                             cudaStream_t st);
+cudaError_t launch_rows_pick(const unsigned long long* my_table, int world, int M, unsigned* picks_done, unsigned timeout_ms, int* status,
+                             int* out_rows, cudaStream_t st);
 cudaError_t launch_comm_pick(const unsigned* my_flags, int world, unsigned* picks_waited, unsigned timeout_ms, int* status, bool overlap,
                              int* out_row, cudaStream_t st);
 

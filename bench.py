@@ -388,8 +388,26 @@ def sharded_projections(pkg, ctx, synth, comm, rank, world, dist, reps=12):
                 dist.barrier()
             for b in sym:
                 comm.symm_free(b)
+            # greedy tokens of the M rows without moving the logits: M keys per rank cross NVLink
+            loc, toks = ctx.alloc(M * n * 2), ctx.alloc(M * 4)
+            t_pick = 0.0
+            for i in range(reps + 2):
+                ctx.l2_flush()
+                comm.signal()
+                comm.wait()
+                ctx.record(ev[0])
+                comm.linear_argmax_sharded_rows(M, n, K, x, qw.buf, loc, toks)
+                ctx.record(ev[1])
+                ctx.sync()
+                if i >= 2:
+                    t_pick += ctx.elapsed_ms(ev[0], ev[1])
+            if dist:
+                dist.barrier()
+            ctx.free(loc)
+            ctx.free(toks)
         else:
             t_fused, t_ag = t_lin, 0.0   # one rank: nothing to gather
+            t_pick = 0.0
         # the whole operator on one GPU, timed the same way, for the efficiency figure t1 / (G * tG)
         t_one = t_lin
         if world > 1:
@@ -407,7 +425,7 @@ def sharded_projections(pkg, ctx, synth, comm, rank, world, dist, reps=12):
                 if i >= 2:
                     t_one += ctx.elapsed_ms(ev[0], ev[1])
             qf.release()
-        t = [t_lin / reps * 1e3, t_ag / reps * 1e3, t_fused / reps * 1e3, t_one / reps * 1e3]
+        t = [t_lin / reps * 1e3, t_ag / reps * 1e3, t_fused / reps * 1e3, t_one / reps * 1e3, t_pick / reps * 1e3]
         if dist:
             import torch
             tt = torch.tensor(t, dtype=torch.float64)
@@ -418,6 +436,9 @@ def sharded_projections(pkg, ctx, synth, comm, rank, world, dist, reps=12):
                      "fused_gather_us": t[2],   # projection with peer stores + flag exchange, one call
                      "single_gpu_us": t[3],     # the unsharded operator on one GPU of this run
                      "efficiency_per_operator": t[3] / (world * t[2]) if t[2] > 0 else None,
+                     # projection + greedy token of every row with one key per row and rank exchanged (no logits moved)
+                     "sharded_pick_us": t[4] if world > 1 else None,
+                     "efficiency_with_sharded_pick": t[3] / (world * t[4]) if (world > 1 and t[4] > 0) else None,
                      "gbps_aggregate": b / (t[2] * 1e-6) / 1e9,
                      "tflops_aggregate": 2.0 * M * N * K / (t[2] * 1e-6) / 1e12})
         for e in ev:

@@ -304,6 +304,13 @@ int nn_comm_free(nn_comm* comm);
  *                       also stored there (ordinary device memory).  Every rank must make the
  *                       same sequence of these calls.  Needs one prior nn_comm_symm_alloc on the
  *                       communicator (which creates the flag and key words).
+ *   nn_linear_argmax_sharded_rows  the same pick for M activation rows at once (batched greedy decode,
+ *                       1 <= M <= 1024): each rank projects its rows of the weight into
+ *                       logits_local ([M][n_local] fp16, ordinary device memory, required), folds every
+ *                       row's n_local values into one key and stores the M keys in a table on every
+ *                       rank; out_index receives M device ints.  8*M bytes per rank cross NVLink
+ *                       instead of 2*M*N.  The first call allocates the key tables (collective; make
+ *                       it outside a recording).
  *   nn_comm_pick_unsent fault injection on the host: one pick round, counted like any other, in
  *                       which no rank stores its key.  The waiting kernel must give up after
  *                       timeout_ms (1..10000), write -1 to out_index, and the next nn_sync must
@@ -314,6 +321,7 @@ int nn_comm_symm_alloc(nn_comm* comm, size_t bytes, nn_buf* out);
 int nn_comm_symm_free(nn_comm* comm, nn_buf buf);
 int nn_linear_gather(nn_comm* comm, int M, int n_local, int K, nn_buf x, nn_buf W, nn_buf gathered);
 int nn_linear_argmax_sharded(nn_comm* comm, int n_local, int K, nn_buf x, nn_buf W, nn_buf logits_local_fp16, nn_buf out_index_i32);
+int nn_linear_argmax_sharded_rows(nn_comm* comm, int M, int n_local, int K, nn_buf x, nn_buf W, nn_buf logits_local_fp16, nn_buf out_index_i32);
 int nn_comm_pick_unsent(nn_comm* comm, unsigned timeout_ms, nn_buf out_index_i32);
 int nn_comm_signal(nn_comm* comm);
 int nn_comm_wait(nn_comm* comm, unsigned timeout_ms);

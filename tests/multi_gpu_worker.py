@@ -126,6 +126,36 @@ def main():
         qw.release()
         for b in (tok, local, g1):
             ctx.free(b)
+    # the batched pick: M tokens per call, one key per row and rank instead of the logits
+    for fmt, N, K, M in (("int8", 4096, 576, 8), ("q4", 2048, 1024, 40), ("int8", 3072, 896, 256), ("fp16", 1536, 896, 5)):
+        W, s = make_weight(fmt, N, K, 9300 + N)
+        Wl, sl = sharding.shard_weight(fmt, W, s, world, rank)
+        lo, n = sharding.shard_rows(N, world, rank)
+        qw = pkg.QuantWeight(ctx, fmt, Wl, sl)
+        toks = ctx.alloc(M * 4)
+        local = ctx.alloc(M * n * 2)
+        g1 = ctx.alloc(M * n * 2 * world)
+        for rep in range(3):
+            x = make_x(M, K, 9400 + K + rep)
+            if rep == 2:
+                x[0] = 0                               # a row whose logits all tie at 0: row 0 of rank 0 wins
+            dx = ctx.upload(x.view(np.uint16))
+            ctx.linear(M, n, K, dx, qw.buf, g1 + rank * M * n * 2)
+            comm.all_gather(g1 + rank * M * n * 2, g1, M * n * 2)
+            bits = sharding.gathered_to_row_major(ctx.download(g1, (world, M, n), np.uint16), world, M, N)
+            b32 = bits.astype(np.uint32)
+            want = np.argmax(np.where(b32 & 0x8000, 0xFFFF - b32, b32 | 0x8000), axis=1)
+            comm.linear_argmax_sharded_rows(M, n, K, dx, qw.buf, local, toks)
+            got = ctx.download(toks, (M,), np.int32)
+            if not np.array_equal(got, want):
+                bad = int((got != want).sum())
+                failures.append(f"batched pick {fmt} N={N} K={K} M={M} rep {rep}: {bad} of {M} rows differ from the gathered logits' arg-max")
+            ctx.free(dx)
+        ctx.sync()
+        dist.barrier()
+        qw.release()
+        for b in (toks, local, g1):
+            ctx.free(b)
     ctx.sync()
     dist.barrier()
     comm.close()

@@ -191,3 +191,46 @@ def test_nccl_that_cannot_be_loaded_is_a_comm_error(nnb, built_lib):
     rc, made, msg = first.split(" ", 2)
     assert int(rc) == nnb.NN_ERR_COMM and made == "False" and "NNB_NCCL_LIB" in msg
     assert second == "0 True"          # a single rank needs no NCCL at all
+
+
+def test_batched_sharded_pick_single_rank(nnb, ctx):
+    """nn_linear_argmax_sharded_rows on one rank: M greedy tokens from one call, each the arg-max of
+    its row of logits (lowest index on ties, -1 for a row of NaNs), over repeated calls with
+    different M (the key tables alternate and grow)."""
+    comm = nnb.Comm(ctx, None, 0, 1)
+    try:
+        comm.symm_alloc(256)
+        N, K = 4096, 576
+        W, s = make_weight("int8", N, K, 911)
+        qw = nnb.QuantWeight(ctx, "int8", W, s)
+        for rep, M in enumerate((8, 40, 3, 300, 16)):
+            x = make_x(M, K, 912 + rep)
+            if M >= 3:
+                x[1] = 0                                   # every logit of this row ties at 0: index 0 wins
+                x[2, 7] = np.float16(np.nan)               # a NaN activation: the whole row of logits is NaN -> -1
+            dx = ctx.upload(x.view(np.uint16))
+            logits, idx = ctx.alloc(M * N * 2), ctx.upload(np.full(M, 77, np.int32))
+            comm.linear_argmax_sharded_rows(M, N, K, dx, qw.buf, logits, idx)
+            ctx.sync()
+            got = ctx.download(idx, (M,), np.int32)
+            lg = ctx.download(logits, (M, N), np.uint16)
+            b32 = lg.astype(np.uint32)
+            keys = np.where((b32 & 0x7FFF) > 0x7C00, 0, np.where(b32 & 0x8000, 0xFFFF - b32, b32 | 0x8000))
+            want = np.where(keys.max(axis=1) > 0, np.argmax(keys, axis=1), -1)
+            assert np.array_equal(got, want), (M, got[:8], want[:8])
+            if M >= 3:
+                assert got[1] == 0 and got[2] == -1
+            ref = cpu.linear("int8", x[:1], W, s, threads=4)
+            assert cpu.rel_l2(lg[:1].view(np.float16), ref) <= TOL
+            for b in (dx, logits, idx):
+                ctx.free(b)
+        L = ctx.L
+        b = ctx.alloc(64)
+        assert L.nn_linear_argmax_sharded_rows(comm.h, 0, N, K, b, qw.buf, b, b) == nnb.NN_ERR_ARG
+        assert L.nn_linear_argmax_sharded_rows(comm.h, 2000, N, K, b, qw.buf, b, b) == nnb.NN_ERR_ARG
+        assert L.nn_linear_argmax_sharded_rows(comm.h, 4, N, K, b, qw.buf, None, b) == nnb.NN_ERR_ARG
+        ctx.free(b)
+        qw.release()
+    finally:
+        ctx.sync()
+        comm.close()
