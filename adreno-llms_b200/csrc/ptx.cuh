@@ -250,6 +250,16 @@ __device__ __forceinline__ void argmax_share_key(const nnb::GatherSignal& s, uns
     }
 }
 
+// Two invariants this signalling rests on:
+//  (1) Ordering of the peer stores.  Every block orders its own stores (local and peer) before its count-in with a
+//      gpu-scope fence; the last block to count in observes all the others through the atomic and issues the one
+//      system-scope fence before it writes the flags, so the other blocks' peer stores become visible to the peers by
+//      cumulativity (valid under the PTX memory model; the stress loop of tests/multi_gpu_worker.py compares several
+//      hundred gathers bit for bit with NCCL's).
+//  (2) Nothing after this call in the projection kernel may touch state that the next launch on the stream reads: the
+//      wait and pick kernels are launched programmatically and never execute griddepcontrol.wait (their own rank's flag
+//      is among those they spin on), so the launch after them is not ordered behind the projection grid's retirement,
+//      only behind its signal.
 __device__ __forceinline__ void gather_signal_block_done(const nnb::GatherSignal& s) {
     __threadfence();
     const unsigned prev = atomicAdd(s.done, 1u);

@@ -126,6 +126,43 @@ def main():
         qw.release()
         for b in (tok, local, g1):
             ctx.free(b)
+    # stress: several hundred alternating gathers and picks on one weight, every gather bit-compared with the NCCL
+    # gather of the same projection and every pick with the arg-max over it (orderings that only show up under load)
+    fmt, N, K, M = "int8", 4096, 576, 1
+    W, s = make_weight(fmt, N, K, 9500)
+    Wl, sl = sharding.shard_weight(fmt, W, s, world, rank)
+    lo, n = sharding.shard_rows(N, world, rank)
+    qw = pkg.QuantWeight(ctx, fmt, Wl, sl)
+    xs = [make_x(M, K, 9501 + i) for i in range(4)]
+    dxs = [ctx.upload(x.view(np.uint16)) for x in xs]
+    g1 = ctx.alloc(M * n * 2 * world)
+    expect, expect_tok = [], []
+    for dx in dxs:
+        ctx.linear(M, n, K, dx, qw.buf, g1 + rank * M * n * 2)
+        comm.all_gather(g1 + rank * M * n * 2, g1, M * n * 2)
+        bits = ctx.download(g1, (world, M, n), np.uint16).copy()
+        expect.append(bits)
+        b32 = bits.reshape(-1).astype(np.uint32)
+        expect_tok.append(int(np.argmax(np.where(b32 & 0x8000, 0xFFFF - b32, b32 | 0x8000))))
+    bufs = [comm.symm_alloc(M * n * 2 * world) for _ in range(2)]
+    tok = ctx.alloc(4)
+    bad_g = bad_p = 0
+    for i in range(300):
+        j = i % 4
+        comm.linear_gather(M, n, K, dxs[j], qw.buf, bufs[i & 1])
+        comm.linear_argmax_sharded(n, K, dxs[j], qw.buf, None, tok)
+        got = ctx.download(bufs[i & 1], (world, M, n), np.uint16)
+        bad_g += int(not np.array_equal(got, expect[j]))
+        bad_p += int(int(ctx.download(tok, (1,), np.int32)[0]) != expect_tok[j])
+    if bad_g or bad_p:
+        failures.append(f"stress: {bad_g} of 300 gathers and {bad_p} of 300 picks differ from the NCCL gather / its arg-max")
+    ctx.sync()
+    dist.barrier()
+    for b in bufs:
+        comm.symm_free(b)
+    qw.release()
+    for b in dxs + [g1, tok]:
+        ctx.free(b)
     # the batched pick: M tokens per call, one key per row and rank instead of the logits
     for fmt, N, K, M in (("int8", 4096, 576, 8), ("q4", 2048, 1024, 40), ("int8", 3072, 896, 256), ("fp16", 1536, 896, 5)):
         W, s = make_weight(fmt, N, K, 9300 + N)
