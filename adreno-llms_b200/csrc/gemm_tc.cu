@@ -127,6 +127,16 @@ __device__ __forceinline__ uint64_t smem_desc_sw128(uint32_t saddr) {
     return d;
 }
 
+// The same descriptor from its halves: the high word never changes, the low word is the 16-byte address (14 bits) plus
+// the constant leading-offset field, so a K step of 32 bytes inside a swizzle span is "+ 2" on the low word.
+constexpr uint32_t DESC_HI = (uint32_t)((1024 >> 4) & 0x3FFF) | (1u << 14) | (2u << 29);
+__device__ __forceinline__ uint32_t smem_desc_lo(uint32_t saddr) { return ((saddr >> 4) & 0x3FFFu) | (1u << 16); }
+__device__ __forceinline__ uint64_t desc_of(uint32_t lo) {
+    uint64_t d;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(d) : "r"(lo), "r"(DESC_HI));
+    return d;
+}
+
 // Instruction descriptor: fp32 accumulate, fp16 x fp16, both operands K-major, M = 128, N = bn.
 __device__ __forceinline__ uint32_t instr_desc_f16(int bn) {
     uint32_t d = 0;
@@ -227,9 +237,14 @@ __global__ void __launch_bounds__(gemm_threads(WFMT)) linear_gemm_tc_kernel(cons
         // ---- MMA issuer: one lane; accumulators alternate between two tensor-memory halves ----
         if (lane == 0) {
             const uint32_t idesc = instr_desc_f16(g_bn);
-            int it = 0, tl = 0, s = 0;
+            // This one thread issues every MMA of the block, in order: whenever the tiles are narrow its instruction count
+            // per K block is the kernel's pace.  So everything that depends on the ring slot (the two barriers, the two
+            // descriptors) is stepped by a constant and reset when the ring wraps, not recomputed.
+            int tl = 0, s = 0;
             uint32_t ph = 0;
             bool ok = true;
+            const uint32_t a_lo0 = smem_desc_lo(ring), b_lo0 = smem_desc_lo(ring + A_BYTES), lo_step = (uint32_t)stage_bytes >> 4;
+            uint32_t full_s = full0, empty_s = empty0, a_lo = a_lo0, b_lo = b_lo0;
             for (int tile = blockIdx.x; tile < ntiles && ok; tile += gridDim.x, ++tl) {
                 const int acc = tl & 1;
                 if (tl >= 2 && !mbar_wait_bounded(acc_empty0 + acc * 8, (uint32_t)(((tl >> 1) - 1) & 1))) {
@@ -238,18 +253,24 @@ __global__ void __launch_bounds__(gemm_threads(WFMT)) linear_gemm_tc_kernel(cons
                 }
                 tc_fence_after();
                 const uint32_t tmem_d = tmem_base + (uint32_t)(acc * g_cols);
-                for (int kb = 0; kb < nkb; ++kb, ++it, s = (s + 1 == g_stages ? 0 : s + 1), ph ^= (s == 0 ? 1u : 0u)) {
-                    if (!mbar_wait_bounded(full0 + s * 8, ph)) {
+                for (int kb = 0; kb < nkb; ++kb) {
+                    if (!mbar_wait_bounded(full_s, ph)) {
                         *reinterpret_cast<volatile int*>(g_status) = 4;
                         ok = false;
                         break;
                     }
                     tc_fence_after();
-                    const uint32_t a_addr = ring + s * stage_bytes, b_addr = a_addr + A_BYTES;
 #pragma unroll
                     for (int k = 0; k < BK / 16; ++k)
-                        umma_f16(tmem_d, smem_desc_sw128(a_addr + k * 32), smem_desc_sw128(b_addr + k * 32), idesc, (uint32_t)((kb | k) != 0));
-                    umma_commit(empty0 + s * 8);  // the stage is free once these MMAs have read it
+                        umma_f16(tmem_d, desc_of(a_lo + 2 * k), desc_of(b_lo + 2 * k), idesc, (uint32_t)((kb | k) != 0));
+                    umma_commit(empty_s);  // the stage is free once these MMAs have read it
+                    if (++s == g_stages) {
+                        s = 0;
+                        ph ^= 1u;
+                        full_s = full0; empty_s = empty0; a_lo = a_lo0; b_lo = b_lo0;
+                    } else {
+                        full_s += 8; empty_s += 8; a_lo += lo_step; b_lo += lo_step;
+                    }
                 }
                 umma_commit(acc_full0 + acc * 8);  // this tile's accumulator is complete
             }
