@@ -627,14 +627,23 @@ def main():
     keys_pick = bool(comm) and MM == 1 and args.only is None
     d2h_bytes = (MM * step.vocab_n * 2 + 4) if (keys_pick or not comm) else MM * shape.vocab * 2
 
-    def e2e_step(i):
+    # The host program's own copies are recorded with the step, as the reference records its whole token into the
+    # replayed queue: one plan per weight copy holds the host -> device copy of the hidden vector, the step, and the
+    # device -> host reads of the logits and the token; a step is one nn_plan_launch and one nn_sync.
+    io_plans = []
+    for i in range(n_sets):
+        ctx.plan_begin()
         pkg._check(ctx.L.nn_buf_write(ctx.h, x_in, 0, hx, MM * shape.hidden * 2))
-        step.launch(i % n_sets)
+        step.enqueue(i, with_argmax=(args.only is None))
         if keys_pick or not comm:
             pkg._check(ctx.L.nn_buf_read(ctx.h, hl, step.logits, 0, MM * step.vocab_n * 2))
             pkg._check(ctx.L.nn_buf_read(ctx.h, hl_tok, step.token, 0, 4))
         else:
-            pkg._check(ctx.L.nn_buf_read(ctx.h, hl, step.gathered[i % n_sets], 0, MM * shape.vocab * 2))
+            pkg._check(ctx.L.nn_buf_read(ctx.h, hl, step.gathered[i], 0, MM * shape.vocab * 2))
+        io_plans.append(ctx.plan_end())
+
+    def e2e_step(i):
+        ctx.plan_launch(io_plans[i % n_sets])
         ctx.sync()
 
     for i in range(5):
@@ -645,6 +654,12 @@ def main():
         e2e_step(i)
     e2e_s = max_over_ranks(time.perf_counter() - t0)
     e2e_value = step_bytes_full / (e2e_s / e2e_steps) / 1e9
+    # what came back through the recorded copies is what the device holds
+    e2e_step(0)
+    e2e_logits = np.ctypeslib.as_array(ctypes.cast(hl, ctypes.POINTER(ctypes.c_uint16)), (MM * step.vocab_n,)).copy() if (keys_pick or not comm) else None
+    e2e_token = int(ctypes.cast(hl_tok, ctypes.POINTER(ctypes.c_int32))[0]) if (keys_pick or not comm) else None
+    for pl in io_plans:
+        ctx.L.nn_plan_free(pl)
     clocks = sampler.stop()
 
     # ---- parity, inside the run: the replay against the same operators launched one by one ----
@@ -661,6 +676,9 @@ def main():
         want = results_of(ctx, step)
         same = bool(np.array_equal(got[0], want[0]) and got[1] == want[1] and np.array_equal(got[2], want[2]))
         lg = want[0].view(np.float16).astype(np.float32)
+        if e2e_logits is not None:
+            e2e_same = bool(np.array_equal(e2e_logits, got[0].reshape(-1)) and e2e_token == got[1])
+            same = same and e2e_same
         parity = {"checked": True, "resident_equals_separate_launches": same, "logits_finite": bool(np.isfinite(lg).all()),
                   "token": int(got[1]), "separate_launches": int(sep_n)}
         if keys_pick:

@@ -202,3 +202,38 @@ def test_withheld_output_times_out_and_context_survives(nnb, ctx):
     assert cpu.rel_l2(got, cpu.linear("fp16", x, W, None, order=2)) <= TOL
     for b in (dw, dx, out):
         ctx.free(b)
+
+
+def test_host_copies_recorded_with_the_step(nnb, ctx):
+    """The host program's own copies between nn_plan_begin and nn_plan_end are part of the plan (the
+    reference records its whole token into the replayed queue): a replay copies the CURRENT contents of
+    the pinned input in, runs the operators as one resident launch, and copies the results out."""
+    fmt, K, N = "int8", 576, 1536
+    W1, s1 = make_weight(fmt, N, K, 601)
+    W2, s2 = make_weight(fmt, K, N, 602)
+    w1, w2 = nnb.QuantWeight(ctx, fmt, W1, s1), nnb.QuantWeight(ctx, fmt, W2, s2)
+    L = ctx.L
+    hx, hy = L.nn_host_alloc(K * 2), L.nn_host_alloc(K * 2)
+    dx, da, dy = ctx.alloc(K * 2), ctx.alloc(N * 2), ctx.alloc(K * 2)
+    ctx.plan_begin()
+    nnb._check(L.nn_buf_write(ctx.h, dx, 0, hx, K * 2))
+    ctx.linear(1, N, K, dx, w1.buf, da)
+    ctx.linear(1, K, N, da, w2.buf, dy)
+    nnb._check(L.nn_buf_read(ctx.h, hy, dy, 0, K * 2))
+    plan = ctx.plan_end()
+    assert L.nn_plan_num_resident_runs(plan) == 1 and L.nn_plan_num_kernels(plan) == 1
+    for rep in range(3):
+        x = make_x(1, K, 610 + rep)
+        ctypes.memmove(hx, x.ctypes.data, K * 2)
+        ctx.plan_launch(plan)
+        ctx.sync()
+        got = np.ctypeslib.as_array(ctypes.cast(hy, ctypes.POINTER(ctypes.c_uint16)), (K,)).copy().view(np.float16)
+        want = cpu.linear(fmt, cpu.linear(fmt, x, W1, s1), W2, s2)
+        check_close(got[None, :], want, what=f"recorded copies, replay {rep}")
+    L.nn_plan_free(plan)
+    L.nn_host_free(hx)
+    L.nn_host_free(hy)
+    for w in (w1, w2):
+        w.release()
+    for b in (dx, da, dy):
+        ctx.free(b)
