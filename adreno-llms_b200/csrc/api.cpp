@@ -232,6 +232,7 @@ extern "C" int nn_shutdown(nn_context* c) {
     if (c->argmax_slot) cudaFree(c->argmax_slot);
     if (c->norm_scratch) cudaFree(c->norm_scratch);
     if (c->stage_img) cudaFree(c->stage_img);
+    if (c->pair_scratch) cudaFree(c->pair_scratch);
     if (c->sk_scratch) cudaFree(c->sk_scratch);
     if (c->sk_flags) cudaFree(c->sk_flags);
     if (c->status_host) cudaFreeHost(c->status_host);
@@ -403,6 +404,62 @@ static int run_gemm_tc(nn_context* c, int fmt, const LinArgs& a, int M, const ch
     return NN_OK;
 }
 
+// The fused forms (three-weight QKV, SwiGLU over two weights, the in-place SiLU gate) at prefill row counts: one
+// tensor-core GEMM per weight, each with an fp16 result, and for the two-weight forms the element-wise SiLU-multiply
+// over those results -- the reference's own M > 1 sequence (src/models/lfm2-5-350m/src/layers/mlp.cpp:101-129).  The
+// single-pass streaming kernel would walk such a batch in slices of 16 rows, re-reading the weights for every slice.
+static int run_fused_forms_tc(nn_context* c, int fmt, const LinArgs& a, int M, const char* who, bool* done) {
+    *done = false;
+    if (a.npeer > 0 || a.sig.world > 0 || a.argmax_slot || a.norm_w) return NN_OK;
+    const bool qkv = a.epi == EPI_STORE && a.nseg > 1, swiglu = a.epi == EPI_SWIGLU && a.nseg == 1, gate = a.epi == EPI_SILU_GATE && a.nseg == 1;
+    if (!qkv && !swiglu && !gate) return NN_OK;
+    for (int i = 0; i < a.nseg; ++i)
+        if (!gemm_tc_supported(fmt, M, a.seg[i].N, a.K, a.x, a.seg[i].W, a.seg[i].out)) return NN_OK;
+    if (swiglu && !gemm_tc_supported(fmt, M, a.seg[0].N, a.K, a.x, a.W2, a.seg[0].out)) return NN_OK;
+    auto gemm = [&](const uint8_t* W, const uint16_t* scale, uint16_t* out, int N, int ld) -> int {
+        cudaError_t e = launch_gemm_tc(fmt, W, scale, a.x, out, M, N, a.K, ld, EPI_STORE, a.status, nullptr, 0, nullptr, c->stream);
+        if (e != cudaSuccess) return NN_FAIL(NN_ERR_CUDA, "%s: tensor-core launch failed: %s (M=%d N=%d K=%d)", who, cudaGetErrorString(e), M, N, a.K);
+        c->launches++;
+        return NN_OK;
+    };
+    if (qkv) {
+        for (int i = 0; i < a.nseg; ++i) {
+            const int rc = gemm(a.seg[i].W, a.seg[i].scale, a.seg[i].out, a.seg[i].N, a.seg[i].ld_out);
+            if (rc) return rc;
+        }
+        *done = true;
+        return NN_OK;
+    }
+    const int N = a.seg[0].N;
+    const size_t one = (size_t)M * N * 2, need = swiglu ? 2 * one : one;
+    if (need > c->pair_scratch_bytes) {
+        if (c->capturing) return NN_OK;   // cannot grow inside a recording: the sliced route still works
+        cudaSetDevice(c->device);
+        CUDA_TRY(cudaStreamSynchronize(c->stream));
+        if (c->pair_scratch) CUDA_TRY(cudaFree(c->pair_scratch));
+        c->pair_scratch = nullptr;
+        c->pair_scratch_bytes = 0;
+        CUDA_TRY(cudaMalloc(&c->pair_scratch, need));
+        c->pair_scratch_bytes = need;
+    }
+    uint16_t* s0 = (uint16_t*)c->pair_scratch;
+    uint16_t* s1 = (uint16_t*)((char*)c->pair_scratch + one);
+    if (swiglu) {
+        int rc = gemm(a.seg[0].W, a.seg[0].scale, s0, N, N);
+        if (!rc) rc = gemm(a.W2, a.scale2, s1, N, N);
+        if (rc) return rc;
+        CUDA_TRY(launch_silu_mul(s0, s1, a.seg[0].out, (size_t)M * N, c->stream));
+    } else {   // gate_inout = silu(gate_inout) * (x . W3^T)
+        const int rc = gemm(a.seg[0].W, a.seg[0].scale, s0, N, N);
+        if (rc) return rc;
+        if (a.seg[0].ld_out != N) return NN_FAIL(NN_ERR_UNSUPPORTED, "%s: the in-place gate form needs a dense [M, N] buffer", who);
+        CUDA_TRY(launch_silu_mul(a.seg[0].out, s0, a.seg[0].out, (size_t)M * N, c->stream));
+    }
+    c->launches++;
+    *done = true;
+    return NN_OK;
+}
+
 // While a step is being recorded, every launch of the streaming kernel is also noted with its
 // arguments and its graph node, so that nn_plan_end can hand runs of them to the resident kernel.
 static void note_recorded(nn_context* c, int fmt, const LinArgs& a, const StreamPlan& p) {
@@ -460,7 +517,9 @@ static int run_linear(nn_context* c, int fmt, LinArgs a, int M_total, const char
     }
     if (M_total > 16) {
         bool done = false;
-        const int rc = run_gemm_tc(c, fmt, a, M_total, who, &done);
+        int rc = run_gemm_tc(c, fmt, a, M_total, who, &done);
+        if (rc != NN_OK || done) return rc;
+        rc = run_fused_forms_tc(c, fmt, a, M_total, who, &done);
         if (rc != NN_OK || done) return rc;
     }
     // M > 16 is walked in slices of 16 activation rows (each slice re-streams the weights).

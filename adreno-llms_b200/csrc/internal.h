@@ -39,6 +39,8 @@ struct nn_context {
     unsigned long long* argmax_slot = nullptr;
     void* stage_img = nullptr;      // staged activations of a batched call, written once per launch (stage_image.cu)
     size_t stage_img_bytes = 0;
+    void* pair_scratch = nullptr;   // fp16 results of the two projections of a two-weight form at prefill row counts
+    size_t pair_scratch_bytes = 0;
     void* norm_scratch = nullptr;   // normalised activations when the fused prologue does not apply
     size_t norm_scratch_bytes = 0;
     float* sk_scratch = nullptr;   // partial sums of blocks that share a tile (balanced K-streaming)

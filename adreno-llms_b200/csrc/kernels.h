@@ -149,6 +149,7 @@ cudaError_t launch_argmax_half(const uint16_t* v, int n, int* out_idx, unsigned 
 cudaError_t launch_fill_u64(unsigned long long* p, unsigned long long v, cudaStream_t st);
 cudaError_t launch_argmax_finish(const unsigned long long* slot, int* out_idx, cudaStream_t st);
 cudaError_t launch_l2_flush(void* buf, size_t bytes, cudaStream_t st);
+cudaError_t launch_silu_mul(const uint16_t* g, const uint16_t* u, uint16_t* out, size_t n, cudaStream_t st);
 // the staged activations of a batched call (layout of the streaming kernel's shared memory), with the optional RMSNorm
 size_t stage_image_bytes(int fmt, int M, int K);
 cudaError_t launch_stage_image(int fmt, const uint16_t* x, int M, int K, const uint16_t* norm_w, float eps, uint8_t* img, cudaStream_t st,

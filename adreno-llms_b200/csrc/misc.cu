@@ -169,6 +169,17 @@ __global__ void __launch_bounds__(32) probe_tma_kernel(const uint8_t* __restrict
     if (!ok) atomicExch(status, 1u);
 }
 
+// The element-wise halves of the two-weight forms at prefill row counts, where each projection is a tensor-core GEMM of
+// its own with an fp16 result, as in the reference (its M > 1 path runs w1, w3 and then a SiLU-multiply kernel over the
+// fp16 results: src/models/lfm2-5-350m/src/layers/mlp.cpp:101-129, kernels/mlp.cl:6):
+//   out[i]  = half(silu(float(g[i])) * float(u[i]))          (g may be out: the in-place gate form)
+__global__ void silu_mul_kernel(const uint16_t* __restrict__ g, const uint16_t* __restrict__ u, uint16_t* __restrict__ out, size_t n) {
+    for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) {
+        const float gv = h2f(g[i]), uv = h2f(u[i]);
+        out[i] = __half_as_ushort(__float2half_rn((gv / (1.0f + expf(-gv))) * uv));
+    }
+}
+
 __global__ void l2_flush_kernel(uint4* buf, size_t n16) {
     for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < n16; i += (size_t)gridDim.x * blockDim.x) {
         uint4 v = buf[i];
@@ -260,6 +271,15 @@ cudaError_t launch_probe_tma(const void* src, size_t bytes, unsigned* status, cu
         configured = true;
     }
     probe_tma_kernel<<<current_sm_count(), 32, smem, st>>>(static_cast<const uint8_t*>(src), bytes / PROBE_CHUNK, status);
+    return cudaGetLastError();
+}
+
+cudaError_t launch_silu_mul(const uint16_t* g, const uint16_t* u, uint16_t* out, size_t n, cudaStream_t st) {
+    if (n == 0) return cudaSuccess;
+    size_t blocks = (n + 1023) / 1024;
+    const size_t cap = (size_t)current_sm_count() * 8;
+    if (blocks > cap) blocks = cap;
+    silu_mul_kernel<<<(unsigned)blocks, 256, 0, st>>>(g, u, out, n);
     return cudaGetLastError();
 }
 

@@ -360,3 +360,50 @@ def test_batch_rows_are_bitwise_the_single_token_results(nnb, ctx, fmt, N, K):
     qw.release()
     for b in (xb, ob, rb):
         ctx.free(b)
+
+
+@pytest.mark.parametrize("fmt", FMTS)
+@pytest.mark.parametrize("M", [40, 300])
+def test_fused_forms_at_prefill_row_counts(nnb, ctx, fmt, M):
+    """Above 16 rows the fused forms (QKV over three weights, SwiGLU over two, the in-place SiLU gate) run as one
+    tensor-core GEMM per weight plus, for the two-weight forms, the SiLU-multiply over the fp16 results: the
+    reference's own sequence for M > 1 (src/models/lfm2-5-350m/src/layers/mlp.cpp:101-129).  The oracle for it is
+    that sequence on the oracle's projections: fp16 results first, then silu(g) * u in fp32, one more rounding."""
+    K, N = 896, 1152
+    x = make_x(M, K, 171)
+    dx = ctx.upload(x.view(np.uint16))
+
+    def silu_mul(g, u):
+        g32, u32 = g.astype(np.float32), u.astype(np.float32)
+        return ((g32 / (1.0 + np.exp(-g32))) * u32).astype(np.float16)
+
+    # SwiGLU over two weights
+    (Wg, sg), (Wu, su) = make_weight(fmt, N, K, 172), make_weight(fmt, N, K, 173)
+    qg, qu = nnb.QuantWeight(ctx, fmt, Wg, sg), nnb.QuantWeight(ctx, fmt, Wu, su)
+    out = ctx.upload(np.full((M, N), 0x7E00, np.uint16))
+    before = ctx.launch_count()
+    ctx.fused_gate_up_silu(M, N, K, dx, qg.buf, qu.buf, out)
+    assert ctx.launch_count() - before == 3          # two GEMMs and the SiLU-multiply, not M / 16 slices
+    got = ctx.download(out, (M, N), np.uint16).view(np.float16)
+    g, u = cpu.linear(fmt, x, Wg, sg, threads=4), cpu.linear(fmt, x, Wu, su, threads=4)
+    check_close(got, silu_mul(g, u), what=f"swiglu at M={M} {fmt}")
+    # the in-place gate form on the same operands
+    gate = ctx.upload(g.view(np.uint16))
+    ctx.linear_silu_gate_fused(M, N, K, dx, qu.buf, gate)
+    got = ctx.download(gate, (M, N), np.uint16).view(np.float16)
+    check_close(got, silu_mul(g, u), what=f"silu gate at M={M} {fmt}")
+    # QKV over three weights
+    Ns = (896, 128, 128)
+    Ws = [make_weight(fmt, n, K, 174 + i) for i, n in enumerate(Ns)]
+    qs = [nnb.QuantWeight(ctx, fmt, W, s) for W, s in Ws]
+    outs = [ctx.upload(np.full((M, n), 0x7E00, np.uint16)) for n in Ns]
+    before = ctx.launch_count()
+    ctx.linear_qkv(M, K, dx, qs[0].buf, Ns[0], qs[1].buf, Ns[1], qs[2].buf, Ns[2], *outs)
+    assert ctx.launch_count() - before == 3
+    for (W, s), ob, n in zip(Ws, outs, Ns):
+        got = ctx.download(ob, (M, n), np.uint16).view(np.float16)
+        check_close(got, cpu.linear(fmt, x, W, s, threads=4), what=f"qkv at M={M} {fmt} N={n}")
+    for q in [qg, qu] + qs:
+        q.release()
+    for b in [dx, out, gate] + outs:
+        ctx.free(b)
