@@ -21,6 +21,8 @@
 #include <cuda_fp16.h>
 #include <cuda_runtime.h>
 
+#include <atomic>
+
 #include "../../include/nnopt_b200.h"
 #include "internal.h"
 #include "kernels.h"
@@ -31,7 +33,7 @@ constexpr int kSlots = 32;  // 256 bytes; slot 0 is the reduction word, the rest
 static __device__ __align__(256) unsigned long long g_static_scratch[kSlots];
 
 constexpr int kMaxDevices = 64;
-unsigned long long* g_scratch_addr[kMaxDevices] = {};  // device address per device, filled on first use
+std::atomic<unsigned long long*> g_scratch_addr[kMaxDevices];  // device address per device, filled on first use (any thread)
 
 __device__ __forceinline__ unsigned long long key_of(float v, int idx) {
     unsigned int b = __float_as_uint(v);
@@ -85,15 +87,16 @@ extern "C" int nn_argmax_static(void* cuda_stream, int n, nn_buf logits_fp16, nn
     cudaError_t e = cudaGetDevice(&dev);
     if (e != cudaSuccess || dev < 0 || dev >= kMaxDevices)
         return NN_FAIL(NN_ERR_CUDA, "nn_argmax_static: no current CUDA device (%s)", cudaGetErrorString(e));
-    if (!g_scratch_addr[dev]) {
+    unsigned long long* slot = g_scratch_addr[dev].load(std::memory_order_acquire);
+    if (!slot) {
         // Once per device, with that device current: the array's name is only a host-side
         // handle; the kernels need its device address.
         void* p = nullptr;
         e = cudaGetSymbolAddress(&p, g_static_scratch);
         if (e != cudaSuccess || !p) return NN_FAIL(NN_ERR_CUDA, "nn_argmax_static: cudaGetSymbolAddress failed: %s", cudaGetErrorString(e));
-        g_scratch_addr[dev] = static_cast<unsigned long long*>(p);
+        slot = static_cast<unsigned long long*>(p);
+        g_scratch_addr[dev].store(slot, std::memory_order_release);   // every thread computes the same value
     }
-    unsigned long long* slot = g_scratch_addr[dev];
     cudaStream_t st = static_cast<cudaStream_t>(cuda_stream);
     static_clear_kernel<<<1, 1, 0, st>>>(slot);
     if (n > 0) {
