@@ -228,6 +228,7 @@ extern "C" int nn_shutdown(nn_context* c) {
         prof_collect(c);
         if (!c->prof.empty()) fprintf(stderr, "\n%s\n", prof_format(c->prof).c_str());
     }
+    for (auto& kv : c->registry) free_scale_pad(kv.second);
     if (c->flush_buf) cudaFree(c->flush_buf);
     if (c->argmax_slot) cudaFree(c->argmax_slot);
     if (c->norm_scratch) cudaFree(c->norm_scratch);
@@ -289,7 +290,10 @@ extern "C" int nn_buf_free(nn_context* c, nn_buf b) {
     CUDA_TRY(cudaStreamSynchronize(c->stream));
     // a freed weight or scale buffer must not keep resolving: the address may be handed out again
     for (auto it = c->registry.begin(); it != c->registry.end();) {
-        if (it->first == (uintptr_t)b || (const void*)it->second.scale == (const void*)b) it = c->registry.erase(it);
+        if (it->first == (uintptr_t)b || (const void*)it->second.scale == (const void*)b) {
+            free_scale_pad(it->second);
+            it = c->registry.erase(it);
+        }
         else ++it;
     }
     CUDA_TRY(cudaFree(b));
@@ -346,6 +350,26 @@ static int register_weight(nn_context* c, int fmt, nn_buf W, nn_buf scale, int N
     q.N = N;
     q.K = K;
     q.rowbytes = fmt_rowbytes(fmt, K);
+    auto old = c->registry.find((uintptr_t)W);
+    if (old != c->registry.end()) free_scale_pad(old->second);
+    if (fmt == FMT_Q4 && (K / 16) % 16 != 0 && !c->capturing) {
+        // scale rows of K / 16 bytes that tensor copies cannot address: keep a copy with 16-byte row pitch
+        const size_t src_pitch = (size_t)K / 16, pitch = (src_pitch + 15) / 16 * 16;
+        cudaSetDevice(c->device);
+        void* pad = nullptr;
+        if (cudaMalloc(&pad, pitch * (size_t)N) == cudaSuccess) {
+            if (cudaMemsetAsync(pad, 0, pitch * (size_t)N, c->stream) == cudaSuccess &&
+                cudaMemcpy2DAsync(pad, pitch, scale, src_pitch, src_pitch, (size_t)N, cudaMemcpyDeviceToDevice, c->stream) == cudaSuccess) {
+                q.scale_pad = (uint16_t*)pad;
+                q.scale_pitch = (int)pitch;
+            } else {
+                cudaFree(pad);
+                cudaGetLastError();
+            }
+        } else {
+            cudaGetLastError();   // no memory for the copy: the per-lane scale path still works
+        }
+    }
     c->registry[(uintptr_t)W] = q;
     return NN_OK;
 }
@@ -358,7 +382,11 @@ extern "C" int nn_register_q4_weight(nn_context* c, nn_buf W, nn_buf s, int N, i
 }
 extern "C" int nn_unregister_weight(nn_context* c, nn_buf W) {
     if (!c) return NN_FAIL(NN_ERR_ARG, "nn_unregister_weight: null context");
-    c->registry.erase((uintptr_t)W);
+    auto it = c->registry.find((uintptr_t)W);
+    if (it != c->registry.end()) {
+        free_scale_pad(it->second);
+        c->registry.erase(it);
+    }
     return NN_OK;
 }
 
@@ -368,6 +396,8 @@ bool nnb::resolve_weight(const nn_context* c, const void* W, int K, ResolvedW* o
     out->fmt = FMT_FP16;
     out->scale = nullptr;
     out->rows_avail = -1;
+    out->scale_pad = nullptr;
+    out->scale_pitch = 0;
     if (c->registry.empty()) return true;
     const uintptr_t p = (uintptr_t)W;
     auto it = c->registry.upper_bound(p);
@@ -384,6 +414,10 @@ bool nnb::resolve_weight(const nn_context* c, const void* W, int K, ResolvedW* o
     out->fmt = q.fmt;
     out->scale = q.fmt == FMT_INT8 ? q.scale + r : q.scale + r * (size_t)(K / 32);
     out->rows_avail = q.N - (int)r;
+    if (q.scale_pad) {
+        out->scale_pad = reinterpret_cast<const uint16_t*>(reinterpret_cast<const char*>(q.scale_pad) + r * (size_t)q.scale_pitch);
+        out->scale_pitch = q.scale_pitch;
+    }
     return true;
 }
 
@@ -476,9 +510,9 @@ static void note_recorded(nn_context* c, int fmt, const LinArgs& a, const Stream
         r.node = tail[0];
     bool q4_ok = true;
     if (fmt == FMT_Q4) {  // block scales must be reachable by tensor copies
-        q4_ok = a.K % 256 == 0;
-        for (int i = 0; i < a.nseg; ++i) q4_ok = q4_ok && (reinterpret_cast<uintptr_t>(a.seg[i].scale) & 15) == 0;
-        if (a.epi == EPI_SWIGLU) q4_ok = q4_ok && (reinterpret_cast<uintptr_t>(a.scale2) & 15) == 0;
+        const uint16_t* base[4];
+        int pitch = 0;
+        q4_ok = q4_scale_views(a, base, &pitch);
     }
     r.eligible = r.node && a.M == 1 && !p.streamk && a.npeer == 0 && a.sig.world == 0 && q4_ok;
     c->rec.push_back(r);
@@ -604,6 +638,8 @@ static int one_weight(nn_context* c, int M, int N, int K, nn_buf x, nn_buf W, nn
     a.nseg = 1;
     a.seg[0].W = (const uint8_t*)W;
     a.seg[0].scale = r.scale;
+    a.scale_pad[0] = r.scale_pad;
+    a.scale_pitch = r.scale_pitch;
     a.seg[0].out = (uint16_t*)out;
     a.seg[0].N = N;
     a.seg[0].ld_out = N;
@@ -651,6 +687,9 @@ static int gate_up_silu(nn_context* c, int M, int N, int K, nn_buf x, nn_buf Wg,
     a.nseg = 1;
     a.seg[0].W = (const uint8_t*)Wg;
     a.seg[0].scale = rg.scale;
+    a.scale_pad[0] = rg.scale_pad;
+    a.scale_pad[3] = ru.scale_pad;
+    a.scale_pitch = rg.scale_pitch;
     a.seg[0].out = (uint16_t*)out;
     a.seg[0].N = N;
     a.seg[0].ld_out = N;
@@ -690,6 +729,8 @@ static int linear_qkv(nn_context* c, int M, int K, nn_buf x, nn_buf Wq, int Nq, 
         fmt = r.fmt;
         a.seg[i].W = (const uint8_t*)Ws[i];
         a.seg[i].scale = r.scale;
+        a.scale_pad[i] = r.scale_pad;
+        a.scale_pitch = r.scale_pitch;
         a.seg[i].out = (uint16_t*)outs[i];
         a.seg[i].N = Ns[i];
         a.seg[i].ld_out = Ns[i];
@@ -796,6 +837,8 @@ int nnb::linear_argmax(nn_context* c, int N, int K, nn_buf x, nn_buf W, nn_buf l
     a.nseg = 1;
     a.seg[0].W = (const uint8_t*)W;
     a.seg[0].scale = r.scale;
+    a.scale_pad[0] = r.scale_pad;
+    a.scale_pitch = r.scale_pitch;
     a.seg[0].out = (uint16_t*)logits;
     a.seg[0].N = N;
     a.seg[0].ld_out = N;

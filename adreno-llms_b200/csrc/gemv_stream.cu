@@ -1037,13 +1037,13 @@ cudaError_t launch_stream(int fmt, const LinArgs& a, const StreamPlan& p, cudaSt
     // Q4 block scales by tensor copy: the scale rows (K / 16 bytes each) must keep 16-byte
     // pitch and alignment; otherwise the consumers fetch them with cp.async
     ka.scale_tma = 0;
-    if (fmt == FMT_Q4 && a.K % 256 == 0) {
+    const uint16_t* sbase[4];
+    int srow = 0;
+    if (fmt == FMT_Q4 && q4_scale_views(a, sbase, &srow)) {
         bool ok = true;
-        for (int i = 0; i < a.nseg; ++i) ok = ok && (reinterpret_cast<uintptr_t>(a.seg[i].scale) & 15) == 0;
-        if (dual) ok = ok && (reinterpret_cast<uintptr_t>(a.scale2) & 15) == 0;
-        const int srow = a.K / 16, bw = p.kcb / 8;
-        for (int i = 0; ok && i < a.nseg; ++i) ok = make_scale_map(&ka.tm_s[i], a.seg[i].scale, a.seg[i].N, srow, bw, tile_rows);
-        if (ok && dual) ok = make_scale_map(&ka.tm_s[3], a.scale2, a.seg[0].N, srow, bw, tile_rows);
+        const int bw = p.kcb / 8;
+        for (int i = 0; ok && i < a.nseg; ++i) ok = make_scale_map(&ka.tm_s[i], sbase[i], a.seg[i].N, srow, bw, tile_rows);
+        if (ok && dual) ok = make_scale_map(&ka.tm_s[3], sbase[3], a.seg[0].N, srow, bw, tile_rows);
         ka.scale_tma = ok ? 1 : 0;
     }
 #define GO(F)                                                                                                  \

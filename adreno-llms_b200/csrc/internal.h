@@ -14,7 +14,15 @@ struct QuantEntry {
     const uint16_t* scale;
     int N, K;
     size_t rowbytes;
+    // Q4 whose scale rows (K / 16 bytes) are not a multiple of 16 bytes: a copy of the scales with the rows padded to
+    // one, owned by the library, so that tensor copies can fetch them (the weights themselves are never repacked)
+    uint16_t* scale_pad = nullptr;
+    int scale_pitch = 0;  // bytes
 };
+inline void free_scale_pad(QuantEntry& q) {
+    if (q.scale_pad) cudaFree(q.scale_pad);
+    q.scale_pad = nullptr;
+}
 
 // Per-launch profile behind the reference's switches NNOPT_KERNEL_PROFILE / NNOPT_PROFILE
 // (src/models/lfm2-5-350m/src/kernel_profiler.cpp:18-62, src/models/smollm2-135m-instruct/src/prof.cpp:36-131):
@@ -62,6 +70,8 @@ struct ResolvedW {
     int fmt;
     const uint16_t* scale;
     int rows_avail;  // -1 when W is not a registered weight (fp16)
+    const uint16_t* scale_pad;  // the padded copy of the Q4 scales from the view's first row on, or null
+    int scale_pitch;
 };
 bool resolve_weight(const nn_context* c, const void* W, int K, ResolvedW* out);
 

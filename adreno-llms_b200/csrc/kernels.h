@@ -77,6 +77,10 @@ struct LinArgs {
     // stage_image_kernel in the kernel's own shared-memory layout; every block copies it in
     const uint8_t* staged;
     unsigned staged_bytes;
+    // host side only: Q4 scales with rows padded to a multiple of 16 bytes (seg[0..2], then the second weight of the
+    // two-weight form), for the tensor copies when K / 16 is not such a multiple; all null otherwise
+    const uint16_t* scale_pad[4];
+    int scale_pitch;
     float* sk_scratch;    // [blocks][consumer threads][2 * NT * 4] partial sums
     unsigned* sk_flags;   // [blocks] "partial written", consumed and cleared by the tile's owner
     int streamk;
@@ -148,6 +152,25 @@ cudaError_t launch_dequant(int fmt, int N, int K, const void* W, const uint16_t*
 cudaError_t launch_argmax_half(const uint16_t* v, int n, int* out_idx, unsigned long long* slot, cudaStream_t st);
 cudaError_t launch_fill_u64(unsigned long long* p, unsigned long long v, cudaStream_t st);
 cudaError_t launch_argmax_finish(const unsigned long long* slot, int* out_idx, cudaStream_t st);
+// Q4 block scales by tensor copy: from the weight's own scale array when its rows (K / 16 bytes) are a multiple of 16 bytes
+// and 16-byte aligned, else from the padded copy made at registration.  False: neither is there (per-lane copies then).
+inline bool q4_scale_views(const LinArgs& a, const uint16_t* base[4], int* pitch) {
+    const bool dual = a.epi == EPI_SWIGLU;
+    bool nat = a.K % 256 == 0, pad = a.scale_pitch > 0;
+    for (int i = 0; i < a.nseg; ++i) {
+        nat = nat && (reinterpret_cast<uintptr_t>(a.seg[i].scale) & 15) == 0;
+        pad = pad && a.scale_pad[i] != nullptr;
+    }
+    if (dual) {
+        nat = nat && (reinterpret_cast<uintptr_t>(a.scale2) & 15) == 0;
+        pad = pad && a.scale_pad[3] != nullptr;
+    }
+    if (!nat && !pad) return false;
+    for (int i = 0; i < 3; ++i) base[i] = nat ? a.seg[i].scale : a.scale_pad[i];
+    base[3] = nat ? a.scale2 : a.scale_pad[3];
+    *pitch = nat ? a.K / 16 : a.scale_pitch;
+    return true;
+}
 cudaError_t launch_l2_flush(void* buf, size_t bytes, cudaStream_t st);
 cudaError_t launch_silu_mul(const uint16_t* g, const uint16_t* u, uint16_t* out, size_t n, cudaStream_t st);
 // the staged activations of a batched call (layout of the streaming kernel's shared memory), with the optional RMSNorm

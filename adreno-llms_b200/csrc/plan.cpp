@@ -213,10 +213,12 @@ cudaError_t build_run(const std::vector<RecordedOp>& rec, const std::vector<OpDe
         }
         if (dual && !make_weight_map(&o.tm[3], a.W2, a.seg[0].N, rowbytes, tile_rows)) { *reason = "weight view"; return cudaErrorInvalidValue; }
         if (r.fmt == FMT_Q4) {
-            const int srow = a.K / 16, bw = r.p.kcb / 8;
-            bool ok = true;
-            for (int k = 0; ok && k < a.nseg; ++k) ok = make_scale_map(&o.tm_s[k], a.seg[k].scale, a.seg[k].N, srow, bw, tile_rows);
-            if (ok && dual) ok = make_scale_map(&o.tm_s[3], a.scale2, a.seg[0].N, srow, bw, tile_rows);
+            const uint16_t* sbase[4];
+            int srow = 0;
+            const int bw = r.p.kcb / 8;
+            bool ok = q4_scale_views(a, sbase, &srow);
+            for (int k = 0; ok && k < a.nseg; ++k) ok = make_scale_map(&o.tm_s[k], sbase[k], a.seg[k].N, srow, bw, tile_rows);
+            if (ok && dual) ok = make_scale_map(&o.tm_s[3], sbase[3], a.seg[0].N, srow, bw, tile_rows);
             if (!ok) { *reason = "scale view"; return cudaErrorInvalidValue; }
         }
         s.ntiles = t0;

@@ -182,7 +182,13 @@ extern "C" int nn_weights_free(nn_weights* w) {
     }
     for (auto& kv : w->tensors) {
         if (kv.second.dev) {
-            if (w->ctx) w->ctx->registry.erase((uintptr_t)kv.second.dev);
+            if (w->ctx) {
+                auto it = w->ctx->registry.find((uintptr_t)kv.second.dev);
+                if (it != w->ctx->registry.end()) {
+                    free_scale_pad(it->second);
+                    w->ctx->registry.erase(it);
+                }
+            }
             cudaFree(kv.second.dev);
         }
     }

@@ -47,7 +47,7 @@ SHAPES = {
 
 
 CASES = [("lfm2", f, w) for f in ("int8", "fp16", "q4") for w in ("fixed", "fixed+norm", "chained+norm")] + \
-        [(s, f, w) for s in ("smollm2", "qwen") for f in ("int8", "fp16") for w in ("fixed", "chained+norm")]
+        [(s, f, w) for s in ("smollm2", "qwen") for f in ("int8", "fp16", "q4") for w in ("fixed", "chained+norm")]
 
 
 @pytest.mark.parametrize("shape_name,fmt,wiring", CASES)
