@@ -76,7 +76,11 @@ int nn_host_free(void* p);
  *      nnopt_register_q4_weight, src/models/lfm2-5-350m/src/utils.h:127,132
  *      (utils.cpp:357-368, 584-595).  Keyed by the weight's device pointer; a
  *      row-range sub-view W + r*rowbytes of a registered weight resolves too (the
- *      reference's row tiles, utils.cpp:427-452).  Nothing is repacked. --------- */
+ *      reference's row tiles, utils.cpp:427-452).  The weights are never repacked.  Register
+ *      after the weight and its scales have been written: for a Q4 weight whose scale rows
+ *      (K / 16 bytes) are not a multiple of 16 bytes the library keeps its own copy of the
+ *      scales with the rows padded to one (N * roundup(K / 16, 16) bytes, freed when the
+ *      weight is unregistered or freed), taken at registration on the context's stream. --- */
 int nn_register_int8_weight(nn_context* ctx, nn_buf W_int8, nn_buf scale_fp16, int N, int K);
 int nn_register_q4_weight(nn_context* ctx, nn_buf W_q4, nn_buf scale_fp16, int N, int K_unpacked);
 int nn_unregister_weight(nn_context* ctx, nn_buf W);
