@@ -710,7 +710,7 @@ extern "C" int nn_fused_gate_up_silu(nn_context* c, int M, int N, int K, nn_buf 
 }
 
 static int linear_qkv(nn_context* c, int M, int K, nn_buf x, nn_buf Wq, int Nq, nn_buf Wk, int Nk, nn_buf Wv, int Nv, nn_buf q, nn_buf k, nn_buf v,
-                      nn_buf gamma, float eps, const char* who) {
+                      nn_buf gamma, float eps, const char* who, nn_buf bq = nullptr, nn_buf bk = nullptr, nn_buf bv = nullptr) {
     if (!c) return NN_FAIL(NN_ERR_ARG, "%s: null context", who);
     if (!x || !Wq || !Wk || !Wv || !q || !k || !v) return NN_FAIL(NN_ERR_ARG, "%s: null buffer", who);
     if (M < 0 || K <= 0 || Nq <= 0 || Nk <= 0 || Nv <= 0) return NN_FAIL(NN_ERR_ARG, "%s: bad shape", who);
@@ -741,6 +741,41 @@ static int linear_qkv(nn_context* c, int M, int K, nn_buf x, nn_buf Wq, int Nq, 
     a.status = c->status_dev;
     a.norm_w = (const uint16_t*)gamma;
     a.norm_eps = eps;
+    if (bq) {
+        // The bias rides in the projection's epilogue when the call takes the streaming kernel (up to 16 rows); otherwise
+        // the projection runs as it would without one and the reference's bias kernel follows it.
+        const void* bs[3] = {bq, bk, bv};
+        bool fused = M <= 16;
+        if (fused) {
+            LinArgs probe = a;
+            probe.M = M;
+            if (M >= 2) probe.norm_w = nullptr;
+            fused = stream_supported(fmt, M, K, probe) && stream_plan(fmt, probe, c->sm_count, c->smem_limit).ok;
+        }
+        if (fused) {
+            for (int i = 0; i < 3; ++i) a.seg[i].bias = (const uint16_t*)bs[i];
+            ProfScope prof(c, op_label(M, Nq + Nk + Nv, K, fmt, gamma ? "_rmsnorm_qkv_bias" : "_qkv_bias"));
+            return run_linear(c, fmt, a, M, who);
+        }
+        int rc;
+        {
+            ProfScope prof(c, op_label(M, Nq + Nk + Nv, K, fmt, gamma ? "_rmsnorm_qkv" : "_qkv"));
+            rc = run_linear(c, fmt, a, M, who);
+        }
+        if (rc) return rc;
+        BiasArgs ba = {};
+        for (int i = 0; i < 3; ++i) {
+            ba.out[i] = (uint16_t*)outs[i];
+            ba.bias[i] = (const uint16_t*)bs[i];
+            ba.cols[i] = Ns[i];
+        }
+        ba.rows = M;
+        ba.nseg = 3;
+        ProfScope prof(c, "bias_add_qkv_rows" + std::to_string(M));
+        CUDA_TRY(launch_bias_add(ba, c->stream));
+        c->launches++;
+        return NN_OK;
+    }
     ProfScope prof(c, op_label(M, Nq + Nk + Nv, K, fmt, gamma ? "_rmsnorm_qkv" : "_qkv"));
     return run_linear(c, fmt, a, M, who);
 }
@@ -769,18 +804,7 @@ extern "C" int nn_bias_add(nn_context* c, int rows, int cols, nn_buf out, nn_buf
 extern "C" int nn_linear_qkv_bias(nn_context* c, int M, int K, nn_buf x, nn_buf Wq, int Nq, nn_buf Wk, int Nk, nn_buf Wv, int Nv,
                                   nn_buf bq, nn_buf bk, nn_buf bv, nn_buf q, nn_buf k, nn_buf v) {
     if (!bq || !bk || !bv) return NN_FAIL(NN_ERR_ARG, "nn_linear_qkv_bias: null bias");
-    int rc = linear_qkv(c, M, K, x, Wq, Nq, Wk, Nk, Wv, Nv, q, k, v, nullptr, 0.f, "nn_linear_qkv_bias");
-    if (rc || M == 0) return rc;
-    BiasArgs a = {};
-    a.out[0] = (uint16_t*)q; a.out[1] = (uint16_t*)k; a.out[2] = (uint16_t*)v;
-    a.bias[0] = (const uint16_t*)bq; a.bias[1] = (const uint16_t*)bk; a.bias[2] = (const uint16_t*)bv;
-    a.cols[0] = Nq; a.cols[1] = Nk; a.cols[2] = Nv;
-    a.rows = M;
-    a.nseg = 3;
-    ProfScope prof(c, "bias_add_qkv_rows" + std::to_string(M));
-    CUDA_TRY(launch_bias_add(a, c->stream));
-    c->launches++;
-    return NN_OK;
+    return linear_qkv(c, M, K, x, Wq, Nq, Wk, Nk, Wv, Nv, q, k, v, nullptr, 0.f, "nn_linear_qkv_bias", bq, bk, bv);
 }
 
 extern "C" int nn_rmsnorm(nn_context* c, int rows, int cols, nn_buf x, nn_buf weight, float eps, nn_buf out) {
@@ -963,6 +987,20 @@ static cudaGraph_t consolidate_runs(nn_context* c, nn_plan* p, cudaGraph_t g) {
     }
     std::vector<HazardOp> hz(rec.size());
     for (size_t i = 0; i < rec.size(); ++i) hz[i] = hazard_view(rec[i]);
+    // bias rows are read like weights, with no ordering of their own: an operator whose bias any recorded operator writes
+    // keeps its own launch
+    std::vector<char> elig(rec.size());
+    for (size_t i = 0; i < rec.size(); ++i) {
+        elig[i] = rec[i].eligible ? 1 : 0;
+        for (int k = 0; k < rec[i].a.nseg && elig[i]; ++k) {
+            const uint16_t* bp = rec[i].a.seg[k].bias;
+            if (!bp) continue;
+            const uintptr_t b0 = (uintptr_t)bp, b1 = b0 + (size_t)rec[i].a.seg[k].N * 2;
+            for (size_t j = 0; j < rec.size() && elig[i]; ++j)
+                for (int o = 0; o < hz[j].nout; ++o)
+                    if (b0 < hz[j].out[o] + hz[j].out_bytes[o] && hz[j].out[o] < b1) elig[i] = 0;
+        }
+    }
     cudaGraph_t g2 = nullptr;
     if (cudaGraphClone(&g2, g) != cudaSuccess) return g;
     auto give_up = [&]() {
@@ -976,10 +1014,10 @@ static cudaGraph_t consolidate_runs(nn_context* c, nn_plan* p, cudaGraph_t g) {
     int removed = 0;
     size_t i = 0;
     while (i < rec.size()) {
-        if (!rec[i].eligible) { ++i; continue; }
+        if (!elig[i]) { ++i; continue; }
         // operators that follow one another directly in the graph
         size_t j = i + 1;
-        while (j < rec.size() && rec[j].eligible && succ.count(rec[j - 1].node) && succ[rec[j - 1].node] == rec[j].node) ++j;
+        while (j < rec.size() && elig[j] && succ.count(rec[j - 1].node) && succ[rec[j - 1].node] == rec[j].node) ++j;
         // [i, j) is a candidate; the data hazards may cut it shorter
         std::vector<HazardOp> cand(hz.begin() + i, hz.begin() + j);
         std::vector<OpDeps> deps;

@@ -549,6 +549,11 @@ __device__ __noinline__ void run_op(const PlanParams& P, const PlanOpScalars& D,
             } else {
                 if (inplace) res1 = D.res_ll ? poll_row(P, S, D.res_ll, n, res_epoch, res_word) : (uint16_t)res_word;
                 hv = finish_row<FMT>(v0, sc1, epi, res1);
+                if (D.flags & PLAN_BIAS) {
+                    // the reference adds the bias to the stored fp16 result, in fp32, and rounds again
+                    const uint16_t* bp = P.bias[op * 3 + tile_segment(tile)];
+                    if (bp) hv = __half_as_ushort(__float2half_rn(__fadd_rn(__half2float(__ushort_as_half(hv)), __half2float(__ushort_as_half(bp[n])))));
+                }
             }
         }
         if (valid && sg.out) sg.out[n] = hv;

@@ -633,6 +633,7 @@ __global__ void __launch_bounds__(THREADS) linear_stream_kernel(const __grid_con
                 const int n = row0 + lane;
                 if (n < seg_n) {
                     if (FMT == FMT_INT8) v = __fmul_rn(v, __half2float(__ushort_as_half(sc1)));  // roundings as in finish_row
+                    if (EXT && sg.bias) v = __fadd_rn(__half2float(__float2half_rn(v)), __half2float(__ushort_as_half(sg.bias[n])));
                     if (epi == EPI_RESIDUAL) {
                         v = __fadd_rn(__half2float(__ushort_as_half(res1)), v);
                     } else if (epi == EPI_SILU_GATE) {
@@ -667,6 +668,7 @@ __global__ void __launch_bounds__(THREADS) linear_stream_kernel(const __grid_con
                             if (m >= m_count) continue;
                             float v = acc[0][rb][nt][i2 * 2 + j];
                             if (FMT == FMT_INT8) v = __fmul_rn(v, __half2float(__ushort_as_half(sc_reg[rb][i2])));  // roundings as in finish_row
+                            if (EXT && sg.bias) v = __fadd_rn(__half2float(__float2half_rn(v)), __half2float(__ushort_as_half(sg.bias[n])));
                             if (epi == EPI_RESIDUAL) {
                                 v = __fadd_rn(__half2float(__ushort_as_half((uint16_t)res_reg[rb][i2][nt][j])), v);
                             } else if (epi == EPI_SILU_GATE) {
@@ -761,7 +763,8 @@ cudaError_t launch_e(const typename KArgsFor<FMT>::type& ka, const StreamPlan& p
 template <int FMT, int NT, bool DUAL>
 cudaError_t launch_t(const typename KArgsFor<FMT>::type& ka, const StreamPlan& p, cudaStream_t st, bool pdl) {
     const LinArgs& a = ka.a;
-    const bool ext = a.streamk || a.npeer > 0 || a.sig.world > 0 || a.argmax_slot != nullptr || a.seg[0].out == nullptr;
+    const bool ext = a.streamk || a.npeer > 0 || a.sig.world > 0 || a.argmax_slot != nullptr || a.seg[0].out == nullptr ||
+                     a.seg[0].bias != nullptr || a.seg[1].bias != nullptr || a.seg[2].bias != nullptr;
     if (ext) return launch_e<FMT, NT, DUAL, 2>(ka, p, st, pdl);
     if (a.norm_w) return launch_e<FMT, NT, DUAL, 1>(ka, p, st, pdl);
     return launch_e<FMT, NT, DUAL, 0>(ka, p, st, pdl);

@@ -39,6 +39,9 @@ struct LinSeg {
     int N;                  // rows of this segment
     int ld_out;             // leading dimension of out (elements)
     int tile0;              // first 32-row tile of this segment in the launch
+    // optional bias row (fp16 [N]) added to the stored result the way the reference's bias kernel does it after the
+    // projection: out = half(float(half(sum)) + float(bias[n])) (bias_add_rowmajor, src/models/qwen2-5-0-5b/kernels/bias_add.cl:18-40)
+    const uint16_t* bias;
 };
 
 struct LinArgs {

@@ -133,6 +133,7 @@ void free_run(PlanRun* run) {
     if (run->d_ops) cudaFree(run->d_ops);
     if (run->d_tiles) cudaFree(run->d_tiles);
     if (run->d_ll) cudaFree(run->d_ll);
+    if (run->d_bias) cudaFree(run->d_bias);
     if (run->d_state) cudaFree(run->d_state);
     *run = PlanRun();
 }
@@ -164,6 +165,8 @@ cudaError_t build_run(const std::vector<RecordedOp>& rec, const std::vector<OpDe
     }
     int k_ll = 0, x_bytes = 0, ctab_bytes = 0, k_norm = 0, max_item = 0;
     long long tile_start = 0;
+    std::vector<const uint16_t*> bias((size_t)count * 3, nullptr);
+    bool any_bias = false;
     for (int i = 0; i < count; ++i) {
         const RecordedOp& r = rec[first + i];
         const LinArgs& a = r.a;
@@ -221,6 +224,12 @@ cudaError_t build_run(const std::vector<RecordedOp>& rec, const std::vector<OpDe
             if (ok && dual) ok = make_scale_map(&o.tm_s[3], sbase[3], a.seg[0].N, srow, bw, tile_rows);
             if (!ok) { *reason = "scale view"; return cudaErrorInvalidValue; }
         }
+        for (int k = 0; k < a.nseg; ++k)
+            if (a.seg[k].bias) {
+                s.flags |= PLAN_BIAS;
+                bias[(size_t)i * 3 + k] = a.seg[k].bias;
+                any_bias = true;
+            }
         s.ntiles = t0;
         s.tile_start = (int)(tile_start % G);
         tiles[i] = make_int2(s.tile_start, s.ntiles);
@@ -285,6 +294,12 @@ cudaError_t build_run(const std::vector<RecordedOp>& rec, const std::vector<OpDe
     P.status = status_dev;
     P.wait_cycles = 400000000ll;  // about 0.2 s of multiprocessor clocks
     P.drop_publish_op = -1;
+    P.bias = nullptr;
+    if (any_bias) {
+        if ((e = cudaMalloc((void**)&run->d_bias, bias.size() * sizeof(const uint16_t*))) != cudaSuccess) return e;
+        if ((e = cudaMemcpy(run->d_bias, bias.data(), bias.size() * sizeof(const uint16_t*), cudaMemcpyHostToDevice)) != cudaSuccess) return e;
+        P.bias = run->d_bias;
+    }
     return cudaSuccess;
 }
 

@@ -58,6 +58,7 @@ enum : int {
     PLAN_EVICT_FIRST = 1,  // weights larger than L2 are streamed with an evict-first policy
     PLAN_SCALE_TMA = 2,    // Q4: block scales arrive by tensor copies
     PLAN_ROW_SCALES = 4,   // int8: the tile's row scales arrive with its last item (bulk copy), when the tile's rows allow it
+    PLAN_BIAS = 8,         // a bias row per segment is added to the stored result (PlanParams::bias)
 };
 constexpr int PLAN_ROW_SCALE_BYTES = 1024;  // room for them at the end of an item: first weight at +0, second at +512
 // Bulk copies move multiples of 16 bytes: a tile's row scales travel with it when its valid rows are a multiple of 8.
@@ -82,6 +83,7 @@ struct PlanParams {
     int* status;            // mapped host word: non-zero when a bounded wait ran out
     long long wait_cycles;  // limit of every wait
     int drop_publish_op;    // fault injection for tests: this operator never publishes its outputs (-1: none)
+    const uint16_t* const* bias;  // [nops][3] bias rows of the operators flagged PLAN_BIAS (null when the run has none)
     int off_tiles, off_desc, off_xraw, off_xs, off_ctab, off_norm, off_gamma, off_red, off_ring, ring_bytes;
 };
 
@@ -124,6 +126,7 @@ struct PlanRun {
     PlanOp* d_ops = nullptr;
     int2* d_tiles = nullptr;
     unsigned long long* d_ll = nullptr;
+    const uint16_t** d_bias = nullptr;
     unsigned* d_state = nullptr;
     PlanParams params = {};
     int grid = 0;

@@ -27,7 +27,7 @@ from . import synth
 
 class DecodeStep:
     def __init__(self, ctx, shape: synth.ModelShape, fmt: str, M: int = 1, n_sets: int = 1, seed: int = 1235,
-                 vocab_rows=None, keep_host=False, only=None, comm=None, norm=False, gather_logits=False, chained=False):
+                 vocab_rows=None, keep_host=False, only=None, comm=None, norm=False, gather_logits=False, chained=False, qkv_bias=False):
         self.ctx, self.shape, self.fmt, self.M = ctx, shape, fmt, M
         # with a communicator the lm_head rows are this rank's shard and the projection
         # stores into every rank's gather buffer (one buffer per weight set, so that
@@ -55,6 +55,15 @@ class DecodeStep:
             self.gamma = ctx.upload(g.view(np.uint16))
             if self.host is not None:
                 self.host["gamma"] = g
+        # qkv_bias=True: Qwen's q/k/v bias rows (src/models/qwen2-5-0-5b/src/layers/attention.cpp:413-469), one set per layer
+        self.qkv_bias = None
+        if qkv_bias:
+            self.qkv_bias = []
+            for layer in range(shape.layers):
+                rows = [(0.5 * rng.standard_normal(n)).astype(np.float32).astype(np.float16) for n in (shape.q_dim, shape.kv_dim, shape.kv_dim)]
+                if self.host is not None:
+                    self.host[f"qkv_bias.{layer}"] = rows
+                self.qkv_bias.append([ctx.upload(b.view(np.uint16)) for b in rows])
         self.x_attn = self._act("x_attn", M, shape.q_dim, rng)   # attention output -> o_proj
         self.x_act = self._act("x_act", M, F, rng)  # SwiGLU output -> down_proj
         self.resid0 = synth.activations(M, H, rng)
@@ -116,6 +125,9 @@ class DecodeStep:
                                      self.q, self.k, self.v)
             elif kind == "gate_up" and self.norm:
                 c.rmsnorm_gate_up_silu(M, sh.ffn, sh.hidden, self.resid, self.gamma, self.eps, w[0], w[1], self.act)
+            elif kind == "qkv" and self.qkv_bias:
+                bq, bk, bv = self.qkv_bias[layer]
+                c.linear_qkv_bias(M, sh.hidden, x_qkv, w[0], sh.q_dim, w[1], sh.kv_dim, w[2], sh.kv_dim, bq, bk, bv, self.q, self.k, self.v)
             elif kind == "qkv":
                 c.linear_qkv(M, sh.hidden, x_qkv, w[0], sh.q_dim, w[1], sh.kv_dim, w[2], sh.kv_dim, self.q, self.k, self.v)
             elif kind == "o_add":

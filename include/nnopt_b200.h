@@ -123,7 +123,9 @@ int nn_linear_qkv(nn_context* ctx, int M, int K, nn_buf x, nn_buf Wq, int Nq, nn
 /* The same with Qwen's q/k/v bias added afterwards, and the bias add on its own:
  * bias_add_rowmajor, src/models/qwen2-5-0-5b/kernels/bias_add.cl:18-40 (host:
  * src/layers/attention.cpp:413-469): out[r,c] = half(float(out[r,c]) + float(bias[c])), applied to
- * the fp16 result of the projection, as the reference does (one launch for the three outputs). */
+ * the fp16 result of the projection, as the reference does: same bits as nn_linear_qkv followed by
+ * nn_bias_add.  Up to 16 rows the bias is part of the projection's epilogue (no launch of its own,
+ * and the call can join a resident run of a recorded step); above, one bias launch follows. */
 int nn_linear_qkv_bias(nn_context* ctx, int M, int K, nn_buf x, nn_buf Wq, int Nq, nn_buf Wk, int Nk, nn_buf Wv, int Nv,
                        nn_buf bias_q, nn_buf bias_k, nn_buf bias_v, nn_buf q, nn_buf k, nn_buf v);
 int nn_bias_add(nn_context* ctx, int rows, int cols, nn_buf out_inout, nn_buf bias_fp16);
