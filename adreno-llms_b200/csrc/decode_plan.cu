@@ -257,6 +257,7 @@ __device__ __noinline__ void run_op(const PlanParams& P, const PlanOpScalars& D,
     const int aK = D.K, epi = D.epi, kcb = D.kcb, nchunks = D.nchunks, groups = D.groups, rowbytes = D.rowbytes;
     const int item_bytes = D.item_bytes, nbox = D.nbox, ntiles = D.ntiles, nseg = D.nseg;
     const bool scale_tma = (D.flags & PLAN_SCALE_TMA) != 0, row_scales = (D.flags & PLAN_ROW_SCALES) != 0;
+    const bool bias_on = (D.flags & PLAN_BIAS) != 0;
     const int scale_off = D.scale_off;
     const int seg1_tile0 = D.seg[1].tile0, seg2_tile0 = D.seg[2].tile0;
     const unsigned epoch = S.ebase + (unsigned)D.epoch;
@@ -549,7 +550,7 @@ __device__ __noinline__ void run_op(const PlanParams& P, const PlanOpScalars& D,
             } else {
                 if (inplace) res1 = D.res_ll ? poll_row(P, S, D.res_ll, n, res_epoch, res_word) : (uint16_t)res_word;
                 hv = finish_row<FMT>(v0, sc1, epi, res1);
-                if (D.flags & PLAN_BIAS) {
+                if (bias_on) {
                     // the reference adds the bias to the stored fp16 result, in fp32, and rounds again
                     const uint16_t* bp = P.bias[op * 3 + tile_segment(tile)];
                     if (bp) hv = __half_as_ushort(__float2half_rn(__fadd_rn(__half2float(__ushort_as_half(hv)), __half2float(__ushort_as_half(bp[n])))));
