@@ -75,6 +75,7 @@ def load():
         "nn_rmsnorm": ([vp, i, i, vp, vp, ctypes.c_float, vp], i),
         "nn_rmsnorm_linear": ([vp, i, i, i, vp, vp, ctypes.c_float, vp, vp], i),
         "nn_rmsnorm_linear_qkv": ([vp, i, i, vp, vp, ctypes.c_float, vp, i, vp, i, vp, i, vp, vp, vp], i),
+        "nn_rmsnorm_linear_qkv_bias": ([vp, i, i, vp, vp, ctypes.c_float, vp, i, vp, i, vp, i, vp, vp, vp, vp, vp, vp], i),
         "nn_rmsnorm_gate_up_silu": ([vp, i, i, i, vp, vp, ctypes.c_float, vp, vp, vp], i),
         "nn_plan_begin": ([vp], i), "nn_plan_end": ([vp, pvp], i), "nn_plan_launch": ([vp, vp], i),
         "nn_plan_num_kernels": ([vp], i), "nn_plan_free": ([vp], i),
@@ -236,6 +237,9 @@ class Context:
 
     def rmsnorm_linear_qkv(self, M, K, x, gamma, eps, Wq, Nq, Wk, Nk, Wv, Nv, q, k, v):
         _check(self.L.nn_rmsnorm_linear_qkv(self.h, M, K, x, gamma, eps, Wq, Nq, Wk, Nk, Wv, Nv, q, k, v))
+
+    def rmsnorm_linear_qkv_bias(self, M, K, x, gamma, eps, Wq, Nq, Wk, Nk, Wv, Nv, bq, bk, bv, q, k, v):
+        _check(self.L.nn_rmsnorm_linear_qkv_bias(self.h, M, K, x, gamma, eps, Wq, Nq, Wk, Nk, Wv, Nv, bq, bk, bv, q, k, v))
 
     def rmsnorm_gate_up_silu(self, M, N, K, x, gamma, eps, Wg, Wu, out):
         _check(self.L.nn_rmsnorm_gate_up_silu(self.h, M, N, K, x, gamma, eps, Wg, Wu, out))

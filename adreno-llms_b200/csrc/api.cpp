@@ -828,6 +828,13 @@ extern "C" int nn_rmsnorm_linear_qkv(nn_context* c, int M, int K, nn_buf x, nn_b
     return linear_qkv(c, M, K, x, Wq, Nq, Wk, Nk, Wv, Nv, q, k, v, gamma, eps, "nn_rmsnorm_linear_qkv");
 }
 
+extern "C" int nn_rmsnorm_linear_qkv_bias(nn_context* c, int M, int K, nn_buf x, nn_buf gamma, float eps, nn_buf Wq, int Nq, nn_buf Wk, int Nk,
+                                          nn_buf Wv, int Nv, nn_buf bq, nn_buf bk, nn_buf bv, nn_buf q, nn_buf k, nn_buf v) {
+    if (!gamma) return NN_FAIL(NN_ERR_ARG, "nn_rmsnorm_linear_qkv_bias: null norm weight");
+    if (!bq || !bk || !bv) return NN_FAIL(NN_ERR_ARG, "nn_rmsnorm_linear_qkv_bias: null bias");
+    return linear_qkv(c, M, K, x, Wq, Nq, Wk, Nk, Wv, Nv, q, k, v, gamma, eps, "nn_rmsnorm_linear_qkv_bias", bq, bk, bv);
+}
+
 extern "C" int nn_rmsnorm_gate_up_silu(nn_context* c, int M, int N, int K, nn_buf x, nn_buf gamma, float eps, nn_buf Wg, nn_buf Wu, nn_buf out) {
     if (!gamma) return NN_FAIL(NN_ERR_ARG, "nn_rmsnorm_gate_up_silu: null norm weight");
     return gate_up_silu(c, M, N, K, x, Wg, Wu, out, gamma, eps, "nn_rmsnorm_gate_up_silu");

@@ -120,7 +120,11 @@ class DecodeStep:
         x_head = self.resid if ch else self.x_h
         for kind, layer, ws in self.ops:
             w = [s[f"{kind}.{layer}.{j}"].buf for j in range(len(ws))]
-            if kind == "qkv" and self.norm:
+            if kind == "qkv" and self.norm and self.qkv_bias:
+                bq, bk, bv = self.qkv_bias[layer]
+                c.rmsnorm_linear_qkv_bias(M, sh.hidden, self.resid, self.gamma, self.eps, w[0], sh.q_dim, w[1], sh.kv_dim, w[2], sh.kv_dim,
+                                          bq, bk, bv, self.q, self.k, self.v)
+            elif kind == "qkv" and self.norm:
                 c.rmsnorm_linear_qkv(M, sh.hidden, self.resid, self.gamma, self.eps, w[0], sh.q_dim, w[1], sh.kv_dim, w[2], sh.kv_dim,
                                      self.q, self.k, self.v)
             elif kind == "gate_up" and self.norm:

@@ -142,6 +142,10 @@ int nn_rmsnorm(nn_context* ctx, int rows, int cols, nn_buf x, nn_buf weight_fp16
 int nn_rmsnorm_linear(nn_context* ctx, int M, int N, int K, nn_buf x, nn_buf norm_weight, float eps, nn_buf W, nn_buf out);
 int nn_rmsnorm_linear_qkv(nn_context* ctx, int M, int K, nn_buf x, nn_buf norm_weight, float eps, nn_buf Wq, int Nq, nn_buf Wk, int Nk,
                           nn_buf Wv, int Nv, nn_buf q, nn_buf k, nn_buf v);
+/* ... and with Qwen's q/k/v bias (input_layernorm -> q/k/v projections -> bias_add_rowmajor,
+ * src/models/qwen2-5-0-5b/src/layers/attention.cpp:303-317,413-469) in the same call. */
+int nn_rmsnorm_linear_qkv_bias(nn_context* ctx, int M, int K, nn_buf x, nn_buf norm_weight, float eps, nn_buf Wq, int Nq, nn_buf Wk, int Nk,
+                               nn_buf Wv, int Nv, nn_buf bias_q, nn_buf bias_k, nn_buf bias_v, nn_buf q, nn_buf k, nn_buf v);
 int nn_rmsnorm_gate_up_silu(nn_context* ctx, int M, int N, int K, nn_buf x, nn_buf norm_weight, float eps, nn_buf Wg, nn_buf Wu, nn_buf out);
 
 /* fp32 [N,K] = the dequantised weight exactly as the kernels unpack it

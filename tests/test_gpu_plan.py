@@ -239,14 +239,15 @@ def test_host_copies_recorded_with_the_step(nnb, ctx):
         ctx.free(b)
 
 
+@pytest.mark.parametrize("norm", [False, True])
 @pytest.mark.parametrize("fmt", ["int8", "fp16", "q4"])
-def test_qkv_bias_rides_in_the_resident_step(nnb, ctx, fmt):
+def test_qkv_bias_rides_in_the_resident_step(nnb, ctx, fmt, norm):
     """Qwen's q/k/v bias (bias_add_rowmajor after the fused QKV projection, src/models/qwen2-5-0-5b/src/layers/
     attention.cpp:413-469) is part of the projection's epilogue, so a Qwen-shaped step with biases still replays as
     one resident launch, with the bits of the calls made one by one, and follows the oracle's chain."""
     synth, dstep = _mods()
     shape = synth.ModelShape("qwen-bias", 896, 2, 896, 128, 4864, 4096)
-    step = dstep.DecodeStep(ctx, shape, fmt, M=1, n_sets=1, keep_host=True, chained=True, qkv_bias=True)
+    step = dstep.DecodeStep(ctx, shape, fmt, M=1, n_sets=1, keep_host=True, chained=True, qkv_bias=True, norm=norm)
     _poison(ctx, step)
     before = ctx.launch_count()
     step.enqueue(0)
@@ -266,11 +267,12 @@ def test_qkv_bias_rides_in_the_resident_step(nnb, ctx, fmt):
     # the oracle's chain, with the reference's two roundings for the bias
     h = step.host
     r = step.resid0.copy()
+    nrm = (lambda v: cpu.rmsnorm(v, h["gamma"], step.eps)) if norm else (lambda v: v)
     for layer in range(shape.layers):
-        q = cpu.linear(fmt, r, *h[f"qkv.{layer}.0"])
+        q = cpu.linear(fmt, nrm(r), *h[f"qkv.{layer}.0"])
         q = (q.astype(np.float32) + h[f"qkv_bias.{layer}"][0].astype(np.float32)[None, :]).astype(np.float16)
         r = cpu.linear_residual(fmt, q, *h[f"o_add.{layer}.0"], r)
-        act = cpu.linear_swiglu(fmt, r, *h[f"gate_up.{layer}.0"], *h[f"gate_up.{layer}.1"])
+        act = cpu.linear_swiglu(fmt, nrm(r), *h[f"gate_up.{layer}.0"], *h[f"gate_up.{layer}.1"])
         r = cpu.linear_residual(fmt, act, *h[f"down_add.{layer}.0"], r)
     check_close(ctx.download(step.q, (1, shape.q_dim), np.uint16).view(np.float16), q, tol=3e-3, what=f"q with bias {fmt}")
     check_close(ctx.download(step.resid, (1, shape.hidden), np.uint16).view(np.float16), r, tol=3e-3, what=f"residual with bias {fmt}")
